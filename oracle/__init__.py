@@ -1,0 +1,198 @@
+"""ctypes access to the test oracle.  TEST INFRASTRUCTURE ONLY.
+
+Two libraries with the same call surface:
+
+* ``port`` -- ``oracle/libkq_oracle.so``, the C restatement (``kq_oracle.c``).
+* ``ref``  -- ``oracle/_ref/libkcref.so``, the reference project's own C++ compiled in place
+  from the mounted reference tree (``None`` when it was never built).
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg may import this package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+_u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+_u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
+_i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
+
+
+class AttnDims(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("n_heads", "ctx", "head_dim", "kv_stride", "group", "ctx_pad", "k_stride")]
+
+
+class FaDims(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("H", "T", "D", "group", "tp", "k_row", "k_head", "v_row", "v_head", "N",
+                                       "q_tok", "q_head", "m_row", "has_mask", "H_kv")]
+
+
+class Mat(C.Structure):
+    _fields_ = [("blocks", C.c_void_p), ("rows", C.c_int), ("k", C.c_int), ("fmt", C.c_int)]
+
+
+class Layer(C.Structure):
+    _fields_ = [(n, Mat) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd")] + [
+        ("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
+
+
+class Model(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("hidden", "inter", "n_layers", "heads", "kv_heads", "head_dim", "vocab",
+                                       "max_ctx")] + [
+        ("eps", C.c_float), ("rope_base", C.c_float), ("layers", C.POINTER(Layer)), ("out_norm", C.c_void_p),
+        ("lm_head", Mat), ("rope_ff", C.c_void_p)]
+
+
+def _sig(lib, prefix):
+    def f(name, res, *args):
+        fn = getattr(lib, prefix + name)
+        fn.restype, fn.argtypes = res, list(args)
+    i, fl = C.c_int, C.c_float
+    f("f16_to_f32", fl, C.c_uint16)
+    f("f32_to_f16", C.c_uint16, fl)
+    f("dequant_row_q4k", None, _u8p, i, _f32p)
+    f("dequant_row_q6k", None, _u8p, i, _f32p)
+    f("quantize_q8x4", None, _f32p, _i32p, _f32p, i)
+    f("quantize_q8k", None, _f32p, _i32p, i)
+    f("matvec_q4k_q8", None, _u8p, _i32p, _f32p, _f32p, i, i)
+    f("matvec_q6k_q8", None, _u8p, _i32p, _f32p, _f32p, i, i)
+    f("matvec_q4k_q8k", None, _u8p, _i32p, _f32p, i, i)
+    f("matvec_q6k_q8k", None, _u8p, _i32p, _f32p, i, i)
+    f("rms_norm", None, _f32p, _f32p, _f32p, i, i, fl)
+    f("add", None, _f32p, _f32p, i)
+    f("add_rms_norm", None, _f32p, _f32p, _f32p, _f32p, i, fl)
+    f("add_sumsq", None, _f32p, _f32p, _i32p, i)
+    f("norm_q8x4", None, _f32p, _f32p, _i32p, i, fl)
+    f("rope", None, _f32p, i, i, i, fl)
+    f("rope_ff", None, _f32p, _f32p, i, i, i, fl)
+    f("rope_ggml", None, _f32p, _f32p, _i32p, _f32p, i, i, i, fl, i)
+    f("append_kv", None, _f32p, _f32p, _f32p, _f32p, i, i, i)
+    f("attn_scores", None, _f32p, _f32p, _f32p, C.POINTER(AttnDims), fl)
+    f("softmax", None, _f32p, i, i, i)
+    f("attn_values", None, _f32p, _f32p, _f32p, C.POINTER(AttnDims))
+    f("silu_mul", None, _f32p, _f32p, _f32p, i)
+    f("silu_mul_q8x4", None, _f32p, _f32p, _i32p, _f32p, i)
+    f("mul_rows", None, _f32p, _f32p, _f32p, i, i)
+    f("add_sumsq_f", None, _f32p, _f32p, _f32p, _i32p, i, i)
+    f("sumsq_part", None, _f32p, _i32p, i, i)
+    f("norm_mul_q8", None, _f32p, _f32p, _f32p, _i32p, i, i, fl)
+    f("norm_mul_q8k", None, _f32p, _f32p, _f32p, _i32p, _i32p, i, i, fl)
+    f("silu_mul_q8f", None, _f32p, _f32p, _f32p, _i32p, i, i)
+    f("silu_mul_q8k", None, _f32p, _f32p, _f32p, _i32p, i, i)
+    f("set_rows_f16", None, _f32p, _i64p, _u16p, i, i, i, i, i)
+    f("flash_attn_f16", None, _f32p, _u16p, _u16p, _u16p, _f32p, C.POINTER(FaDims), fl)
+
+
+class _Lib:
+    """Attribute access strips the library's symbol prefix: ``port.rms_norm(...)``."""
+
+    def __init__(self, path, prefix):
+        self.path, self.prefix = path, prefix
+        self.lib = C.CDLL(path)
+        _sig(self.lib, prefix)
+
+    def __getattr__(self, name):
+        return getattr(self.lib, self.prefix + name)
+
+
+def build(with_ref: bool = True) -> None:
+    """Compile the oracle (and, where the reference tree is mounted, oracle/_ref)."""
+    subprocess.run(["make", "-C", _HERE, "all" if with_ref else "port"], check=True, stdout=subprocess.DEVNULL)
+
+
+def _load_port():
+    path = os.path.join(_HERE, "libkq_oracle.so")
+    if not os.path.exists(path):
+        build(with_ref=False)
+    lib = _Lib(path, "kqo_")
+    i = C.c_int
+    lib.lib.kqo_matvec_dequant_f64.restype = None
+    lib.lib.kqo_matvec_dequant_f64.argtypes = [_u8p, _f32p, _f32p, i, i, i]
+    lib.lib.kqo_decode_token.restype = None
+    lib.lib.kqo_decode_token.argtypes = [C.POINTER(Model), _f32p, i, _f32p, _f32p, _i32p]
+    lib.lib.kqo_decode_scratch_floats.restype = C.c_long
+    lib.lib.kqo_decode_scratch_floats.argtypes = [C.POINTER(Model)]
+    lib.lib.kqo_decode_scratch_ints.restype = C.c_long
+    lib.lib.kqo_decode_scratch_ints.argtypes = [C.POINTER(Model)]
+    return lib
+
+
+def _load_ref():
+    path = os.path.join(_HERE, "_ref", "libkcref.so")
+    if not os.path.exists(path):
+        return None
+    lib = _Lib(path, "kcref_")
+    i = C.c_int
+    L = lib.lib
+    L.kcref_stream_ints.restype, L.kcref_stream_ints.argtypes = C.c_long, [i, i, i]
+    L.kcref_repack.restype, L.kcref_repack.argtypes = None, [_u8p, i, i, i, _i32p]
+    L.kcref_matvec_stream_q8.restype = None
+    L.kcref_matvec_stream_q8.argtypes = [_i32p, _i32p, _f32p, _f32p, i, i, i]
+    L.kcref_matvec_stream_q8k.restype = None
+    L.kcref_matvec_stream_q8k.argtypes = [_i32p, _i32p, _f32p, i, i, i]
+    L.kcref_model_open.restype, L.kcref_model_open.argtypes = C.c_void_p, [C.POINTER(Model)]
+    L.kcref_model_decode.restype, L.kcref_model_decode.argtypes = i, [C.c_void_p, _f32p, i, _f32p]
+    L.kcref_model_close.restype, L.kcref_model_close.argtypes = None, [C.c_void_p]
+    return lib
+
+
+port = _load_port()
+ref = _load_ref()
+
+
+# ---- numpy conveniences shared by the tests ------------------------------------------------------
+
+def quantize_q8x4(lib, x):
+    """x: float32[k] -> (xq int32[k/32*8], xd float32[k/32*2])."""
+    x = np.ascontiguousarray(x, np.float32)
+    nb = x.size // 32
+    xq, xd = np.zeros(nb * 8, np.int32), np.zeros(nb * 2, np.float32)
+    lib.quantize_q8x4(x, xq, xd, nb)
+    return xq, xd
+
+
+def quantize_q8k(lib, x):
+    x = np.ascontiguousarray(x, np.float32)
+    nsb = x.size // 256
+    q = np.zeros(nsb * 85, np.int32)
+    lib.quantize_q8k(x, q, nsb)
+    return q
+
+
+def dequant(lib, blocks, rows, k, q6):
+    out = np.zeros((rows, k), np.float32)
+    rb = (k // 256) * (210 if q6 else 144)
+    blocks = np.ascontiguousarray(blocks, np.uint8).reshape(rows, rb)
+    fn = lib.dequant_row_q6k if q6 else lib.dequant_row_q4k
+    for r in range(rows):
+        fn(np.ascontiguousarray(blocks[r]), k, out[r])
+    return out
+
+
+def matvec_q8(lib, blocks, x, rows, k, q6):
+    """The reference's decode matvec: quantize x per 32, integer dot products."""
+    xq, xd = quantize_q8x4(lib, x)
+    y = np.zeros(rows, np.float32)
+    (lib.matvec_q6k_q8 if q6 else lib.matvec_q4k_q8)(np.ascontiguousarray(blocks, np.uint8).ravel(), xq, xd, y, rows, k)
+    return y
+
+
+def matvec_q8k(lib, blocks, x, rows, k, q6):
+    q = quantize_q8k(lib, x)
+    y = np.zeros(rows, np.float32)
+    (lib.matvec_q6k_q8k if q6 else lib.matvec_q4k_q8k)(np.ascontiguousarray(blocks, np.uint8).ravel(), q, y, rows, k)
+    return y
+
+
+def matvec_dequant_f64(blocks, x, rows, k, q6):
+    y = np.zeros(rows, np.float32)
+    port.lib.kqo_matvec_dequant_f64(np.ascontiguousarray(blocks, np.uint8).ravel(),
+                                    np.ascontiguousarray(x, np.float32), y, rows, k, int(q6))
+    return y
