@@ -1,0 +1,67 @@
+// Shared device helpers for the sm_100a kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace kcb {
+
+// Status codes returned across the C ABI: the integer values of the reference's kc::Error
+// (include/kernelcore/error.hpp:8-25 of the reference project).
+enum : int {
+    KCB_SUCCESS = 0,
+    KCB_NOT_INITIALIZED = 1,
+    KCB_INVALID_VALUE = 2,
+    KCB_INVALID_DEVICE = 3,
+    KCB_OUT_OF_MEMORY = 4,
+    KCB_INVALID_POINTER = 5,
+    KCB_INVALID_RESOURCE_HANDLE = 6,
+    KCB_UNSUPPORTED_OPERATION = 7,
+    KCB_INVALID_KERNEL_IMAGE = 8,
+    KCB_KERNEL_NOT_FOUND = 9,
+    KCB_DYNAMIC_CODE_BLOCKED = 10,
+    KCB_LAUNCH_FAILURE = 11,
+    KCB_KERNEL_FAULT = 12,
+    KCB_CONTEXT_POISONED = 13,
+    KCB_NOT_READY = 14,
+    KCB_INTERNAL_ERROR = 15,
+};
+
+constexpr int kQ4KBlock = 144;  // bytes per 256 weights
+constexpr int kQ6KBlock = 210;
+constexpr int kSmCount = 148;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// 128-bit streaming load: weights are read exactly once, keep them out of L1.
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float half_bits_to_float(unsigned h) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
+}
+
+// Launch-error to status code; never synchronises.
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? KCB_SUCCESS : KCB_LAUNCH_FAILURE; }
+
+}  // namespace kcb

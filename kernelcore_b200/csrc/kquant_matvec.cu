@@ -1,0 +1,488 @@
+// Dequant-fused K-quant matvec for decode, y[rows] = W[rows][k] . x[k], sm_100a.
+//
+// Replaces the reference's one-thread-per-row kernels kernels/llm/matvec_q4k_q8.cu:33-88 and
+// kernels/llm/matvec_q6k_q8.cu:33-105.  Same arithmetic contract -- weights are never expanded in
+// memory, activations are the Q8 blocks of 32 that quantize_q8x4 writes, all dot products are exact
+// 8-bit integer dot products -- but laid out for a GPU:
+//
+//   * W stays in its GGUF super-block bytes (4.5 bits/weight Q4_K, 6.5625 Q6_K).  Q4_K blocks are
+//     used as they are (144 B, 16-byte aligned).  Q6_K blocks (210 B, only 2-byte aligned) are split
+//     once at load time into four planes of identical total size: ql[rows][nsb][128],
+//     qh[rows][nsb][64], sc[rows][nsb][16], d[rows][nsb] -- every plane 16-byte aligned per block.
+//   * one warp owns RPW rows; every lane streams 16 B of quants per row per step with a 128-bit
+//     no-allocate load, so a warp request covers whole contiguous 512 B runs of the row;
+//   * the activation words, their scales and (Q6_K) their half-block sums are staged once per CTA in
+//     shared memory and reused by every row the CTA touches;
+//   * lanes combine through one shuffle tree per row.
+//
+// Integer partial sums are exact; the fp32 scale products are summed in a different order from the
+// reference's single-thread loop, so y agrees with it to fp32 rounding (tests bound it at 1e-5 of
+// max|y|, the reference's own cross-compiler bar), not bit for bit.
+
+#include "common.cuh"
+#include "ops.h"
+
+namespace kcb {
+namespace {
+
+constexpr unsigned kLo4 = 0x0F0F0F0Fu;
+constexpr unsigned kHi2 = 0x30303030u;
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+__device__ __forceinline__ int sbyte_of(unsigned w, int i) { return static_cast<int>(w << (24 - 8 * i)) >> 24; }
+
+// ---- shared staging of the Q8 activation scratch ------------------------------------------------
+// xw: packed int8 words as quantize_q8x4 wrote them; dx[b] = {d_b, d_b * sum_b}; s16[2b+h] = sum of
+// the h-th 16 values of block b (Q6_K only).
+template <bool kQ6>
+__device__ __forceinline__ void stage_q8(const int* __restrict__ xq, const float* __restrict__ xd, int nsb, int* xw,
+                                         float2* dx, int* s16) {
+    const int nwords = nsb * 64, nb = nsb * 8;
+    for (int i = threadIdx.x; i < nwords; i += kThreads) xw[i] = xq[i];
+    for (int i = threadIdx.x; i < nb; i += kThreads) {
+        const float d = xd[2 * i], s = xd[2 * i + 1];
+        dx[i] = make_float2(d, __fmul_rn(d, s));
+    }
+    if (kQ6) {
+        for (int i = threadIdx.x; i < nb * 2; i += kThreads) {
+            int s = 0;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) s = __dp4a(0x01010101, xq[i * 4 + w], s);
+            s16[i] = s;
+        }
+    }
+    __syncthreads();
+}
+
+// ---- Q4_K ---------------------------------------------------------------------------------------
+// Lane (g, c8): super-block sb = 4*it + g, 16-byte chunk c8 of its 128 quant bytes.  Chunk c8 holds
+// the low nibbles of sub-block 2j (weights 16h..16h+15) and the high nibbles of sub-block 2j+1, with
+// j = c8 >> 1, h = c8 & 1.
+struct Q4Regs {
+    uint4 hd, q;
+};
+
+template <int RPW>
+__global__ void __launch_bounds__(kThreads) matvec_q4k_q8_kernel(const uint8_t* __restrict__ w,
+                                                                  const int* __restrict__ xq,
+                                                                  const float* __restrict__ xd, float* __restrict__ y,
+                                                                  int rows, int nsb) {
+    extern __shared__ __align__(16) int sm[];
+    int* xw = sm;
+    float2* dx = reinterpret_cast<float2*>(sm + nsb * 64);
+    stage_q8<false>(xq, xd, nsb, xw, dx, nullptr);
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 3, c8 = lane & 7, j = c8 >> 1, h = c8 & 1;
+    const size_t row_bytes = static_cast<size_t>(nsb) * kQ4KBlock;
+    const int stride = gridDim.x * kWarps * RPW;
+
+    for (int row0 = (blockIdx.x * kWarps + warp) * RPW; row0 < rows; row0 += stride) {
+        float acc[RPW];
+        Q4Regs nxt[RPW];
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            acc[r] = 0.0f;
+            if (row0 + r < rows && g < nsb) {
+                const uint8_t* blk = w + (row0 + r) * row_bytes + static_cast<size_t>(g) * kQ4KBlock;
+                nxt[r].hd = ldg_stream(blk);
+                nxt[r].q = ldg_stream(blk + 16 + 16 * c8);
+            }
+        }
+        for (int sb = g; sb < nsb; sb += 4) {
+            Q4Regs cur[RPW];
+#pragma unroll
+            for (int r = 0; r < RPW; ++r) cur[r] = nxt[r];
+            if (sb + 4 < nsb) {
+#pragma unroll
+                for (int r = 0; r < RPW; ++r)
+                    if (row0 + r < rows) {
+                        const uint8_t* blk = w + (row0 + r) * row_bytes + static_cast<size_t>(sb + 4) * kQ4KBlock;
+                        nxt[r].hd = ldg_stream(blk);
+                        nxt[r].q = ldg_stream(blk + 16 + 16 * c8);
+                    }
+            }
+            const int b = sb * 8 + 2 * j;
+            const uint4 xa = *reinterpret_cast<const uint4*>(xw + b * 8 + 4 * h);
+            const uint4 xb = *reinterpret_cast<const uint4*>(xw + b * 8 + 8 + 4 * h);
+            const float4 dd = *reinterpret_cast<const float4*>(dx + b);  // {d_b, d_b*sum_b, d_b+1, d_b+1*sum_b+1}
+#pragma unroll
+            for (int r = 0; r < RPW; ++r) {
+                if (row0 + r >= rows) continue;
+                const uint4 q = cur[r].q, hd = cur[r].hd;
+                int da = 0, db = 0;
+                da = __dp4a(static_cast<int>(q.x & kLo4), static_cast<int>(xa.x), da);
+                da = __dp4a(static_cast<int>(q.y & kLo4), static_cast<int>(xa.y), da);
+                da = __dp4a(static_cast<int>(q.z & kLo4), static_cast<int>(xa.z), da);
+                da = __dp4a(static_cast<int>(q.w & kLo4), static_cast<int>(xa.w), da);
+                db = __dp4a(static_cast<int>((q.x >> 4) & kLo4), static_cast<int>(xb.x), db);
+                db = __dp4a(static_cast<int>((q.y >> 4) & kLo4), static_cast<int>(xb.y), db);
+                db = __dp4a(static_cast<int>((q.z >> 4) & kLo4), static_cast<int>(xb.z), db);
+                db = __dp4a(static_cast<int>((q.w >> 4) & kLo4), static_cast<int>(xb.w), db);
+                // 6-bit scales/mins of sub-blocks 2j, 2j+1 out of the 12 packed bytes (words hd.y..hd.w)
+                unsigned scw, mw;
+                if (j < 2) {
+                    scw = hd.y & 0x3F3F3F3Fu;
+                    mw = hd.z & 0x3F3F3F3Fu;
+                } else {
+                    scw = (hd.w & kLo4) | ((hd.y >> 2) & kHi2);
+                    mw = ((hd.w >> 4) & kLo4) | ((hd.z >> 2) & kHi2);
+                }
+                const int sh = 16 * (j & 1);
+                const int sca = (scw >> sh) & 255, scb = (scw >> (sh + 8)) & 255;
+                const float d = half_bits_to_float(hd.x & 0xFFFFu), dmin = half_bits_to_float(hd.x >> 16);
+                float t = static_cast<float>(sca * da) * dd.x + static_cast<float>(scb * db) * dd.z;
+                float part = d * t;
+                if (h == 0) {  // the min term belongs to the whole sub-block: one lane of the pair adds it
+                    const int ma = (mw >> sh) & 255, mb = (mw >> (sh + 8)) & 255;
+                    part -= dmin * (static_cast<float>(ma) * dd.y + static_cast<float>(mb) * dd.w);
+                }
+                acc[r] += part;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            const float s = warp_sum(acc[r]);
+            if (lane == 0 && row0 + r < rows) y[row0 + r] = s;
+        }
+    }
+}
+
+// ---- Q6_K (planes) ------------------------------------------------------------------------------
+// Lane (g, r8): super-block sb = 4*it + g; r8 = 4n + 2a + h picks the 16-byte chunk r8 of the block's
+// 128 ql bytes: low nibbles are weights 16h..16h+15 of 32-block t = a of half n, high nibbles the same
+// positions of block t = a + 2; both take their two high bits from qh bytes [32n + 16h, +16), shifted by
+// 2t.  Each 16 weights share one int8 scale (index 8n + 2t + h).
+struct Q6Regs {
+    uint4 ql, qh;
+    uint2 sc;
+    unsigned d;
+};
+
+template <int RPW>
+__global__ void __launch_bounds__(kThreads) matvec_q6k_q8_kernel(const uint8_t* __restrict__ w,
+                                                                  const int* __restrict__ xq,
+                                                                  const float* __restrict__ xd, float* __restrict__ y,
+                                                                  int rows, int nsb, int rows_total) {
+    extern __shared__ __align__(16) int sm[];
+    int* xw = sm;
+    float2* dx = reinterpret_cast<float2*>(sm + nsb * 64);
+    int* s16 = sm + nsb * 64 + nsb * 16;
+    stage_q8<true>(xq, xd, nsb, xw, dx, s16);
+
+    const size_t nblk = static_cast<size_t>(rows_total) * nsb;
+    const uint8_t* ql = w;
+    const uint8_t* qh = w + nblk * 128;
+    const uint8_t* sc = w + nblk * 192;
+    const unsigned short* dp = reinterpret_cast<const unsigned short*>(w + nblk * 208);
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 3, r8 = lane & 7, n = r8 >> 2, a = (r8 >> 1) & 1, h = r8 & 1;
+    const int shl = 4 - 2 * a, shr = 2 * a, sci = 2 * a + h;
+    const int stride = gridDim.x * kWarps * RPW;
+
+    auto load = [&](Q6Regs& t, int row, int sb) {
+        const size_t blk = static_cast<size_t>(row) * nsb + sb;
+        t.ql = ldg_stream(ql + blk * 128 + 16 * r8);
+        t.qh = ldg_stream(qh + blk * 64 + 32 * n + 16 * h);
+        t.sc = __ldg(reinterpret_cast<const uint2*>(sc + blk * 16 + 8 * n));
+        t.d = __ldg(dp + blk);
+    };
+
+    for (int row0 = (blockIdx.x * kWarps + warp) * RPW; row0 < rows; row0 += stride) {
+        float acc[RPW];
+        Q6Regs nxt[RPW];
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            acc[r] = 0.0f;
+            if (row0 + r < rows && g < nsb) load(nxt[r], row0 + r, g);
+        }
+        for (int sb = g; sb < nsb; sb += 4) {
+            Q6Regs cur[RPW];
+#pragma unroll
+            for (int r = 0; r < RPW; ++r) cur[r] = nxt[r];
+            if (sb + 4 < nsb) {
+#pragma unroll
+                for (int r = 0; r < RPW; ++r)
+                    if (row0 + r < rows) load(nxt[r], row0 + r, sb + 4);
+            }
+            const int b = sb * 8 + 4 * n + a;  // 32-block of the low nibbles; the high nibbles' is b + 2
+            const uint4 xa = *reinterpret_cast<const uint4*>(xw + b * 8 + 4 * h);
+            const uint4 xb = *reinterpret_cast<const uint4*>(xw + (b + 2) * 8 + 4 * h);
+            const float dxa = dx[b].x, dxb = dx[b + 2].x;
+            const int sa = 32 * s16[2 * b + h], sb2 = 32 * s16[2 * (b + 2) + h];
+#pragma unroll
+            for (int r = 0; r < RPW; ++r) {
+                if (row0 + r >= rows) continue;
+                const uint4 l = cur[r].ql, hq = cur[r].qh;
+                int dl = 0, dh = 0;
+                dl = __dp4a(static_cast<int>((l.x & kLo4) | ((hq.x << shl) & kHi2)), static_cast<int>(xa.x), dl);
+                dl = __dp4a(static_cast<int>((l.y & kLo4) | ((hq.y << shl) & kHi2)), static_cast<int>(xa.y), dl);
+                dl = __dp4a(static_cast<int>((l.z & kLo4) | ((hq.z << shl) & kHi2)), static_cast<int>(xa.z), dl);
+                dl = __dp4a(static_cast<int>((l.w & kLo4) | ((hq.w << shl) & kHi2)), static_cast<int>(xa.w), dl);
+                dh = __dp4a(static_cast<int>(((l.x >> 4) & kLo4) | ((hq.x >> shr) & kHi2)), static_cast<int>(xb.x), dh);
+                dh = __dp4a(static_cast<int>(((l.y >> 4) & kLo4) | ((hq.y >> shr) & kHi2)), static_cast<int>(xb.y), dh);
+                dh = __dp4a(static_cast<int>(((l.z >> 4) & kLo4) | ((hq.z >> shr) & kHi2)), static_cast<int>(xb.z), dh);
+                dh = __dp4a(static_cast<int>(((l.w >> 4) & kLo4) | ((hq.w >> shr) & kHi2)), static_cast<int>(xb.w), dh);
+                const int tl = sbyte_of(cur[r].sc.x, sci) * (dl - sa);   // the -32 offset through the x sums
+                const int th = sbyte_of(cur[r].sc.y, sci) * (dh - sb2);
+                const float d = half_bits_to_float(cur[r].d);
+                acc[r] += d * (static_cast<float>(tl) * dxa + static_cast<float>(th) * dxb);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            const float s = warp_sum(acc[r]);
+            if (lane == 0 && row0 + r < rows) y[row0 + r] = s;
+        }
+    }
+}
+
+// ---- fp32 activations: exact dequantised weight times x, fp32 accumulate --------------------------
+// Same lane mapping; the weight is rebuilt exactly as the reference's dequantisers do
+// (llm/llm_reference.cpp:342-383: separately rounded products) and multiplied with fp32 x from shared
+// memory.  Slower than the integer path (one FMA per weight); it exists for callers that hold fp32
+// activations and want the float product rather than the Q8 one.
+__global__ void __launch_bounds__(kThreads) matvec_q4k_f32_kernel(const uint8_t* __restrict__ w,
+                                                                   const float* __restrict__ x, float* __restrict__ y,
+                                                                   int rows, int nsb) {
+    extern __shared__ __align__(16) int sm[];
+    float* xs = reinterpret_cast<float*>(sm);
+    for (int i = threadIdx.x; i < nsb * 256; i += kThreads) xs[i] = x[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 3, c8 = lane & 7, j = c8 >> 1, h = c8 & 1;
+    const size_t row_bytes = static_cast<size_t>(nsb) * kQ4KBlock;
+    for (int row = blockIdx.x * kWarps + warp; row < rows; row += gridDim.x * kWarps) {
+        float acc = 0.0f;
+        for (int sb = g; sb < nsb; sb += 4) {
+            const uint8_t* blk = w + row * row_bytes + static_cast<size_t>(sb) * kQ4KBlock;
+            const uint4 hd = ldg_stream(blk);
+            const uint4 q = ldg_stream(blk + 16 + 16 * c8);
+            unsigned scw, mw;
+            if (j < 2) {
+                scw = hd.y & 0x3F3F3F3Fu;
+                mw = hd.z & 0x3F3F3F3Fu;
+            } else {
+                scw = (hd.w & kLo4) | ((hd.y >> 2) & kHi2);
+                mw = ((hd.w >> 4) & kLo4) | ((hd.z >> 2) & kHi2);
+            }
+            const int sh = 16 * (j & 1);
+            const float d = half_bits_to_float(hd.x & 0xFFFFu), dmin = half_bits_to_float(hd.x >> 16);
+            const float dl = __fmul_rn(d, static_cast<float>((scw >> sh) & 255));
+            const float dh = __fmul_rn(d, static_cast<float>((scw >> (sh + 8)) & 255));
+            const float ml = __fmul_rn(dmin, static_cast<float>((mw >> sh) & 255));
+            const float mh = __fmul_rn(dmin, static_cast<float>((mw >> (sh + 8)) & 255));
+            const float* xl = xs + sb * 256 + 64 * j + 16 * h;
+            const unsigned qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int bq = 0; bq < 4; ++bq) {
+                    const unsigned byte = (qw[i] >> (8 * bq)) & 255u;
+                    const float wl = __fsub_rn(__fmul_rn(dl, static_cast<float>(byte & 15u)), ml);
+                    const float wh = __fsub_rn(__fmul_rn(dh, static_cast<float>(byte >> 4)), mh);
+                    acc = fmaf(wl, xl[4 * i + bq], acc);
+                    acc = fmaf(wh, xl[32 + 4 * i + bq], acc);
+                }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) y[row] = acc;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) matvec_q6k_f32_kernel(const uint8_t* __restrict__ w,
+                                                                   const float* __restrict__ x, float* __restrict__ y,
+                                                                   int rows, int nsb, int rows_total) {
+    extern __shared__ __align__(16) int sm[];
+    float* xs = reinterpret_cast<float*>(sm);
+    for (int i = threadIdx.x; i < nsb * 256; i += kThreads) xs[i] = x[i];
+    __syncthreads();
+    const size_t nblk = static_cast<size_t>(rows_total) * nsb;
+    const uint8_t* ql = w;
+    const uint8_t* qh = w + nblk * 128;
+    const uint8_t* sc = w + nblk * 192;
+    const unsigned short* dp = reinterpret_cast<const unsigned short*>(w + nblk * 208);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 3, r8 = lane & 7, n = r8 >> 2, a = (r8 >> 1) & 1, h = r8 & 1;
+    for (int row = blockIdx.x * kWarps + warp; row < rows; row += gridDim.x * kWarps) {
+        float acc = 0.0f;
+        for (int sb = g; sb < nsb; sb += 4) {
+            const size_t blk = static_cast<size_t>(row) * nsb + sb;
+            const uint4 l = ldg_stream(ql + blk * 128 + 16 * r8);
+            const uint4 hq = ldg_stream(qh + blk * 64 + 32 * n + 16 * h);
+            const uint2 s8 = __ldg(reinterpret_cast<const uint2*>(sc + blk * 16 + 8 * n));
+            const float d = half_bits_to_float(__ldg(dp + blk));
+            // d * float(sc) first, then * float(q): the reference's left-to-right product
+            const float dsl = __fmul_rn(d, static_cast<float>(sbyte_of(s8.x, 2 * a + h)));
+            const float dsh = __fmul_rn(d, static_cast<float>(sbyte_of(s8.y, 2 * a + h)));
+            const float* xl = xs + sb * 256 + 128 * n + 32 * a + 16 * h;
+            const unsigned lw[4] = {l.x, l.y, l.z, l.w}, hw[4] = {hq.x, hq.y, hq.z, hq.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int bq = 0; bq < 4; ++bq) {
+                    const unsigned lb = (lw[i] >> (8 * bq)) & 255u, hb = (hw[i] >> (8 * bq)) & 255u;
+                    const int q1 = static_cast<int>((lb & 15u) | (((hb >> (2 * a)) & 3u) << 4)) - 32;
+                    const int q2 = static_cast<int>((lb >> 4) | (((hb >> (2 * a + 4)) & 3u) << 4)) - 32;
+                    acc = fmaf(__fmul_rn(dsl, static_cast<float>(q1)), xl[4 * i + bq], acc);
+                    acc = fmaf(__fmul_rn(dsh, static_cast<float>(q2)), xl[64 + 4 * i + bq], acc);
+                }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) y[row] = acc;
+    }
+}
+
+// ---- bit-exact dequantisation to fp32 ------------------------------------------------------------
+// One thread per 16-byte quant chunk (32 weights); products rounded separately, as the reference.
+__global__ void dequant_q4k_kernel(const uint8_t* __restrict__ w, float* __restrict__ out, size_t nblk) {
+    const size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= nblk * 8) return;
+    const size_t blk = t >> 3;
+    const int c8 = static_cast<int>(t & 7), j = c8 >> 1, h = c8 & 1;
+    const uint8_t* p = w + blk * kQ4KBlock;
+    const uint4 hd = *reinterpret_cast<const uint4*>(p);
+    const uint4 q = *reinterpret_cast<const uint4*>(p + 16 + 16 * c8);
+    unsigned scw, mw;
+    if (j < 2) {
+        scw = hd.y & 0x3F3F3F3Fu;
+        mw = hd.z & 0x3F3F3F3Fu;
+    } else {
+        scw = (hd.w & kLo4) | ((hd.y >> 2) & kHi2);
+        mw = ((hd.w >> 4) & kLo4) | ((hd.z >> 2) & kHi2);
+    }
+    const int sh = 16 * (j & 1);
+    const float d = half_bits_to_float(hd.x & 0xFFFFu), dmin = half_bits_to_float(hd.x >> 16);
+    const float dl = __fmul_rn(d, static_cast<float>((scw >> sh) & 255));
+    const float dh = __fmul_rn(d, static_cast<float>((scw >> (sh + 8)) & 255));
+    const float ml = __fmul_rn(dmin, static_cast<float>((mw >> sh) & 255));
+    const float mh = __fmul_rn(dmin, static_cast<float>((mw >> (sh + 8)) & 255));
+    float* o = out + blk * 256 + 64 * j + 16 * h;
+    const unsigned qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int bq = 0; bq < 4; ++bq) {
+            const unsigned byte = (qw[i] >> (8 * bq)) & 255u;
+            o[4 * i + bq] = __fsub_rn(__fmul_rn(dl, static_cast<float>(byte & 15u)), ml);
+            o[32 + 4 * i + bq] = __fsub_rn(__fmul_rn(dh, static_cast<float>(byte >> 4)), mh);
+        }
+}
+
+__global__ void dequant_q6k_kernel(const uint8_t* __restrict__ w, float* __restrict__ out, size_t nblk) {
+    const size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= nblk * 8) return;
+    const size_t blk = t >> 3;
+    const int r8 = static_cast<int>(t & 7), n = r8 >> 2, a = (r8 >> 1) & 1, h = r8 & 1;
+    const uint4 l = *reinterpret_cast<const uint4*>(w + blk * 128 + 16 * r8);
+    const uint4 hq = *reinterpret_cast<const uint4*>(w + nblk * 128 + blk * 64 + 32 * n + 16 * h);
+    const uint2 s8 = *reinterpret_cast<const uint2*>(w + nblk * 192 + blk * 16 + 8 * n);
+    const float d = half_bits_to_float(*reinterpret_cast<const unsigned short*>(w + nblk * 208 + blk * 2));
+    const float dsl = __fmul_rn(d, static_cast<float>(sbyte_of(s8.x, 2 * a + h)));
+    const float dsh = __fmul_rn(d, static_cast<float>(sbyte_of(s8.y, 2 * a + h)));
+    float* o = out + blk * 256 + 128 * n + 32 * a + 16 * h;
+    const unsigned lw[4] = {l.x, l.y, l.z, l.w}, hw[4] = {hq.x, hq.y, hq.z, hq.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int bq = 0; bq < 4; ++bq) {
+            const unsigned lb = (lw[i] >> (8 * bq)) & 255u, hb = (hw[i] >> (8 * bq)) & 255u;
+            const int q1 = static_cast<int>((lb & 15u) | (((hb >> (2 * a)) & 3u) << 4)) - 32;
+            const int q2 = static_cast<int>((lb >> 4) | (((hb >> (2 * a + 4)) & 3u) << 4)) - 32;
+            o[4 * i + bq] = __fmul_rn(dsl, static_cast<float>(q1));
+            o[64 + 4 * i + bq] = __fmul_rn(dsh, static_cast<float>(q2));
+        }
+}
+
+// ---- Q6_K: GGUF blocks <-> planes ----------------------------------------------------------------
+// One thread per 2 bytes of a block (105 threads' worth); load-time only.
+__global__ void q6k_planes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, size_t nblk, int to_planes) {
+    const size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= nblk * 105) return;
+    const size_t blk = t / 105;
+    const int o = static_cast<int>(t % 105) * 2;  // byte offset inside the 210-byte block
+    size_t plane;
+    if (o < 128) plane = blk * 128 + o;
+    else if (o < 192) plane = nblk * 128 + blk * 64 + (o - 128);
+    else if (o < 208) plane = nblk * 192 + blk * 16 + (o - 192);
+    else plane = nblk * 208 + blk * 2;
+    const size_t gg = blk * kQ6KBlock + o;
+    if (to_planes) *reinterpret_cast<unsigned short*>(dst + plane) = *reinterpret_cast<const unsigned short*>(src + gg);
+    else *reinterpret_cast<unsigned short*>(dst + gg) = *reinterpret_cast<const unsigned short*>(src + plane);
+}
+
+int grid_for_rows(int rows, int rpw) {
+    const int need = (rows + kWarps * rpw - 1) / (kWarps * rpw);
+    const int cap = kSmCount * 6;  // 6 CTAs of 8 warps per SM keep 48 warps streaming
+    return need < 1 ? 1 : (need < cap ? need : cap);
+}
+
+bool shape_ok(int rows, int k) { return rows >= 0 && k > 0 && k % 256 == 0 && k <= 32768; }
+
+}  // namespace
+
+int matvec_q4k_q8(const void* w, const int* xq, const float* xd, float* y, int rows, int k, cudaStream_t s) {
+    if (!shape_ok(rows, k) || !w || !xq || !xd || !y) return KCB_INVALID_VALUE;
+    if (rows == 0) return KCB_SUCCESS;
+    const int nsb = k / 256;
+    const size_t smem = static_cast<size_t>(nsb) * (64 * 4 + 8 * 8);
+    if (rows >= kSmCount * 6 * kWarps * 2)
+        matvec_q4k_q8_kernel<2><<<grid_for_rows(rows, 2), kThreads, smem, s>>>(static_cast<const uint8_t*>(w), xq, xd, y, rows, nsb);
+    else
+        matvec_q4k_q8_kernel<1><<<grid_for_rows(rows, 1), kThreads, smem, s>>>(static_cast<const uint8_t*>(w), xq, xd, y, rows, nsb);
+    return launch_status();
+}
+
+int matvec_q6k_q8(const void* w, const int* xq, const float* xd, float* y, int rows, int k, cudaStream_t s) {
+    if (!shape_ok(rows, k) || !w || !xq || !xd || !y) return KCB_INVALID_VALUE;
+    if (rows == 0) return KCB_SUCCESS;
+    const int nsb = k / 256;
+    const size_t smem = static_cast<size_t>(nsb) * (64 * 4 + 8 * 8 + 16 * 4);
+    if (rows >= kSmCount * 6 * kWarps * 2)
+        matvec_q6k_q8_kernel<2><<<grid_for_rows(rows, 2), kThreads, smem, s>>>(static_cast<const uint8_t*>(w), xq, xd, y, rows, nsb, rows);
+    else
+        matvec_q6k_q8_kernel<1><<<grid_for_rows(rows, 1), kThreads, smem, s>>>(static_cast<const uint8_t*>(w), xq, xd, y, rows, nsb, rows);
+    return launch_status();
+}
+
+int matvec_q4k_f32(const void* w, const float* x, float* y, int rows, int k, cudaStream_t s) {
+    if (!shape_ok(rows, k) || k > 12288 || !w || !x || !y) return KCB_INVALID_VALUE;
+    if (rows == 0) return KCB_SUCCESS;
+    matvec_q4k_f32_kernel<<<grid_for_rows(rows, 1), kThreads, static_cast<size_t>(k) * 4, s>>>(static_cast<const uint8_t*>(w), x, y, rows, k / 256);
+    return launch_status();
+}
+
+int matvec_q6k_f32(const void* w, const float* x, float* y, int rows, int k, cudaStream_t s) {
+    if (!shape_ok(rows, k) || k > 12288 || !w || !x || !y) return KCB_INVALID_VALUE;
+    if (rows == 0) return KCB_SUCCESS;
+    matvec_q6k_f32_kernel<<<grid_for_rows(rows, 1), kThreads, static_cast<size_t>(k) * 4, s>>>(static_cast<const uint8_t*>(w), x, y, rows, k / 256, rows);
+    return launch_status();
+}
+
+int dequant_q4k(const void* w, float* out, int rows, int k, cudaStream_t s) {
+    if (!shape_ok(rows, k) || !w || !out) return KCB_INVALID_VALUE;
+    const size_t nblk = static_cast<size_t>(rows) * (k / 256);
+    if (nblk == 0) return KCB_SUCCESS;
+    dequant_q4k_kernel<<<static_cast<unsigned>((nblk * 8 + 255) / 256), 256, 0, s>>>(static_cast<const uint8_t*>(w), out, nblk);
+    return launch_status();
+}
+
+int dequant_q6k(const void* w, float* out, int rows, int k, cudaStream_t s) {
+    if (!shape_ok(rows, k) || !w || !out) return KCB_INVALID_VALUE;
+    const size_t nblk = static_cast<size_t>(rows) * (k / 256);
+    if (nblk == 0) return KCB_SUCCESS;
+    dequant_q6k_kernel<<<static_cast<unsigned>((nblk * 8 + 255) / 256), 256, 0, s>>>(static_cast<const uint8_t*>(w), out, nblk);
+    return launch_status();
+}
+
+int q6k_convert(const void* src, void* dst, int rows, int k, int to_planes, cudaStream_t s) {
+    if (!shape_ok(rows, k) || !src || !dst) return KCB_INVALID_VALUE;
+    const size_t nblk = static_cast<size_t>(rows) * (k / 256);
+    if (nblk == 0) return KCB_SUCCESS;
+    q6k_planes_kernel<<<static_cast<unsigned>((nblk * 105 + 255) / 256), 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), nblk, to_planes);
+    return launch_status();
+}
+
+}  // namespace kcb
