@@ -1,0 +1,304 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-LLM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): the Q6_K LM-head matvec, W 128256 x 3072 in GGUF Q6_K (323 MB), x fp32[3072],
+logits fp32[128256].  One step = the reference's Backend::matvec for a K-quant matrix: quantize x to
+Q8 blocks of 32 (quantize_q8x4) and run the integer-dot matvec (matvec_q6k_q8).  Four distinct
+matrices are rotated so that every step streams weights that left L2 long ago.  At N > 1 the rows
+are sharded evenly over the ranks (x replicated) and the logits are all-gathered: strong scaling.
+
+Prints ONE JSON line (rank 0).  `value` is GB/s of algorithmic bytes (GGUF weight bytes + x + y) over
+the K timed steps, inputs resident in HBM; `e2e` is the same metric through host buffers (pinned x
+copied in, logits copied out, every step); `roofline` is the matvec kernel alone, timed with CUDA
+events inside the timed region; `cpu_baseline` is the reference's own AVX2 kernels on all host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, K = 128256, 3072
+NSB = K // 256
+NMAT = 4
+METRIC, UNIT = "q6k_lm_head_matvec_hbm_gbs", "GB/s"
+# DRAM bytes per full-size launch of the matvec kernel (dram__bytes_read.sum + dram__bytes_write.sum),
+# from the ncu capture summarised in profiles/matvec_q6k_q8_lm_head.md; None until captured.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def algorithmic_bytes(rows: int) -> int:
+    """GGUF bytes of the weight rows + fp32 x + fp32 y (layout-independent)."""
+    return rows * NSB * 210 + K * 4 + rows * 4
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---- the reference's CPU path --------------------------------------------------------------------
+
+def cpu_reference_matvec(blocks: np.ndarray, x: np.ndarray, rows: int, reps: int, warm: int):
+    """Times the reference's CPU implementation of this matvec on the host cores.  Uses its generated
+    AVX2 kernels on all threads (oracle/_ref/libkcref_simd.so) when that library was built, else the
+    scalar C restatement on one thread.  Returns (seconds per matvec, cores, kind, y)."""
+    import oracle
+    simd_path = os.path.join(ROOT, "oracle", "_ref", "libkcref_simd.so")
+    if oracle.ref is not None and os.path.exists(simd_path):
+        L = C.CDLL(simd_path)
+        i32p, f32p = np.ctypeslib.ndpointer(np.int32), np.ctypeslib.ndpointer(np.float32)
+        L.kcref_simd_matvec.argtypes = [C.c_int, i32p, i32p, f32p, f32p, C.c_int, C.c_int, C.c_int]
+        L.kcref_simd_quantize_q8x4.argtypes = [f32p, i32p, f32p, C.c_int]
+        L.kcref_simd_threads.argtypes = [C.c_int]
+        cores = L.kcref_simd_threads(0)
+        qw = np.zeros(oracle.ref.lib.kcref_stream_ints(rows, K, 1), np.int32)
+        oracle.ref.lib.kcref_repack(np.ascontiguousarray(blocks[:rows]).ravel(), rows, K, 1, qw)
+        xq, xd, y = np.zeros(K // 4, np.int32), np.zeros(K // 16, np.float32), np.zeros(rows, np.float32)
+
+        def step():
+            L.kcref_simd_quantize_q8x4(x, xq, xd, K // 32)
+            L.kcref_simd_matvec(1, qw, xq, xd, y, rows, K, 16)
+        kind = "reference"
+    else:
+        cores = 1
+        w = np.ascontiguousarray(blocks[:rows]).ravel()
+        xq, xd, y = np.zeros(K // 4, np.int32), np.zeros(K // 16, np.float32), np.zeros(rows, np.float32)
+
+        def step():
+            oracle.port.quantize_q8x4(x, xq, xd, K // 32)
+            oracle.port.matvec_q6k_q8(w, xq, xd, y, rows, K)
+        kind = "port"
+    for _ in range(warm):
+        step()
+    t = time.perf_counter()
+    for _ in range(reps):
+        step()
+    return (time.perf_counter() - t) / reps, cores, kind, y
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from kernelcore_b200 import synth
+    blocks = synth.q6k_blocks(ROWS, K, 0)
+    x = synth.activations(K, 100)
+    sec, cores, kind, _ = cpu_reference_matvec(blocks, x, ROWS, args.steps, args.warmup)
+    gbs = algorithmic_bytes(ROWS) / sec / 1e9
+    sample = f"{args.steps} full {ROWS}x{K} Q6_K matvecs (quantize_q8x4 + matvec_q6k_q8)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8 dot, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"Q6_K lm_head matvec {ROWS}x{K}, reference CPU kernels on host cores", "rows": ROWS, "k": K},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---- our arm ----------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from kernelcore_b200 import kquant, lib, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path for these kernels")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    assert ROWS % (8 * world) == 0
+    rows = ROWS // world
+    r0 = rank * rows
+
+    # inputs resident in HBM: NMAT distinct weight matrices (this rank's rows), replicated x
+    mats, host_blocks0 = [], None
+    for i in range(NMAT):
+        blocks = synth.q6k_blocks(ROWS, K, i)
+        if i == 0 and rank == 0 and world == 1:
+            host_blocks0 = blocks
+        mats.append(kquant.KMatrix(blocks[r0:r0 + rows], rows, K, True))
+        del blocks
+    x_host = torch.from_numpy(synth.activations(K, 100)).pin_memory()
+    x = x_host.cuda()
+    scratch = kquant.Q8Scratch(K)
+    y_local = torch.empty(rows, dtype=torch.float32, device="cuda")
+    y_full = torch.empty(ROWS, dtype=torch.float32, device="cuda") if world > 1 else y_local
+    y_host = torch.empty(ROWS, dtype=torch.float32).pin_memory()
+    stream = torch.cuda.current_stream()
+
+    def step(i, ev=None):
+        m = mats[i % NMAT]
+        xq, xd = kquant.quantize_q8x4(x, scratch)
+        if ev is not None:
+            ev[0].record(stream)
+        kquant.matvec_q8(m, xq, xd, y_local)
+        if ev is not None:
+            ev[1].record(stream)
+        if world > 1:
+            dist.all_gather_into_tensor(y_full, y_local)
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    fence()
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    fence()
+    t0.record(stream)
+    for i in range(args.steps):
+        step(i, kev[i])
+    t1.record(stream)
+    fence()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t0.elapsed_time(t1)
+    kern_ms = statistics.mean(a.elapsed_time(b) for a, b in kev)
+
+    # end to end through host buffers: x in from pinned memory, logits out, every step
+    def e2e_step(i):
+        x.copy_(x_host, non_blocking=True)
+        step(i)
+        y_host.copy_(y_full, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    fence()
+    w0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    fence()
+    e2e_ms = (time.perf_counter() - w0) * 1e3
+
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms, kern_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms, kern_ms = (float(v) for v in t.cpu())
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = measured_peak()
+    alg_total = algorithmic_bytes(ROWS)
+    alg_launch = algorithmic_bytes(rows)
+    value = alg_total * args.steps / (total_ms * 1e-3) / 1e9
+    achieved = alg_launch / (kern_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 dot, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"Q6_K lm_head matvec {ROWS}x{K} (BASELINE configs[1]): quantize_q8x4 + matvec_q6k_q8"
+                               + (f", rows sharded over {world} GPUs + NCCL all-gather of the logits" if world > 1 else ""),
+                   "rows": ROWS, "k": K, "rows_per_gpu": rows,
+                   "l2": f"inputs larger than L2: {NMAT} rotating {rows * NSB * 210 / 1e6:.0f} MB weight matrices"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": "matvec_q6k_q8_kernel",
+                     "algorithmic_bytes_per_launch": alg_launch, "kernel_us": kern_ms * 1e3, "peak_source": peak_src,
+                     "frac_of_8tbs_nominal": achieved / 8000.0},
+        "e2e": {"value": alg_total * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": K * 4,
+                "d2h_bytes_per_step": ROWS * 4, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+    }
+    if world == 1:
+        sec, cores, kind, y_cpu = cpu_reference_matvec(host_blocks0, x_host.numpy(), ROWS, 20, 3)
+        line["cpu_baseline"] = {"value": alg_total / sec / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
+                                "sample": f"20 full {ROWS}x{K} Q6_K matvecs, reference AVX2 kernels, all host threads"
+                                if kind == "reference" else f"20 full {ROWS}x{K} matvecs, scalar C port"}
+        step(0)
+        torch.cuda.synchronize()
+        err = float((y_local.cpu() - torch.from_numpy(y_cpu)).abs().max() / np.abs(y_cpu).max())
+        line["check_vs_cpu_rel"] = err
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
