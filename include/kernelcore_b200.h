@@ -27,6 +27,11 @@ const char* kcb_build_arch(void);
 /* Text for a status code: kcGetErrorString, include/kernelcore/api.hpp:80. */
 const char* kcb_error_string(int status);
 
+/* Number of bounded device-side waits (mbarrier polls of the bulk-copy pipelines) that gave up since
+ * the library was loaded; 0 in a healthy process.  Synchronous.  No counterpart in the reference: its
+ * fault reporting is kcGetLastFault (include/kernelcore/api.hpp:79). */
+unsigned kcb_tma_timeouts(void);
+
 /* ---- weight layouts -------------------------------------------------------------------------
  * Q4_K matrices live on the device as canonical GGUF super-blocks, row-major: rows*(k/256) blocks
  * of 144 bytes.  Q6_K matrices live as four planes (ql | qh | scales | d) of the same total size,

@@ -35,6 +35,8 @@ const char* kcb_error_string(int e) {
     return "unknown error";
 }
 
+unsigned kcb_tma_timeouts(void) { return tma_timeouts(); }
+
 size_t kcb_kquant_bytes(int rows, int k, int q6) {
     if (rows < 0 || k < 0 || k % 256) return 0;
     return static_cast<size_t>(rows) * (k / 256) * (q6 ? kQ6KBlock : kQ4KBlock);

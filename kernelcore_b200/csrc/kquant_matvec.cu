@@ -22,6 +22,8 @@
 #include "common.cuh"
 #include "ops.h"
 
+#include <cstdlib>
+
 namespace kcb {
 namespace {
 
@@ -413,6 +415,448 @@ __global__ void q6k_planes_kernel(const uint8_t* __restrict__ src, uint8_t* __re
     else *reinterpret_cast<unsigned short*>(dst + gg) = *reinterpret_cast<const unsigned short*>(src + plane);
 }
 
+// ---- register-resident activations (k <= 4096) -----------------------------------------------------
+// A lane's k-positions are fixed by its lane id, so for ITERS = ceil(nsb / 4) <= 4 the lane keeps its
+// whole slice of the Q8 activations (words, scales, half-block sums) in registers for the life of the
+// kernel: the row loop then holds nothing but the weight loads, the unpack and the dot products.  All
+// loads of a row are issued before its arithmetic, and (PF) the next row's loads before this row's
+// arithmetic, so every warp keeps 4-8 KB in flight.
+template <int ITERS, bool PF>
+__global__ void __launch_bounds__(kThreads) matvec_q4k_q8_reg_kernel(const uint8_t* __restrict__ w,
+                                                                      const int* __restrict__ xq,
+                                                                      const float* __restrict__ xd,
+                                                                      float* __restrict__ y, int rows, int nsb) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 3, c8 = lane & 7, j = c8 >> 1, h = c8 & 1;
+    const int sh = 16 * (j & 1);
+
+    uint4 xa[ITERS], xb[ITERS];
+    float4 dd[ITERS];  // {d_b, d_b * sum_b, d_b+1, d_b+1 * sum_b+1}; the min part is zero on h == 1 lanes
+    bool ok[ITERS];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int sb = 4 * it + g;
+        ok[it] = sb < nsb;
+        xa[it] = xb[it] = make_uint4(0, 0, 0, 0);
+        dd[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ok[it]) {
+            const int b = sb * 8 + 2 * j;
+            xa[it] = __ldg(reinterpret_cast<const uint4*>(xq + b * 8 + 4 * h));
+            xb[it] = __ldg(reinterpret_cast<const uint4*>(xq + b * 8 + 8 + 4 * h));
+            const float4 t = __ldg(reinterpret_cast<const float4*>(xd + 2 * b));  // {d_b, sum_b, d_b+1, sum_b+1}
+            dd[it] = make_float4(t.x, h == 0 ? __fmul_rn(t.x, t.y) : 0.f, t.z, h == 0 ? __fmul_rn(t.z, t.w) : 0.f);
+        }
+    }
+
+    const size_t row_bytes = static_cast<size_t>(nsb) * kQ4KBlock;
+    const int nwarps = gridDim.x * kWarps;
+    const uint8_t* lane_base = w + static_cast<size_t>(g) * kQ4KBlock;
+
+    auto load = [&](Q4Regs (&t)[ITERS], int row) {
+        const uint8_t* p = lane_base + row * row_bytes;
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it)
+            if (ok[it]) {
+                t[it].hd = ldg_stream(p + it * 4 * kQ4KBlock);
+                t[it].q = ldg_stream(p + it * 4 * kQ4KBlock + 16 + 16 * c8);
+            }
+    };
+    auto compute = [&](const Q4Regs (&t)[ITERS]) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            if (!ok[it]) continue;
+            const uint4 q = t[it].q, hd = t[it].hd;
+            int da = 0, db = 0;
+            da = __dp4a(static_cast<int>(q.x & kLo4), static_cast<int>(xa[it].x), da);
+            da = __dp4a(static_cast<int>(q.y & kLo4), static_cast<int>(xa[it].y), da);
+            da = __dp4a(static_cast<int>(q.z & kLo4), static_cast<int>(xa[it].z), da);
+            da = __dp4a(static_cast<int>(q.w & kLo4), static_cast<int>(xa[it].w), da);
+            db = __dp4a(static_cast<int>((q.x >> 4) & kLo4), static_cast<int>(xb[it].x), db);
+            db = __dp4a(static_cast<int>((q.y >> 4) & kLo4), static_cast<int>(xb[it].y), db);
+            db = __dp4a(static_cast<int>((q.z >> 4) & kLo4), static_cast<int>(xb[it].z), db);
+            db = __dp4a(static_cast<int>((q.w >> 4) & kLo4), static_cast<int>(xb[it].w), db);
+            unsigned scw, mw;
+            if (j < 2) {
+                scw = hd.y & 0x3F3F3F3Fu;
+                mw = hd.z & 0x3F3F3F3Fu;
+            } else {
+                scw = (hd.w & kLo4) | ((hd.y >> 2) & kHi2);
+                mw = ((hd.w >> 4) & kLo4) | ((hd.z >> 2) & kHi2);
+            }
+            const int sca = (scw >> sh) & 255, scb = (scw >> (sh + 8)) & 255;
+            const int ma = (mw >> sh) & 255, mb = (mw >> (sh + 8)) & 255;
+            const float d = half_bits_to_float(hd.x & 0xFFFFu), dmin = half_bits_to_float(hd.x >> 16);
+            const float t1 = static_cast<float>(sca * da) * dd[it].x + static_cast<float>(scb * db) * dd[it].z;
+            const float t2 = static_cast<float>(ma) * dd[it].y + static_cast<float>(mb) * dd[it].w;
+            acc += d * t1 - dmin * t2;
+        }
+        return acc;
+    };
+
+    int row = blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    Q4Regs cur[ITERS];
+    load(cur, row);
+    for (; row < rows; row += nwarps) {
+        float acc;
+        if (PF) {
+            Q4Regs nxt[ITERS];
+            const int rn = row + nwarps;
+            if (rn < rows) load(nxt, rn);
+            acc = compute(cur);
+#pragma unroll
+            for (int it = 0; it < ITERS; ++it) cur[it] = nxt[it];
+        } else {
+            acc = compute(cur);
+            if (row + nwarps < rows) load(cur, row + nwarps);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) y[row] = acc;
+    }
+}
+
+template <int ITERS, bool PF>
+__global__ void __launch_bounds__(kThreads) matvec_q6k_q8_reg_kernel(const uint8_t* __restrict__ w,
+                                                                      const int* __restrict__ xq,
+                                                                      const float* __restrict__ xd,
+                                                                      float* __restrict__ y, int rows, int nsb) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 3, r8 = lane & 7, n = r8 >> 2, a = (r8 >> 1) & 1, h = r8 & 1;
+    const int shl = 4 - 2 * a, shr = 2 * a;
+    // byte (2a + h) of a scale word, sign-extended, in one permute: selector nibbles {i, i|8, i|8, i|8}
+    const unsigned sel = static_cast<unsigned>(2 * a + h) * 0x1111u | 0x8880u;
+
+    uint4 xa[ITERS], xb[ITERS];
+    float dxa[ITERS], dxb[ITERS];
+    int sa[ITERS], sb2[ITERS];
+    bool ok[ITERS];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int sb = 4 * it + g;
+        ok[it] = sb < nsb;
+        xa[it] = xb[it] = make_uint4(0, 0, 0, 0);
+        dxa[it] = dxb[it] = 0.f;
+        sa[it] = sb2[it] = 0;
+        if (ok[it]) {
+            const int b = sb * 8 + 4 * n + a;
+            xa[it] = __ldg(reinterpret_cast<const uint4*>(xq + b * 8 + 4 * h));
+            xb[it] = __ldg(reinterpret_cast<const uint4*>(xq + (b + 2) * 8 + 4 * h));
+            dxa[it] = __ldg(xd + 2 * b);
+            dxb[it] = __ldg(xd + 2 * (b + 2));
+            int s0 = 0, s1 = 0;
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].x), s0);
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].y), s0);
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].z), s0);
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].w), s0);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].x), s1);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].y), s1);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].z), s1);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].w), s1);
+            sa[it] = 32 * s0;  // the -32 weight offset, applied through the activation sums
+            sb2[it] = 32 * s1;
+        }
+    }
+
+    const size_t nblk = static_cast<size_t>(rows) * nsb;
+    const uint8_t* ql = w + static_cast<size_t>(g) * 128 + 16 * r8;
+    const uint8_t* qh = w + nblk * 128 + static_cast<size_t>(g) * 64 + 32 * n + 16 * h;
+    const uint8_t* sc = w + nblk * 192 + static_cast<size_t>(g) * 16 + 8 * n;
+    const uint8_t* dp = w + nblk * 208 + static_cast<size_t>(g) * 2;
+    const int nwarps = gridDim.x * kWarps;
+
+    auto load = [&](Q6Regs (&t)[ITERS], int row) {
+        const size_t blk = static_cast<size_t>(row) * nsb;
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it)
+            if (ok[it]) {
+                t[it].ql = ldg_stream(ql + (blk + 4 * it) * 128);
+                t[it].qh = ldg_stream(qh + (blk + 4 * it) * 64);
+                t[it].sc = __ldg(reinterpret_cast<const uint2*>(sc + (blk + 4 * it) * 16));
+                t[it].d = __ldg(reinterpret_cast<const unsigned short*>(dp + (blk + 4 * it) * 2));
+            }
+    };
+    auto compute = [&](const Q6Regs (&t)[ITERS]) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            if (!ok[it]) continue;
+            const uint4 l = t[it].ql, hq = t[it].qh;
+            int dl = 0, dh = 0;
+            dl = __dp4a(static_cast<int>((l.x & kLo4) | ((hq.x << shl) & kHi2)), static_cast<int>(xa[it].x), dl);
+            dl = __dp4a(static_cast<int>((l.y & kLo4) | ((hq.y << shl) & kHi2)), static_cast<int>(xa[it].y), dl);
+            dl = __dp4a(static_cast<int>((l.z & kLo4) | ((hq.z << shl) & kHi2)), static_cast<int>(xa[it].z), dl);
+            dl = __dp4a(static_cast<int>((l.w & kLo4) | ((hq.w << shl) & kHi2)), static_cast<int>(xa[it].w), dl);
+            dh = __dp4a(static_cast<int>(((l.x >> 4) & kLo4) | ((hq.x >> shr) & kHi2)), static_cast<int>(xb[it].x), dh);
+            dh = __dp4a(static_cast<int>(((l.y >> 4) & kLo4) | ((hq.y >> shr) & kHi2)), static_cast<int>(xb[it].y), dh);
+            dh = __dp4a(static_cast<int>(((l.z >> 4) & kLo4) | ((hq.z >> shr) & kHi2)), static_cast<int>(xb[it].z), dh);
+            dh = __dp4a(static_cast<int>(((l.w >> 4) & kLo4) | ((hq.w >> shr) & kHi2)), static_cast<int>(xb[it].w), dh);
+            const int tl = prmt_sbyte(t[it].sc.x, sel) * (dl - sa[it]);
+            const int th = prmt_sbyte(t[it].sc.y, sel) * (dh - sb2[it]);
+            acc += half_bits_to_float(t[it].d) * (static_cast<float>(tl) * dxa[it] + static_cast<float>(th) * dxb[it]);
+        }
+        return acc;
+    };
+
+    int row = blockIdx.x * kWarps + warp;
+    if (row >= rows) return;
+    Q6Regs cur[ITERS];
+    load(cur, row);
+    for (; row < rows; row += nwarps) {
+        float acc;
+        if (PF) {
+            Q6Regs nxt[ITERS];
+            const int rn = row + nwarps;
+            if (rn < rows) load(nxt, rn);
+            acc = compute(cur);
+#pragma unroll
+            for (int it = 0; it < ITERS; ++it) cur[it] = nxt[it];
+        } else {
+            acc = compute(cur);
+            if (row + nwarps < rows) load(cur, row + nwarps);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) y[row] = acc;
+    }
+}
+
+// ---- bulk-copy (TMA) pipelined kernels: the roofline path for large matrices --------------------------
+// One persistent CTA per SM.  Tiles of TR consecutive rows are brought into a ring of shared-memory
+// stages by cp.async.bulk (one copy per tile for Q4_K, one per plane for Q6_K), each stage completing
+// on its own mbarrier; warp w of the CTA consumes row w of the tile straight out of shared memory with
+// the same lane mapping as above and the activation slice held in registers.  With 4-5 stages of 28-40
+// KB the SM keeps > 100 KB of weight bytes in flight no matter how the warps are scheduled, which is
+// what HBM3e needs; the register-only kernels above top out near 65 % of the roofline.
+// Stage reuse is ordered by one __syncthreads per tile: after it, thread 0 refills the stage just
+// consumed.  Every mbarrier wait is bounded; on expiry the CTA records it in g_tma_timeouts and leaves.
+__device__ unsigned g_tma_timeouts = 0;
+
+constexpr int kTmaMaxStages = 8;
+
+template <bool kQ6, int ITERS, int TR>
+__global__ void __launch_bounds__(TR * 32, 1) matvec_kq_q8_tma_kernel(const uint8_t* __restrict__ w,
+                                                                       const int* __restrict__ xq,
+                                                                       const float* __restrict__ xd,
+                                                                       float* __restrict__ y, int rows, int nsb,
+                                                                       int stages) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint8_t* buf = smem + 128;
+    constexpr int kBlk = kQ6 ? kQ6KBlock : kQ4KBlock;
+    const uint32_t stage_bytes = static_cast<uint32_t>(TR) * nsb * kBlk;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 3, c8 = lane & 7;
+    const int ntiles = (rows + TR - 1) / TR;
+    const int my_tiles = blockIdx.x < ntiles ? (ntiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+    const size_t nblk = static_cast<size_t>(rows) * nsb;
+
+    auto issue = [&](int i) {  // thread 0 only
+        const int s = i % stages;
+        const int r0 = (blockIdx.x + i * gridDim.x) * TR;
+        const int nr = min(TR, rows - r0);
+        uint8_t* dst = buf + static_cast<size_t>(s) * stage_bytes;
+        const size_t b0 = static_cast<size_t>(r0) * nsb;
+        const uint32_t nb = static_cast<uint32_t>(nr) * nsb;
+        mbar_expect_tx(&full[s], nb * kBlk);
+        if (kQ6) {
+            bulk_g2s(dst, w + b0 * 128, nb * 128, &full[s]);
+            bulk_g2s(dst + TR * nsb * 128, w + nblk * 128 + b0 * 64, nb * 64, &full[s]);
+            bulk_g2s(dst + TR * nsb * 192, w + nblk * 192 + b0 * 16, nb * 16, &full[s]);
+            bulk_g2s(dst + TR * nsb * 208, w + nblk * 208 + b0 * 2, nb * 2, &full[s]);
+        } else {
+            bulk_g2s(dst, w + b0 * kQ4KBlock, nb * kQ4KBlock, &full[s]);
+        }
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (int i = 0; i < stages && i < my_tiles; ++i) issue(i);
+
+    // ---- this lane's slice of the activations, in registers ----
+    uint4 xa[ITERS], xb[ITERS];
+    float4 dd[ITERS];
+    int sa[ITERS], sb2[ITERS];
+    bool ok[ITERS];
+    // Q4_K lane roles
+    const int j = c8 >> 1, h = c8 & 1, sh = 16 * (j & 1);
+    // Q6_K lane roles
+    const int n = c8 >> 2, a = (c8 >> 1) & 1;
+    const int shl = 4 - 2 * a, shr = 2 * a;
+    const unsigned sel = static_cast<unsigned>(2 * a + h) * 0x1111u | 0x8880u;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int sb = 4 * it + g;
+        ok[it] = sb < nsb;
+        xa[it] = xb[it] = make_uint4(0, 0, 0, 0);
+        dd[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+        sa[it] = sb2[it] = 0;
+        if (!ok[it]) continue;
+        if (kQ6) {
+            const int b = sb * 8 + 4 * n + a;
+            xa[it] = __ldg(reinterpret_cast<const uint4*>(xq + b * 8 + 4 * h));
+            xb[it] = __ldg(reinterpret_cast<const uint4*>(xq + (b + 2) * 8 + 4 * h));
+            dd[it].x = __ldg(xd + 2 * b);
+            dd[it].z = __ldg(xd + 2 * (b + 2));
+            int s0 = 0, s1 = 0;
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].x), s0);
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].y), s0);
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].z), s0);
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].w), s0);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].x), s1);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].y), s1);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].z), s1);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].w), s1);
+            sa[it] = 32 * s0;
+            sb2[it] = 32 * s1;
+        } else {
+            const int b = sb * 8 + 2 * j;
+            xa[it] = __ldg(reinterpret_cast<const uint4*>(xq + b * 8 + 4 * h));
+            xb[it] = __ldg(reinterpret_cast<const uint4*>(xq + b * 8 + 8 + 4 * h));
+            const float4 t = __ldg(reinterpret_cast<const float4*>(xd + 2 * b));
+            dd[it] = make_float4(t.x, h == 0 ? __fmul_rn(t.x, t.y) : 0.f, t.z, h == 0 ? __fmul_rn(t.z, t.w) : 0.f);
+        }
+    }
+
+    for (int i = 0; i < my_tiles; ++i) {
+        const int s = i % stages;
+        const uint32_t parity = static_cast<uint32_t>(i / stages) & 1u;
+        if (!mbar_wait_bounded(&full[s], parity)) {
+            if (lane == 0) atomicAdd(&g_tma_timeouts, 1u);
+            for (int t = 0; t < 1000; ++t) __nanosleep(1000);  // bounded grace for copies still in flight
+            return;  // data never arrived: leave without touching y
+        }
+        const int row = (blockIdx.x + i * gridDim.x) * TR + warp;
+        if (row < rows) {
+            const uint8_t* st = buf + static_cast<size_t>(s) * stage_bytes;
+            float acc = 0.0f;
+            if (kQ6) {
+                const uint8_t* pl = st + (static_cast<size_t>(warp) * nsb + g) * 128 + 16 * c8;
+                const uint8_t* ph = st + TR * nsb * 128 + (static_cast<size_t>(warp) * nsb + g) * 64 + 32 * n + 16 * h;
+                const uint8_t* ps = st + TR * nsb * 192 + (static_cast<size_t>(warp) * nsb + g) * 16 + 8 * n;
+                const uint8_t* pd = st + TR * nsb * 208 + (static_cast<size_t>(warp) * nsb + g) * 2;
+#pragma unroll
+                for (int it = 0; it < ITERS; ++it) {
+                    if (!ok[it]) continue;
+                    const uint4 l = *reinterpret_cast<const uint4*>(pl + it * 4 * 128);
+                    const uint4 hq = *reinterpret_cast<const uint4*>(ph + it * 4 * 64);
+                    const uint2 sc = *reinterpret_cast<const uint2*>(ps + it * 4 * 16);
+                    const unsigned dq = *reinterpret_cast<const unsigned short*>(pd + it * 4 * 2);
+                    int dl = 0, dh = 0;
+                    dl = __dp4a(static_cast<int>((l.x & kLo4) | ((hq.x << shl) & kHi2)), static_cast<int>(xa[it].x), dl);
+                    dl = __dp4a(static_cast<int>((l.y & kLo4) | ((hq.y << shl) & kHi2)), static_cast<int>(xa[it].y), dl);
+                    dl = __dp4a(static_cast<int>((l.z & kLo4) | ((hq.z << shl) & kHi2)), static_cast<int>(xa[it].z), dl);
+                    dl = __dp4a(static_cast<int>((l.w & kLo4) | ((hq.w << shl) & kHi2)), static_cast<int>(xa[it].w), dl);
+                    dh = __dp4a(static_cast<int>(((l.x >> 4) & kLo4) | ((hq.x >> shr) & kHi2)), static_cast<int>(xb[it].x), dh);
+                    dh = __dp4a(static_cast<int>(((l.y >> 4) & kLo4) | ((hq.y >> shr) & kHi2)), static_cast<int>(xb[it].y), dh);
+                    dh = __dp4a(static_cast<int>(((l.z >> 4) & kLo4) | ((hq.z >> shr) & kHi2)), static_cast<int>(xb[it].z), dh);
+                    dh = __dp4a(static_cast<int>(((l.w >> 4) & kLo4) | ((hq.w >> shr) & kHi2)), static_cast<int>(xb[it].w), dh);
+                    const int tl = prmt_sbyte(sc.x, sel) * (dl - sa[it]);
+                    const int th = prmt_sbyte(sc.y, sel) * (dh - sb2[it]);
+                    acc += half_bits_to_float(dq) * (static_cast<float>(tl) * dd[it].x + static_cast<float>(th) * dd[it].z);
+                }
+            } else {
+                const uint8_t* pb = st + (static_cast<size_t>(warp) * nsb + g) * kQ4KBlock;
+#pragma unroll
+                for (int it = 0; it < ITERS; ++it) {
+                    if (!ok[it]) continue;
+                    const uint4 hd = *reinterpret_cast<const uint4*>(pb + it * 4 * kQ4KBlock);
+                    const uint4 q = *reinterpret_cast<const uint4*>(pb + it * 4 * kQ4KBlock + 16 + 16 * c8);
+                    int da = 0, db = 0;
+                    da = __dp4a(static_cast<int>(q.x & kLo4), static_cast<int>(xa[it].x), da);
+                    da = __dp4a(static_cast<int>(q.y & kLo4), static_cast<int>(xa[it].y), da);
+                    da = __dp4a(static_cast<int>(q.z & kLo4), static_cast<int>(xa[it].z), da);
+                    da = __dp4a(static_cast<int>(q.w & kLo4), static_cast<int>(xa[it].w), da);
+                    db = __dp4a(static_cast<int>((q.x >> 4) & kLo4), static_cast<int>(xb[it].x), db);
+                    db = __dp4a(static_cast<int>((q.y >> 4) & kLo4), static_cast<int>(xb[it].y), db);
+                    db = __dp4a(static_cast<int>((q.z >> 4) & kLo4), static_cast<int>(xb[it].z), db);
+                    db = __dp4a(static_cast<int>((q.w >> 4) & kLo4), static_cast<int>(xb[it].w), db);
+                    unsigned scw, mw;
+                    if (j < 2) {
+                        scw = hd.y & 0x3F3F3F3Fu;
+                        mw = hd.z & 0x3F3F3F3Fu;
+                    } else {
+                        scw = (hd.w & kLo4) | ((hd.y >> 2) & kHi2);
+                        mw = ((hd.w >> 4) & kLo4) | ((hd.z >> 2) & kHi2);
+                    }
+                    const int sca = (scw >> sh) & 255, scb = (scw >> (sh + 8)) & 255;
+                    const int ma = (mw >> sh) & 255, mb = (mw >> (sh + 8)) & 255;
+                    const float d = half_bits_to_float(hd.x & 0xFFFFu), dmin = half_bits_to_float(hd.x >> 16);
+                    const float t1 = static_cast<float>(sca * da) * dd[it].x + static_cast<float>(scb * db) * dd[it].z;
+                    const float t2 = static_cast<float>(ma) * dd[it].y + static_cast<float>(mb) * dd[it].w;
+                    acc += d * t1 - dmin * t2;
+                }
+            }
+            acc = warp_sum(acc);
+            if (lane == 0) y[row] = acc;
+        }
+        __syncthreads();  // every warp is done with stage s
+        if (threadIdx.x == 0 && i + stages < my_tiles) issue(i + stages);
+    }
+}
+
+template <bool kQ6, int ITERS>
+int launch_tma(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s) {
+    constexpr int TR = 16;
+    auto kern = matvec_kq_q8_tma_kernel<kQ6, ITERS, TR>;
+    const size_t stage_bytes = static_cast<size_t>(TR) * nsb * (kQ6 ? kQ6KBlock : kQ4KBlock);
+    int stages = static_cast<int>((200 * 1024) / stage_bytes);
+    if (stages > kTmaMaxStages) stages = kTmaMaxStages;
+    if (stages < 2) return KCB_UNSUPPORTED_OPERATION;
+    const size_t smem = 128 + stages * stage_bytes;
+    static bool attr_set = false;  // per instantiation
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess)
+            return KCB_LAUNCH_FAILURE;
+        attr_set = true;
+    }
+    const int ntiles = (rows + TR - 1) / TR;
+    const int grid = ntiles < kSmCount ? ntiles : kSmCount;
+    kern<<<grid, TR * 32, smem, s>>>(wb, xq, xd, y, rows, nsb, stages);
+    return launch_status();
+}
+
+template <bool kQ6>
+int launch_tma_iters(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s) {
+    switch ((nsb + 3) / 4) {
+    case 1: return launch_tma<kQ6, 1>(wb, xq, xd, y, rows, nsb, s);
+    case 2: return launch_tma<kQ6, 2>(wb, xq, xd, y, rows, nsb, s);
+    case 3: return launch_tma<kQ6, 3>(wb, xq, xd, y, rows, nsb, s);
+    case 4: return launch_tma<kQ6, 4>(wb, xq, xd, y, rows, nsb, s);
+    }
+    return KCB_UNSUPPORTED_OPERATION;
+}
+
+// The pipelined path needs whole 8-row groups (16-byte aligned d plane tiles) and enough tiles to give
+// every SM work.
+bool use_tma(int rows, int nsb) { return rows % 8 == 0 && nsb <= 16 && rows >= 16 * kSmCount; }
+
+// Resident CTAs per SM of a kernel, asked of the driver once per kernel and device.
+template <class Kern>
+int ctas_per_sm(Kern kern, size_t smem) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem) != cudaSuccess || n < 1) n = 1;
+    return n;
+}
+
+int env_variant() {
+    static const int v = [] {
+        const char* e = getenv("KCB_MATVEC_VARIANT");
+        return e ? atoi(e) : 0;
+    }();
+    return v;
+}
+
+template <class Kern>
+int grid_for(Kern kern, int rows, int rows_per_cta, size_t smem = 0) {
+    const int need = (rows + rows_per_cta - 1) / rows_per_cta;
+    const int cap = kSmCount * ctas_per_sm(kern, smem);
+    return need < cap ? need : cap;
+}
+
 int grid_for_rows(int rows, int rpw) {
     const int need = (rows + kWarps * rpw - 1) / (kWarps * rpw);
     const int cap = kSmCount * 6;  // 6 CTAs of 8 warps per SM keep 48 warps streaming
@@ -423,27 +867,68 @@ bool shape_ok(int rows, int k) { return rows >= 0 && k > 0 && k % 256 == 0 && k 
 
 }  // namespace
 
+unsigned tma_timeouts() {
+    unsigned v = 0;
+    cudaMemcpyFromSymbol(&v, g_tma_timeouts, sizeof v);
+    return v;
+}
+
+#define KCB_LAUNCH_REG(KERN, ITERS_)                                                                         \
+    do {                                                                                                     \
+        if (pf) {                                                                                            \
+            auto kern = KERN<ITERS_, true>;                                                                  \
+            kern<<<grid_for(kern, rows, kWarps), kThreads, 0, s>>>(wb, xq, xd, y, rows, nsb);                \
+        } else {                                                                                             \
+            auto kern = KERN<ITERS_, false>;                                                                 \
+            kern<<<grid_for(kern, rows, kWarps), kThreads, 0, s>>>(wb, xq, xd, y, rows, nsb);                \
+        }                                                                                                    \
+    } while (0)
+
 int matvec_q4k_q8(const void* w, const int* xq, const float* xd, float* y, int rows, int k, cudaStream_t s) {
     if (!shape_ok(rows, k) || !w || !xq || !xd || !y) return KCB_INVALID_VALUE;
     if (rows == 0) return KCB_SUCCESS;
-    const int nsb = k / 256;
+    const int nsb = k / 256, iters = (nsb + 3) / 4;
+    const uint8_t* wb = static_cast<const uint8_t*>(w);
+    const bool pf = env_variant() != 1;
+    if (use_tma(rows, nsb) && env_variant() == 0) return launch_tma_iters<false>(wb, xq, xd, y, rows, nsb, s);
+    if (iters <= 4 && env_variant() != 2) {
+        switch (iters) {
+        case 1: KCB_LAUNCH_REG(matvec_q4k_q8_reg_kernel, 1); break;
+        case 2: KCB_LAUNCH_REG(matvec_q4k_q8_reg_kernel, 2); break;
+        case 3: KCB_LAUNCH_REG(matvec_q4k_q8_reg_kernel, 3); break;
+        default: KCB_LAUNCH_REG(matvec_q4k_q8_reg_kernel, 4); break;
+        }
+        return launch_status();
+    }
     const size_t smem = static_cast<size_t>(nsb) * (64 * 4 + 8 * 8);
     if (rows >= kSmCount * 6 * kWarps * 2)
-        matvec_q4k_q8_kernel<2><<<grid_for_rows(rows, 2), kThreads, smem, s>>>(static_cast<const uint8_t*>(w), xq, xd, y, rows, nsb);
+        matvec_q4k_q8_kernel<2><<<grid_for_rows(rows, 2), kThreads, smem, s>>>(wb, xq, xd, y, rows, nsb);
     else
-        matvec_q4k_q8_kernel<1><<<grid_for_rows(rows, 1), kThreads, smem, s>>>(static_cast<const uint8_t*>(w), xq, xd, y, rows, nsb);
+        matvec_q4k_q8_kernel<1><<<grid_for_rows(rows, 1), kThreads, smem, s>>>(wb, xq, xd, y, rows, nsb);
     return launch_status();
 }
 
 int matvec_q6k_q8(const void* w, const int* xq, const float* xd, float* y, int rows, int k, cudaStream_t s) {
     if (!shape_ok(rows, k) || !w || !xq || !xd || !y) return KCB_INVALID_VALUE;
     if (rows == 0) return KCB_SUCCESS;
-    const int nsb = k / 256;
+    const int nsb = k / 256, iters = (nsb + 3) / 4;
+    const uint8_t* wb = static_cast<const uint8_t*>(w);
+    const bool pf = env_variant() != 1;
+    if (use_tma(rows, nsb) && env_variant() == 0) return launch_tma_iters<true>(wb, xq, xd, y, rows, nsb, s);
+    if (iters <= 4 && env_variant() != 2) {
+        switch (iters) {
+        case 1: KCB_LAUNCH_REG(matvec_q6k_q8_reg_kernel, 1); break;
+        case 2: KCB_LAUNCH_REG(matvec_q6k_q8_reg_kernel, 2); break;
+        case 3: KCB_LAUNCH_REG(matvec_q6k_q8_reg_kernel, 3); break;
+        default: KCB_LAUNCH_REG(matvec_q6k_q8_reg_kernel, 4); break;
+        }
+        return launch_status();
+    }
     const size_t smem = static_cast<size_t>(nsb) * (64 * 4 + 8 * 8 + 16 * 4);
     if (rows >= kSmCount * 6 * kWarps * 2)
-        matvec_q6k_q8_kernel<2><<<grid_for_rows(rows, 2), kThreads, smem, s>>>(static_cast<const uint8_t*>(w), xq, xd, y, rows, nsb, rows);
+        matvec_q6k_q8_kernel<2><<<grid_for_rows(rows, 2), kThreads, smem, s>>>(wb, xq, xd, y, rows, nsb, rows);
     else
-        matvec_q6k_q8_kernel<1><<<grid_for_rows(rows, 1), kThreads, smem, s>>>(static_cast<const uint8_t*>(w), xq, xd, y, rows, nsb, rows);
+        matvec_q6k_q8_kernel<1><<<grid_for_rows(rows, 1), kThreads, smem, s>>>(wb, xq, xd, y, rows, nsb, rows);
     return launch_status();
 }
 

@@ -14,6 +14,7 @@ int matvec_q4k_f32(const void* w, const float* x, float* y, int rows, int k, cud
 int matvec_q6k_f32(const void* w, const float* x, float* y, int rows, int k, cudaStream_t s);
 int dequant_q4k(const void* w, float* out, int rows, int k, cudaStream_t s);
 int dequant_q6k(const void* w, float* out, int rows, int k, cudaStream_t s);
+unsigned tma_timeouts();  // bounded mbarrier waits that expired since load (synchronous read)
 int q6k_convert(const void* src, void* dst, int rows, int k, int to_planes, cudaStream_t s);
 
 // quantize.cu
