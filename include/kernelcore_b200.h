@@ -71,6 +71,71 @@ int kcb_matvec_q6k_q8(const void* planes_dev, const int32_t* xq_dev, const float
 int kcb_matvec_q4k_f32(const void* w_dev, const float* x_dev, float* y_dev, int rows, int k, void* stream);
 int kcb_matvec_q6k_f32(const void* planes_dev, const float* x_dev, float* y_dev, int rows, int k, void* stream);
 
+/* ---- normalisation ------------------------------------------------------------------------------- */
+/* kernel "rms_norm", llm::RmsNormArgs (llm/llm_kernels.hpp:118-125; kernels/llm/rms_norm.cu:2-11):
+ * y[r] = x[r] / sqrt(mean(x[r]^2) + eps) * w for `rows` rows of n. */
+int kcb_rms_norm(const float* x_dev, const float* w_dev, float* y_dev, int n, int rows, float eps, void* stream);
+/* kernel "add_rms_norm", llm::AddRmsNormArgs (llm/llm_kernels.hpp:72-80): x += t; y = norm(x) * w, one row. */
+int kcb_add_rms_norm(float* x_dev, const float* t_dev, const float* w_dev, float* y_dev, int n, float eps, void* stream);
+/* kernels "add_sumsq" / "norm_q8x4", llm::AddSumsqArgs / NormQ8Args (llm/llm_kernels.hpp:91-106):
+ * x += t with per-32 partial sums of squares into the scratch q (11*nb ints); then
+ * norm(x) * w quantized into q.  kcb_add_norm_q8x4 runs both in one launch (Backend::addRmsNormQuant,
+ * llm/llm_model.cpp:417-423). */
+int kcb_add_sumsq(float* x_dev, const float* t_dev, int32_t* q_dev, int nb, void* stream);
+int kcb_norm_q8x4(const float* x_dev, const float* w_dev, int32_t* q_dev, int nb, float eps, void* stream);
+int kcb_add_norm_q8x4(float* x_dev, const float* t_dev, const float* w_dev, int32_t* q_dev, int nb, float eps, void* stream);
+/* ggml-graph forms, rows of n (n % 256 == 0), one scratch slot of 11*n/32 ints per row:
+ * kernels "add_sumsq_f" (AddSumsqFArgs), "sumsq_part" (SumsqPartArgs), "norm_mul_q8_f" (NormMulQ8Args)
+ * and "norm_mul_q8k_f" (per-256 slots of 85*n/256 ints in q, partial sums in sq)
+ * (llm/llm_kernels.hpp:170-216). */
+int kcb_add_sumsq_f(const float* a_dev, const float* b_dev, float* out_dev, int32_t* q_dev, int n, int rows, void* stream);
+int kcb_sumsq_part(const float* x_dev, int32_t* q_dev, int n, int rows, void* stream);
+int kcb_norm_mul_q8_f(const float* x_dev, const float* w_dev, float* y_dev, int32_t* q_dev, int n, int rows, float eps, void* stream);
+int kcb_norm_mul_q8k_f(const float* x_dev, const float* w_dev, float* y_dev, int32_t* q_dev, const int32_t* sq_dev, int n,
+                       int rows, float eps, void* stream);
+
+/* ---- SwiGLU and elementwise ------------------------------------------------------------------------ */
+/* kernel "silu_mul", llm::SiluMulArgs (llm/llm_kernels.hpp:248-253). */
+int kcb_silu_mul(const float* g_dev, const float* u_dev, float* out_dev, int count, void* stream);
+/* kernel "silu_mul_q8x4", llm::SiluMulQ8Args (llm/llm_kernels.hpp:108-116): count blocks of 32. */
+int kcb_silu_mul_q8x4(const float* g_dev, const float* u_dev, int32_t* xq_dev, float* xd_dev, int count, void* stream);
+/* kernels "silu_mul_q8x4f" / "silu_mul_q8kf", llm::SiluMulQ8FArgs (llm/llm_kernels.hpp:200-216): cols columns
+ * of n, fp32 y stored, slots per column. */
+int kcb_silu_mul_q8x4f(const float* g_dev, const float* u_dev, float* y_dev, int32_t* q_dev, int n, int cols, void* stream);
+int kcb_silu_mul_q8kf(const float* g_dev, const float* u_dev, float* y_dev, int32_t* q_dev, int n, int cols, void* stream);
+/* kernel "mul_rows", llm::MulRowsArgs (llm/llm_kernels.hpp:146-153); kernel "vector_add",
+ * kc::kernels::VectorAddArgs (include/kernelcore/kernels.hpp:10-16). */
+int kcb_mul_rows(const float* x_dev, const float* w_dev, float* y_dev, int n, int count, void* stream);
+int kcb_vector_add(const float* a_dev, const float* b_dev, float* out_dev, int count, void* stream);
+
+/* ---- RoPE ----------------------------------------------------------------------------------------- */
+/* kernels "rope" / "rope_ff", llm::RopeArgs / RopeFFArgs (llm/llm_kernels.hpp:127-144): in place, adjacent
+ * pairs, one position; ff_dev may be NULL (no frequency factors). */
+int kcb_rope(float* x_dev, const float* ff_dev, int pairs_per_head, int pos, int count, float log2_base, void* stream);
+/* kernel "rope_ggml", llm::RopeGgmlArgs (llm/llm_kernels.hpp:155-168): out of place, per-token positions,
+ * NORM or NEOX pairing; ff_dev may be NULL. */
+int kcb_rope_ggml(const float* x_dev, float* y_dev, const int32_t* pos_dev, const float* ff_dev, int head_dim, int n_head,
+                  int n_tokens, float log2_base, int neox, void* stream);
+
+/* ---- attention over the decode loop's fp32 cache -------------------------------------------------------
+ * llm::AttnDims as seven ints {n_heads, ctx, head_dim, kv_stride, group, ctx_pad, k_stride}
+ * (llm/llm_kernels.hpp:14-23), passed by value instead of a device int[7]. */
+/* kernel "kv_append", llm::KvAppendArgs (llm/llm_kernels.hpp:234-241): writes position ctx-1. */
+int kcb_kv_append(const float* k_dev, const float* v_dev, float* kt_dev, float* vc_dev, const int* attn_dims7, void* stream);
+/* kernels "attn_scores", "softmax", "attn_values" (llm/llm_kernels.hpp:218-247). */
+int kcb_attn_scores(const float* q_dev, const float* kt_dev, float* scores_dev, const int* attn_dims7, float scale, void* stream);
+int kcb_softmax(float* x_dev, int n, int stride, int rows, void* stream);
+int kcb_attn_values(const float* p_dev, const float* v_dev, float* out_dev, const int* attn_dims7, void* stream);
+
+/* ---- fp16 KV cache (the ggml backend's path) ----------------------------------------------------------- */
+/* kernel "set_rows_f16", llm::SetRowsF16Args (llm/llm_kernels.hpp:298-311). */
+int kcb_set_rows_f16(const float* src_dev, const int64_t* idx_dev, void* dst_dev, int pairs, int rows, int src_row,
+                     int dst_row, int dst_rows, void* stream);
+/* kernels "fa_scores" + "fa_max" + "fa_exp" + "fa_values" as one launch; fa_dims15 = llm::FaDims in
+ * faDimsInts order (llm/llm_kernels.hpp:316-338), host memory.  mask_dev may be NULL when has_mask == 0. */
+int kcb_flash_attn_f16(const float* q_dev, const void* k_dev, const void* v_dev, const void* mask_dev, float* out_dev,
+                       const int* fa_dims15, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

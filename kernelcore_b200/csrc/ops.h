@@ -22,4 +22,28 @@ int quantize_q8x4(const float* x, int* xq, float* xd, int count, cudaStream_t s)
 int quantize_cols(const float* x, int* q, int k, int ncols, cudaStream_t s);
 int quantize_cols_k(const float* x, int* q, int k, int ncols, cudaStream_t s);
 
+
+// glue.cu
+int rms_norm(const float* x, const float* w, float* y, int n, int rows, float eps, cudaStream_t s);
+int add_rms_norm(float* x, const float* t, const float* w, float* y, int n, float eps, cudaStream_t s);
+int add_norm_q8(const float* a, const float* t, float* out, const float* w, float* y, int* q, int* sq, int n, int rows,
+                float eps, int phases, int kq, cudaStream_t s);
+int silu_mul(const float* g, const float* u, float* out, size_t count, cudaStream_t s);
+int silu_mul_q8(const float* g, const float* u, float* y, int* q, int* xq, float* xd, int n, int cols, cudaStream_t s);
+int mul_rows(const float* x, const float* w, float* y, int n, size_t count, cudaStream_t s);
+int vector_add(const float* a, const float* b, float* out, size_t count, cudaStream_t s);
+int rope(float* x, const float* ff, int pairs, int pos, int count, float log2_base, cudaStream_t s);
+int rope_ggml(const float* x, float* y, const int* pos, const float* ff, int head_dim, int n_head, int n_tokens,
+              float log2_base, int neox, cudaStream_t s);
+int kv_append(const float* k, const float* v, float* kt, float* vc, int n, int k_stride, int pos, cudaStream_t s);
+int attn_scores(const float* q, const float* kt, float* scores, int n_heads, int ctx, int head_dim, int group,
+                int ctx_pad, int k_stride, float scale, cudaStream_t s);
+int softmax(float* x, int n, int stride, int rows, cudaStream_t s);
+int attn_values(const float* p, const float* v, float* out, int n_heads, int ctx, int head_dim, int kv_stride, int group,
+                int ctx_pad, cudaStream_t s);
+int set_rows_f16(const float* src, const long long* idx, void* dst, int pairs, int rows, int src_row, int dst_row,
+                 int dst_rows, cudaStream_t s);
+int flash_attn_f16(const float* q, const void* k, const void* v, const void* mask, float* out, const int* dims15,
+                   float scale, cudaStream_t s);
+
 }  // namespace kcb
