@@ -633,16 +633,17 @@ __device__ unsigned g_tma_timeouts = 0;
 
 constexpr int kTmaMaxStages = 8;
 
-template <bool kQ6, int ITERS, int TR>
-__global__ void __launch_bounds__(TR * 32, 1) matvec_kq_q8_tma_kernel(const uint8_t* __restrict__ w,
-                                                                       const int* __restrict__ xq,
-                                                                       const float* __restrict__ xd,
-                                                                       float* __restrict__ y, int rows, int nsb,
-                                                                       int stages) {
+template <bool kQ6, int ITERS, int TR, int RPW>
+__global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(const uint8_t* __restrict__ w,
+                                                                             const int* __restrict__ xq,
+                                                                             const float* __restrict__ xd,
+                                                                             float* __restrict__ y, int rows, int nsb,
+                                                                             int stages) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint8_t* buf = smem + 128;
     constexpr int kBlk = kQ6 ? kQ6KBlock : kQ4KBlock;
+    constexpr int NW = TR / RPW;  // warps per CTA; warp w owns tile rows w, w + NW, ...
     const uint32_t stage_bytes = static_cast<uint32_t>(TR) * nsb * kBlk;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 3, c8 = lane & 7;
@@ -721,6 +722,55 @@ __global__ void __launch_bounds__(TR * 32, 1) matvec_kq_q8_tma_kernel(const uint
         }
     }
 
+    // one (row, super-block step) of work out of shared memory
+    auto q6_step = [&](const uint8_t* st, int rl, int it) -> float {
+        const size_t blk = static_cast<size_t>(rl) * nsb + g + 4 * it;
+        const uint4 l = *reinterpret_cast<const uint4*>(st + blk * 128 + 16 * c8);
+        const uint4 hq = *reinterpret_cast<const uint4*>(st + TR * nsb * 128 + blk * 64 + 32 * n + 16 * h);
+        const uint2 sc = *reinterpret_cast<const uint2*>(st + TR * nsb * 192 + blk * 16 + 8 * n);
+        const unsigned dq = *reinterpret_cast<const unsigned short*>(st + TR * nsb * 208 + blk * 2);
+        int dl0 = 0, dl1 = 0, dh0 = 0, dh1 = 0;
+        dl0 = __dp4a(static_cast<int>((l.x & kLo4) | ((hq.x << shl) & kHi2)), static_cast<int>(xa[it].x), dl0);
+        dl1 = __dp4a(static_cast<int>((l.y & kLo4) | ((hq.y << shl) & kHi2)), static_cast<int>(xa[it].y), dl1);
+        dl0 = __dp4a(static_cast<int>((l.z & kLo4) | ((hq.z << shl) & kHi2)), static_cast<int>(xa[it].z), dl0);
+        dl1 = __dp4a(static_cast<int>((l.w & kLo4) | ((hq.w << shl) & kHi2)), static_cast<int>(xa[it].w), dl1);
+        dh0 = __dp4a(static_cast<int>(((l.x >> 4) & kLo4) | ((hq.x >> shr) & kHi2)), static_cast<int>(xb[it].x), dh0);
+        dh1 = __dp4a(static_cast<int>(((l.y >> 4) & kLo4) | ((hq.y >> shr) & kHi2)), static_cast<int>(xb[it].y), dh1);
+        dh0 = __dp4a(static_cast<int>(((l.z >> 4) & kLo4) | ((hq.z >> shr) & kHi2)), static_cast<int>(xb[it].z), dh0);
+        dh1 = __dp4a(static_cast<int>(((l.w >> 4) & kLo4) | ((hq.w >> shr) & kHi2)), static_cast<int>(xb[it].w), dh1);
+        const int tl = prmt_sbyte(sc.x, sel) * (dl0 + dl1 - sa[it]);
+        const int th = prmt_sbyte(sc.y, sel) * (dh0 + dh1 - sb2[it]);
+        return half_bits_to_float(dq) * (static_cast<float>(tl) * dd[it].x + static_cast<float>(th) * dd[it].z);
+    };
+    auto q4_step = [&](const uint8_t* st, int rl, int it) -> float {
+        const uint8_t* pb = st + (static_cast<size_t>(rl) * nsb + g + 4 * it) * kQ4KBlock;
+        const uint4 hd = *reinterpret_cast<const uint4*>(pb);
+        const uint4 q = *reinterpret_cast<const uint4*>(pb + 16 + 16 * c8);
+        int da0 = 0, da1 = 0, db0 = 0, db1 = 0;
+        da0 = __dp4a(static_cast<int>(q.x & kLo4), static_cast<int>(xa[it].x), da0);
+        da1 = __dp4a(static_cast<int>(q.y & kLo4), static_cast<int>(xa[it].y), da1);
+        da0 = __dp4a(static_cast<int>(q.z & kLo4), static_cast<int>(xa[it].z), da0);
+        da1 = __dp4a(static_cast<int>(q.w & kLo4), static_cast<int>(xa[it].w), da1);
+        db0 = __dp4a(static_cast<int>((q.x >> 4) & kLo4), static_cast<int>(xb[it].x), db0);
+        db1 = __dp4a(static_cast<int>((q.y >> 4) & kLo4), static_cast<int>(xb[it].y), db1);
+        db0 = __dp4a(static_cast<int>((q.z >> 4) & kLo4), static_cast<int>(xb[it].z), db0);
+        db1 = __dp4a(static_cast<int>((q.w >> 4) & kLo4), static_cast<int>(xb[it].w), db1);
+        unsigned scw, mw;
+        if (j < 2) {
+            scw = hd.y & 0x3F3F3F3Fu;
+            mw = hd.z & 0x3F3F3F3Fu;
+        } else {
+            scw = (hd.w & kLo4) | ((hd.y >> 2) & kHi2);
+            mw = ((hd.w >> 4) & kLo4) | ((hd.z >> 2) & kHi2);
+        }
+        const int sca = (scw >> sh) & 255, scb = (scw >> (sh + 8)) & 255;
+        const int ma = (mw >> sh) & 255, mb = (mw >> (sh + 8)) & 255;
+        const float d = half_bits_to_float(hd.x & 0xFFFFu), dmin = half_bits_to_float(hd.x >> 16);
+        const float t1 = static_cast<float>(sca * (da0 + da1)) * dd[it].x + static_cast<float>(scb * (db0 + db1)) * dd[it].z;
+        const float t2 = static_cast<float>(ma) * dd[it].y + static_cast<float>(mb) * dd[it].w;
+        return d * t1 - dmin * t2;
+    };
+
     for (int i = 0; i < my_tiles; ++i) {
         const int s = i % stages;
         const uint32_t parity = static_cast<uint32_t>(i / stages) & 1u;
@@ -729,82 +779,44 @@ __global__ void __launch_bounds__(TR * 32, 1) matvec_kq_q8_tma_kernel(const uint
             for (int t = 0; t < 1000; ++t) __nanosleep(1000);  // bounded grace for copies still in flight
             return;  // data never arrived: leave without touching y
         }
-        const int row = (blockIdx.x + i * gridDim.x) * TR + warp;
-        if (row < rows) {
-            const uint8_t* st = buf + static_cast<size_t>(s) * stage_bytes;
-            float acc = 0.0f;
-            if (kQ6) {
-                const uint8_t* pl = st + (static_cast<size_t>(warp) * nsb + g) * 128 + 16 * c8;
-                const uint8_t* ph = st + TR * nsb * 128 + (static_cast<size_t>(warp) * nsb + g) * 64 + 32 * n + 16 * h;
-                const uint8_t* ps = st + TR * nsb * 192 + (static_cast<size_t>(warp) * nsb + g) * 16 + 8 * n;
-                const uint8_t* pd = st + TR * nsb * 208 + (static_cast<size_t>(warp) * nsb + g) * 2;
+        const int row0 = (blockIdx.x + i * gridDim.x) * TR;
+        const uint8_t* st = buf + static_cast<size_t>(s) * stage_bytes;
+        float acc[RPW];
 #pragma unroll
-                for (int it = 0; it < ITERS; ++it) {
-                    if (!ok[it]) continue;
-                    const uint4 l = *reinterpret_cast<const uint4*>(pl + it * 4 * 128);
-                    const uint4 hq = *reinterpret_cast<const uint4*>(ph + it * 4 * 64);
-                    const uint2 sc = *reinterpret_cast<const uint2*>(ps + it * 4 * 16);
-                    const unsigned dq = *reinterpret_cast<const unsigned short*>(pd + it * 4 * 2);
-                    int dl = 0, dh = 0;
-                    dl = __dp4a(static_cast<int>((l.x & kLo4) | ((hq.x << shl) & kHi2)), static_cast<int>(xa[it].x), dl);
-                    dl = __dp4a(static_cast<int>((l.y & kLo4) | ((hq.y << shl) & kHi2)), static_cast<int>(xa[it].y), dl);
-                    dl = __dp4a(static_cast<int>((l.z & kLo4) | ((hq.z << shl) & kHi2)), static_cast<int>(xa[it].z), dl);
-                    dl = __dp4a(static_cast<int>((l.w & kLo4) | ((hq.w << shl) & kHi2)), static_cast<int>(xa[it].w), dl);
-                    dh = __dp4a(static_cast<int>(((l.x >> 4) & kLo4) | ((hq.x >> shr) & kHi2)), static_cast<int>(xb[it].x), dh);
-                    dh = __dp4a(static_cast<int>(((l.y >> 4) & kLo4) | ((hq.y >> shr) & kHi2)), static_cast<int>(xb[it].y), dh);
-                    dh = __dp4a(static_cast<int>(((l.z >> 4) & kLo4) | ((hq.z >> shr) & kHi2)), static_cast<int>(xb[it].z), dh);
-                    dh = __dp4a(static_cast<int>(((l.w >> 4) & kLo4) | ((hq.w >> shr) & kHi2)), static_cast<int>(xb[it].w), dh);
-                    const int tl = prmt_sbyte(sc.x, sel) * (dl - sa[it]);
-                    const int th = prmt_sbyte(sc.y, sel) * (dh - sb2[it]);
-                    acc += half_bits_to_float(dq) * (static_cast<float>(tl) * dd[it].x + static_cast<float>(th) * dd[it].z);
-                }
-            } else {
-                const uint8_t* pb = st + (static_cast<size_t>(warp) * nsb + g) * kQ4KBlock;
+        for (int r = 0; r < RPW; ++r) acc[r] = 0.0f;
 #pragma unroll
-                for (int it = 0; it < ITERS; ++it) {
-                    if (!ok[it]) continue;
-                    const uint4 hd = *reinterpret_cast<const uint4*>(pb + it * 4 * kQ4KBlock);
-                    const uint4 q = *reinterpret_cast<const uint4*>(pb + it * 4 * kQ4KBlock + 16 + 16 * c8);
-                    int da = 0, db = 0;
-                    da = __dp4a(static_cast<int>(q.x & kLo4), static_cast<int>(xa[it].x), da);
-                    da = __dp4a(static_cast<int>(q.y & kLo4), static_cast<int>(xa[it].y), da);
-                    da = __dp4a(static_cast<int>(q.z & kLo4), static_cast<int>(xa[it].z), da);
-                    da = __dp4a(static_cast<int>(q.w & kLo4), static_cast<int>(xa[it].w), da);
-                    db = __dp4a(static_cast<int>((q.x >> 4) & kLo4), static_cast<int>(xb[it].x), db);
-                    db = __dp4a(static_cast<int>((q.y >> 4) & kLo4), static_cast<int>(xb[it].y), db);
-                    db = __dp4a(static_cast<int>((q.z >> 4) & kLo4), static_cast<int>(xb[it].z), db);
-                    db = __dp4a(static_cast<int>((q.w >> 4) & kLo4), static_cast<int>(xb[it].w), db);
-                    unsigned scw, mw;
-                    if (j < 2) {
-                        scw = hd.y & 0x3F3F3F3Fu;
-                        mw = hd.z & 0x3F3F3F3Fu;
-                    } else {
-                        scw = (hd.w & kLo4) | ((hd.y >> 2) & kHi2);
-                        mw = ((hd.w >> 4) & kLo4) | ((hd.z >> 2) & kHi2);
-                    }
-                    const int sca = (scw >> sh) & 255, scb = (scw >> (sh + 8)) & 255;
-                    const int ma = (mw >> sh) & 255, mb = (mw >> (sh + 8)) & 255;
-                    const float d = half_bits_to_float(hd.x & 0xFFFFu), dmin = half_bits_to_float(hd.x >> 16);
-                    const float t1 = static_cast<float>(sca * da) * dd[it].x + static_cast<float>(scb * db) * dd[it].z;
-                    const float t2 = static_cast<float>(ma) * dd[it].y + static_cast<float>(mb) * dd[it].w;
-                    acc += d * t1 - dmin * t2;
-                }
+        for (int it = 0; it < ITERS; ++it) {
+            if (!ok[it]) continue;
+#pragma unroll
+            for (int r = 0; r < RPW; ++r) {
+                const int rl = warp + r * NW;
+                if (row0 + rl < rows) acc[r] += kQ6 ? q6_step(st, rl, it) : q4_step(st, rl, it);
             }
-            acc = warp_sum(acc);
-            if (lane == 0) y[row] = acc;
+        }
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            const float v = warp_sum(acc[r]);
+            const int row = row0 + warp + r * NW;
+            if (lane == 0 && row < rows) y[row] = v;
         }
         __syncthreads();  // every warp is done with stage s
         if (threadIdx.x == 0 && i + stages < my_tiles) issue(i + stages);
     }
 }
 
-template <bool kQ6, int ITERS>
-int launch_tma(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s) {
-    constexpr int TR = 16;
-    auto kern = matvec_kq_q8_tma_kernel<kQ6, ITERS, TR>;
+int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+
+template <bool kQ6, int ITERS, int TR, int RPW>
+int launch_tma_cfg(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s) {
+    auto kern = matvec_kq_q8_tma_kernel<kQ6, ITERS, TR, RPW>;
     const size_t stage_bytes = static_cast<size_t>(TR) * nsb * (kQ6 ? kQ6KBlock : kQ4KBlock);
     int stages = static_cast<int>((200 * 1024) / stage_bytes);
     if (stages > kTmaMaxStages) stages = kTmaMaxStages;
+    static const int forced = env_int("KCB_TMA_STAGES", 0);
+    if (forced > 0 && forced < stages) stages = forced;
     if (stages < 2) return KCB_UNSUPPORTED_OPERATION;
     const size_t smem = 128 + stages * stage_bytes;
     static bool attr_set = false;  // per instantiation
@@ -815,8 +827,15 @@ int launch_tma(const uint8_t* wb, const int* xq, const float* xd, float* y, int 
     }
     const int ntiles = (rows + TR - 1) / TR;
     const int grid = ntiles < kSmCount ? ntiles : kSmCount;
-    kern<<<grid, TR * 32, smem, s>>>(wb, xq, xd, y, rows, nsb, stages);
+    kern<<<grid, TR / RPW * 32, smem, s>>>(wb, xq, xd, y, rows, nsb, stages);
     return launch_status();
+}
+
+template <bool kQ6, int ITERS>
+int launch_tma(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s) {
+    // Measured on B200 (lm_head 128256 x 3072 Q6_K): 16 warps x 2 interleaved rows 94 % of the copy
+    // roofline; 32 warps x 1 row 87 %; 16 warps x 1 row 82 %; 8 warps x 2 rows 71 %.
+    return launch_tma_cfg<kQ6, ITERS, 32, 2>(wb, xq, xd, y, rows, nsb, s);
 }
 
 template <bool kQ6>
@@ -832,7 +851,7 @@ int launch_tma_iters(const uint8_t* wb, const int* xq, const float* xd, float* y
 
 // The pipelined path needs whole 8-row groups (16-byte aligned d plane tiles) and enough tiles to give
 // every SM work.
-bool use_tma(int rows, int nsb) { return rows % 8 == 0 && nsb <= 16 && rows >= 16 * kSmCount; }
+bool use_tma(int rows, int nsb) { return rows % 8 == 0 && nsb <= 16 && rows >= 32 * kSmCount; }
 
 // Resident CTAs per SM of a kernel, asked of the driver once per kernel and device.
 template <class Kern>
