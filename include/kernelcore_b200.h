@@ -27,6 +27,52 @@ const char* kcb_build_arch(void);
 /* Text for a status code: kcGetErrorString, include/kernelcore/api.hpp:80. */
 const char* kcb_error_string(int status);
 
+/* ---- runtime: the C layer under the reference's kc* functions (include/kernelcore/api.hpp:15-85) -----
+ * Each kcb_x below is what kcX forwards to; handles are opaque pointers; `kind` is kc::CopyKind
+ * (0 H2D, 1 D2H, 2 D2D, 3 H2H).  A NULL stream handle means the current device's default stream, on
+ * which launches are synchronous (api.hpp:34-35). */
+int kcb_init(void);                                   /* kcInit, api.hpp:16 */
+int kcb_shutdown(void);                               /* kcShutdown, api.hpp:17 */
+int kcb_device_reset(void);                           /* kcDeviceReset, api.hpp:18 */
+int kcb_get_device_count(int* count);                 /* kcGetDeviceCount, api.hpp:21 */
+int kcb_get_device_properties(char* name128, unsigned* sm_count, size_t* total_memory, int device); /* api.hpp:22 */
+int kcb_set_device(int device);                       /* kcSetDevice, api.hpp:23 (per calling thread) */
+int kcb_get_device(int* device);                      /* kcGetDevice, api.hpp:24 */
+int kcb_device_synchronize(void);                     /* kcDeviceSynchronize, api.hpp:25 */
+int kcb_malloc(void** ptr, size_t bytes);             /* kcMalloc, api.hpp:28 */
+int kcb_free(void* ptr);                              /* kcFree, api.hpp:29 */
+int kcb_memcpy(void* dst, const void* src, size_t bytes, int kind); /* kcMemcpy, api.hpp:30 */
+int kcb_memset(void* dst, int value, size_t bytes);   /* kcMemset, api.hpp:31 */
+/* LaunchContext::checkDeviceRange (include/kernelcore/kernel_registry.hpp:27-33): 0 iff the range lies
+ * inside one live allocation of the current device. */
+int kcb_check_range(const void* ptr, size_t bytes);
+int kcb_register_kernel(const void* kernel_entry);    /* kcRegisterKernel, api.hpp:33 (kc::KernelEntry*) */
+/* kcLaunchKernel / kcLaunchKernelChunked, api.hpp:35-39: typed_args points at the kernel's llm::*Args
+ * struct (llm/llm_kernels.hpp), host memory. */
+int kcb_launch_kernel(const char* name, const void* typed_args, void* stream);
+int kcb_stream_create(void** stream);                 /* kcStreamCreate, api.hpp:42 */
+int kcb_stream_destroy(void* stream);                 /* kcStreamDestroy, api.hpp:43 */
+int kcb_stream_synchronize(void* stream);             /* kcStreamSynchronize, api.hpp:44 */
+int kcb_stream_query(void* stream);                   /* kcStreamQuery, api.hpp:45 */
+int kcb_launch_host_func(void* stream, void (*fn)(void*), void* user); /* kcLaunchHostFunc, api.hpp:46 */
+int kcb_event_create(void** event);                   /* kcEventCreate, api.hpp:47 */
+int kcb_event_destroy(void* event);                   /* kcEventDestroy, api.hpp:48 */
+int kcb_event_record(void* event, void* stream);      /* kcEventRecord, api.hpp:49 */
+int kcb_event_synchronize(void* event);               /* kcEventSynchronize, api.hpp:50 */
+int kcb_event_query(void* event);                     /* kcEventQuery, api.hpp:51 */
+int kcb_event_elapsed_ms(void* start, void* stop, float* ms); /* device time between two recorded events;
+                                                         the reference times with host clocks (app/llm_bench.cpp:207-262) */
+int kcb_stream_wait_event(void* stream, void* event); /* kcStreamWaitEvent, api.hpp:52 */
+int kcb_stream_begin_capture(void* stream);           /* kcStreamBeginCapture, api.hpp:59 */
+int kcb_stream_end_capture(void* stream, void** graph); /* kcStreamEndCapture, api.hpp:60 */
+int kcb_graph_launch(void* graph, void* stream);      /* kcGraphLaunch, api.hpp:65 */
+int kcb_graph_destroy(void* graph);                   /* kcGraphDestroy, api.hpp:70 */
+int kcb_stream_concurrent(void* stream, int begin);   /* kcStreamConcurrentBegin/End, api.hpp:68-69 */
+int kcb_get_last_fault(void* fault_info);             /* kcGetLastFault, api.hpp:79 (kc::FaultInfo*) */
+const char* kcb_last_error_detail(void);              /* kcGetLastErrorDetail, api.hpp:85 */
+/* The cudaStream_t behind a stream handle, for callers that mix kcb_* op entry points with runtime streams. */
+void* kcb_stream_native(void* stream);
+
 /* Number of bounded device-side waits (mbarrier polls of the bulk-copy pipelines) that gave up since
  * the library was loaded; 0 in a healthy process.  Synchronous.  No counterpart in the reference: its
  * fault reporting is kcGetLastFault (include/kernelcore/api.hpp:79). */
@@ -135,6 +181,33 @@ int kcb_set_rows_f16(const float* src_dev, const int64_t* idx_dev, void* dst_dev
  * faDimsInts order (llm/llm_kernels.hpp:316-338), host memory.  mask_dev may be NULL when has_mask == 0. */
 int kcb_flash_attn_f16(const float* q_dev, const void* k_dev, const void* v_dev, const void* mask_dev, float* out_dev,
                        const int* fa_dims15, float scale, void* stream);
+
+/* ---- decoder model and decode loop ----------------------------------------------------------------------
+ * C view of llm::Model / llm::decodeToken / llm::makeKcBackend (llm/llm_model.hpp:100-207 of the reference;
+ * model assembly as llm/gguf_model.cpp:51-106).  Weights are given as canonical GGUF blocks in HOST
+ * memory (fmt 4 = Q4_K, 6 = Q6_K); the library packs and uploads them to the current device.  Embeddings
+ * are tied to lm_head.  q_norm / k_norm are read only when qk_norm != 0. */
+typedef struct { const void* blocks; int rows, k, fmt; } kcb_mat;
+typedef struct {
+    kcb_mat wq, wk, wv, wo, wg, wu, wd;
+    const float* attn_norm; const float* ffn_norm; const float* q_norm; const float* k_norm;
+} kcb_layer;
+typedef struct {
+    int hidden, inter, n_layers, heads, kv_heads, head_dim, vocab, max_ctx;
+    float eps, rope_base;
+    int neox, qk_norm;
+    const kcb_layer* layers; const float* out_norm; kcb_mat lm_head; const float* rope_ff;
+} kcb_model_desc;
+/* Needs kcb_init.  The host blocks of lm_head must stay valid for the model's lifetime (embedding lookups
+ * read them).  graphs != 0: each token's launches are recorded and run as one CUDA graph. */
+int kcb_model_create(const kcb_model_desc* desc, int graphs, void** model);
+/* llm::decodeToken: one decode step for `token` at position pos (0-based, == tokens decoded so far).
+ * logits_host (vocab floats) may be NULL; argmax may be NULL. */
+int kcb_model_decode(void* model, int token, int pos, float* logits_host, int* argmax);
+int kcb_model_destroy(void* model);
+/* Text of the last exception a kcb_model_* call on this thread turned into a status code (the reference's
+ * decode loop reports failures as C++ exceptions, llm/llm_model.cpp:91-97). */
+const char* kcb_model_last_error(void);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,80 @@
+"""Python handle on the C++ decode loop (kcb_model_* of the C ABI)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import lib, tiny_model as tm
+
+
+class _Mat(C.Structure):
+    _fields_ = [("blocks", C.c_void_p), ("rows", C.c_int), ("k", C.c_int), ("fmt", C.c_int)]
+
+
+class _Layer(C.Structure):
+    _fields_ = [(n, _Mat) for n in tm.MATS] + [(n, C.c_void_p) for n in ("attn_norm", "ffn_norm", "q_norm", "k_norm")]
+
+
+class _Desc(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("hidden", "inter", "n_layers", "heads", "kv_heads", "head_dim", "vocab", "max_ctx")] + [
+        ("eps", C.c_float), ("rope_base", C.c_float), ("neox", C.c_int), ("qk_norm", C.c_int),
+        ("layers", C.POINTER(_Layer)), ("out_norm", C.c_void_p), ("lm_head", _Mat), ("rope_ff", C.c_void_p)]
+
+
+class Model:
+    """Uploads a numpy model (tiny_model.build) to the current GPU and decodes token by token through
+    llm::decodeToken on the kc backend."""
+
+    def __init__(self, shape: tm.Shape, model: dict, graphs: int = 1):
+        L = lib.raw
+        lib.check(L.kcb_init(), "kcb_init")
+        self.shape, self._keep = shape, []
+        layers = (_Layer * shape.layers)()
+        ms = tm.mat_shapes(shape)
+        for l, src in enumerate(model["layers"]):
+            for name in tm.MATS:
+                rows, k, q6 = ms[name]
+                setattr(layers[l], name, _Mat(self._ptr(src[name]), rows, k, 6 if q6 else 4))
+            layers[l].attn_norm, layers[l].ffn_norm = self._ptr(src["attn_norm"]), self._ptr(src["ffn_norm"])
+            if shape.qk_norm:
+                layers[l].q_norm, layers[l].k_norm = self._ptr(src["q_norm"]), self._ptr(src["k_norm"])
+        d = _Desc()
+        for f in ("hidden", "inter", "heads", "kv_heads", "head_dim", "vocab", "max_ctx"):
+            setattr(d, f, getattr(shape, f))
+        d.n_layers, d.eps, d.rope_base = shape.layers, shape.eps, shape.rope_base
+        d.neox, d.qk_norm = int(shape.neox), int(shape.qk_norm)
+        d.layers = C.cast(layers, C.POINTER(_Layer))
+        d.out_norm = self._ptr(model["out_norm"])
+        d.lm_head = _Mat(self._ptr(model["lm_head"]), shape.vocab, shape.hidden, 6)
+        self._keep.append(layers)
+        self.handle = C.c_void_p()
+        st = L.kcb_model_create(C.byref(d), graphs, C.byref(self.handle))
+        if st != 0:
+            L.kcb_model_last_error.restype = C.c_char_p
+            raise RuntimeError(f"kcb_model_create: status {st}: {L.kcb_model_last_error().decode()}")
+
+    def _ptr(self, a):
+        a = np.ascontiguousarray(a)
+        self._keep.append(a)
+        return a.ctypes.data
+
+    def decode(self, token: int, pos: int):
+        logits = np.zeros(self.shape.vocab, np.float32)
+        arg = C.c_int()
+        st = lib.raw.kcb_model_decode(self.handle, token, pos, logits.ctypes.data_as(C.c_void_p), C.byref(arg))
+        if st != 0:
+            lib.raw.kcb_model_last_error.restype = C.c_char_p
+            raise RuntimeError(f"kcb_model_decode: status {st}: {lib.raw.kcb_model_last_error().decode()}")
+        return logits, arg.value
+
+    def close(self):
+        if self.handle:
+            lib.raw.kcb_model_destroy(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
