@@ -117,6 +117,16 @@ int kcb_matvec_q6k_q8(const void* planes_dev, const int32_t* xq_dev, const float
 int kcb_matvec_q4k_f32(const void* w_dev, const float* x_dev, float* y_dev, int rows, int k, void* stream);
 int kcb_matvec_q6k_f32(const void* planes_dev, const float* x_dev, float* y_dev, int rows, int k, void* stream);
 
+/* No counterpart in the reference.  y = W x for a Q4_K matrix and fp32 x like kcb_quantize_q8x4 followed by
+ * kcb_matvec_q4k_q8, but the 8-bit activation scratch lives in a fixed device array inside the library, so
+ * the call allocates nothing and needs no caller scratch -- for hosts that may not allocate device memory
+ * at call time (plugins under an application that owns all buffers, allocation-free serving loops).
+ * k % 256 == 0 and k <= kcb_static_scratch_max_k() (16384), else InvalidValue.  The first call on a device
+ * looks up the array's address: make it before any stream capture.  All calls share the one array per GPU:
+ * calls whose GPU work may overlap race; keep them on one stream. */
+int kcb_matvec_q4k_f32x_static(const void* w_dev, const float* x_dev, float* y_dev, int rows, int k, void* stream);
+int kcb_static_scratch_max_k(void);
+
 /* ---- normalisation ------------------------------------------------------------------------------- */
 /* kernel "rms_norm", llm::RmsNormArgs (llm/llm_kernels.hpp:118-125; kernels/llm/rms_norm.cu:2-11):
  * y[r] = x[r] / sqrt(mean(x[r]^2) + eps) * w for `rows` rows of n. */
