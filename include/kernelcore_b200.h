@@ -219,6 +219,24 @@ int kcb_model_destroy(void* model);
  * decode loop reports failures as C++ exceptions, llm/llm_model.cpp:91-97). */
 const char* kcb_model_last_error(void);
 
+/* ---- graph-replayed decoder ---------------------------------------------------------------------------
+ * The fast form of the decode loop (llm/llm_model.cpp:287-360; the reference's own CUDA comparison re-uses one
+ * graph per token too, app/llm_bench.cpp:155-179): one CUDA graph captured at creation, replayed per token;
+ * position and token live on the device; greedy next-token pick on the device; fp16 KV cache.
+ * kcb_decoder_set_prompt places `n` forced tokens at positions start_pos.. (teacher forcing; after them the
+ * decoder feeds back its own picks) and sets the position; kcb_decoder_run enqueues `steps` steps without
+ * synchronising; kcb_decoder_read synchronises and copies the last step's logits (vocab floats), the picks
+ * made at positions [0, n_history) and the current position.  Any output pointer may be NULL. */
+int kcb_decoder_create(const kcb_model_desc* desc, void** decoder);
+int kcb_decoder_set_prompt(void* decoder, const int* tokens, int n, int start_pos);
+int kcb_decoder_run(void* decoder, int steps);
+int kcb_decoder_sync(void* decoder);
+int kcb_decoder_read(void* decoder, float* logits_host, int* history_host, int n_history, int* pos_host);
+int kcb_decoder_info(void* decoder, int* launches_per_token, long long* weight_bytes);
+void* kcb_decoder_stream(void* decoder);   /* the cudaStream_t the decoder runs on */
+int kcb_decoder_destroy(void* decoder);
+const char* kcb_decoder_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -61,6 +61,15 @@ __device__ __forceinline__ float half_bits_to_float(unsigned h) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
 }
 
+// fp32 -> fp16 bits as the reference's SET_ROWS kernel converts (kernels/llm/set_rows_f16.cu:20-62): round to
+// nearest even; 65520 and above (and NaN) give 0x7bff with the sign of "x < 0"; an input of -0 gives +0.
+__device__ __forceinline__ unsigned f32_to_f16_bits(float x) {
+    const unsigned sign = x < 0.0f ? 0x8000u : 0u;
+    const float a = fabsf(x);
+    if (!(a < 65520.0f)) return sign | 0x7bffu;
+    return sign | (static_cast<unsigned>(__half_as_ushort(__float2half_rn(a))) & 0x7fffu);
+}
+
 // ---- mbarrier + bulk-copy (TMA) primitives ---------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {

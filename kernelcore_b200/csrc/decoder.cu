@@ -1,0 +1,650 @@
+// Graph-replayed decoder: one CUDA graph per model, captured once and replayed for every token.
+//
+// The reference's decode loop (llm/llm_model.cpp:287-360) re-records ~450 launches per token because its
+// kernels take the position by value.  Here every position-dependent kernel reads the position (and the
+// input token) from device memory, the last kernel of a step picks the next token (greedy argmax) and
+// advances the position, so the host only replays the same graph: no per-token capture, no host
+// round trip between tokens.  Same arithmetic as the Backend path -- Q8 activations per 32, integer-dot
+// matvecs, RMSNorm / RoPE / SwiGLU formulas of kernels/llm/*.cu -- with two deliberate layout changes:
+// q|k and gate|up are stored as one matrix each when their formats agree (as the reference's fused
+// Layer::wqkv / wgu, llm/llm_model.hpp:100-113), and the KV cache is fp16 rows [ctx][kv_heads*head_dim]
+// (the ggml backend's cache, kernels/llm/set_rows_f16.cu, fa_*.cu) attended by a split-KV kernel with an
+// online exp2 softmax.
+
+#include "../../include/kernelcore_b200.h"
+
+#include "common.cuh"
+#include "ops.h"
+
+#include <cmath>
+#include <cstring>
+#include <string>
+#include <vector>
+
+namespace kcb {
+namespace {
+
+__device__ __forceinline__ int sbyte_of(unsigned w, int i) { return static_cast<int>(w << (24 - 8 * i)) >> 24; }
+
+// x[hidden] = dequantised row `token` of a Q6_K (planes) or Q4_K matrix: the tied-embedding lookup
+// (llm/gguf_model.cpp:96-104), bit-exact with llm::ref::dequantRowQ6K / Q4K.
+__global__ void embed_kernel(const uint8_t* __restrict__ w, size_t nblk, int nsb, int q6, int vocab,
+                             const int* __restrict__ token_p, const int* __restrict__ forced, const int* __restrict__ n_forced,
+                             const int* __restrict__ pos_p, int* token_used, float* __restrict__ x) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= nsb * 8) return;
+    const int pos = *pos_p;
+    int token = pos < *n_forced ? forced[pos] : *token_p;
+    token = min(max(token, 0), vocab - 1);
+    if (t == 0) *token_used = token;
+    const size_t blk = static_cast<size_t>(token) * nsb + (t >> 3);
+    const int c8 = t & 7;
+    float* out = x + (t >> 3) * 256;
+    if (q6) {
+        const int n = c8 >> 2, a = (c8 >> 1) & 1, h = c8 & 1;
+        const uint4 l = *reinterpret_cast<const uint4*>(w + blk * 128 + 16 * c8);
+        const uint4 hq = *reinterpret_cast<const uint4*>(w + nblk * 128 + blk * 64 + 32 * n + 16 * h);
+        const uint2 s8 = *reinterpret_cast<const uint2*>(w + nblk * 192 + blk * 16 + 8 * n);
+        const float d = half_bits_to_float(*reinterpret_cast<const unsigned short*>(w + nblk * 208 + blk * 2));
+        const float dsl = __fmul_rn(d, static_cast<float>(sbyte_of(s8.x, 2 * a + h)));
+        const float dsh = __fmul_rn(d, static_cast<float>(sbyte_of(s8.y, 2 * a + h)));
+        float* o = out + 128 * n + 32 * a + 16 * h;
+        const unsigned lw[4] = {l.x, l.y, l.z, l.w}, hw[4] = {hq.x, hq.y, hq.z, hq.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const unsigned lb = (lw[i] >> (8 * b)) & 255u, hb = (hw[i] >> (8 * b)) & 255u;
+                const int q1 = static_cast<int>((lb & 15u) | (((hb >> (2 * a)) & 3u) << 4)) - 32;
+                const int q2 = static_cast<int>((lb >> 4) | (((hb >> (2 * a + 4)) & 3u) << 4)) - 32;
+                o[4 * i + b] = __fmul_rn(dsl, static_cast<float>(q1));
+                o[64 + 4 * i + b] = __fmul_rn(dsh, static_cast<float>(q2));
+            }
+    } else {
+        const int j = c8 >> 1, h = c8 & 1;
+        const uint8_t* p = w + blk * kQ4KBlock;
+        const uint4 hd = *reinterpret_cast<const uint4*>(p);
+        const uint4 q = *reinterpret_cast<const uint4*>(p + 16 + 16 * c8);
+        unsigned scw, mw;
+        if (j < 2) {
+            scw = hd.y & 0x3F3F3F3Fu;
+            mw = hd.z & 0x3F3F3F3Fu;
+        } else {
+            scw = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
+            mw = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
+        }
+        const int sh = 16 * (j & 1);
+        const float d = half_bits_to_float(hd.x & 0xFFFFu), dmin = half_bits_to_float(hd.x >> 16);
+        const float dl = __fmul_rn(d, static_cast<float>((scw >> sh) & 255)), dh = __fmul_rn(d, static_cast<float>((scw >> (sh + 8)) & 255));
+        const float ml = __fmul_rn(dmin, static_cast<float>((mw >> sh) & 255)), mh = __fmul_rn(dmin, static_cast<float>((mw >> (sh + 8)) & 255));
+        float* o = out + 64 * j + 16 * h;
+        const unsigned qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const unsigned byte = (qw[i] >> (8 * b)) & 255u;
+                o[4 * i + b] = __fsub_rn(__fmul_rn(dl, static_cast<float>(byte & 15u)), ml);
+                o[32 + 4 * i + b] = __fsub_rn(__fmul_rn(dh, static_cast<float>(byte >> 4)), mh);
+            }
+    }
+}
+
+// RoPE of q and k (+ optional per-head RMSNorm first) at the device-side position, K and V appended to the
+// fp16 cache rows of that position.  One warp per head: q heads, then k heads, then v heads.
+// kernels/llm/rope.cu:4-17 / rope_ff.cu / rope_ggml.cu:21-44 for the rotation, set_rows_f16.cu for the cast.
+__global__ void rope_kv_f16_kernel(float* qkv, const int* __restrict__ pos_p, unsigned short* kc, unsigned short* vc,
+                                   const float* __restrict__ ff, const float* __restrict__ qn, const float* __restrict__ kn,
+                                   int heads, int kv_heads, int hd, float log2_base, int neox, float eps, int max_ctx) {
+    const int lane = threadIdx.x & 31;
+    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (w >= heads + 2 * kv_heads) return;
+    const int pos = min(*pos_p, max_ctx - 1);
+    const int kvdim = kv_heads * hd;
+    float* base = qkv + static_cast<size_t>(w) * hd;
+    if (w >= heads + kv_heads) {  // v head: cast and store
+        unsigned short* dst = vc + static_cast<size_t>(pos) * kvdim + static_cast<size_t>(w - heads - kv_heads) * hd;
+        for (int i = lane; i < hd; i += 32) dst[i] = static_cast<unsigned short>(f32_to_f16_bits(base[i]));
+        return;
+    }
+    const float* wn = w < heads ? qn : kn;
+    float r = 1.0f;
+    if (wn) {
+        float ss = 0.0f;
+        for (int i = lane; i < hd; i += 32) ss += base[i] * base[i];
+        ss = warp_sum(ss);
+        r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(hd)), eps)));
+    }
+    const int pairs = hd / 2;
+    unsigned short* kdst = w >= heads ? kc + static_cast<size_t>(pos) * kvdim + static_cast<size_t>(w - heads) * hd : nullptr;
+    for (int p = lane; p < pairs; p += 32) {
+        const int a = neox ? p : 2 * p, b = neox ? p + pairs : 2 * p + 1;
+        float x0 = base[a], x1 = base[b];
+        if (wn) {
+            x0 = __fmul_rn(__fmul_rn(x0, r), wn[a]);
+            x1 = __fmul_rn(__fmul_rn(x1, r), wn[b]);
+        }
+        const float e = __fmul_rn(__fdiv_rn(-static_cast<float>(p), static_cast<float>(pairs)), log2_base);
+        float th = __fmul_rn(static_cast<float>(pos), exp2f(e));
+        if (ff) th = __fdiv_rn(th, ff[p]);
+        const float ang = __fmul_rn(__fmul_rn(th, 0.159154943f), 6.28318548f);
+        float s, c;
+        sincosf(ang, &s, &c);
+        const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        const float y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+        if (kdst) {
+            kdst[a] = static_cast<unsigned short>(f32_to_f16_bits(y0));
+            kdst[b] = static_cast<unsigned short>(f32_to_f16_bits(y1));
+        } else {
+            base[a] = y0;
+            base[b] = y1;
+        }
+    }
+}
+
+// Split-KV decode attention over the fp16 cache.  CTA (kvh, sp) covers positions [sp*chunk, (sp+1)*chunk) of
+// kv head kvh for the G query heads that share it.  A warp scores four positions per step (8 lanes per
+// position, HD/8 channels per lane), keeps an online exp2 softmax (running max m, sum l, weighted V sum)
+// per lane group, and the CTA merges its groups into one partial {m, l, acc[HD]} per query head.
+// Same quantities as kernels/llm/fa_scores.cu ... fa_values.cu: s = scale * q.k, p = 2^((s - max) log2 e),
+// out = sum p v / sum p.
+template <int HD, int G>
+__global__ void __launch_bounds__(128) attn_partial_kernel(const float* __restrict__ qkv, const unsigned short* __restrict__ kc,
+                                                            const unsigned short* __restrict__ vc, const int* __restrict__ pos_p,
+                                                            float* __restrict__ part, int heads, int kv_heads, int nsplit,
+                                                            float scale, int max_ctx) {
+    constexpr int DPL = HD / 8;  // channels per lane
+    constexpr int NW = 4;
+    extern __shared__ float sm[];  // [NW*4][G][HD + 2]
+    const int kvh = blockIdx.x, sp = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, grp = lane >> 3, l8 = lane & 7;
+    const int ctx = min(*pos_p, max_ctx - 1) + 1;
+    const int chunk = (ctx + nsplit - 1) / nsplit;
+    const int t0 = sp * chunk, t1 = min(ctx, t0 + chunk);
+    const int kvdim = kv_heads * HD;
+
+    float q[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) q[g][i] = qkv[static_cast<size_t>(kvh * G + g) * HD + l8 * DPL + i];
+    float m[G], l[G], acc[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[g][i] = 0.0f;
+    }
+    for (int tb = t0 + warp * 4; tb < t1; tb += NW * 4) {  // warp-uniform trip count: every lane takes part in the shuffles
+        const int t = tb + grp;
+        const bool live = t < t1;
+        float kf[DPL], vf[DPL];
+        if (live) {
+            const unsigned short* kr = kc + static_cast<size_t>(t) * kvdim + kvh * HD + l8 * DPL;
+            const unsigned short* vr = vc + static_cast<size_t>(t) * kvdim + kvh * HD + l8 * DPL;
+#pragma unroll
+            for (int i = 0; i < DPL; i += 8) {
+                const uint4 kw = *reinterpret_cast<const uint4*>(kr + i);
+                const uint4 vw = *reinterpret_cast<const uint4*>(vr + i);
+                const unsigned ku[4] = {kw.x, kw.y, kw.z, kw.w}, vu[4] = {vw.x, vw.y, vw.z, vw.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    kf[i + 2 * j] = half_bits_to_float(ku[j] & 0xFFFFu);
+                    kf[i + 2 * j + 1] = half_bits_to_float(ku[j] >> 16);
+                    vf[i + 2 * j] = half_bits_to_float(vu[j] & 0xFFFFu);
+                    vf[i + 2 * j + 1] = half_bits_to_float(vu[j] >> 16);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) kf[i] = vf[i] = 0.0f;
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) s += q[g][i] * kf[i];
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            if (live) {
+                s *= scale;
+                const float mn = fmaxf(m[g], s);
+                const float corr = exp2f((m[g] - mn) * 1.44269504f);
+                const float p = exp2f((s - mn) * 1.44269504f);
+                l[g] = l[g] * corr + p;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) acc[g][i] = acc[g][i] * corr + p * vf[i];
+                m[g] = mn;
+            }
+        }
+    }
+    // lane groups -> shared memory
+    float* mine = sm + static_cast<size_t>(warp * 4 + grp) * G * (HD + 2);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) mine[g * (HD + 2) + l8 * DPL + i] = acc[g][i];
+        if (l8 == 0) {
+            mine[g * (HD + 2) + HD] = m[g];
+            mine[g * (HD + 2) + HD + 1] = l[g];
+        }
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < G * HD; o += blockDim.x) {
+        const int g = o / HD, d = o % HD;
+        float mm = -INFINITY;
+        for (int pi = 0; pi < NW * 4; ++pi) mm = fmaxf(mm, sm[static_cast<size_t>(pi) * G * (HD + 2) + g * (HD + 2) + HD]);
+        float ll = 0.0f, aa = 0.0f;
+        for (int pi = 0; pi < NW * 4; ++pi) {
+            const float* pp = sm + static_cast<size_t>(pi) * G * (HD + 2) + g * (HD + 2);
+            const float wgt = pp[HD] == -INFINITY ? 0.0f : exp2f((pp[HD] - mm) * 1.44269504f);
+            ll += pp[HD + 1] * wgt;
+            aa += pp[d] * wgt;
+        }
+        float* dst = part + (static_cast<size_t>(kvh * G + g) * nsplit + sp) * (HD + 2);
+        dst[d] = aa;
+        if (d == 0) {
+            dst[HD] = mm;
+            dst[HD + 1] = ll;
+        }
+    }
+}
+
+// Merges the nsplit partials of every head, normalises, and writes attn[heads*HD] together with its Q8
+// quantization (the wo matvec's input): one warp per block of 32 output channels.
+__global__ void attn_combine_q8_kernel(const float* __restrict__ part, float* __restrict__ attn, int* xq, float* xd, int heads,
+                                       int hd, int nsplit) {
+    const int lane = threadIdx.x & 31;
+    const int b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;  // block of 32 channels
+    if (b >= heads * hd / 32) return;
+    const int h = b * 32 / hd, d = (b * 32) % hd + lane;
+    const float* ph = part + static_cast<size_t>(h) * nsplit * (hd + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, ph[s * (hd + 2) + hd]);
+    float ll = 0.0f, aa = 0.0f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float pm = ph[s * (hd + 2) + hd];
+        const float wgt = pm == -INFINITY ? 0.0f : exp2f((pm - mm) * 1.44269504f);
+        ll += ph[s * (hd + 2) + hd + 1] * wgt;
+        aa += ph[s * (hd + 2) + d] * wgt;
+    }
+    const float v = __fdiv_rn(aa, ll);
+    attn[b * 32 + lane] = v;
+    // quantize_q8x4 of this block
+    const float amax = warp_max(fabsf(v));
+    const float dq = __fdiv_rn(amax, 127.0f);
+    const float id = dq > 0.0f ? __fdiv_rn(1.0f, dq) : 0.0f;
+    const float t = __fmul_rn(v, id);
+    int qi = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
+    qi = max(-127, min(127, qi));
+    const int sum = warp_sum_i(qi);
+    unsigned word = (static_cast<unsigned>(qi) & 255u) << (8 * (lane & 3));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    if ((lane & 3) == 0) xq[b * 8 + (lane >> 2)] = static_cast<int>(word);
+    if (lane == 0) {
+        xd[b * 2] = dq;
+        xd[b * 2 + 1] = static_cast<float>(sum);
+    }
+}
+
+// Greedy pick (first maximum, as a sequential scan would), token history, position advance.
+__global__ void argmax_advance_kernel(const float* __restrict__ logits, int vocab, int* token, int* history, int* pos_p, int max_ctx) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = logits[i];
+        if (v > best) best = v, idx = i;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) bv[warp] = best, bi[warp] = idx;
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? bv[lane] : -INFINITY;
+        idx = lane < nw ? bi[lane] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+        }
+        if (lane == 0) {
+            const int pos = *pos_p;
+            *token = idx;
+            if (pos < max_ctx) history[pos] = idx;
+            *pos_p = pos + 1;
+        }
+    }
+}
+
+struct DMat {
+    uint8_t* data = nullptr;
+    int rows = 0, k = 0;
+    bool q6 = false;
+};
+struct DLayer {
+    std::vector<DMat> qkv, gu;  // merged where formats agree: {q|k, v} and {gate|up} for the Q4_K_M mix
+    DMat wo, wd;
+    float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    unsigned short *kc = nullptr, *vc = nullptr;
+};
+
+#define CU(x)                                                            \
+    do {                                                                 \
+        if ((x) != cudaSuccess) {                                        \
+            err_ = std::string(#x) + ": " + cudaGetErrorString(cudaGetLastError()); \
+            return KCB_INTERNAL_ERROR;                                   \
+        }                                                                \
+    } while (0)
+
+class Decoder {
+public:
+    ~Decoder() {
+        if (exec_) cudaGraphExecDestroy(exec_);
+        if (graph_) cudaGraphDestroy(graph_);
+        if (stream_) cudaStreamDestroy(stream_);
+        for (void* p : owned_) cudaFree(p);
+    }
+    std::string err_;
+
+    int init(const kcb_model_desc& d) {
+        hidden = d.hidden, inter = d.inter, heads = d.heads, kv_heads = d.kv_heads, hd = d.head_dim, vocab = d.vocab;
+        max_ctx = d.max_ctx, eps = d.eps, log2_base = std::log2(d.rope_base), neox = d.neox, qk_norm = d.qk_norm;
+        if (hidden % 256 || inter % 256 || (heads * hd) % 256 || heads % kv_heads || (hd != 64 && hd != 128) || max_ctx < 1) {
+            err_ = "unsupported model shape (hidden, inter, heads*head_dim multiples of 256; head_dim 64 or 128)";
+            return KCB_INVALID_VALUE;
+        }
+        const int group = heads / kv_heads;
+        if (group != 1 && group != 2 && group != 3 && group != 4 && group != 8) {
+            err_ = "unsupported query-group size";
+            return KCB_INVALID_VALUE;
+        }
+        CU(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+        for (int l = 0; l < d.n_layers; ++l) {
+            const kcb_layer& s = d.layers[l];
+            DLayer L;
+            const kcb_mat qkv_parts[3] = {s.wq, s.wk, s.wv};
+            const kcb_mat gu_parts[2] = {s.wg, s.wu};
+            if (const int e = merged(L.qkv, qkv_parts, 3); e) return e;
+            if (const int e = merged(L.gu, gu_parts, 2); e) return e;
+            if (const int e = merged_one(L.wo, s.wo); e) return e;
+            if (const int e = merged_one(L.wd, s.wd); e) return e;
+            if (const int e = up(L.attn_norm, s.attn_norm, hidden); e) return e;
+            if (const int e = up(L.ffn_norm, s.ffn_norm, hidden); e) return e;
+            if (qk_norm) {
+                if (const int e = up(L.q_norm, s.q_norm, hd); e) return e;
+                if (const int e = up(L.k_norm, s.k_norm, hd); e) return e;
+            }
+            const size_t cache = static_cast<size_t>(max_ctx) * kv_heads * hd * 2;
+            if (const int e = dev(reinterpret_cast<void**>(&L.kc), cache); e) return e;
+            if (const int e = dev(reinterpret_cast<void**>(&L.vc), cache); e) return e;
+            layers.push_back(L);
+        }
+        if (const int e = merged_one(lm_head, d.lm_head); e) return e;
+        if (const int e = up(out_norm, d.out_norm, hidden); e) return e;
+        if (d.rope_ff)
+            if (const int e = up(rope_ff, d.rope_ff, hd / 2); e) return e;
+        const int qd = heads * hd, kv = kv_heads * hd;
+        const int maxk = std::max(std::max(hidden, inter), qd);
+        nsplit = std::max(1, std::min(16, (kSmCount + kv_heads - 1) / kv_heads));
+        nsplit = std::min(nsplit, std::max(1, max_ctx / 64));
+        if (const int e = dev(reinterpret_cast<void**>(&x), hidden * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&t), hidden * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&qkv), (qd + 2 * kv) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&attn), qd * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&gu), 2 * inter * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&logits), static_cast<size_t>(vocab) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&xq), static_cast<size_t>(11) * (maxk / 32) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&part), static_cast<size_t>(heads) * nsplit * (hd + 2) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&state), 64); e) return e;  // {pos, token, n_forced, token_used}
+        if (const int e = dev(reinterpret_cast<void**>(&forced), static_cast<size_t>(max_ctx) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&history), static_cast<size_t>(max_ctx) * 4); e) return e;
+        CU(cudaMemsetAsync(state, 0, 64, stream_));
+        CU(cudaMemsetAsync(history, 0, static_cast<size_t>(max_ctx) * 4, stream_));
+        // warm every kernel once outside capture (lazy module loading, one-time attribute calls), then capture
+        if (const int e = record(); e) return e;
+        CU(cudaStreamSynchronize(stream_));
+        CU(cudaMemsetAsync(state, 0, 64, stream_));
+        CU(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeRelaxed));
+        const int e = record();
+        cudaGraph_t g = nullptr;
+        const cudaError_t ce = cudaStreamEndCapture(stream_, &g);
+        if (e) {
+            if (g) cudaGraphDestroy(g);
+            return e;
+        }
+        if (ce != cudaSuccess || !g) {
+            err_ = "stream capture failed";
+            return KCB_INTERNAL_ERROR;
+        }
+        graph_ = g;
+        CU(cudaGraphInstantiate(&exec_, graph_, 0));
+        size_t n = 0;
+        cudaGraphGetNodes(graph_, nullptr, &n);
+        launches_per_token = static_cast<int>(n);
+        CU(cudaStreamSynchronize(stream_));
+        return KCB_SUCCESS;
+    }
+
+    int set_prompt(const int* tokens, int n, int start_pos) {
+        if (n < 0 || start_pos < 0 || start_pos + n > max_ctx || (n && !tokens)) return KCB_INVALID_VALUE;
+        std::vector<int> f(static_cast<size_t>(max_ctx), 0);
+        for (int i = 0; i < n; ++i) f[static_cast<size_t>(start_pos + i)] = tokens[i];
+        const int st[4] = {start_pos, 0, start_pos + n, 0};
+        CU(cudaMemcpyAsync(forced, f.data(), f.size() * 4, cudaMemcpyHostToDevice, stream_));
+        CU(cudaMemcpyAsync(state, st, sizeof st, cudaMemcpyHostToDevice, stream_));
+        CU(cudaStreamSynchronize(stream_));
+        return KCB_SUCCESS;
+    }
+    int run(int steps) {
+        for (int i = 0; i < steps; ++i) CU(cudaGraphLaunch(exec_, stream_));
+        return KCB_SUCCESS;
+    }
+    int sync() {
+        CU(cudaStreamSynchronize(stream_));
+        return KCB_SUCCESS;
+    }
+    int read(float* logits_host, int* history_host, int n_hist, int* pos_host) {
+        CU(cudaStreamSynchronize(stream_));
+        if (logits_host) CU(cudaMemcpy(logits_host, logits, static_cast<size_t>(vocab) * 4, cudaMemcpyDeviceToHost));
+        if (history_host && n_hist > 0) CU(cudaMemcpy(history_host, history, static_cast<size_t>(std::min(n_hist, max_ctx)) * 4, cudaMemcpyDeviceToHost));
+        if (pos_host) CU(cudaMemcpy(pos_host, state, 4, cudaMemcpyDeviceToHost));
+        return KCB_SUCCESS;
+    }
+    cudaStream_t stream() const { return stream_; }
+    int launches_per_token = 0;
+    long long weight_bytes = 0;
+
+private:
+    int dev(void** p, size_t bytes) {
+        CU(cudaMalloc(p, bytes));
+        owned_.push_back(*p);
+        return KCB_SUCCESS;
+    }
+    int up(float*& dst, const float* src, int n) {
+        if (!src) {
+            err_ = "missing norm / frequency vector";
+            return KCB_INVALID_VALUE;
+        }
+        if (const int e = dev(reinterpret_cast<void**>(&dst), static_cast<size_t>(n) * 4); e) return e;
+        CU(cudaMemcpy(dst, src, static_cast<size_t>(n) * 4, cudaMemcpyHostToDevice));
+        return KCB_SUCCESS;
+    }
+    // Uploads GGUF blocks of one or more row-concatenated matrices of the same format and k.
+    int upload(DMat& m, const kcb_mat* parts, int nparts) {
+        m.k = parts[0].k, m.q6 = parts[0].fmt == 6, m.rows = 0;
+        for (int i = 0; i < nparts; ++i) m.rows += parts[i].rows;
+        if (m.k % 256 || m.rows % 8) {
+            err_ = "matrix shape not supported (rows % 8, k % 256)";
+            return KCB_INVALID_VALUE;
+        }
+        const size_t bytes = kcb_kquant_bytes(m.rows, m.k, m.q6);
+        weight_bytes += static_cast<long long>(bytes);
+        if (const int e = dev(reinterpret_cast<void**>(&m.data), bytes); e) return e;
+        uint8_t* staging = m.data;
+        void* tmp = nullptr;
+        if (m.q6) {
+            CU(cudaMalloc(&tmp, bytes));
+            staging = static_cast<uint8_t*>(tmp);
+        }
+        size_t off = 0;
+        for (int i = 0; i < nparts; ++i) {
+            const kcb_mat& p = parts[i];
+            const size_t b = kcb_kquant_bytes(p.rows, p.k, m.q6);
+            if (cudaMemcpy(staging + off, p.blocks, b, cudaMemcpyHostToDevice) != cudaSuccess) {
+                if (tmp) cudaFree(tmp);
+                err_ = "weight upload failed";
+                return KCB_INTERNAL_ERROR;
+            }
+            off += b;
+        }
+        if (m.q6) {
+            const int e = q6k_convert(staging, m.data, m.rows, m.k, 1, stream_);
+            cudaStreamSynchronize(stream_);
+            cudaFree(tmp);
+            if (e) return e;
+        }
+        return KCB_SUCCESS;
+    }
+    int merged_one(DMat& m, const kcb_mat& p) { return upload(m, &p, 1); }
+    int merged(std::vector<DMat>& out, const kcb_mat* parts, int n) {
+        int i = 0;
+        while (i < n) {
+            int j = i + 1;
+            while (j < n && parts[j].fmt == parts[i].fmt && parts[j].k == parts[i].k) ++j;
+            DMat m;
+            if (const int e = upload(m, parts + i, j - i); e) return e;
+            out.push_back(m);
+            i = j;
+        }
+        return KCB_SUCCESS;
+    }
+    int mv(const DMat& m, float* y) {
+        float* xd = reinterpret_cast<float*>(xq + (m.k / 32) * 8);
+        return m.q6 ? matvec_q6k_q8(m.data, xq, xd, y, m.rows, m.k, stream_) : matvec_q4k_q8(m.data, xq, xd, y, m.rows, m.k, stream_);
+    }
+    template <int HD>
+    int attention(const DLayer& L) {
+        const int group = heads / kv_heads;
+        const dim3 grid(kv_heads, nsplit);
+        const size_t smem = static_cast<size_t>(16) * group * (HD + 2) * 4;
+        const float scale = 1.0f / std::sqrt(static_cast<float>(HD));
+        int* pos_p = state;
+#define KCB_ATTN(G_)                                                                                                        \
+    attn_partial_kernel<HD, G_><<<grid, 128, smem, stream_>>>(qkv, L.kc, L.vc, pos_p, part, heads, kv_heads, nsplit, scale, max_ctx)
+        switch (group) {
+        case 1: KCB_ATTN(1); break;
+        case 2: KCB_ATTN(2); break;
+        case 3: KCB_ATTN(3); break;
+        case 4: KCB_ATTN(4); break;
+        default: KCB_ATTN(8); break;
+        }
+#undef KCB_ATTN
+        return launch_status();
+    }
+    // Enqueues one decode step on stream_.
+    int record() {
+        const int qd = heads * hd, kv = kv_heads * hd;
+        int *pos_p = state, *tok_p = state + 1, *nforced_p = state + 2, *used_p = state + 3;
+        const size_t nblk = static_cast<size_t>(lm_head.rows) * (hidden / 256);
+        embed_kernel<<<(hidden / 256 * 8 + 127) / 128, 128, 0, stream_>>>(lm_head.data, nblk, hidden / 256, lm_head.q6, vocab, tok_p, forced,
+                                                                          nforced_p, pos_p, used_p, x);
+        if (const int e = launch_status(); e) return e;
+        if (const int e = add_norm_q8(x, nullptr, nullptr, layers[0].attn_norm, nullptr, xq, nullptr, hidden, 1, eps, 3, 0, stream_); e) return e;
+        for (size_t l = 0; l < layers.size(); ++l) {
+            const DLayer& L = layers[l];
+            float* y = qkv;
+            for (const DMat& m : L.qkv) {
+                if (const int e = mv(m, y); e) return e;
+                y += m.rows;
+            }
+            rope_kv_f16_kernel<<<(heads + 2 * kv_heads + 3) / 4, 128, 0, stream_>>>(qkv, pos_p, L.kc, L.vc, rope_ff, L.q_norm, L.k_norm, heads,
+                                                                                     kv_heads, hd, log2_base, neox, eps, max_ctx);
+            if (const int e = launch_status(); e) return e;
+            if (const int e = hd == 128 ? attention<128>(L) : attention<64>(L); e) return e;
+            attn_combine_q8_kernel<<<(qd / 32 + 3) / 4, 128, 0, stream_>>>(part, attn, xq, reinterpret_cast<float*>(xq + (qd / 32) * 8), heads, hd, nsplit);
+            if (const int e = launch_status(); e) return e;
+            if (const int e = mv(L.wo, t); e) return e;
+            if (const int e = add_norm_q8(x, t, x, L.ffn_norm, nullptr, xq, nullptr, hidden, 1, eps, 3, 0, stream_); e) return e;
+            y = gu;
+            for (const DMat& m : L.gu) {
+                if (const int e = mv(m, y); e) return e;
+                y += m.rows;
+            }
+            if (const int e = silu_mul_q8(gu, gu + inter, nullptr, nullptr, xq, reinterpret_cast<float*>(xq + (inter / 32) * 8), inter, 1, stream_); e) return e;
+            if (const int e = mv(L.wd, t); e) return e;
+            const float* next = l + 1 < layers.size() ? layers[l + 1].attn_norm : out_norm;
+            if (const int e = add_norm_q8(x, t, x, next, nullptr, xq, nullptr, hidden, 1, eps, 3, 0, stream_); e) return e;
+        }
+        if (const int e = mv(lm_head, logits); e) return e;
+        argmax_advance_kernel<<<1, 1024, 0, stream_>>>(logits, vocab, tok_p, history, pos_p, max_ctx);
+        (void)kv;
+        return launch_status();
+    }
+
+    int hidden = 0, inter = 0, heads = 0, kv_heads = 0, hd = 0, vocab = 0, max_ctx = 0, neox = 0, qk_norm = 0, nsplit = 1;
+    float eps = 1e-5f, log2_base = 0.f;
+    std::vector<DLayer> layers;
+    DMat lm_head;
+    float *out_norm = nullptr, *rope_ff = nullptr;
+    float *x = nullptr, *t = nullptr, *qkv = nullptr, *attn = nullptr, *gu = nullptr, *logits = nullptr, *part = nullptr;
+    int *xq = nullptr, *state = nullptr, *forced = nullptr, *history = nullptr;
+    cudaStream_t stream_ = nullptr;
+    cudaGraph_t graph_ = nullptr;
+    cudaGraphExec_t exec_ = nullptr;
+    std::vector<void*> owned_;
+};
+
+thread_local std::string tl_err;
+
+}  // namespace
+}  // namespace kcb
+
+using kcb::Decoder;
+
+extern "C" {
+
+int kcb_decoder_create(const kcb_model_desc* desc, void** out) {
+    if (!desc || !out || !desc->layers || desc->n_layers <= 0) return kcb::KCB_INVALID_VALUE;
+    *out = nullptr;
+    auto* d = new Decoder;
+    const int e = d->init(*desc);
+    if (e != kcb::KCB_SUCCESS) {
+        kcb::tl_err = d->err_;
+        delete d;
+        return e;
+    }
+    *out = d;
+    return kcb::KCB_SUCCESS;
+}
+int kcb_decoder_set_prompt(void* h, const int* tokens, int n, int start_pos) {
+    return h ? static_cast<Decoder*>(h)->set_prompt(tokens, n, start_pos) : kcb::KCB_INVALID_VALUE;
+}
+int kcb_decoder_run(void* h, int steps) { return h && steps >= 0 ? static_cast<Decoder*>(h)->run(steps) : kcb::KCB_INVALID_VALUE; }
+int kcb_decoder_sync(void* h) { return h ? static_cast<Decoder*>(h)->sync() : kcb::KCB_INVALID_VALUE; }
+int kcb_decoder_read(void* h, float* logits_host, int* history_host, int n_history, int* pos_host) {
+    return h ? static_cast<Decoder*>(h)->read(logits_host, history_host, n_history, pos_host) : kcb::KCB_INVALID_VALUE;
+}
+int kcb_decoder_info(void* h, int* launches_per_token, long long* weight_bytes) {
+    if (!h) return kcb::KCB_INVALID_VALUE;
+    if (launches_per_token) *launches_per_token = static_cast<Decoder*>(h)->launches_per_token;
+    if (weight_bytes) *weight_bytes = static_cast<Decoder*>(h)->weight_bytes;
+    return kcb::KCB_SUCCESS;
+}
+void* kcb_decoder_stream(void* h) { return h ? static_cast<Decoder*>(h)->stream() : nullptr; }
+int kcb_decoder_destroy(void* h) {
+    delete static_cast<Decoder*>(h);
+    return kcb::KCB_SUCCESS;
+}
+const char* kcb_decoder_last_error(void) { return kcb::tl_err.c_str(); }
+
+}  // extern "C"

@@ -302,12 +302,6 @@ __global__ void attn_values_kernel(const float* __restrict__ p, const float* __r
 // ---- fp16 KV cache: SET_ROWS and attention ---------------------------------------------------------------
 // kernels/llm/set_rows_f16.cu:67-83.  Round to nearest even; 65520 and above (and NaN) give 0x7bff with
 // the sign of "x < 0"; an input of -0 gives +0 (negative values that round to zero keep their sign bit).
-__device__ __forceinline__ unsigned f32_to_f16_bits(float x) {
-    const unsigned sign = x < 0.0f ? 0x8000u : 0u;
-    const float a = fabsf(x);
-    if (!(a < 65520.0f)) return sign | 0x7bffu;
-    return sign | (static_cast<unsigned>(__half_as_ushort(__float2half_rn(a))) & 0x7fffu);
-}
 __global__ void set_rows_f16_kernel(const float* __restrict__ src, const long long* __restrict__ idx, unsigned* dst,
                                     int pairs, int rows, int src_row, int dst_row, int dst_rows) {
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;

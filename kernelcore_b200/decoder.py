@@ -78,3 +78,78 @@ class Model:
 
     def __exit__(self, *a):
         self.close()
+
+
+class FastDecoder:
+    """The graph-replayed decoder (kcb_decoder_*): one captured CUDA graph replayed per token, position and
+    token on the device, fp16 KV cache, greedy pick on the device."""
+
+    def __init__(self, shape: tm.Shape, model: dict):
+        L = lib.raw
+        self.shape, self._keep = shape, []
+        layers = (_Layer * shape.layers)()
+        ms = tm.mat_shapes(shape)
+        for l, src in enumerate(model["layers"]):
+            for name in tm.MATS:
+                rows, k, q6 = ms[name]
+                setattr(layers[l], name, _Mat(self._ptr(src[name]), rows, k, 6 if q6 else 4))
+            layers[l].attn_norm, layers[l].ffn_norm = self._ptr(src["attn_norm"]), self._ptr(src["ffn_norm"])
+            if shape.qk_norm:
+                layers[l].q_norm, layers[l].k_norm = self._ptr(src["q_norm"]), self._ptr(src["k_norm"])
+        d = _Desc()
+        for f in ("hidden", "inter", "heads", "kv_heads", "head_dim", "vocab", "max_ctx"):
+            setattr(d, f, getattr(shape, f))
+        d.n_layers, d.eps, d.rope_base = shape.layers, shape.eps, shape.rope_base
+        d.neox, d.qk_norm = int(shape.neox), int(shape.qk_norm)
+        d.layers = C.cast(layers, C.POINTER(_Layer))
+        d.out_norm = self._ptr(model["out_norm"])
+        d.lm_head = _Mat(self._ptr(model["lm_head"]), shape.vocab, shape.hidden, 6)
+        self._keep.append(layers)
+        self.handle = C.c_void_p()
+        st = L.kcb_decoder_create(C.byref(d), C.byref(self.handle))
+        if st != 0:
+            L.kcb_decoder_last_error.restype = C.c_char_p
+            raise RuntimeError(f"kcb_decoder_create: status {st}: {L.kcb_decoder_last_error().decode()}")
+        n, wb = C.c_int(), C.c_longlong()
+        L.kcb_decoder_info(self.handle, C.byref(n), C.byref(wb))
+        self.launches_per_token, self.weight_bytes = n.value, wb.value
+        self._keep.clear()  # weights now live on the device
+
+    def _ptr(self, a):
+        a = np.ascontiguousarray(a)
+        self._keep.append(a)
+        return a.ctypes.data
+
+    def set_prompt(self, tokens, start_pos=0):
+        t = np.ascontiguousarray(tokens, np.int32)
+        lib.check(lib.raw.kcb_decoder_set_prompt(self.handle, t.ctypes.data_as(C.c_void_p), int(t.size), int(start_pos)), "kcb_decoder_set_prompt")
+
+    def run(self, steps: int):
+        lib.check(lib.raw.kcb_decoder_run(self.handle, int(steps)), "kcb_decoder_run")
+
+    def sync(self):
+        lib.check(lib.raw.kcb_decoder_sync(self.handle), "kcb_decoder_sync")
+
+    def read(self, n_history=0, want_logits=True):
+        logits = np.zeros(self.shape.vocab, np.float32) if want_logits else None
+        hist = np.zeros(max(n_history, 1), np.int32)
+        pos = C.c_int()
+        lib.check(lib.raw.kcb_decoder_read(self.handle, logits.ctypes.data_as(C.c_void_p) if want_logits else None,
+                                           hist.ctypes.data_as(C.c_void_p), int(n_history), C.byref(pos)), "kcb_decoder_read")
+        return logits, hist[:n_history], pos.value
+
+    @property
+    def cuda_stream(self) -> int:
+        lib.raw.kcb_decoder_stream.restype = C.c_void_p
+        return lib.raw.kcb_decoder_stream(self.handle) or 0
+
+    def close(self):
+        if self.handle:
+            lib.raw.kcb_decoder_destroy(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()

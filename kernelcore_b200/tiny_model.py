@@ -41,6 +41,11 @@ def tiny(max_ctx: int = 40) -> Shape:
     return Shape("tiny", 256, 512, 2, 4, 2, 64, 256, max_ctx)
 
 
+def tiny_qwen(max_ctx: int = 40) -> Shape:
+    """Tiny shapes with the Qwen3 features: NEOX RoPE pairing, per-head q/k RMSNorm, head_dim 128, group 4."""
+    return Shape("tiny-qwen", 256, 512, 2, 4, 1, 128, 256, max_ctx, eps=1e-6, rope_base=1e6, neox=True, qk_norm=True)
+
+
 def llama32_3b(max_ctx: int) -> Shape:
     return Shape("llama-3.2-3b-arch", 3072, 8192, 28, 24, 8, 128, 128256, max_ctx)
 

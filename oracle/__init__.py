@@ -40,7 +40,8 @@ class Mat(C.Structure):
 
 class Layer(C.Structure):
     _fields_ = [(n, Mat) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd")] + [
-        ("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
+        ("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("q_norm", C.c_void_p), ("k_norm", C.c_void_p)]
 
 
 class Model(C.Structure):
@@ -117,6 +118,8 @@ def _load_port():
     lib.lib.kqo_matvec_dequant_f64.argtypes = [_u8p, _f32p, _f32p, i, i, i]
     lib.lib.kqo_decode_token.restype = None
     lib.lib.kqo_decode_token.argtypes = [C.POINTER(Model), _f32p, i, _f32p, _f32p, _i32p]
+    lib.lib.kqo_decode_token_ex.restype = None
+    lib.lib.kqo_decode_token_ex.argtypes = [C.POINTER(Model), _f32p, i, _f32p, _f32p, _i32p, i]
     lib.lib.kqo_decode_scratch_floats.restype = C.c_long
     lib.lib.kqo_decode_scratch_floats.argtypes = [C.POINTER(Model)]
     lib.lib.kqo_decode_scratch_ints.restype = C.c_long

@@ -670,8 +670,12 @@ static void mv_f(const kqo_mat* w, const float* x, int32_t* xq, float* y) { /* C
     mv_q(w, xq, y);
 }
 
-/* llm/llm_model.cpp:287-360 for a model with quantized activations and split q/k/v, gate/up. */
-void kqo_decode_token(const kqo_model* m, const float* x_in, int pos, float* logits, float* sf, int32_t* xq) {
+/* llm/llm_model.cpp:287-360 for a model with quantized activations and split q/k/v, gate/up.
+ * flags (extensions used by the GPU decoder's tests; 0 = the reference's loop exactly):
+ *   1  K and V are rounded to fp16 as they enter the cache (the ggml path's fp16 cache: setRowsF16 ref:765-772),
+ *   2  NEOX RoPE pairing (ropeGgml ref:620-635), 4  per-head RMSNorm of q and k before RoPE (rmsNorm ref:153-162
+ *      on rows of head_dim, as ggml-kernelcore.cpp:757-767 runs it for Qwen3). */
+void kqo_decode_token_ex(const kqo_model* m, const float* x_in, int pos, float* logits, float* sf, int32_t* xq, int flags) {
     const int hid = m->hidden, qd = m->heads * m->head_dim, kv = m->kv_heads * m->head_dim;
     const int ctx = pos + 1;
     const kqo_attn_dims ad = {m->heads, ctx, m->head_dim, kv, m->heads / m->kv_heads, pad8(ctx), pad8(m->max_ctx)};
@@ -697,8 +701,26 @@ void kqo_decode_token(const kqo_model* m, const float* x_in, int pos, float* log
         else mv_q(&L->wq, xq, q);
         mv_q(&L->wk, xq, kk);
         mv_q(&L->wv, xq, vv);
-        if (m->rope_ff) kqo_rope_ff(q, m->rope_ff, pairs, pos, (m->heads + m->kv_heads) * pairs, lb);
+        if (flags & 4) {
+            kqo_rms_norm(q, L->q_norm, q, m->head_dim, m->heads, m->eps);
+            kqo_rms_norm(kk, L->k_norm, kk, m->head_dim, m->kv_heads, m->eps);
+        }
+        if (flags & 2) {
+            float* ones = (float*)malloc((size_t)pairs * sizeof(float));
+            float* tmp = (float*)malloc((size_t)(qd + kv) * sizeof(float));
+            for (int i = 0; i < pairs; ++i) ones[i] = 1.0f;
+            const int32_t p1 = pos;
+            kqo_rope_ggml(q, tmp, &p1, m->rope_ff ? m->rope_ff : ones, m->head_dim, m->heads + m->kv_heads, 1, lb, 1);
+            memcpy(q, tmp, (size_t)(qd + kv) * sizeof(float));
+            free(ones);
+            free(tmp);
+        } else if (m->rope_ff) kqo_rope_ff(q, m->rope_ff, pairs, pos, (m->heads + m->kv_heads) * pairs, lb);
         else kqo_rope(q, pairs, pos, (m->heads + m->kv_heads) * pairs, lb);
+        if (flags & 1)
+            for (int j = 0; j < kv; ++j) {
+                kk[j] = kqo_f16_to_f32(kqo_f32_to_f16(kk[j]));
+                vv[j] = kqo_f16_to_f32(kqo_f32_to_f16(vv[j]));
+            }
         kqo_append_kv(kk, vv, L->k_cache, L->v_cache, kv, pad8(m->max_ctx), pos);
         kqo_attn_scores(q, L->k_cache, scores, &ad, scale);
         kqo_softmax(scores, ctx, pad8(ctx), m->heads);
@@ -715,4 +737,8 @@ void kqo_decode_token(const kqo_model* m, const float* x_in, int pos, float* log
         kqo_norm_q8x4(x, next, xq, hid / 32, m->eps);
     }
     mv_q(&m->lm_head, xq, logits);
+}
+
+void kqo_decode_token(const kqo_model* m, const float* x_in, int pos, float* logits, float* sf, int32_t* xq) {
+    kqo_decode_token_ex(m, x_in, pos, logits, sf, xq, 0);
 }

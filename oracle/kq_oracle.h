@@ -105,6 +105,8 @@ typedef struct {
     const float* ffn_norm;
     float* k_cache; /* transposed fp32 [kv_stride][k_stride] */
     float* v_cache; /* fp32 [max_ctx][kv_stride] */
+    const float* q_norm; /* [head_dim], only read with flag 4 of kqo_decode_token_ex */
+    const float* k_norm;
 } kqo_layer;
 
 typedef struct {
@@ -122,6 +124,9 @@ typedef struct {
  *            + heads*head_dim + 3*inter floats; scratch_q: 11*max(hidden,inter,heads*head_dim)/32 ints. */
 void kqo_decode_token(const kqo_model* m, const float* x_in, int pos, float* logits, float* scratch_f,
                       int32_t* scratch_q);
+/* flags: 1 = fp16-rounded KV cache, 2 = NEOX RoPE, 4 = per-head q/k RMSNorm; 0 = kqo_decode_token. */
+void kqo_decode_token_ex(const kqo_model* m, const float* x_in, int pos, float* logits, float* scratch_f,
+                         int32_t* scratch_q, int flags);
 long kqo_decode_scratch_floats(const kqo_model* m);
 long kqo_decode_scratch_ints(const kqo_model* m);
 

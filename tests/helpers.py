@@ -50,6 +50,9 @@ class OracleModel:
                 setattr(self.layers[l], name, self._mat(L[name], rows, k, q6))
             self.layers[l].attn_norm = self._ptr(L["attn_norm"])
             self.layers[l].ffn_norm = self._ptr(L["ffn_norm"])
+            if s.qk_norm:
+                self.layers[l].q_norm = self._ptr(L["q_norm"])
+                self.layers[l].k_norm = self._ptr(L["k_norm"])
             kc = np.zeros((s.kv, pad8(s.max_ctx)), np.float32)
             vc = np.zeros((s.max_ctx, s.kv), np.float32)
             self.k_cache.append(kc)
@@ -81,9 +84,12 @@ class OracleModel:
         oracle.port.dequant_row_q6k(np.ascontiguousarray(self.model["lm_head"][token]), self.shape.hidden, out)
         return out
 
-    def decode_port(self, x_in, pos):
+    def decode_port(self, x_in, pos, kv_f16=False):
+        """One decode step on the CPU oracle.  kv_f16: K/V rounded to fp16 on entry to the cache; the
+        model shape's neox / qk_norm select the Qwen3-style variants."""
         logits = np.zeros(self.shape.vocab, np.float32)
         sf = np.zeros(oracle.port.lib.kqo_decode_scratch_floats(C.byref(self.c)), np.float32)
         sq = np.zeros(oracle.port.lib.kqo_decode_scratch_ints(C.byref(self.c)), np.int32)
-        oracle.port.lib.kqo_decode_token(C.byref(self.c), np.ascontiguousarray(x_in, np.float32), pos, logits, sf, sq)
+        flags = (1 if kv_f16 else 0) | (2 if self.shape.neox else 0) | (4 if self.shape.qk_norm else 0)
+        oracle.port.lib.kqo_decode_token_ex(C.byref(self.c), np.ascontiguousarray(x_in, np.float32), pos, logits, sf, sq, flags)
         return logits
