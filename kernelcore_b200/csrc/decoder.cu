@@ -291,14 +291,16 @@ __global__ void attn_combine_q8_kernel(const float* __restrict__ part, float* __
 }
 
 // Greedy pick (first maximum, as a sequential scan would), token history, position advance.
-__global__ void argmax_advance_kernel(const float* __restrict__ logits, int vocab, int* token, int* history, int* pos_p, int max_ctx) {
+__global__ void argmax_advance_kernel(const float* __restrict__ cand_v, const int* __restrict__ cand_i, int ncand, int* token,
+                                      int* history, int* pos_p, int max_ctx) {
     __shared__ float bv[32];
     __shared__ int bi[32];
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = logits[i];
-        if (v > best) best = v, idx = i;
+    for (int i = threadIdx.x; i < ncand; i += blockDim.x) {
+        const float v = cand_v[i];
+        const int ci = cand_i[i];
+        if (v > best || (v == best && ci < idx)) best = v, idx = ci;
     }
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -405,6 +407,8 @@ public:
         if (const int e = dev(reinterpret_cast<void**>(&logits), static_cast<size_t>(vocab) * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&xq), static_cast<size_t>(11) * (maxk / 32) * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&part), static_cast<size_t>(heads) * nsplit * (hd + 2) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&cand_v), kCand * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&cand_i), kCand * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&state), 64); e) return e;  // {pos, token, n_forced, token_used}
         if (const int e = dev(reinterpret_cast<void**>(&forced), static_cast<size_t>(max_ctx) * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&history), static_cast<size_t>(max_ctx) * 4); e) return e;
@@ -559,7 +563,7 @@ private:
         embed_kernel<<<(hidden / 256 * 8 + 127) / 128, 128, 0, stream_>>>(lm_head.data, nblk, hidden / 256, lm_head.q6, vocab, tok_p, forced,
                                                                           nforced_p, pos_p, used_p, x);
         if (const int e = launch_status(); e) return e;
-        if (const int e = add_norm_q8(x, nullptr, nullptr, layers[0].attn_norm, nullptr, xq, nullptr, hidden, 1, eps, 3, 0, stream_); e) return e;
+        if (const int e = add_norm_q8_fast(x, nullptr, layers[0].attn_norm, xq, reinterpret_cast<float*>(xq + (hidden / 32) * 8), hidden, eps, stream_); e) return e;
         for (size_t l = 0; l < layers.size(); ++l) {
             const DLayer& L = layers[l];
             float* y = qkv;
@@ -574,7 +578,7 @@ private:
             attn_combine_q8_kernel<<<(qd / 32 + 3) / 4, 128, 0, stream_>>>(part, attn, xq, reinterpret_cast<float*>(xq + (qd / 32) * 8), heads, hd, nsplit);
             if (const int e = launch_status(); e) return e;
             if (const int e = mv(L.wo, t); e) return e;
-            if (const int e = add_norm_q8(x, t, x, L.ffn_norm, nullptr, xq, nullptr, hidden, 1, eps, 3, 0, stream_); e) return e;
+            if (const int e = add_norm_q8_fast(x, t, L.ffn_norm, xq, reinterpret_cast<float*>(xq + (hidden / 32) * 8), hidden, eps, stream_); e) return e;
             y = gu;
             for (const DMat& m : L.gu) {
                 if (const int e = mv(m, y); e) return e;
@@ -583,10 +587,11 @@ private:
             if (const int e = silu_mul_q8(gu, gu + inter, nullptr, nullptr, xq, reinterpret_cast<float*>(xq + (inter / 32) * 8), inter, 1, stream_); e) return e;
             if (const int e = mv(L.wd, t); e) return e;
             const float* next = l + 1 < layers.size() ? layers[l + 1].attn_norm : out_norm;
-            if (const int e = add_norm_q8(x, t, x, next, nullptr, xq, nullptr, hidden, 1, eps, 3, 0, stream_); e) return e;
+            if (const int e = add_norm_q8_fast(x, t, next, xq, reinterpret_cast<float*>(xq + (hidden / 32) * 8), hidden, eps, stream_); e) return e;
         }
         if (const int e = mv(lm_head, logits); e) return e;
-        argmax_advance_kernel<<<1, 1024, 0, stream_>>>(logits, vocab, tok_p, history, pos_p, max_ctx);
+        if (const int e = argmax_partial(logits, vocab, cand_v, cand_i, kCand, stream_); e) return e;
+        argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, tok_p, history, pos_p, max_ctx);
         (void)kv;
         return launch_status();
     }
@@ -597,6 +602,9 @@ private:
     DMat lm_head;
     float *out_norm = nullptr, *rope_ff = nullptr;
     float *x = nullptr, *t = nullptr, *qkv = nullptr, *attn = nullptr, *gu = nullptr, *logits = nullptr, *part = nullptr;
+    static constexpr int kCand = 296;
+    float* cand_v = nullptr;
+    int* cand_i = nullptr;
     int *xq = nullptr, *state = nullptr, *forced = nullptr, *history = nullptr;
     cudaStream_t stream_ = nullptr;
     cudaGraph_t graph_ = nullptr;

@@ -180,6 +180,58 @@ __global__ void add_norm_q8_kernel(const float* __restrict__ a, const float* __r
     }
 }
 
+// The same operation for the graph decoder, where latency matters more than summation order: one CTA,
+// the sum of squares by a tree reduction.  x += t (t may be null), Q8 blocks of norm(x) * w into (xq, xd).
+__global__ void __launch_bounds__(1024) add_norm_q8_fast_kernel(float* x, const float* __restrict__ t, const float* __restrict__ w,
+                                                                 int* xq, float* xd, int n, float eps) {
+    extern __shared__ float sh[];  // n floats
+    __shared__ float red[32];
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        float v = x[j];
+        if (t) {
+            v = __fadd_rn(v, t[j]);
+            x[j] = v;
+        }
+        sh[j] = v;
+        ss += v * v;
+    }
+    const float r = rinv_rms(block_sum(ss, red), n, eps);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int b = warp; b < n / 32; b += nw)
+        quantize_block_warp(__fmul_rn(__fmul_rn(sh[b * 32 + lane], r), w[b * 32 + lane]), xq, xd, b, lane);
+}
+
+// Two-stage greedy pick over the logits: per-CTA (value, index) candidates, first index wins ties.
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, int vocab, float* cand_v, int* cand_i) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) {
+        const float v = logits[i];
+        if (v > best) best = v, idx = i;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+    }
+    if (lane == 0) bv[warp] = best, bi[warp] = idx;
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < nw ? bv[lane] : -INFINITY;
+        idx = lane < nw ? bi[lane] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+        }
+        if (lane == 0) cand_v[blockIdx.x] = best, cand_i[blockIdx.x] = idx;
+    }
+}
+
 // ---- SwiGLU (+ quantize) ----------------------------------------------------------------------------
 // kernels/llm/silu_mul.cu:2-9, silu_mul_q8x4.cu:5-41, silu_mul_q8x4f.cu:18-60, silu_mul_q8kf.cu:16-75.
 __global__ void silu_mul_kernel(const float* __restrict__ g, const float* __restrict__ u, float* out, size_t count) {
@@ -386,6 +438,16 @@ int add_norm_q8(const float* a, const float* t, float* out, const float* w, floa
     const size_t smem = (static_cast<size_t>(n) + n / 32) * sizeof(float);
     if (smem > 48 * 1024) return KCB_INVALID_VALUE;
     add_norm_q8_kernel<<<rows, n >= 2048 ? 1024 : 256, smem, s>>>(a, t, out, w, y, q, sq, n, eps, phases, kq);
+    return launch_status();
+}
+int add_norm_q8_fast(float* x, const float* t, const float* w, int* xq, float* xd, int n, float eps, cudaStream_t s) {
+    if (n <= 0 || n % 32 || n > 11264 || !x || !w || !xq || !xd) return KCB_INVALID_VALUE;
+    add_norm_q8_fast_kernel<<<1, 1024, static_cast<size_t>(n) * sizeof(float), s>>>(x, t, w, xq, xd, n, eps);
+    return launch_status();
+}
+int argmax_partial(const float* logits, int vocab, float* cand_v, int* cand_i, int ncand, cudaStream_t s) {
+    if (vocab <= 0 || ncand <= 0 || !logits || !cand_v || !cand_i) return KCB_INVALID_VALUE;
+    argmax_partial_kernel<<<ncand, 256, 0, s>>>(logits, vocab, cand_v, cand_i);
     return launch_status();
 }
 int silu_mul(const float* g, const float* u, float* out, size_t count, cudaStream_t s) {

@@ -31,6 +31,8 @@ int rms_norm(const float* x, const float* w, float* y, int n, int rows, float ep
 int add_rms_norm(float* x, const float* t, const float* w, float* y, int n, float eps, cudaStream_t s);
 int add_norm_q8(const float* a, const float* t, float* out, const float* w, float* y, int* q, int* sq, int n, int rows,
                 float eps, int phases, int kq, cudaStream_t s);
+int add_norm_q8_fast(float* x, const float* t, const float* w, int* xq, float* xd, int n, float eps, cudaStream_t s);
+int argmax_partial(const float* logits, int vocab, float* cand_v, int* cand_i, int ncand, cudaStream_t s);
 int silu_mul(const float* g, const float* u, float* out, size_t count, cudaStream_t s);
 int silu_mul_q8(const float* g, const float* u, float* y, int* q, int* xq, float* xd, int n, int cols, cudaStream_t s);
 int mul_rows(const float* x, const float* w, float* y, int n, size_t count, cudaStream_t s);
