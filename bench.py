@@ -35,9 +35,10 @@ ROWS, K = 128256, 3072
 NSB = K // 256
 NMAT = 4
 METRIC, UNIT = "q6k_lm_head_matvec_hbm_gbs", "GB/s"
-# DRAM bytes per full-size launch of the matvec kernel (dram__bytes_read.sum + dram__bytes_write.sum),
-# from the ncu capture summarised in profiles/matvec_q6k_q8_lm_head.md; None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes per full-size launch of the matvec kernel (dram__bytes_read.sum + dram__bytes_write.sum):
+# the ncu capture summarised in profiles/matvec_q6k_q8_lm_head.md measured 161.65 MB + 5.0 MB on a 64128-row
+# case; traffic grows linearly with rows, so a 128256-row launch moves twice that.
+NCU_TRAFFIC_BYTES_PER_LAUNCH_FULL = 2 * (161_651_968 + 4_995_840)
 
 
 def algorithmic_bytes(rows: int) -> int:
@@ -179,7 +180,7 @@ def run_ours(args):
     mats, host_blocks0 = [], None
     for i in range(NMAT):
         blocks = synth.q6k_blocks(ROWS, K, i)
-        if i == 0 and rank == 0 and world == 1:
+        if i == 0 and rank == 0 and world == 1 and not args.skip_cpu_baseline:
             host_blocks0 = blocks
         mats.append(kquant.KMatrix(blocks[r0:r0 + rows], rows, K, True))
         del blocks
@@ -265,7 +266,7 @@ def run_ours(args):
                    "rows": ROWS, "k": K, "rows_per_gpu": rows,
                    "l2": f"inputs larger than L2: {NMAT} rotating {rows * NSB * 210 / 1e6:.0f} MB weight matrices"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": "matvec_q6k_q8_kernel",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH_FULL * rows // 128256, "kernel": "matvec_kq_q8_tma_kernel<Q6_K>",
                      "algorithmic_bytes_per_launch": alg_launch, "kernel_us": kern_ms * 1e3, "peak_source": peak_src,
                      "frac_of_8tbs_nominal": achieved / 8000.0},
         "e2e": {"value": alg_total * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": K * 4,
@@ -273,7 +274,7 @@ def run_ours(args):
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,
     }
-    if world == 1:
+    if world == 1 and not args.skip_cpu_baseline:
         sec, cores, kind, y_cpu = cpu_reference_matvec(host_blocks0, x_host.numpy(), ROWS, 20, 3)
         line["cpu_baseline"] = {"value": alg_total / sec / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
                                 "sample": f"20 full {ROWS}x{K} Q6_K matvecs, reference AVX2 kernels, all host threads"
@@ -282,19 +283,107 @@ def run_ours(args):
         torch.cuda.synchronize()
         err = float((y_local.cpu() - torch.from_numpy(y_cpu)).abs().max() / np.abs(y_cpu).max())
         line["check_vs_cpu_rel"] = err
+    if world == 1 and not args.skip_cpu_baseline:
+        del mats
+        torch.cuda.empty_cache()
+        line["extra"] = {"q4k_matvec_config0": q4k_config0(torch, kquant, synth, peak),
+                         "decode_llama32_3b": decode_bench(640, 512, 128, peak)}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
+def q4k_config0(torch, kquant, synth, peak):
+    """BASELINE configs[0]: Q4_K matvec 8192 x 3072.  The 14 MB matrix fits L2 many times over, so 40 distinct
+    copies rotate; 80 launches are timed inside one CUDA graph (the kernel is shorter than a launch)."""
+    rows, k, nmat, n = 8192, 3072, 40, 80
+    base = synth.q4k_blocks(rows, k, 0)
+    mats = [kquant.KMatrix(np.roll(base, i, axis=0), rows, k, False) for i in range(nmat)]
+    x = torch.from_numpy(synth.activations(k, 1)).cuda()
+    sc = kquant.Q8Scratch(k)
+    xq, xd = kquant.quantize_q8x4(x, sc)
+    y = torch.empty(rows, device="cuda")
+    st = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(st):
+        for i in range(3):
+            kquant.matvec_q8(mats[i], xq, xd, y)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(n):
+                kquant.matvec_q8(mats[i % nmat], xq, xd, y)
+    times = []
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / n * 1e3)
+    us = statistics.median(times[1:])
+    alg = rows * (k // 256) * 144 + k * 4 + rows * 4
+    return {"us_per_matvec": us, "gbs": alg / us / 1e3, "frac_of_measured_hbm": alg / us / 1e3 / peak, "algorithmic_bytes": alg,
+            "protocol": f"{n} launches in one CUDA graph over {nmat} rotating matrices, median of 5 replays"}
+
+
+def decode_bench(max_ctx, n_prompt, n_gen, peak):
+    """BASELINE configs[3]: random-init Llama-3.2-3B-architecture model, Q4_K_M mix, batch 1, fp16 KV cache, greedy.
+    The prompt is processed token by token through the same graph (no batched prefill yet)."""
+    import torch
+
+    from kernelcore_b200 import decoder, tiny_model as tm
+    shape = tm.llama32_3b(max_ctx)
+    d = decoder.FastDecoder(shape, tm.build(shape, seed=0))
+    prompt = np.random.default_rng(1).integers(0, shape.vocab, n_prompt)
+    stream = torch.cuda.ExternalStream(d.cuda_stream)
+
+    def timed(steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        d.run(steps)
+        e1.record(stream)
+        d.sync()
+        return e0.elapsed_time(e1)
+
+    d.set_prompt(prompt)
+    timed(min(4, n_prompt))
+    d.set_prompt(prompt)
+    ms_p, ms_g = timed(n_prompt), timed(n_gen)
+    out = {"model": shape.name, "prompt_tokens": n_prompt, "generated_tokens": n_gen, "prompt_tok_s": n_prompt / ms_p * 1e3,
+           "decode_tok_s": n_gen / ms_g * 1e3, "us_per_token": ms_g / n_gen * 1e3, "launches_per_token": d.launches_per_token,
+           "weight_bytes_per_token": d.weight_bytes,
+           "frac_of_measured_hbm_weights_only": d.weight_bytes * (n_gen / ms_g * 1e3) / (peak * 1e9),
+           "kv_cache": "fp16", "prompt_mode": "token by token through the decode graph"}
+    d.close()
+    return out
+
+
+def run_decode(args):
+    peak, _ = measured_peak()
+    out = decode_bench(max(64, args.prompt + args.gen), args.prompt, args.gen, peak)
+    print(json.dumps({"metric": "llama32_3b_decode_tok_s", "value": out["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1,
+                      "higher_is_better": True, "data": "synthetic", "dtype": "int8 dot, fp32 accumulate",
+                      "config": {"workload": "BASELINE configs[3] decode, graph-replayed decoder"}, "detail": out}))
+
+
 def main():
+    global ROWS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="lm_head", choices=["lm_head", "decode"],
+                    help="lm_head: the benchmark line; decode: Llama-3.2-3B-shape decode only (profiling, quick checks)")
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--gen", type=int, default=128)
+    ap.add_argument("--rows", type=int, default=ROWS, help="shrink the matrix (profiling captures only; the bench line is the default size)")
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU baseline leg (profiling captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    ROWS = args.rows
+    if args.workload == "decode":
+        run_decode(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
