@@ -117,6 +117,17 @@ int kcb_matvec_q6k_q8(const void* planes_dev, const int32_t* xq_dev, const float
 int kcb_matvec_q4k_f32(const void* w_dev, const float* x_dev, float* y_dev, int rows, int k, void* stream);
 int kcb_matvec_q6k_f32(const void* planes_dev, const float* x_dev, float* y_dev, int rows, int k, void* stream);
 
+/* ---- prompt matmul -------------------------------------------------------------------------------- */
+/* kernels "matmul_q4k_q8x4/x8", "matmul_q6k_q8x4/x8" (q8k = 0: per-32 slots of 11*k/32 ints per column) and
+ * "matmul_q4k_q8kx4/x8", "matmul_q6k_q8kx4/x8" (q8k = 1: per-256 slots of 85*k/256 ints), llm::MatmulKQ8Args
+ * (llm/llm_kernels.hpp:255-271): Y[c*rows + r] for ncols activation columns.  Q4_K with per-256 slots and
+ * rows % 128 == 0 runs on the tensor cores (tcgen05, int8), bit-identical per column to
+ * llm::ref::matvecQ4KQ8K (llm/llm_reference.cpp:529-562); other cases on CUDA cores. */
+int kcb_matmul_kq_q8(const void* w_dev, const int32_t* slots_dev, float* y_dev, int rows, int k, int ncols, int q6, int q8k,
+                     void* stream);
+/* Bounded waits of the tensor-core kernel that expired since load (0 in a healthy process); synchronous. */
+unsigned kcb_tc_timeouts(void);
+
 /* No counterpart in the reference.  y = W x for a Q4_K matrix and fp32 x like kcb_quantize_q8x4 followed by
  * kcb_matvec_q4k_q8, but the 8-bit activation scratch lives in a fixed device array inside the library, so
  * the call allocates nothing and needs no caller scratch -- for hosts that may not allocate device memory

@@ -148,4 +148,9 @@ int kcb_flash_attn_f16(const float* q, const void* k, const void* v, const void*
     return flash_attn_f16(q, k, v, mask, out, dims, scale, st(s));
 }
 
+int kcb_matmul_kq_q8(const void* w, const int32_t* xq, float* y, int rows, int k, int ncols, int q6, int q8k, void* s) {
+    return matmul_kq_q8(w, xq, y, rows, k, ncols, q6, q8k, st(s));
+}
+unsigned kcb_tc_timeouts(void) { return tc_timeouts(); }
+
 }  // extern "C"

@@ -1,0 +1,254 @@
+// Q4_K x Q8_K-activation matmul on the 5th-generation tensor cores (tcgen05, int8 -> int32, TMEM).
+//
+// Replaces the reference's kernels/llm/matmul_q4k_q8kx4.cu:41 / matmul_q4k_q8kx8.cu:41-239 (prompt
+// processing; one thread per (row, 4 or 8 columns) with dp4a there).  Y[c*rows + r] = sum over super-blocks
+//     (d * dx_c) * float(is) - (dmin * dx_c) * float(im),
+//     is = sum_j sc_j * dot32(q_j, x_j),   im = sum_j m_j * B_j         (llm/llm_reference.cpp:529-562)
+// with q 4-bit weights, sc/m 6-bit sub-block scales/mins, x int8 activations with one scale dx per 256 and
+// B_j the activation sums per 32.  Both integer sums are exact GEMMs once the scale is folded into the weight:
+//   * w' = sc_j * q is at most 945, so it is split as w' = 32 a + b with a, b < 32: two int8 planes, two
+//     accumulators, is = 32 Da + Db, each a K = 256 contraction per super-block on the tensor core;
+//   * the min term is a K = 8 contraction of the mins with the activation sums; the reference already stores
+//     the sums as two bytes (B >> 6, B & 63), so im = 64 Dh + Dl with two more accumulators.
+// One CTA owns a 128-row x 128-column output tile: per super-block it unpacks the weight planes into shared
+// memory (no-swizzle K-major core-matrix layout), copies the activation bytes, one thread issues 18
+// tcgen05.mma (M 128, N 128, K 32) into four TMEM accumulators, and all 8 warps read them back with tcgen05.ld
+// and apply the two fp32 scale products in the reference's order -- so every output is bit-identical to the
+// reference's per-column mirror.  Accumulators across super-blocks stay in registers (64 per thread).
+// Every wait on the MMA-completion mbarrier is bounded; on expiry the CTA records it, frees its TMEM and leaves.
+
+#include "common.cuh"
+#include "ops.h"
+
+namespace kcb {
+namespace {
+
+constexpr int TM = 128, TN = 128;
+constexpr int kSlab = 128 * 32;  // one K-step (32 bytes of K) of a 128-row operand
+constexpr int kThreads = 256;
+
+// shared-memory map (bytes)
+constexpr int kOffAa = 0;                   // 8 slabs: plane a (w' >> 5)
+constexpr int kOffAb = kOffAa + 8 * kSlab;  // 8 slabs: plane b (w' & 31)
+constexpr int kOffAm = kOffAb + 8 * kSlab;  // 1 slab: mins in K bytes 0..7
+constexpr int kOffBx = kOffAm + kSlab;      // 8 slabs: activation bytes
+constexpr int kOffBh = kOffBx + 8 * kSlab;  // 1 slab: activation sums >> 6
+constexpr int kOffBl = kOffBh + kSlab;      // 1 slab: activation sums & 63
+constexpr int kOffDx = kOffBl + kSlab;      // 128 floats: activation scale of each column for this super-block
+constexpr int kOffBar = kOffDx + 512;       // mbarrier, TMEM base
+constexpr int kSmemBytes = kOffBar + 64;
+
+__device__ unsigned g_tc_timeouts = 0;
+
+// K-major, no swizzle: 8-row x 16-byte core matrices; the two 16-byte K chunks of a K-step are 128 B apart
+// (leading byte offset), consecutive 8-row groups 256 B apart (stride byte offset); version 1 descriptor.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(128 >> 4) << 16) |
+           (static_cast<uint64_t>(256 >> 4) << 32) | (static_cast<uint64_t>(1) << 46);
+}
+// int32 accumulate, signed 8-bit A and B, both K-major, N = 128, M = 128.
+constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TN >> 3) << 17) | (static_cast<uint32_t>(TM >> 4) << 24);
+
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr));
+}
+
+// Two 16-bit lanes at a time: (four 4-bit values in bytes) * sc, split into (>> 5) and (& 31) byte planes.
+__device__ __forceinline__ void scale_split(unsigned nib4, unsigned sc, unsigned& a, unsigned& b) {
+    const unsigned pe = (nib4 & 0x00FF00FFu) * sc, po = ((nib4 >> 8) & 0x00FF00FFu) * sc;
+    a = ((pe >> 5) & 0x00FF00FFu) | (((po >> 5) & 0x00FF00FFu) << 8);
+    b = (pe & 0x001F001Fu) | ((po & 0x001F001Fu) << 8);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const uint8_t* __restrict__ w, const int* __restrict__ xq,
+                                                                         float* __restrict__ y, int rows, int nsb, int ncols) {
+    extern __shared__ __align__(1024) uint8_t sm[];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(sm + kOffBar);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kOffBar + 16);
+    float* dxs = reinterpret_cast<float*>(sm + kOffDx);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r_tile = blockIdx.x * TM, c_tile = blockIdx.y * TN;
+    const int slot_ints = nsb * 85;
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        mbar_init_fence();
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    // epilogue role: TMEM lane (= tile row) 32 * (warp & 3) + lane, columns [64 * (warp >> 2), +64)
+    const int erow = 32 * (warp & 3) + lane, ecol0 = 64 * (warp >> 2);
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+    // unpack role: tile row tid / 2, quant chunks 2 * (tid & 1) and + 1 (sub-blocks 4 * hsel .. + 3)
+    const int urow = tid >> 1, hsel = tid & 1;
+    const uint8_t* urow_blocks = w + static_cast<size_t>(r_tile + urow) * nsb * kQ4KBlock;
+    const uint8_t* erow_blocks = w + static_cast<size_t>(r_tile + erow) * nsb * kQ4KBlock;
+    const uint32_t ubase = (urow >> 3) * 256 + (urow & 7) * 16;
+
+    bool failed = false;
+    for (int sb = 0; sb < nsb && !failed; ++sb) {
+        // ---- weight planes ----
+        {
+            const uint8_t* blk = urow_blocks + static_cast<size_t>(sb) * kQ4KBlock;
+            const uint4 hd = __ldg(reinterpret_cast<const uint4*>(blk));
+            const unsigned sclo = hd.y & 0x3F3F3F3Fu, schi = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
+            const unsigned scw = hsel ? schi : sclo;  // scales of sub-blocks 4*hsel .. 4*hsel+3
+            uint4 qv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qv[i] = ldg_stream(blk + 16 + 64 * hsel + 16 * i);
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {  // quant chunk 2*hsel + jj -> K-steps s_lo (low nibbles), s_lo + 1 (high)
+                const int s_lo = 4 * hsel + 2 * jj;
+                const unsigned sc_l = (scw >> (16 * jj)) & 255u, sc_h = (scw >> (16 * jj + 8)) & 255u;
+                const unsigned qw[8] = {qv[2 * jj].x, qv[2 * jj].y, qv[2 * jj].z, qv[2 * jj].w,
+                                        qv[2 * jj + 1].x, qv[2 * jj + 1].y, qv[2 * jj + 1].z, qv[2 * jj + 1].w};
+                unsigned al[8], bl[8], ah[8], bh[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    scale_split(qw[i] & 0x0F0F0F0Fu, sc_l, al[i], bl[i]);
+                    scale_split((qw[i] >> 4) & 0x0F0F0F0Fu, sc_h, ah[i], bh[i]);
+                }
+                uint8_t* pa = sm + kOffAa + s_lo * kSlab + ubase;
+                uint8_t* pb = sm + kOffAb + s_lo * kSlab + ubase;
+                *reinterpret_cast<uint4*>(pa) = make_uint4(al[0], al[1], al[2], al[3]);
+                *reinterpret_cast<uint4*>(pa + 128) = make_uint4(al[4], al[5], al[6], al[7]);
+                *reinterpret_cast<uint4*>(pb) = make_uint4(bl[0], bl[1], bl[2], bl[3]);
+                *reinterpret_cast<uint4*>(pb + 128) = make_uint4(bl[4], bl[5], bl[6], bl[7]);
+                *reinterpret_cast<uint4*>(pa + kSlab) = make_uint4(ah[0], ah[1], ah[2], ah[3]);
+                *reinterpret_cast<uint4*>(pa + kSlab + 128) = make_uint4(ah[4], ah[5], ah[6], ah[7]);
+                *reinterpret_cast<uint4*>(pb + kSlab) = make_uint4(bh[0], bh[1], bh[2], bh[3]);
+                *reinterpret_cast<uint4*>(pb + kSlab + 128) = make_uint4(bh[4], bh[5], bh[6], bh[7]);
+            }
+            if (hsel == 0) {  // mins of the 8 sub-blocks as K bytes 0..7, zeros behind
+                const unsigned mlo = hd.z & 0x3F3F3F3Fu, mhi = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
+                *reinterpret_cast<uint4*>(sm + kOffAm + ubase) = make_uint4(mlo, mhi, 0u, 0u);
+                *reinterpret_cast<uint4*>(sm + kOffAm + ubase + 128) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        // ---- activation bytes, sums and scales of this super-block ----
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int i = tid + kThreads * it, col = i >> 4, part = i & 15;  // part = 2 * K-step + 16-byte half
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (c_tile + col < ncols) v = __ldg(reinterpret_cast<const uint4*>(xq + static_cast<size_t>(c_tile + col) * slot_ints + sb * 64 + part * 4));
+            *reinterpret_cast<uint4*>(sm + kOffBx + (part >> 1) * kSlab + (col >> 3) * 256 + (part & 1) * 128 + (col & 7) * 16) = v;
+        }
+        if (tid < TN) {
+            const int col = tid;
+            uint4 pw = make_uint4(0u, 0u, 0u, 0u);
+            float dx = 0.0f;
+            if (c_tile + col < ncols) {
+                const int* slot = xq + static_cast<size_t>(c_tile + col) * slot_ints;
+                pw = __ldg(reinterpret_cast<const uint4*>(slot + nsb * 81 + sb * 4));
+                dx = __int_as_float(__ldg(slot + nsb * 64 + sb));
+            }
+            const uint32_t o = (col >> 3) * 256 + (col & 7) * 16;
+            *reinterpret_cast<uint4*>(sm + kOffBh + o) = make_uint4(pw.x, pw.y, 0u, 0u);
+            *reinterpret_cast<uint4*>(sm + kOffBh + o + 128) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(sm + kOffBl + o) = make_uint4(pw.z, pw.w, 0u, 0u);
+            *reinterpret_cast<uint4*>(sm + kOffBl + o + 128) = make_uint4(0u, 0u, 0u, 0u);
+            dxs[col] = dx;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+        __syncthreads();
+        // ---- 18 MMAs by one thread, completion on the mbarrier ----
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t base = smem_u32(sm);
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const uint64_t bd = smem_desc(base + kOffBx + s * kSlab);
+                mma_i8(tmem + 0, smem_desc(base + kOffAa + s * kSlab), bd, s > 0);
+                mma_i8(tmem + 128, smem_desc(base + kOffAb + s * kSlab), bd, s > 0);
+            }
+            const uint64_t md = smem_desc(base + kOffAm);
+            mma_i8(tmem + 256, md, smem_desc(base + kOffBh), 0);
+            mma_i8(tmem + 384, md, smem_desc(base + kOffBl), 0);
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+        }
+        // ---- epilogue: read the four accumulators, apply the reference's two scale products ----
+        const bool ok = mbar_wait_bounded(bar, static_cast<uint32_t>(sb) & 1u);
+        if (__syncthreads_or(!ok)) {
+            failed = true;
+            break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned hdw = __ldg(reinterpret_cast<const unsigned*>(erow_blocks + static_cast<size_t>(sb) * kQ4KBlock));
+        const float d = half_bits_to_float(hdw & 0xFFFFu), dmin = half_bits_to_float(hdw >> 16);
+        const uint32_t trow = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + ecol0;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+            int va[16], vb[16], vh[16], vl[16];
+            tmem_ld16(trow + 16 * ch, va);
+            tmem_ld16(trow + 128 + 16 * ch, vb);
+            tmem_ld16(trow + 256 + 16 * ch, vh);
+            tmem_ld16(trow + 384 + 16 * ch, vl);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float dx = dxs[ecol0 + 16 * ch + i];
+                const int is = 32 * va[i] + vb[i], im = 64 * vh[i] + vl[i];
+                const float t1 = __fmul_rn(__fmul_rn(d, dx), static_cast<float>(is));
+                const float t2 = __fmul_rn(__fmul_rn(dmin, dx), static_cast<float>(im));
+                acc[16 * ch + i] = __fadd_rn(acc[16 * ch + i], __fsub_rn(t1, t2));
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();  // TMEM and the operand slabs are free for the next super-block
+    }
+    if (failed) {
+        if (tid == 0) atomicAdd(&g_tc_timeouts, 1u);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+            const int c = c_tile + ecol0 + i;
+            if (c < ncols) y[static_cast<size_t>(c) * rows + r_tile + erow] = acc[i];
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+}
+
+}  // namespace
+
+unsigned tc_timeouts() {
+    unsigned v = 0;
+    cudaMemcpyFromSymbol(&v, g_tc_timeouts, sizeof v);
+    return v;
+}
+
+// Tensor-core path for Q4_K weights and per-256 activation slots; rows must be a multiple of 128.
+int matmul_q4k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s) {
+    if (rows <= 0 || rows % TM || k <= 0 || k % 256 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(matmul_q4k_q8k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return KCB_LAUNCH_FAILURE;
+        attr_set = true;
+    }
+    const dim3 grid(rows / TM, (ncols + TN - 1) / TN);
+    matmul_q4k_q8k_tc_kernel<<<grid, kThreads, kSmemBytes, s>>>(static_cast<const uint8_t*>(w), xq, y, rows, k / 256, ncols);
+    return launch_status();
+}
+
+}  // namespace kcb

@@ -26,6 +26,10 @@ int quantize_cols_k(const float* x, int* q, int k, int ncols, cudaStream_t s);
 // matmul_kq.cu
 int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int ncols, int q6, int q8k, cudaStream_t s);
 
+// matmul_tc.cu
+int matmul_q4k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s);
+unsigned tc_timeouts();
+
 // glue.cu
 int rms_norm(const float* x, const float* w, float* y, int n, int rows, float eps, cudaStream_t s);
 int add_rms_norm(float* x, const float* t, const float* w, float* y, int n, float eps, cudaStream_t s);
