@@ -287,6 +287,7 @@ def run_ours(args):
         del mats
         torch.cuda.empty_cache()
         line["extra"] = {"q4k_matvec_config0": q4k_config0(torch, kquant, synth, peak),
+                         "q4k_matmul_config2": matmul_bench(),
                          "decode_llama32_3b": decode_bench(640, 512, 128, peak)}
     print(json.dumps(line))
     if world > 1:
@@ -324,6 +325,44 @@ def q4k_config0(torch, kquant, synth, peak):
     alg = rows * (k // 256) * 144 + k * 4 + rows * 4
     return {"us_per_matvec": us, "gbs": alg / us / 1e3, "frac_of_measured_hbm": alg / us / 1e3 / peak, "algorithmic_bytes": alg,
             "protocol": f"{n} launches in one CUDA graph over {nmat} rotating matrices, median of 5 replays"}
+
+
+def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5):
+    """BASELINE configs[2]: Y[M x 8192] = X[M x 3072] . W^T, W Q4_K; X quantized on the fly to per-256 int8 slots
+    (quantize_cols_k) and contracted on the tensor cores (tcgen05 int8).  One step = quantize + matmul."""
+    import torch
+
+    from kernelcore_b200 import kquant, lib, synth
+    rows, k = 8192, 3072
+    w = kquant.KMatrix(synth.q4k_blocks(rows, k, 0), rows, k, False)
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    bf16 = float(peaks.get("bf16_tflops", 1590.0))
+    out = {}
+    for M in ms_list:
+        X = torch.randn(M, k, device="cuda")
+        slots = torch.zeros((M, 85 * k // 256), dtype=torch.int32, device="cuda")
+        y = torch.empty((M, rows), device="cuda")
+
+        def step():
+            lib.call("quantize_cols_k", X, slots, k, M)
+            lib.call("matmul_kq_q8", w.data, slots, y, rows, k, M, 0, 1)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(4):
+                step()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / 4)
+        ms = statistics.median(ts)
+        tf = 2.0 * M * rows * k / ms / 1e9
+        out[f"M{M}"] = {"us": ms * 1e3, "tflops": tf, "frac_of_measured_bf16_burst": tf / bf16, "prompt_tok_s_one_matrix": M / ms * 1e3}
+    out["note"] = "int8 tcgen05 path; fraction quoted against the measured bf16 cuBLAS burst peak (no int8 peak was measured on this pool)"
+    return out
 
 
 def decode_bench(max_ctx, n_prompt, n_gen, peak):
@@ -373,7 +412,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="lm_head", choices=["lm_head", "decode"],
+    ap.add_argument("--workload", default="lm_head", choices=["lm_head", "decode", "matmul"],
                     help="lm_head: the benchmark line; decode: Llama-3.2-3B-shape decode only (profiling, quick checks)")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=128)
@@ -383,6 +422,8 @@ def main():
     ROWS = args.rows
     if args.workload == "decode":
         run_decode(args)
+    elif args.workload == "matmul":
+        print(json.dumps({"metric": "q4k_matmul_tflops", "unit": "TFLOP/s", "n_gpus": 1, "data": "synthetic", "detail": matmul_bench((args.prompt,), reps=2)}))
     elif args.impl == "reference":
         run_reference(args)
     else:
