@@ -5,7 +5,7 @@
 
 Workload (N = 1): the Q6_K LM-head matvec, W 128256 x 3072 in GGUF Q6_K (323 MB), x fp32[3072],
 logits fp32[128256].  One step = the reference's Backend::matvec for a K-quant matrix: quantize x to
-Q8 blocks of 32 (quantize_q8x4) and run the integer-dot matvec (matvec_q6k_q8).  Four distinct
+Q8 blocks of 32 (quantize_q8x4's arithmetic, done inside the kernel) and the integer-dot matvec (matvec_q6k_q8) -- one launch.  Four distinct
 matrices are rotated so that every step streams weights that left L2 long ago.  At N > 1 the rows
 are sharded evenly over the ranks (x replicated) and the logits are all-gathered: strong scaling.
 
@@ -189,19 +189,47 @@ def run_ours(args):
     scratch = kquant.Q8Scratch(K)
     y_local = torch.empty(rows, dtype=torch.float32, device="cuda")
     y_full = torch.empty(ROWS, dtype=torch.float32, device="cuda") if world > 1 else y_local
+    # N > 1: the all-gather is fused into the matvec -- every rank stores its rows straight into all ranks'
+    # logits buffers through NVLink peer mappings (symmetric memory), followed by a small bounded barrier kernel.
+    # If peer mappings cannot be set up on this box, fall back to an NCCL all-gather and say so in `config`.
+    gather_mode, fused = "none", None
+    if world > 1:
+        gather_mode = "nccl all_gather_into_tensor"
+        if not args.nccl_gather:
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+                from kernelcore_b200 import shard
+                y_sym = symm_mem.empty(ROWS, dtype=torch.float32, device=torch.device("cuda", local))
+                f_sym = symm_mem.empty(64, dtype=torch.int32, device=torch.device("cuda", local))
+                f_sym.zero_()
+                hy = symm_mem.rendezvous(y_sym, dist.group.WORLD.group_name)
+                hf = symm_mem.rendezvous(f_sym, dist.group.WORLD.group_name)
+                own, peers = shard.gather_targets(list(hy.buffer_ptrs), rank, r0)
+                fused = {"own": C.c_void_p(own), "peers": (C.c_void_p * len(peers))(*peers), "n": len(peers),
+                         "flags": (C.c_void_p * world)(*list(hf.buffer_ptrs)),
+                         "counters": torch.zeros(2, dtype=torch.int32, device="cuda")}
+                y_full = y_sym
+                torch.cuda.synchronize()
+                dist.barrier()
+                gather_mode = "fused: peer stores from the matvec epilogue + bounded flag barrier"
+            except Exception as e:  # noqa: BLE001 - any failure to map peers means: use NCCL
+                fused = None
+                gather_mode = f"nccl all_gather_into_tensor (peer mapping unavailable: {type(e).__name__})"
     y_host = torch.empty(ROWS, dtype=torch.float32).pin_memory()
     stream = torch.cuda.current_stream()
 
     def step(i, ev=None):
+        """One call into the library per step: quantize + matvec (+ fused gather + barrier)."""
         m = mats[i % NMAT]
-        xq, xd = kquant.quantize_q8x4(x, scratch)
-        if ev is not None:
-            ev[0].record(stream)
-        kquant.matvec_q8(m, xq, xd, y_local)
-        if ev is not None:
-            ev[1].record(stream)
-        if world > 1:
-            dist.all_gather_into_tensor(y_full, y_local)
+        e0 = C.c_void_p(ev[0].cuda_event) if ev is not None else None
+        e1 = C.c_void_p(ev[1].cuda_event) if ev is not None else None
+        if fused is not None:
+            lib.call("matvec_q6k_f32x_sharded", m.data, x, fused["own"], fused["peers"], fused["n"], fused["flags"],
+                     fused["counters"], rank, world, rows, K, e0, e1)
+        else:
+            lib.call("matvec_q6k_f32x_sharded", m.data, x, y_local, None, 0, None, None, rank, 1, rows, K, e0, e1)
+            if world > 1:
+                dist.all_gather_into_tensor(y_full, y_local)
 
     def fence():
         if world > 1:
@@ -211,21 +239,38 @@ def run_ours(args):
     for i in range(max(args.warmup, 3)):
         step(i)
     fence()
-    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    # The timed region replays a CUDA graph of NMAT steps (one launch each, one per rotating matrix): at 30-60 us
+    # per step the Python call overhead would otherwise be what is measured, most of all at N > 1.
+    reps, tail_steps = divmod(args.steps, NMAT)
+    steps_timed = args.steps
+    gstream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(gstream):
+        step(0)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=gstream):
+            for i in range(NMAT):
+                step(i)
+    fence()
+    for _ in range(3):
+        graph.replay()
+    fence()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
     fence()
-    t0.record(stream)
-    for i in range(args.steps):
-        step(i, kev[i])
-    t1.record(stream)
+    t0.record()
+    for _ in range(reps):
+        graph.replay()
+    for i in range(tail_steps):  # K not a multiple of the graph length: the rest as plain launches
+        step(i)
+    t1.record()
     fence()
     clocks = sampler.stop() if rank == 0 else None
     total_ms = t0.elapsed_time(t1)
-    kern_ms = statistics.mean(a.elapsed_time(b) for a, b in kev)
+    kern_ms = total_ms / steps_timed  # a step is exactly one launch of the matvec kernel
 
     # end to end through host buffers: x in from pinned memory, logits out, every step
     def e2e_step(i):
@@ -243,10 +288,19 @@ def run_ours(args):
     fence()
     e2e_ms = (time.perf_counter() - w0) * 1e3
 
+    gather_ok = None
     if world > 1:
         t = torch.tensor([total_ms, e2e_ms, kern_ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, e2e_ms, kern_ms = (float(v) for v in t.cpu())
+        # every rank must now hold the same full logits: compare a checksum of the gathered vector
+        step(0)
+        fence()
+        cs = torch.stack([y_full.double().sum(), y_full.double().abs().sum()])
+        lo, hi = cs.clone(), cs.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        gather_ok = bool(torch.equal(lo, hi)) and lib.raw.kcb_peer_timeouts() == 0
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -255,23 +309,24 @@ def run_ours(args):
     peak, peak_src = measured_peak()
     alg_total = algorithmic_bytes(ROWS)
     alg_launch = algorithmic_bytes(rows)
-    value = alg_total * args.steps / (total_ms * 1e-3) / 1e9
+    value = alg_total * steps_timed / (total_ms * 1e-3) / 1e9
     achieved = alg_launch / (kern_ms * 1e-3) / 1e9
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps_timed, "warmup": max(args.warmup, 3) + 3 * NMAT,
+        "ms_per_step": total_ms / steps_timed, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 dot, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"Q6_K lm_head matvec {ROWS}x{K} (BASELINE configs[1]): quantize_q8x4 + matvec_q6k_q8"
-                               + (f", rows sharded over {world} GPUs + NCCL all-gather of the logits" if world > 1 else ""),
-                   "rows": ROWS, "k": K, "rows_per_gpu": rows,
+        "config": {"workload": f"Q6_K lm_head matvec {ROWS}x{K} (BASELINE configs[1]): Backend::matvec = Q8 quantize + matvec_q6k_q8 in one launch"
+                               + (f", rows sharded over {world} GPUs + all-gather of the logits" if world > 1 else ""),
+                   "rows": ROWS, "k": K, "rows_per_gpu": rows, "all_gather": gather_mode, "gather_identical_on_all_ranks": gather_ok,
                    "l2": f"inputs larger than L2: {NMAT} rotating {rows * NSB * 210 / 1e6:.0f} MB weight matrices"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH_FULL * rows // 128256, "kernel": "matvec_kq_q8_tma_kernel<Q6_K>",
-                     "algorithmic_bytes_per_launch": alg_launch, "kernel_us": kern_ms * 1e3, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": alg_launch, "kernel_us": kern_ms * 1e3,
+                     "timing": "CUDA events around the timed region on the launching stream / launches (graph replay, one kernel per step)", "peak_source": peak_src,
                      "frac_of_8tbs_nominal": achieved / 8000.0},
         "e2e": {"value": alg_total * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": K * 4,
                 "d2h_bytes_per_step": ROWS * 4, "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": steps_timed,
         "clocks": clocks,
     }
     if world == 1 and not args.skip_cpu_baseline:
@@ -416,6 +471,7 @@ def main():
                     help="lm_head: the benchmark line; decode: Llama-3.2-3B-shape decode only (profiling, quick checks)")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=128)
+    ap.add_argument("--nccl-gather", action="store_true", help="N > 1: use an NCCL all-gather instead of the fused peer stores")
     ap.add_argument("--rows", type=int, default=ROWS, help="shrink the matrix (profiling captures only; the bench line is the default size)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU baseline leg (profiling captures)")
     args = ap.parse_args()

@@ -128,6 +128,30 @@ int kcb_matmul_kq_q8(const void* w_dev, const int32_t* slots_dev, float* y_dev, 
 /* Bounded waits of the tensor-core kernel that expired since load (0 in a healthy process); synchronous. */
 unsigned kcb_tc_timeouts(void);
 
+/* ---- row-sharded matvec across GPUs (no counterpart in the reference, which is single-device) -------------
+ * One process per GPU, rank r owning `rows` consecutive rows of a Q6_K matrix (its own planes).  The kernel
+ * writes each result to y_local[row] and, through NVLink peer mappings, to y_peers[i][row] for the npeers <= 7
+ * other ranks: y_local / y_peers[i] point at THIS rank's first row inside each rank's full-length output, so
+ * the all-gather of the logits rides on the matvec's stores.  rows % 8 == 0, k <= 4096. */
+int kcb_matvec_q6k_q8_gather(const void* planes_dev, const int32_t* xq_dev, const float* xd_dev, float* y_local,
+                             float* const* y_peers, int npeers, int rows, int k, void* stream);
+/* Cross-GPU step barrier for the gathered output: flags[i] is rank i's array of `world` 32-bit counters (peer
+ * mapped, zero-initialised).  Rank `rank` stores `epoch` (release, system scope) into flags[i][rank] for all i
+ * and waits until flags[rank][i] >= epoch for all i.  The wait is bounded; an expiry is counted in
+ * kcb_peer_timeouts() and the kernel returns.  Use a fresh, increasing epoch per step. */
+int kcb_peer_barrier(unsigned* const* flags, int rank, int world, unsigned epoch, void* stream);
+unsigned kcb_peer_timeouts(void);
+/* The whole sharded step in ONE kernel launch: x (fp32, k floats) is quantized to Q8 blocks of 32 inside the
+ * kernel (quantize_q8x4's arithmetic), the row shard is multiplied, results go to y_local and to the npeers other
+ * ranks' outputs, and -- world > 1 -- the last CTA to finish runs the step barrier on `flags` (as
+ * kcb_peer_barrier).  counters: two zero-initialised device words owned by this rank (epoch, finished CTAs); NULL
+ * when world == 1.  ev_before / ev_after: optional cudaEvent_t recorded around the launch on `stream`.  With
+ * npeers == 0 and world == 1 this is Backend::matvec for one Q6_K matrix (llm/llm_model.cpp:385-397) in a single
+ * launch.  rows % 8 == 0, k <= 4096. */
+int kcb_matvec_q6k_f32x_sharded(const void* planes_dev, const float* x_dev, float* y_local, float* const* y_peers, int npeers,
+                                unsigned* const* flags, unsigned* counters, int rank, int world, int rows, int k, void* ev_before,
+                                void* ev_after, void* stream);
+
 /* No counterpart in the reference.  y = W x for a Q4_K matrix and fp32 x like kcb_quantize_q8x4 followed by
  * kcb_matvec_q4k_q8, but the 8-bit activation scratch lives in a fixed device array inside the library, so
  * the call allocates nothing and needs no caller scratch -- for hosts that may not allocate device memory

@@ -152,5 +152,22 @@ int kcb_matmul_kq_q8(const void* w, const int32_t* xq, float* y, int rows, int k
     return matmul_kq_q8(w, xq, y, rows, k, ncols, q6, q8k, st(s));
 }
 unsigned kcb_tc_timeouts(void) { return tc_timeouts(); }
+int kcb_matvec_q6k_q8_gather(const void* w, const int32_t* xq, const float* xd, float* y_local, float* const* y_peers, int npeers,
+                             int rows, int k, void* s) {
+    return matvec_q6k_q8_gather(w, xq, xd, y_local, y_peers, npeers, rows, k, st(s));
+}
+int kcb_peer_barrier(unsigned* const* flags, int rank, int world, unsigned epoch, void* s) { return peer_barrier(flags, rank, world, epoch, nullptr, st(s)); }
+int kcb_matvec_q6k_f32x_sharded(const void* w, const float* x, float* y_local, float* const* y_peers, int npeers,
+                                unsigned* const* flags, unsigned* counters, int rank, int world, int rows, int k, void* ev_before,
+                                void* ev_after, void* s) {
+    if (ev_before && cudaEventRecord(static_cast<cudaEvent_t>(ev_before), st(s)) != cudaSuccess) return KCB_INVALID_RESOURCE_HANDLE;
+    const int e = matvec_q6k_f32x_sharded(w, x, y_local, y_peers, npeers, flags, counters, counters ? counters + 1 : nullptr, rank, world,
+                                          rows, k, st(s));
+    if (e != KCB_SUCCESS) return e;
+    if (ev_after && cudaEventRecord(static_cast<cudaEvent_t>(ev_after), st(s)) != cudaSuccess) return KCB_INVALID_RESOURCE_HANDLE;
+    return KCB_SUCCESS;
+}
+
+unsigned kcb_peer_timeouts(void) { return peer_timeouts() + tma_timeouts(); }
 
 }  // extern "C"

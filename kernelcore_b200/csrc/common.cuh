@@ -70,6 +70,25 @@ __device__ __forceinline__ unsigned f32_to_f16_bits(float x) {
     return sign | (static_cast<unsigned>(__half_as_ushort(__float2half_rn(a))) & 0x7fffu);
 }
 
+// Quantizes the 32 values held one per lane into Q8 block `b` of (xq, xd) -- quantize_q8x4's block.
+__device__ __forceinline__ void quantize_block_warp(float v, int* xq, float* xd, int b, int lane) {
+    const float amax = warp_max(fabsf(v));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    const float t = __fmul_rn(v, id);
+    int q = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
+    q = max(-127, min(127, q));
+    const int sum = warp_sum_i(q);
+    unsigned word = (static_cast<unsigned>(q) & 255u) << (8 * (lane & 3));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    if ((lane & 3) == 0) xq[b * 8 + (lane >> 2)] = static_cast<int>(word);
+    if (lane == 0) {
+        xd[b * 2] = d;
+        xd[b * 2 + 1] = static_cast<float>(sum);
+    }
+}
+
 // ---- mbarrier + bulk-copy (TMA) primitives ---------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {

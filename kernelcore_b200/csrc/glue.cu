@@ -37,25 +37,6 @@ __device__ __forceinline__ float rinv_rms(float sumsq, int n, float eps) {  // 1
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, static_cast<float>(n)), eps)));
 }
 
-// Quantizes the 32 values held one per lane into Q8 block `b` of (xq, xd) -- quantize_q8x4's block.
-__device__ __forceinline__ void quantize_block_warp(float v, int* xq, float* xd, int b, int lane) {
-    const float amax = warp_max(fabsf(v));
-    const float d = __fdiv_rn(amax, 127.0f);
-    const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-    const float t = __fmul_rn(v, id);
-    int q = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
-    q = max(-127, min(127, q));
-    const int sum = warp_sum_i(q);
-    unsigned word = (static_cast<unsigned>(q) & 255u) << (8 * (lane & 3));
-    word |= __shfl_xor_sync(0xffffffffu, word, 1);
-    word |= __shfl_xor_sync(0xffffffffu, word, 2);
-    if ((lane & 3) == 0) xq[b * 8 + (lane >> 2)] = static_cast<int>(word);
-    if (lane == 0) {
-        xd[b * 2] = d;
-        xd[b * 2 + 1] = static_cast<float>(sum);
-    }
-}
-
 __device__ __forceinline__ float swiglu(float g, float u) {  // g / (1 + 2^(-g log2 e)) * u
     const float e = exp2f(__fmul_rn(-g, 1.44269504f));
     return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, e)), u);

@@ -631,6 +631,18 @@ __global__ void __launch_bounds__(kThreads) matvec_q6k_q8_reg_kernel(const uint8
 // consumed.  Every mbarrier wait is bounded; on expiry the CTA records it in g_tma_timeouts and leaves.
 __device__ unsigned g_tma_timeouts = 0;
 
+// Other ranks' gather buffers (already offset to this rank's first row), for the fused all-gather epilogue.
+struct PeerOut {
+    float* y[7] = {};
+    int n = 0;
+    // optional step barrier run by the last CTA to finish (world > 1): flags[i] = rank i's counters
+    unsigned* flags[8] = {};
+    unsigned* epoch_counter = nullptr;  // local device word, incremented once per launch
+    unsigned* done_counter = nullptr;   // local device word, CTAs finished in this launch
+    int rank = 0, world = 1;
+};
+constexpr int kProlBytes = 5120;  // shared-memory room for an in-kernel Q8 copy of x (k <= 4096)
+
 constexpr int kTmaMaxStages = 8;
 
 template <bool kQ6, int ITERS, int TR, int RPW>
@@ -638,10 +650,11 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
                                                                              const int* __restrict__ xq,
                                                                              const float* __restrict__ xd,
                                                                              float* __restrict__ y, int rows, int nsb,
-                                                                             int stages) {
+                                                                             int stages, PeerOut peers,
+                                                                             const float* __restrict__ xf32) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-    uint8_t* buf = smem + 128;
+    uint8_t* buf = smem + 128 + kProlBytes;
     constexpr int kBlk = kQ6 ? kQ6KBlock : kQ4KBlock;
     constexpr int NW = TR / RPW;  // warps per CTA; warp w owns tile rows w, w + NW, ...
     const uint32_t stage_bytes = static_cast<uint32_t>(TR) * nsb * kBlk;
@@ -677,6 +690,28 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
     if (threadIdx.x == 0)
         for (int i = 0; i < stages && i < my_tiles; ++i) issue(i);
 
+    // fp32 activations: every CTA quantizes x itself (quantize_q8x4's arithmetic, one warp per block of 32) while
+    // its first weight tiles are in flight; saves a launch and the scratch round trip.
+    if (xf32) {
+        int* sxq = reinterpret_cast<int*>(smem + 128);
+        float* sxd = reinterpret_cast<float*>(sxq + nsb * 64);
+        constexpr int kMaxPerWarp = (16 * 8 + NW - 1) / NW;  // nsb <= 16
+        float xv[kMaxPerWarp];
+#pragma unroll
+        for (int i = 0; i < kMaxPerWarp; ++i) {  // all loads first: one memory latency, not one per block
+            const int b = warp + i * NW;
+            xv[i] = b < nsb * 8 ? __ldg(xf32 + b * 32 + lane) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < kMaxPerWarp; ++i) {
+            const int b = warp + i * NW;
+            if (b < nsb * 8) quantize_block_warp(xv[i], sxq, sxd, b, lane);
+        }
+        __syncthreads();
+        xq = sxq;
+        xd = sxd;
+    }
+
     // ---- this lane's slice of the activations, in registers ----
     uint4 xa[ITERS], xb[ITERS];
     float4 dd[ITERS];
@@ -698,10 +733,10 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
         if (!ok[it]) continue;
         if (kQ6) {
             const int b = sb * 8 + 4 * n + a;
-            xa[it] = __ldg(reinterpret_cast<const uint4*>(xq + b * 8 + 4 * h));
-            xb[it] = __ldg(reinterpret_cast<const uint4*>(xq + (b + 2) * 8 + 4 * h));
-            dd[it].x = __ldg(xd + 2 * b);
-            dd[it].z = __ldg(xd + 2 * (b + 2));
+            xa[it] = *reinterpret_cast<const uint4*>(xq + b * 8 + 4 * h);
+            xb[it] = *reinterpret_cast<const uint4*>(xq + (b + 2) * 8 + 4 * h);
+            dd[it].x = xd[2 * b];
+            dd[it].z = xd[2 * (b + 2)];
             int s0 = 0, s1 = 0;
             s0 = __dp4a(0x01010101, static_cast<int>(xa[it].x), s0);
             s0 = __dp4a(0x01010101, static_cast<int>(xa[it].y), s0);
@@ -715,9 +750,9 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
             sb2[it] = 32 * s1;
         } else {
             const int b = sb * 8 + 2 * j;
-            xa[it] = __ldg(reinterpret_cast<const uint4*>(xq + b * 8 + 4 * h));
-            xb[it] = __ldg(reinterpret_cast<const uint4*>(xq + b * 8 + 8 + 4 * h));
-            const float4 t = __ldg(reinterpret_cast<const float4*>(xd + 2 * b));
+            xa[it] = *reinterpret_cast<const uint4*>(xq + b * 8 + 4 * h);
+            xb[it] = *reinterpret_cast<const uint4*>(xq + b * 8 + 8 + 4 * h);
+            const float4 t = *reinterpret_cast<const float4*>(xd + 2 * b);
             dd[it] = make_float4(t.x, h == 0 ? __fmul_rn(t.x, t.y) : 0.f, t.z, h == 0 ? __fmul_rn(t.z, t.w) : 0.f);
         }
     }
@@ -797,10 +832,36 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
         for (int r = 0; r < RPW; ++r) {
             const float v = warp_sum(acc[r]);
             const int row = row0 + warp + r * NW;
-            if (lane == 0 && row < rows) y[row] = v;
+            if (lane == 0 && row < rows) {
+                y[row] = v;
+                // fused all-gather: the same value into every other rank's gather buffer (plain peer stores)
+                for (int p = 0; p < peers.n; ++p) peers.y[p][row] = v;
+            }
         }
         __syncthreads();  // every warp is done with stage s
         if (threadIdx.x == 0 && i + stages < my_tiles) issue(i + stages);
+    }
+    // Step barrier across GPUs, run once per launch by whichever CTA finishes last: release this launch's epoch
+    // into every rank's flag array, then wait (bounded) until every rank's epoch has arrived here.
+    if (peers.world > 1 && threadIdx.x == 0) {
+        __threadfence_system();  // this CTA's peer stores before its arrival
+        if (atomicAdd(peers.done_counter, 1u) == gridDim.x - 1) {
+            atomicExch(peers.done_counter, 0u);
+            const unsigned epoch = atomicAdd(peers.epoch_counter, 1u) + 1u;
+            __threadfence_system();
+            for (int r = 0; r < peers.world; ++r)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[r] + peers.rank), "r"(epoch) : "memory");
+            for (int r = 0; r < peers.world; ++r) {
+                bool arrived = false;
+                for (int it = 0; it < (1 << 22) && !arrived; ++it) {
+                    unsigned v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(peers.flags[peers.rank] + r) : "memory");
+                    arrived = static_cast<int>(v - epoch) >= 0;
+                    if (!arrived) __nanosleep(64);
+                }
+                if (!arrived) atomicAdd(&g_tma_timeouts, 1u);
+            }
+        }
     }
 }
 
@@ -810,41 +871,44 @@ int env_int(const char* name, int dflt) {
 }
 
 template <bool kQ6, int ITERS, int TR, int RPW>
-int launch_tma_cfg(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s) {
+int launch_tma_cfg(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s, const PeerOut& peers,
+                   const float* xf32) {
     auto kern = matvec_kq_q8_tma_kernel<kQ6, ITERS, TR, RPW>;
     const size_t stage_bytes = static_cast<size_t>(TR) * nsb * (kQ6 ? kQ6KBlock : kQ4KBlock);
-    int stages = static_cast<int>((200 * 1024) / stage_bytes);
+    int stages = static_cast<int>((226 * 1024 - 128 - kProlBytes) / stage_bytes);  // 227 KB of shared memory per CTA on sm_100
     if (stages > kTmaMaxStages) stages = kTmaMaxStages;
     static const int forced = env_int("KCB_TMA_STAGES", 0);
     if (forced > 0 && forced < stages) stages = forced;
     if (stages < 2) return KCB_UNSUPPORTED_OPERATION;
-    const size_t smem = 128 + stages * stage_bytes;
+    const size_t smem = 128 + kProlBytes + stages * stage_bytes;
     static bool attr_set = false;  // per instantiation
     if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess)
             return KCB_LAUNCH_FAILURE;
         attr_set = true;
     }
     const int ntiles = (rows + TR - 1) / TR;
     const int grid = ntiles < kSmCount ? ntiles : kSmCount;
-    kern<<<grid, TR / RPW * 32, smem, s>>>(wb, xq, xd, y, rows, nsb, stages);
+    kern<<<grid, TR / RPW * 32, smem, s>>>(wb, xq, xd, y, rows, nsb, stages, peers, xf32);
     return launch_status();
 }
 
 template <bool kQ6, int ITERS>
-int launch_tma(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s) {
+int launch_tma(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s, const PeerOut& peers,
+               const float* xf32) {
     // Measured on B200 (lm_head 128256 x 3072 Q6_K): 16 warps x 2 interleaved rows 94 % of the copy
     // roofline; 32 warps x 1 row 87 %; 16 warps x 1 row 82 %; 8 warps x 2 rows 71 %.
-    return launch_tma_cfg<kQ6, ITERS, 32, 2>(wb, xq, xd, y, rows, nsb, s);
+    return launch_tma_cfg<kQ6, ITERS, 32, 2>(wb, xq, xd, y, rows, nsb, s, peers, xf32);
 }
 
 template <bool kQ6>
-int launch_tma_iters(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s) {
+int launch_tma_iters(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s,
+                     const PeerOut& peers = PeerOut{}, const float* xf32 = nullptr) {
     switch ((nsb + 3) / 4) {
-    case 1: return launch_tma<kQ6, 1>(wb, xq, xd, y, rows, nsb, s);
-    case 2: return launch_tma<kQ6, 2>(wb, xq, xd, y, rows, nsb, s);
-    case 3: return launch_tma<kQ6, 3>(wb, xq, xd, y, rows, nsb, s);
-    case 4: return launch_tma<kQ6, 4>(wb, xq, xd, y, rows, nsb, s);
+    case 1: return launch_tma<kQ6, 1>(wb, xq, xd, y, rows, nsb, s, peers, xf32);
+    case 2: return launch_tma<kQ6, 2>(wb, xq, xd, y, rows, nsb, s, peers, xf32);
+    case 3: return launch_tma<kQ6, 3>(wb, xq, xd, y, rows, nsb, s, peers, xf32);
+    case 4: return launch_tma<kQ6, 4>(wb, xq, xd, y, rows, nsb, s, peers, xf32);
     }
     return KCB_UNSUPPORTED_OPERATION;
 }
@@ -885,6 +949,91 @@ int grid_for_rows(int rows, int rpw) {
 bool shape_ok(int rows, int k) { return rows >= 0 && k > 0 && k % 256 == 0 && k <= 32768; }
 
 }  // namespace
+
+// ---- row-sharded matvec fused with its all-gather, and the cross-GPU step barrier --------------------
+// One rank per GPU.  Rank r owns rows [r0, r0 + rows) of the matrix; its kernel writes every result both into
+// its own full-length y and, with plain stores through NVLink peer mappings, into every other rank's y at the
+// same offset -- the transfer rides on the matvec's own stores instead of a separate collective.
+// peer_barrier then makes the step visible: each rank releases `epoch` into its slot of every peer's flag
+// array and waits (bounded) until all its own slots reach `epoch`.
+__device__ unsigned g_peer_timeouts = 0;
+
+struct PeerFlags {
+    unsigned* f[8] = {};
+};
+
+__global__ void peer_barrier_kernel(PeerFlags flags, int rank, int world, unsigned epoch, unsigned* epoch_counter) {
+    __shared__ unsigned next;
+    if (epoch_counter) {  // device-side step counter: the same launch can be replayed (CUDA graphs, one call per step)
+        if (threadIdx.x == 0) next = atomicAdd(epoch_counter, 1u) + 1u;
+        __syncthreads();
+        epoch = next;
+    }
+    const int r = threadIdx.x;
+    if (r >= world) return;
+    __threadfence_system();  // order this GPU's earlier peer stores before the flag
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.f[r] + rank), "r"(epoch) : "memory");
+    const unsigned* mine = flags.f[rank] + r;
+    for (int i = 0; i < (1 << 22); ++i) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if (static_cast<int>(v - epoch) >= 0) return;
+        __nanosleep(64);
+    }
+    atomicAdd(&g_peer_timeouts, 1u);  // a peer never arrived: report and leave, nothing spins forever
+}
+
+unsigned peer_timeouts() {
+    unsigned v = 0;
+    cudaMemcpyFromSymbol(&v, g_peer_timeouts, sizeof v);
+    return v;
+}
+
+int peer_barrier(unsigned* const* flags, int rank, int world, unsigned epoch, unsigned* epoch_counter, cudaStream_t s) {
+    if (!flags || world < 1 || world > 8 || rank < 0 || rank >= world) return KCB_INVALID_VALUE;
+    PeerFlags pf;
+    for (int i = 0; i < world; ++i) {
+        if (!flags[i]) return KCB_INVALID_VALUE;
+        pf.f[i] = flags[i];
+    }
+    peer_barrier_kernel<<<1, 32, 0, s>>>(pf, rank, world, epoch, epoch_counter);
+    return launch_status();
+}
+
+int matvec_q6k_q8_gather(const void* w, const int* xq, const float* xd, float* y_local, float* const* y_peers, int npeers, int rows,
+                         int k, cudaStream_t s) {
+    if (!shape_ok(rows, k) || !w || !xq || !xd || !y_local || npeers < 0 || npeers > 7 || (npeers && !y_peers)) return KCB_INVALID_VALUE;
+    if (rows == 0) return KCB_SUCCESS;
+    const int nsb = k / 256;
+    if (!(rows % 8 == 0 && nsb <= 16)) return KCB_UNSUPPORTED_OPERATION;
+    PeerOut po;
+    po.n = npeers;
+    for (int i = 0; i < npeers; ++i) {
+        if (!y_peers[i]) return KCB_INVALID_VALUE;
+        po.y[i] = y_peers[i];
+    }
+    return launch_tma_iters<true>(static_cast<const uint8_t*>(w), xq, xd, y_local, rows, nsb, s, po);
+}
+
+// Row shard of a Q6_K matrix times fp32 x in ONE launch: in-kernel activation quantization, matvec, stores into
+// the other ranks' outputs and the cross-GPU step barrier (world > 1).
+int matvec_q6k_f32x_sharded(const void* w, const float* x, float* y_local, float* const* y_peers, int npeers, unsigned* const* flags,
+                            unsigned* epoch_counter, unsigned* done_counter, int rank, int world, int rows, int k, cudaStream_t s) {
+    if (!shape_ok(rows, k) || !w || !x || !y_local || npeers < 0 || npeers > 7 || (npeers && !y_peers) || world < 1 || world > 8)
+        return KCB_INVALID_VALUE;
+    if (rows == 0) return KCB_SUCCESS;
+    const int nsb = k / 256;
+    if (!(rows % 8 == 0 && nsb <= 16)) return KCB_UNSUPPORTED_OPERATION;
+    PeerOut po;
+    po.n = npeers;
+    for (int i = 0; i < npeers; ++i) po.y[i] = y_peers[i];
+    if (world > 1) {
+        if (!flags || !epoch_counter || !done_counter || rank < 0 || rank >= world) return KCB_INVALID_VALUE;
+        for (int i = 0; i < world; ++i) po.flags[i] = flags[i];
+        po.epoch_counter = epoch_counter, po.done_counter = done_counter, po.rank = rank, po.world = world;
+    }
+    return launch_tma_iters<true>(static_cast<const uint8_t*>(w), nullptr, nullptr, y_local, rows, nsb, s, po, x);
+}
 
 unsigned tma_timeouts() {
     unsigned v = 0;

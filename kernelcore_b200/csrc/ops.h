@@ -14,7 +14,13 @@ int matvec_q4k_f32(const void* w, const float* x, float* y, int rows, int k, cud
 int matvec_q6k_f32(const void* w, const float* x, float* y, int rows, int k, cudaStream_t s);
 int dequant_q4k(const void* w, float* out, int rows, int k, cudaStream_t s);
 int dequant_q6k(const void* w, float* out, int rows, int k, cudaStream_t s);
-unsigned tma_timeouts();  // bounded mbarrier waits that expired since load (synchronous read)
+unsigned tma_timeouts();
+int matvec_q6k_f32x_sharded(const void* w, const float* x, float* y_local, float* const* y_peers, int npeers, unsigned* const* flags,
+                            unsigned* epoch_counter, unsigned* done_counter, int rank, int world, int rows, int k, cudaStream_t s);
+unsigned peer_timeouts();
+int peer_barrier(unsigned* const* flags, int rank, int world, unsigned epoch, unsigned* epoch_counter, cudaStream_t s);
+int matvec_q6k_q8_gather(const void* w, const int* xq, const float* xd, float* y_local, float* const* y_peers, int npeers, int rows,
+                         int k, cudaStream_t s);  // bounded mbarrier waits that expired since load (synchronous read)
 int q6k_convert(const void* src, void* dst, int rows, int k, int to_planes, cudaStream_t s);
 
 // quantize.cu
