@@ -241,20 +241,23 @@ def run_ours(args):
     fence()
     # The timed region replays a CUDA graph of NMAT steps (one launch each, one per rotating matrix): at 30-60 us
     # per step the Python call overhead would otherwise be what is measured, most of all at N > 1.
-    reps, tail_steps = divmod(args.steps, NMAT)
+    use_graph = world == 1 or fused is not None  # the NCCL fallback is launched step by step, not captured
+    reps, tail_steps = divmod(args.steps, NMAT) if use_graph else (0, args.steps)
     steps_timed = args.steps
-    gstream = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(gstream):
-        step(0)
-        torch.cuda.synchronize()
-        with torch.cuda.graph(graph, stream=gstream):
-            for i in range(NMAT):
-                step(i)
-    fence()
-    for _ in range(3):
-        graph.replay()
-    fence()
+    graph = None
+    if use_graph:
+        gstream = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(gstream):
+            step(0)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=gstream):
+                for i in range(NMAT):
+                    step(i)
+        fence()
+        for _ in range(3):
+            graph.replay()
+        fence()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
     if rank == 0:
