@@ -396,6 +396,55 @@ __global__ void flash_attn_f16_kernel(const float* __restrict__ q, const unsigne
     }
 }
 
+// The four-launch form of the same attention, kept because the reference's graph code launches them by name
+// (kernels/llm/fa_scores.cu:41-99, fa_max.cu:14-25, fa_exp.cu:15-24, fa_values.cu:36-95): scores with mask, row
+// maxima, in-place exp2, and the weighted V sum divided by the row sum.  Sequential sums in the reference's order.
+__global__ void fa_scores_kernel(const float* __restrict__ q, const unsigned* __restrict__ k, const unsigned short* __restrict__ mask,
+                                 float* s, FaParams d, float scale) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<long long>(d.H) * d.N * d.T) return;
+    const int t = static_cast<int>(idx % d.T), i = static_cast<int>((idx / d.T) % d.N), h = static_cast<int>(idx / (static_cast<long long>(d.T) * d.N));
+    const unsigned* kr = k + static_cast<size_t>(t) * d.k_row + static_cast<size_t>(h / d.group) * d.k_head;
+    const float* qh = q + static_cast<size_t>(i) * d.q_tok + static_cast<size_t>(h) * d.q_head;
+    float a = 0.0f;
+    for (int j = 0; j < d.D / 2; ++j) {
+        const unsigned w = kr[j];
+        a = __fadd_rn(a, __fadd_rn(__fmul_rn(qh[2 * j], half_bits_to_float(w & 0xFFFFu)), __fmul_rn(qh[2 * j + 1], half_bits_to_float(w >> 16))));
+    }
+    const float mv = d.has_mask ? half_bits_to_float(mask[static_cast<size_t>(i) * d.m_row * 2 + t]) : 0.0f;
+    s[(static_cast<size_t>(h) * d.N + i) * d.tp + t] = __fadd_rn(__fmul_rn(a, scale), mv);
+}
+__global__ void fa_max_kernel(const float* __restrict__ s, float* m, FaParams d) {
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= d.H * d.N) return;
+    const float* sr = s + static_cast<size_t>(row) * d.tp;
+    float mx = sr[0];
+    for (int t = 1; t < d.T; ++t) mx = fmaxf(mx, sr[t]);
+    m[row] = mx;
+}
+__global__ void fa_exp_kernel(float* s, const float* __restrict__ m, FaParams d) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<long long>(d.H) * d.N * d.T) return;
+    const int t = static_cast<int>(idx % d.T);
+    const long long row = idx / d.T;
+    float* p = s + row * d.tp + t;
+    *p = exp2f(__fmul_rn(__fsub_rn(*p, m[row]), 1.44269504f));
+}
+__global__ void fa_values_kernel(const float* __restrict__ p, const unsigned* __restrict__ v, float* out, FaParams d) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<long long>(d.N) * d.H * d.D) return;
+    const int dd = static_cast<int>(idx % d.D), h = static_cast<int>((idx / d.D) % d.H), i = static_cast<int>(idx / (static_cast<long long>(d.D) * d.H));
+    const float* pr = p + (static_cast<size_t>(h) * d.N + i) * d.tp;
+    const unsigned short* vp = reinterpret_cast<const unsigned short*>(v) + static_cast<size_t>(h / d.group) * d.v_head * 2 + dd;
+    float a = 0.0f, sum = 0.0f;
+    for (int t = 0; t < d.T; ++t) {
+        const float w = pr[t];
+        a = __fadd_rn(a, __fmul_rn(w, half_bits_to_float(vp[static_cast<size_t>(t) * d.v_row * 2])));
+        sum = __fadd_rn(sum, w);
+    }
+    out[idx] = __fdiv_rn(a, sum);
+}
+
 inline unsigned blocks_for(size_t n, int per) { return static_cast<unsigned>((n + per - 1) / per); }
 
 }  // namespace
@@ -518,6 +567,37 @@ int flash_attn_f16(const float* q, const void* k, const void* v, const void* mas
     }
     flash_attn_f16_kernel<<<d.N * d.H, 256, smem, s>>>(q, static_cast<const unsigned*>(k), static_cast<const unsigned*>(v),
                                                          static_cast<const unsigned*>(mask), out, d, scale);
+    return launch_status();
+}
+
+// which: 0 fa_scores, 1 fa_max, 2 fa_exp, 3 fa_values.  Pointers not used by a stage may be null.
+int fa_stage(int which, const float* q, const void* k, const void* v, const void* mask, float* s_buf, float* m_buf, float* out,
+             const int* dims15, float scale, cudaStream_t s) {
+    if (!dims15) return KCB_INVALID_VALUE;
+    FaParams d;
+    int* f = reinterpret_cast<int*>(&d);
+    for (int i = 0; i < 15; ++i) f[i] = dims15[i];
+    if (d.H <= 0 || d.T <= 0 || d.D <= 0 || d.D % 2 || d.group <= 0 || d.N <= 0 || d.tp < d.T) return KCB_INVALID_VALUE;
+    const size_t cells = static_cast<size_t>(d.H) * d.N * d.T;
+    switch (which) {
+    case 0:
+        if (!q || !k || !s_buf || (d.has_mask && !mask)) return KCB_INVALID_VALUE;
+        fa_scores_kernel<<<blocks_for(cells, 256), 256, 0, s>>>(q, static_cast<const unsigned*>(k), static_cast<const unsigned short*>(mask), s_buf, d, scale);
+        break;
+    case 1:
+        if (!s_buf || !m_buf) return KCB_INVALID_VALUE;
+        fa_max_kernel<<<blocks_for(static_cast<size_t>(d.H) * d.N, 64), 64, 0, s>>>(s_buf, m_buf, d);
+        break;
+    case 2:
+        if (!s_buf || !m_buf) return KCB_INVALID_VALUE;
+        fa_exp_kernel<<<blocks_for(cells, 256), 256, 0, s>>>(s_buf, m_buf, d);
+        break;
+    case 3:
+        if (!s_buf || !v || !out) return KCB_INVALID_VALUE;
+        fa_values_kernel<<<blocks_for(static_cast<size_t>(d.N) * d.H * d.D, 128), 128, 0, s>>>(s_buf, static_cast<const unsigned*>(v), out, d);
+        break;
+    default: return KCB_INVALID_VALUE;
+    }
     return launch_status();
 }
 

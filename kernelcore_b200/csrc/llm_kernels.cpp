@@ -301,6 +301,52 @@ int k_flash_attn_f16(const void* p, const RangeChecker& rc, cudaStream_t s) {
     faDimsInts(d, dims);
     return flash_attn_f16(a.q, a.k, a.v, a.mask, a.out, dims, a.scale, s);
 }
+// fa_scores / fa_max / fa_exp / fa_values: score rows s[H*N][tp], maxima m[H*N] (llm/llm_kernels.hpp:339-366)
+int k_fa_scores(const void* p, const RangeChecker& rc, cudaStream_t s) {
+    const auto& a = *static_cast<const FaScoresArgs*>(p);
+    if (!fa_shape_ok(a.d)) return KCB_INVALID_VALUE;
+    const FaDims& d = a.d;
+    TRY(rc.check(a.q, f32(static_cast<long long>(d.N - 1) * d.q_tok + static_cast<long long>(d.H - 1) * d.q_head + d.D), "q"));
+    TRY(fa_check_kv(d, a.k, nullptr, rc));
+    if (d.has_mask) TRY(rc.check(a.mask, i32(static_cast<long long>(d.N - 1) * d.m_row + (d.T + 1) / 2), "mask"));
+    TRY(rc.check(a.s, f32(static_cast<long long>(d.H) * d.N * d.tp), "s"));
+    TRY(rc.check(a.dims, kFaDims * sizeof(int), "dims"));
+    int dims[kFaDims];
+    faDimsInts(d, dims);
+    return fa_stage(0, a.q, a.k, nullptr, a.mask, a.s, nullptr, nullptr, dims, a.scale, s);
+}
+int k_fa_max(const void* p, const RangeChecker& rc, cudaStream_t s) {
+    const auto& a = *static_cast<const FaMaxArgs*>(p);
+    if (!fa_shape_ok(a.d)) return KCB_INVALID_VALUE;
+    TRY(rc.check(a.s, f32(static_cast<long long>(a.d.H) * a.d.N * a.d.tp), "s"));
+    TRY(rc.check(a.m, f32(static_cast<long long>(a.d.H) * a.d.N), "m"));
+    TRY(rc.check(a.dims, kFaDims * sizeof(int), "dims"));
+    int dims[kFaDims];
+    faDimsInts(a.d, dims);
+    return fa_stage(1, nullptr, nullptr, nullptr, nullptr, const_cast<float*>(a.s), a.m, nullptr, dims, 0.f, s);
+}
+int k_fa_exp(const void* p, const RangeChecker& rc, cudaStream_t s) {
+    const auto& a = *static_cast<const FaExpArgs*>(p);
+    if (!fa_shape_ok(a.d)) return KCB_INVALID_VALUE;
+    TRY(rc.check(a.s, f32(static_cast<long long>(a.d.H) * a.d.N * a.d.tp), "s"));
+    TRY(rc.check(a.m, f32(static_cast<long long>(a.d.H) * a.d.N), "m"));
+    TRY(rc.check(a.dims, kFaDims * sizeof(int), "dims"));
+    int dims[kFaDims];
+    faDimsInts(a.d, dims);
+    return fa_stage(2, nullptr, nullptr, nullptr, nullptr, a.s, const_cast<float*>(a.m), nullptr, dims, 0.f, s);
+}
+int k_fa_values(const void* p, const RangeChecker& rc, cudaStream_t s) {
+    const auto& a = *static_cast<const FaValuesArgs*>(p);
+    if (!fa_shape_ok(a.d)) return KCB_INVALID_VALUE;
+    const FaDims& d = a.d;
+    TRY(rc.check(a.p, f32(static_cast<long long>(d.H) * d.N * d.tp), "p"));
+    TRY(fa_check_kv(d, nullptr, a.v, rc));
+    TRY(rc.check(a.out, f32(static_cast<long long>(d.N) * d.H * d.D), "out"));
+    TRY(rc.check(a.dims, kFaDims * sizeof(int), "dims"));
+    int dims[kFaDims];
+    faDimsInts(d, dims);
+    return fa_stage(3, nullptr, nullptr, a.v, nullptr, const_cast<float*>(a.p), nullptr, a.out, dims, 0.f, s);
+}
 int k_unbuilt(const void*, const RangeChecker&, cudaStream_t) { return KCB_UNSUPPORTED_OPERATION; }
 
 const KernelDesc kTable[] = {
@@ -340,6 +386,10 @@ const KernelDesc kTable[] = {
     {"attn_values", &k_attn_values},
     {"set_rows_f16", &k_set_rows_f16},
     {"flash_attn_f16", &k_flash_attn_f16},
+    {"fa_scores", &k_fa_scores},
+    {"fa_max", &k_fa_max},
+    {"fa_exp", &k_fa_exp},
+    {"fa_values", &k_fa_values},
     // Names of the reference's table that this build does not implement yet: launching them reports
     // UnsupportedOperation instead of KernelNotFound.
     {"matvec_q8", &k_unbuilt},
@@ -348,10 +398,7 @@ const KernelDesc kTable[] = {
     {"matvec_q4x8_q8", &k_unbuilt},
     {"matvec_q4x8_q8x2", &k_unbuilt},
     {"matmul_f16", &k_unbuilt},
-    {"fa_scores", &k_unbuilt},
-    {"fa_max", &k_unbuilt},
-    {"fa_exp", &k_unbuilt},
-    {"fa_values", &k_unbuilt},
+
 };
 constexpr int kCount = sizeof(kTable) / sizeof(kTable[0]);
 

@@ -61,4 +61,7 @@ int set_rows_f16(const float* src, const long long* idx, void* dst, int pairs, i
 int flash_attn_f16(const float* q, const void* k, const void* v, const void* mask, float* out, const int* dims15,
                    float scale, cudaStream_t s);
 
+int fa_stage(int which, const float* q, const void* k, const void* v, const void* mask, float* s_buf, float* m_buf, float* out,
+             const int* dims15, float scale, cudaStream_t s);
+
 }  // namespace kcb

@@ -184,3 +184,40 @@ def test_device_reset_frees_everything(runtime):
     assert L.kcb_device_reset() == 0
     assert L.kcb_check_range(d, C.c_size_t(4)) == 5
     assert L.kcb_tma_timeouts() == 0
+
+
+def test_four_launch_flash_attention_by_name(runtime, golden):
+    """fa_scores -> fa_max -> fa_exp -> fa_values launched by name with the reference's FaDims structs, against the
+    reference's flashAttnF16 output (tests/test_llm_kernels.cpp:741-794, relDiff < 2e-6)."""
+    from helpers import pad8, rel_diff
+    g = golden("glue")
+
+    class FaDims(C.Structure):
+        _fields_ = [(n, C.c_int) for n in ("H", "T", "D", "group", "tp", "k_row", "k_head", "v_row", "v_head", "N", "q_tok",
+                                           "q_head", "m_row", "has_mask", "H_kv")]
+
+    class FaScoresArgs(C.Structure):
+        _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("mask", C.c_void_p), ("s", C.c_void_p), ("dims", C.c_void_p),
+                    ("d", FaDims), ("scale", C.c_float)]
+
+    class FaMaxArgs(C.Structure):
+        _fields_ = [("s", C.c_void_p), ("m", C.c_void_p), ("dims", C.c_void_p), ("d", FaDims)]
+
+    class FaValuesArgs(C.Structure):
+        _fields_ = [("p", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p), ("dims", C.c_void_p), ("d", FaDims)]
+
+    for tag in "abc":
+        H, Hkv, D, T, N, mask = (int(v) for v in g[f"fa_{tag}_dims"])
+        tp = pad8(T)
+        d = FaDims(H, T, D, H // Hkv, tp, Hkv * D // 2, D // 2, Hkv * D // 2, D // 2, N, H * D, D, tp // 2, mask, Hkv)
+        dq, dk, dv = upload(g[f"fa_{tag}_q"]), upload(g[f"fa_{tag}_k"]), upload(g[f"fa_{tag}_v"])
+        dm, ddims = upload(g[f"fa_{tag}_mask"]), upload(np.zeros(15, np.int32))
+        ds, dmx, dout = dmalloc(H * N * tp * 4), dmalloc(H * N * 4), dmalloc(N * H * D * 4)
+        a = FaScoresArgs(dq, dk, dm, ds, ddims, d, float(D) ** -0.5)
+        assert L.kcb_launch_kernel(b"fa_scores", C.byref(a), None) == 0, L.kcb_last_error_detail()
+        b = FaMaxArgs(ds, dmx, ddims, d)
+        assert L.kcb_launch_kernel(b"fa_max", C.byref(b), None) == 0
+        assert L.kcb_launch_kernel(b"fa_exp", C.byref(b), None) == 0      # FaExpArgs has the same layout
+        c = FaValuesArgs(ds, dv, dout, ddims, d)
+        assert L.kcb_launch_kernel(b"fa_values", C.byref(c), None) == 0
+        assert rel_diff(download(dout, (N, H, D), np.float32), g[f"fa_{tag}_out"]) < 2e-6
