@@ -346,7 +346,7 @@ def run_ours(args):
         torch.cuda.empty_cache()
         line["extra"] = {"q4k_matvec_config0": q4k_config0(torch, kquant, synth, peak),
                          "q4k_matmul_config2": matmul_bench(),
-                         "decode_llama32_3b": decode_bench(640, 512, 128, peak)}
+                         "decode_llama32_3b": decode_bench(640, 512, 128, peak)[0]}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -423,44 +423,79 @@ def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5):
     return out
 
 
-def decode_bench(max_ctx, n_prompt, n_gen, peak):
-    """BASELINE configs[3]: random-init Llama-3.2-3B-architecture model, Q4_K_M mix, batch 1, fp16 KV cache, greedy.
-    The prompt is processed token by token through the same graph (no batched prefill yet)."""
+def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b"):
+    """BASELINE configs[3] (or [4] with model="qwen3_8b"): random-init model, Q4_K_M mix, batch 1, fp16 KV cache,
+    greedy.  The prompt is processed token by token through the same graph (no batched prefill yet).
+    Under torchrun (WORLD_SIZE > 1) the ranks run the tensor-parallel decoder: heads, FFN rows and vocabulary rows
+    sharded, partial hidden vectors summed inside the norm kernels over NVLink peer loads; times are the max over
+    ranks of device-side event times."""
     import torch
 
     from kernelcore_b200 import decoder, tiny_model as tm
-    shape = tm.llama32_3b(max_ctx)
-    d = decoder.FastDecoder(shape, tm.build(shape, seed=0))
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    shape = (tm.qwen3_8b if model == "qwen3_8b" else tm.llama32_3b)(max_ctx)
+    tp = None
+    if world > 1:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        dist.init_process_group("nccl", device_id=dev)
+        area = symm_mem.empty(decoder.FastDecoder.tp_shared_bytes(shape), dtype=torch.uint8, device=dev)
+        area.zero_()
+        handle = symm_mem.rendezvous(area, dist.group.WORLD.group_name)
+        torch.cuda.synchronize()
+        dist.barrier()
+        tp = (rank, world, list(handle.buffer_ptrs))
+    d = decoder.FastDecoder(shape, tm.build(shape, seed=0), tp=tp)
     prompt = np.random.default_rng(1).integers(0, shape.vocab, n_prompt)
     stream = torch.cuda.ExternalStream(d.cuda_stream)
 
     def timed(steps):
+        if world > 1:
+            torch.cuda.synchronize()
+            dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         d.run(steps)
         e1.record(stream)
         d.sync()
-        return e0.elapsed_time(e1)
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
 
     d.set_prompt(prompt)
     timed(min(4, n_prompt))
     d.set_prompt(prompt)
     ms_p, ms_g = timed(n_prompt), timed(n_gen)
-    out = {"model": shape.name, "prompt_tokens": n_prompt, "generated_tokens": n_gen, "prompt_tok_s": n_prompt / ms_p * 1e3,
+    _, hist, _ = d.read(n_prompt + n_gen, want_logits=False)
+    total_weight_bytes = tm.weight_bytes_per_token(shape)
+    out = {"model": shape.name, "n_gpus": world, "prompt_tokens": n_prompt, "generated_tokens": n_gen, "prompt_tok_s": n_prompt / ms_p * 1e3,
            "decode_tok_s": n_gen / ms_g * 1e3, "us_per_token": ms_g / n_gen * 1e3, "launches_per_token": d.launches_per_token,
-           "weight_bytes_per_token": d.weight_bytes,
-           "frac_of_measured_hbm_weights_only": d.weight_bytes * (n_gen / ms_g * 1e3) / (peak * 1e9),
-           "kv_cache": "fp16", "prompt_mode": "token by token through the decode graph"}
+           "weight_bytes_per_token_this_rank": d.weight_bytes, "weight_bytes_per_token": total_weight_bytes,
+           "frac_of_measured_hbm_weights_only": total_weight_bytes * (n_gen / ms_g * 1e3) / (peak * 1e9 * world),
+           "kv_cache": "fp16", "prompt_mode": "token by token through the decode graph",
+           "picks_digest": int(np.asarray(hist, np.int64).sum() % 1000003),
+           "sharding": "none" if world == 1 else f"tp{world}: heads / FFN rows / vocabulary rows; K-split wo, wd; in-kernel sum over peer loads",
+           "exchange_timeouts": decoder.FastDecoder.tp_timeouts()}
     d.close()
-    return out
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out, rank
 
 
 def run_decode(args):
     peak, _ = measured_peak()
-    out = decode_bench(max(64, args.prompt + args.gen), args.prompt, args.gen, peak)
-    print(json.dumps({"metric": "llama32_3b_decode_tok_s", "value": out["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1,
-                      "higher_is_better": True, "data": "synthetic", "dtype": "int8 dot, fp32 accumulate",
-                      "config": {"workload": "BASELINE configs[3] decode, graph-replayed decoder"}, "detail": out}))
+    out, rank = decode_bench(max(64, args.prompt + args.gen), args.prompt, args.gen, peak, args.model)
+    if rank == 0:
+        cfg = "configs[4]" if args.model == "qwen3_8b" else "configs[3]"
+        print(json.dumps({"metric": f"{args.model}_decode_tok_s", "value": out["decode_tok_s"], "unit": "tokens/s", "n_gpus": out["n_gpus"],
+                          "higher_is_better": True, "scaling": "strong", "data": "synthetic", "dtype": "int8 dot, fp32 accumulate",
+                          "config": {"workload": f"BASELINE {cfg} decode, graph-replayed decoder"}, "detail": out}))
 
 
 def main():
@@ -474,6 +509,7 @@ def main():
                     help="lm_head: the benchmark line; decode: Llama-3.2-3B-shape decode only (profiling, quick checks)")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=128)
+    ap.add_argument("--model", default="llama32_3b", choices=["llama32_3b", "qwen3_8b"], help="--workload decode: which architecture")
     ap.add_argument("--nccl-gather", action="store_true", help="N > 1: use an NCCL all-gather instead of the fused peer stores")
     ap.add_argument("--rows", type=int, default=ROWS, help="shrink the matrix (profiling captures only; the bench line is the default size)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU baseline leg (profiling captures)")

@@ -263,6 +263,19 @@ const char* kcb_model_last_error(void);
  * synchronising; kcb_decoder_read synchronises and copies the last step's logits (vocab floats), the picks
  * made at positions [0, n_history) and the current position.  Any output pointer may be NULL. */
 int kcb_decoder_create(const kcb_model_desc* desc, void** decoder);
+/* Tensor-parallel form over `world` (1..8) ranks, one process per GPU (the reference decodes on one device; its
+ * row-chunked launches, llm/llm_kernels.cpp:281-288, are the split this extends across GPUs).  `desc` is the
+ * whole model on every rank; rank r keeps heads, kv heads, FFN rows and vocabulary rows [r/world, (r+1)/world)
+ * and the matching K windows of the attention-output and FFN-down matrices.  The two partial hidden vectors of
+ * a layer are summed inside the following norm kernel straight out of the ranks' memories (ordinary loads over
+ * NVLink, rank order, bounded waits), the greedy pick likewise over per-rank candidates.  shared[r] is rank r's
+ * exchange area as mapped into this process (kcb_decoder_tp_shared_bytes bytes, peer-accessible, zero-filled
+ * before any rank is created).  Ranks must replay in lockstep: same prompts, same step counts.
+ * kcb_decoder_read returns vocab floats of which only this rank's rows are filled (others 0).
+ * kcb_decoder_tp_timeouts: waits that gave up on this device since the library was loaded (0 = healthy). */
+size_t kcb_decoder_tp_shared_bytes(const kcb_model_desc* desc);
+int kcb_decoder_create_tp(const kcb_model_desc* desc, int rank, int world, void* const* shared, void** decoder);
+unsigned kcb_decoder_tp_timeouts(void);
 int kcb_decoder_set_prompt(void* decoder, const int* tokens, int n, int start_pos);
 int kcb_decoder_run(void* decoder, int steps);
 int kcb_decoder_sync(void* decoder);

@@ -89,6 +89,21 @@ __device__ __forceinline__ void quantize_block_warp(float v, int* xq, float* xd,
     }
 }
 
+// ---- block-wide sum and the RMSNorm factor ---------------------------------------------------------------
+__device__ __forceinline__ float block_sum(float v, float* red) {  // red: >= 32 floats of shared memory
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = lane < nw ? red[lane] : 0.0f;
+    return warp_sum(t);
+}
+__device__ __forceinline__ float rinv_rms(float sumsq, int n, float eps) {  // 1 / sqrt(ss / n + eps)
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, static_cast<float>(n)), eps)));
+}
+
+
 // ---- mbarrier + bulk-copy (TMA) primitives ---------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {

@@ -328,6 +328,138 @@ __global__ void argmax_advance_kernel(const float* __restrict__ cand_v, const in
     }
 }
 
+// ---- tensor parallelism: exchange points of a decode step -------------------------------------------------
+// Heads and FFN rows are sharded over `world` ranks (one process per GPU); the attention-output and FFN-down
+// matrices are split along K, so each rank holds a partial hidden vector at those two points of a layer
+// (the all-reduce boundaries of Megatron-style sharding).  The exchange is fused into the kernel that consumes
+// the sum: it announces this rank's arrival in every rank's flag array, waits (bounded) for all ranks, reads
+// every rank's partial straight out of that rank's memory with ordinary loads over NVLink, and adds them in
+// rank order -- every rank computes the same bits, so the replicated residual stream never diverges.
+// Partials are double-buffered by exchange parity: a rank can be at most one exchange ahead of a peer that is
+// still reading.  Waits give up after a fixed number of polls, count the event and mark the group dead so
+// later waits return at once; nothing spins forever.
+struct TpCtx {
+    float* partial[8] = {};   // rank r: [2][hidden] floats
+    unsigned* flags[8] = {};  // rank r: flags[src] = last exchange number src announced to r
+    float* cand_v[8] = {};    // rank r's argmax candidates
+    int* cand_i[8] = {};
+    unsigned* epoch = nullptr;  // this rank's exchange counter (local memory)
+    int rank = 0, world = 1;
+};
+__device__ unsigned g_tp_timeouts = 0;
+__device__ unsigned g_tp_dead = 0;
+
+__device__ __forceinline__ float ld_peer_f32(const float* p) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ld_peer_s32(const int* p) {
+    int v;
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Every thread of a single-CTA kernel calls this; on return all ranks have entered the same exchange and their
+// earlier kernels' writes are visible to this CTA's sys-scope loads.
+__device__ void tp_arrive_and_wait(const TpCtx& c) {
+    __shared__ unsigned e_sh;
+    if (threadIdx.x == 0) e_sh = atomicAdd(c.epoch, 1u) + 1u;
+    __syncthreads();
+    const unsigned e = e_sh;
+    if (threadIdx.x < static_cast<unsigned>(c.world)) {
+        const int r = threadIdx.x;
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(c.flags[r] + c.rank), "r"(e) : "memory");
+        const unsigned limit = *reinterpret_cast<volatile unsigned*>(&g_tp_dead) ? 1u : (1u << 22);
+        bool arrived = false;
+        for (unsigned i = 0; i < limit; ++i) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(c.flags[c.rank] + r) : "memory");
+            if (static_cast<int>(v - e) >= 0) {
+                arrived = true;
+                break;
+            }
+            if (i > 64) __nanosleep(64);
+        }
+        if (!arrived) {
+            atomicAdd(&g_tp_timeouts, 1u);
+            atomicExch(&g_tp_dead, 1u);
+        }
+    }
+    __syncthreads();
+}
+
+// x += sum over ranks of partial (rank order); then RMSNorm(x) * w quantized to Q8 blocks, as
+// add_norm_q8_fast_kernel does for one GPU.
+__global__ void __launch_bounds__(1024) tp_add_norm_q8_kernel(float* x, TpCtx c, int parity, const float* __restrict__ w, int* xq,
+                                                               float* xd, int n, float eps) {
+    extern __shared__ float sh[];  // n floats
+    __shared__ float red[32];
+    tp_arrive_and_wait(c);
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        float t = ld_peer_f32(c.partial[0] + static_cast<size_t>(parity) * n + j);
+        for (int r = 1; r < c.world; ++r) t = __fadd_rn(t, ld_peer_f32(c.partial[r] + static_cast<size_t>(parity) * n + j));
+        const float v = __fadd_rn(x[j], t);
+        x[j] = v;
+        sh[j] = v;
+        ss += v * v;
+    }
+    const float r = rinv_rms(block_sum(ss, red), n, eps);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int b = warp; b < n / 32; b += nw)
+        quantize_block_warp(__fmul_rn(__fmul_rn(sh[b * 32 + lane], r), w[b * 32 + lane]), xq, xd, b, lane);
+}
+
+// Greedy pick over every rank's candidates (rank r's indices are local to its vocab/world rows), first index
+// wins ties; token history and position advance -- identical on every rank.
+__global__ void tp_argmax_advance_kernel(TpCtx c, int ncand, int rows_per_rank, int* token, int* history, int* pos_p, int max_ctx) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    tp_arrive_and_wait(c);
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < ncand * c.world; i += blockDim.x) {
+        const int r = i / ncand, k = i - r * ncand;
+        const float v = ld_peer_f32(c.cand_v[r] + k);
+        const int ci = ld_peer_s32(c.cand_i[r] + k);
+        const int gi = ci == 0x7fffffff ? ci : ci + r * rows_per_rank;
+        if (v > best || (v == best && gi < idx)) best = v, idx = gi;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) bv[warp] = best, bi[warp] = idx;
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? bv[lane] : -INFINITY;
+        idx = lane < nw ? bi[lane] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+        }
+        if (lane == 0) {
+            const int pos = *pos_p;
+            *token = idx;
+            if (pos < max_ctx) history[pos] = idx;
+            *pos_p = pos + 1;
+        }
+    }
+}
+
+constexpr int kCand = 296;
+constexpr size_t kTpFlagBytes = 256;
+inline size_t tp_shared_bytes(int hidden) {
+    const size_t b = kTpFlagBytes + static_cast<size_t>(2) * hidden * 4 + static_cast<size_t>(kCand) * 8;
+    return (b + 255) / 256 * 256;
+}
+
 struct DMat {
     uint8_t* data = nullptr;
     int rows = 0, k = 0;
@@ -358,28 +490,52 @@ public:
     }
     std::string err_;
 
-    int init(const kcb_model_desc& d) {
-        hidden = d.hidden, inter = d.inter, heads = d.heads, kv_heads = d.kv_heads, hd = d.head_dim, vocab = d.vocab;
+    // rank / world / shared: tensor-parallel placement.  world == 1 ignores `shared`; otherwise shared[r] is rank r's
+    // exchange area (tp_shared_bytes, zero-filled before any rank is created) as mapped into this process.
+    int init(const kcb_model_desc& d, int rank = 0, int world = 1, void* const* shared = nullptr) {
         max_ctx = d.max_ctx, eps = d.eps, log2_base = std::log2(d.rope_base), neox = d.neox, qk_norm = d.qk_norm;
-        if (hidden % 256 || inter % 256 || (heads * hd) % 256 || heads % kv_heads || (hd != 64 && hd != 128) || max_ctx < 1) {
+        hidden = d.hidden, hd = d.head_dim;
+        if (d.hidden % 256 || d.inter % 256 || (d.heads * hd) % 256 || d.heads % d.kv_heads || (hd != 64 && hd != 128) || max_ctx < 1) {
             err_ = "unsupported model shape (hidden, inter, heads*head_dim multiples of 256; head_dim 64 or 128)";
             return KCB_INVALID_VALUE;
         }
+        if (world < 1 || world > 8 || rank < 0 || rank >= world || (world > 1 && !shared) || d.kv_heads % world || d.inter % (32 * world) ||
+            d.vocab % (8 * world)) {
+            err_ = "unsupported sharding (1..8 ranks; kv heads, FFN rows / 32 and vocabulary rows / 8 must divide by the rank count)";
+            return KCB_INVALID_VALUE;
+        }
+        // local shares: heads and kv heads, FFN rows, vocabulary rows
+        heads = d.heads / world, kv_heads = d.kv_heads / world, inter = d.inter / world, vocab = d.vocab / world;
+        vocab_total = d.vocab;
+        tp.rank = rank, tp.world = world;
         const int group = heads / kv_heads;
         if (group != 1 && group != 2 && group != 3 && group != 4 && group != 8) {
             err_ = "unsupported query-group size";
             return KCB_INVALID_VALUE;
         }
         CU(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+        // K windows of the attention-output and FFN-down matrices: whole super-blocks covering this rank's
+        // channels; activations outside the share stay zero Q8 blocks (d = 0, q = 0), which add exactly 0.
+        const int qd = heads * hd;
+        wo_win = k_window(rank * qd, qd);
+        wd_win = k_window(rank * inter, inter);
         for (int l = 0; l < d.n_layers; ++l) {
             const kcb_layer& s = d.layers[l];
             DLayer L;
-            const kcb_mat qkv_parts[3] = {s.wq, s.wk, s.wv};
-            const kcb_mat gu_parts[2] = {s.wg, s.wu};
+            const kcb_mat qkv_parts[3] = {row_slice(s.wq, static_cast<long long>(rank) * qd, qd),
+                                          row_slice(s.wk, static_cast<long long>(rank) * kv_heads * hd, kv_heads * hd),
+                                          row_slice(s.wv, static_cast<long long>(rank) * kv_heads * hd, kv_heads * hd)};
+            const kcb_mat gu_parts[2] = {row_slice(s.wg, static_cast<long long>(rank) * inter, inter),
+                                         row_slice(s.wu, static_cast<long long>(rank) * inter, inter)};
+            if (s.wq.rows != d.heads * hd || s.wk.rows != d.kv_heads * hd || s.wv.rows != d.kv_heads * hd || s.wg.rows != d.inter ||
+                s.wu.rows != d.inter || s.wo.k != d.heads * hd || s.wd.k != d.inter || s.wo.rows != hidden || s.wd.rows != hidden) {
+                err_ = "layer matrix shapes do not match the model dimensions";
+                return KCB_INVALID_VALUE;
+            }
             if (const int e = merged(L.qkv, qkv_parts, 3); e) return e;
             if (const int e = merged(L.gu, gu_parts, 2); e) return e;
-            if (const int e = merged_one(L.wo, s.wo); e) return e;
-            if (const int e = merged_one(L.wd, s.wd); e) return e;
+            if (const int e = upload_k(L.wo, s.wo, wo_win.sb0, wo_win.nsb); e) return e;
+            if (const int e = upload_k(L.wd, s.wd, wd_win.sb0, wd_win.nsb); e) return e;
             if (const int e = up(L.attn_norm, s.attn_norm, hidden); e) return e;
             if (const int e = up(L.ffn_norm, s.ffn_norm, hidden); e) return e;
             if (qk_norm) {
@@ -391,12 +547,26 @@ public:
             if (const int e = dev(reinterpret_cast<void**>(&L.vc), cache); e) return e;
             layers.push_back(L);
         }
-        if (const int e = merged_one(lm_head, d.lm_head); e) return e;
+        if (d.lm_head.rows != d.vocab || d.lm_head.k != hidden) {
+            err_ = "lm_head shape does not match the model dimensions";
+            return KCB_INVALID_VALUE;
+        }
+        // The tied embedding needs any row of the full matrix; the logits matvec only this rank's rows.
+        if (world > 1) {
+            const long long counted = weight_bytes;
+            if (const int e = merged_one(embed_w, d.lm_head); e) return e;
+            weight_bytes = counted;  // one row per token is read from it
+            const kcb_mat mine = row_slice(d.lm_head, static_cast<long long>(rank) * vocab, vocab);
+            if (const int e = merged_one(lm_head, mine); e) return e;
+        } else {
+            if (const int e = merged_one(lm_head, d.lm_head); e) return e;
+            embed_w = lm_head;
+        }
         if (const int e = up(out_norm, d.out_norm, hidden); e) return e;
         if (d.rope_ff)
             if (const int e = up(rope_ff, d.rope_ff, hd / 2); e) return e;
-        const int qd = heads * hd, kv = kv_heads * hd;
-        const int maxk = std::max(std::max(hidden, inter), qd);
+        const int kv = kv_heads * hd;
+        const int maxk = hidden;
         nsplit = std::max(1, std::min(16, (kSmCount + kv_heads - 1) / kv_heads));
         nsplit = std::min(nsplit, std::max(1, max_ctx / 64));
         if (const int e = dev(reinterpret_cast<void**>(&x), hidden * 4); e) return e;
@@ -404,22 +574,47 @@ public:
         if (const int e = dev(reinterpret_cast<void**>(&qkv), (qd + 2 * kv) * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&attn), qd * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&gu), 2 * inter * 4); e) return e;
-        if (const int e = dev(reinterpret_cast<void**>(&logits), static_cast<size_t>(vocab) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&logits), static_cast<size_t>(vocab_total) * 4); e) return e;
+        CU(cudaMemsetAsync(logits, 0, static_cast<size_t>(vocab_total) * 4, stream_));
         if (const int e = dev(reinterpret_cast<void**>(&xq), static_cast<size_t>(11) * (maxk / 32) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&xq_wo), static_cast<size_t>(11) * (wo_win.nsb * 8) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&xq_wd), static_cast<size_t>(11) * (wd_win.nsb * 8) * 4); e) return e;
+        CU(cudaMemsetAsync(xq_wo, 0, static_cast<size_t>(11) * (wo_win.nsb * 8) * 4, stream_));
+        CU(cudaMemsetAsync(xq_wd, 0, static_cast<size_t>(11) * (wd_win.nsb * 8) * 4, stream_));
+        if (world > 1) {
+            for (int r = 0; r < world; ++r) {
+                if (!shared[r]) {
+                    err_ = "missing exchange area of a rank";
+                    return KCB_INVALID_VALUE;
+                }
+                uint8_t* b = static_cast<uint8_t*>(shared[r]);
+                tp.flags[r] = reinterpret_cast<unsigned*>(b);
+                tp.partial[r] = reinterpret_cast<float*>(b + kTpFlagBytes);
+                tp.cand_v[r] = tp.partial[r] + 2 * hidden;
+                tp.cand_i[r] = reinterpret_cast<int*>(tp.cand_v[r] + kCand);
+            }
+            if (const int e = dev(reinterpret_cast<void**>(&tp.epoch), 64); e) return e;
+            CU(cudaMemsetAsync(tp.epoch, 0, 64, stream_));
+        }
         if (const int e = dev(reinterpret_cast<void**>(&part), static_cast<size_t>(heads) * nsplit * (hd + 2) * 4); e) return e;
-        if (const int e = dev(reinterpret_cast<void**>(&cand_v), kCand * 4); e) return e;
-        if (const int e = dev(reinterpret_cast<void**>(&cand_i), kCand * 4); e) return e;
+        if (world > 1) {
+            cand_v = tp.cand_v[rank], cand_i = tp.cand_i[rank];
+        } else {
+            if (const int e = dev(reinterpret_cast<void**>(&cand_v), kCand * 4); e) return e;
+            if (const int e = dev(reinterpret_cast<void**>(&cand_i), kCand * 4); e) return e;
+        }
         if (const int e = dev(reinterpret_cast<void**>(&state), 64); e) return e;  // {pos, token, n_forced, token_used}
         if (const int e = dev(reinterpret_cast<void**>(&forced), static_cast<size_t>(max_ctx) * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&history), static_cast<size_t>(max_ctx) * 4); e) return e;
         CU(cudaMemsetAsync(state, 0, 64, stream_));
         CU(cudaMemsetAsync(history, 0, static_cast<size_t>(max_ctx) * 4, stream_));
         // warm every kernel once outside capture (lazy module loading, one-time attribute calls), then capture
-        if (const int e = record(); e) return e;
+        // (the warm-up step exchanges with nobody: ranks are created at different times and only meet at the first replay)
+        if (const int e = record(false); e) return e;
         CU(cudaStreamSynchronize(stream_));
         CU(cudaMemsetAsync(state, 0, 64, stream_));
         CU(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeRelaxed));
-        const int e = record();
+        const int e = record(true);
         cudaGraph_t g = nullptr;
         const cudaError_t ce = cudaStreamEndCapture(stream_, &g);
         if (e) {
@@ -459,7 +654,7 @@ public:
     }
     int read(float* logits_host, int* history_host, int n_hist, int* pos_host) {
         CU(cudaStreamSynchronize(stream_));
-        if (logits_host) CU(cudaMemcpy(logits_host, logits, static_cast<size_t>(vocab) * 4, cudaMemcpyDeviceToHost));
+        if (logits_host) CU(cudaMemcpy(logits_host, logits, static_cast<size_t>(vocab_total) * 4, cudaMemcpyDeviceToHost));
         if (history_host && n_hist > 0) CU(cudaMemcpy(history_host, history, static_cast<size_t>(std::min(n_hist, max_ctx)) * 4, cudaMemcpyDeviceToHost));
         if (pos_host) CU(cudaMemcpy(pos_host, state, 4, cudaMemcpyDeviceToHost));
         return KCB_SUCCESS;
@@ -480,7 +675,10 @@ private:
             return KCB_INVALID_VALUE;
         }
         if (const int e = dev(reinterpret_cast<void**>(&dst), static_cast<size_t>(n) * 4); e) return e;
-        CU(cudaMemcpy(dst, src, static_cast<size_t>(n) * 4, cudaMemcpyHostToDevice));
+        // on the decoder's own stream: a blocking copy from pageable memory may return before the DMA lands, and
+        // this (non-blocking) stream would not wait for it
+        CU(cudaMemcpyAsync(dst, src, static_cast<size_t>(n) * 4, cudaMemcpyHostToDevice, stream_));
+        CU(cudaStreamSynchronize(stream_));
         return KCB_SUCCESS;
     }
     // Uploads GGUF blocks of one or more row-concatenated matrices of the same format and k.
@@ -504,7 +702,8 @@ private:
         for (int i = 0; i < nparts; ++i) {
             const kcb_mat& p = parts[i];
             const size_t b = kcb_kquant_bytes(p.rows, p.k, m.q6);
-            if (cudaMemcpy(staging + off, p.blocks, b, cudaMemcpyHostToDevice) != cudaSuccess) {
+            if (cudaMemcpyAsync(staging + off, p.blocks, b, cudaMemcpyHostToDevice, stream_) != cudaSuccess ||
+                cudaStreamSynchronize(stream_) != cudaSuccess) {
                 if (tmp) cudaFree(tmp);
                 err_ = "weight upload failed";
                 return KCB_INTERNAL_ERROR;
@@ -520,6 +719,55 @@ private:
         return KCB_SUCCESS;
     }
     int merged_one(DMat& m, const kcb_mat& p) { return upload(m, &p, 1); }
+    static kcb_mat row_slice(const kcb_mat& m, long long r0, int n) {
+        kcb_mat s = m;
+        s.blocks = static_cast<const uint8_t*>(m.blocks) + static_cast<size_t>(r0) * (m.k / 256) * (m.fmt == 6 ? kQ6KBlock : kQ4KBlock);
+        s.rows = n;
+        return s;
+    }
+    struct KWindow {
+        int sb0 = 0, nsb = 0, first_block = 0;  // super-blocks [sb0, sb0 + nsb); the share starts at Q8 block first_block of the window
+    };
+    static KWindow k_window(int ch0, int n) {
+        KWindow w;
+        w.sb0 = ch0 / 256;
+        w.nsb = (ch0 + n + 255) / 256 - w.sb0;
+        w.first_block = (ch0 - w.sb0 * 256) / 32;
+        return w;
+    }
+    // Uploads columns [sb0*256, (sb0+nsb)*256) of every row of one matrix.
+    int upload_k(DMat& m, const kcb_mat& p, int sb0, int nsb) {
+        m.k = nsb * 256, m.q6 = p.fmt == 6, m.rows = p.rows;
+        if (p.k % 256 || m.rows % 8 || sb0 < 0 || nsb < 1 || (sb0 + nsb) * 256 > p.k) {
+            err_ = "matrix shape not supported (rows % 8, k % 256)";
+            return KCB_INVALID_VALUE;
+        }
+        const size_t blk = m.q6 ? kQ6KBlock : kQ4KBlock;
+        const size_t bytes = kcb_kquant_bytes(m.rows, m.k, m.q6);
+        weight_bytes += static_cast<long long>(bytes);
+        if (const int e = dev(reinterpret_cast<void**>(&m.data), bytes); e) return e;
+        uint8_t* staging = m.data;
+        void* tmp = nullptr;
+        if (m.q6) {
+            CU(cudaMalloc(&tmp, bytes));
+            staging = static_cast<uint8_t*>(tmp);
+        }
+        cudaError_t ce = cudaMemcpy2DAsync(staging, nsb * blk, static_cast<const uint8_t*>(p.blocks) + sb0 * blk, (p.k / 256) * blk, nsb * blk,
+                                           m.rows, cudaMemcpyHostToDevice, stream_);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(stream_);
+        if (ce != cudaSuccess) {
+            if (tmp) cudaFree(tmp);
+            err_ = "weight upload failed";
+            return KCB_INTERNAL_ERROR;
+        }
+        if (m.q6) {
+            const int e = q6k_convert(staging, m.data, m.rows, m.k, 1, stream_);
+            cudaStreamSynchronize(stream_);
+            cudaFree(tmp);
+            if (e) return e;
+        }
+        return KCB_SUCCESS;
+    }
     int merged(std::vector<DMat>& out, const kcb_mat* parts, int n) {
         int i = 0;
         while (i < n) {
@@ -532,10 +780,24 @@ private:
         }
         return KCB_SUCCESS;
     }
-    int mv(const DMat& m, float* y) {
-        float* xd = reinterpret_cast<float*>(xq + (m.k / 32) * 8);
-        return m.q6 ? matvec_q6k_q8(m.data, xq, xd, y, m.rows, m.k, stream_) : matvec_q4k_q8(m.data, xq, xd, y, m.rows, m.k, stream_);
+    // Q8 scratch of a k-channel vector: words, then {d, sum} pairs (llm/llm_kernels.hpp:82-85).
+    static float* xd_of(int* q, int k) { return reinterpret_cast<float*>(q + (k / 32) * 8); }
+    int mv(const DMat& m, int* in, float* y) {
+        return m.q6 ? matvec_q6k_q8(m.data, in, xd_of(in, m.k), y, m.rows, m.k, stream_) : matvec_q4k_q8(m.data, in, xd_of(in, m.k), y, m.rows, m.k, stream_);
     }
+    // x += (sum over ranks of) t, then norm + quantize into xq; `exchange` false keeps the sum local (warm-up).
+    int add_norm(float* t_local, const float* w, bool exchange) {
+        if (tp.world == 1) return add_norm_q8_fast(x, t_local, w, xq, xd_of(xq, hidden), hidden, eps, stream_);
+        TpCtx c = tp;
+        if (!exchange) {  // a group of one: this rank's own areas in slot 0
+            c.world = 1, c.rank = 0;
+            c.partial[0] = tp.partial[tp.rank], c.flags[0] = tp.flags[tp.rank] + tp.rank;
+        }
+        tp_add_norm_q8_kernel<<<1, 1024, static_cast<size_t>(hidden) * sizeof(float), stream_>>>(x, c, xchg_ & 1, w, xq, xd_of(xq, hidden), hidden, eps);
+        ++xchg_;
+        return launch_status();
+    }
+    float* partial_out() { return tp.world == 1 ? t : tp.partial[tp.rank] + static_cast<size_t>(xchg_ & 1) * hidden; }
     template <int HD>
     int attention(const DLayer& L) {
         const int group = heads / kv_heads;
@@ -556,56 +818,75 @@ private:
         return launch_status();
     }
     // Enqueues one decode step on stream_.
-    int record() {
-        const int qd = heads * hd, kv = kv_heads * hd;
+    int record(bool exchange) {
+        const int qd = heads * hd;
         int *pos_p = state, *tok_p = state + 1, *nforced_p = state + 2, *used_p = state + 3;
-        const size_t nblk = static_cast<size_t>(lm_head.rows) * (hidden / 256);
-        embed_kernel<<<(hidden / 256 * 8 + 127) / 128, 128, 0, stream_>>>(lm_head.data, nblk, hidden / 256, lm_head.q6, vocab, tok_p, forced,
+        xchg_ = 0;
+        const size_t nblk = static_cast<size_t>(embed_w.rows) * (hidden / 256);
+        embed_kernel<<<(hidden / 256 * 8 + 127) / 128, 128, 0, stream_>>>(embed_w.data, nblk, hidden / 256, embed_w.q6, vocab_total, tok_p, forced,
                                                                           nforced_p, pos_p, used_p, x);
         if (const int e = launch_status(); e) return e;
-        if (const int e = add_norm_q8_fast(x, nullptr, layers[0].attn_norm, xq, reinterpret_cast<float*>(xq + (hidden / 32) * 8), hidden, eps, stream_); e) return e;
+        if (const int e = add_norm_q8_fast(x, nullptr, layers[0].attn_norm, xq, xd_of(xq, hidden), hidden, eps, stream_); e) return e;
         for (size_t l = 0; l < layers.size(); ++l) {
             const DLayer& L = layers[l];
             float* y = qkv;
             for (const DMat& m : L.qkv) {
-                if (const int e = mv(m, y); e) return e;
+                if (const int e = mv(m, xq, y); e) return e;
                 y += m.rows;
             }
             rope_kv_f16_kernel<<<(heads + 2 * kv_heads + 3) / 4, 128, 0, stream_>>>(qkv, pos_p, L.kc, L.vc, rope_ff, L.q_norm, L.k_norm, heads,
                                                                                      kv_heads, hd, log2_base, neox, eps, max_ctx);
             if (const int e = launch_status(); e) return e;
             if (const int e = hd == 128 ? attention<128>(L) : attention<64>(L); e) return e;
-            attn_combine_q8_kernel<<<(qd / 32 + 3) / 4, 128, 0, stream_>>>(part, attn, xq, reinterpret_cast<float*>(xq + (qd / 32) * 8), heads, hd, nsplit);
+            attn_combine_q8_kernel<<<(qd / 32 + 3) / 4, 128, 0, stream_>>>(part, attn, xq_wo + wo_win.first_block * 8,
+                                                                            xd_of(xq_wo, L.wo.k) + wo_win.first_block * 2, heads, hd, nsplit);
             if (const int e = launch_status(); e) return e;
-            if (const int e = mv(L.wo, t); e) return e;
-            if (const int e = add_norm_q8_fast(x, t, L.ffn_norm, xq, reinterpret_cast<float*>(xq + (hidden / 32) * 8), hidden, eps, stream_); e) return e;
+            float* po = partial_out();
+            if (const int e = mv(L.wo, xq_wo, po); e) return e;
+            if (const int e = add_norm(po, L.ffn_norm, exchange); e) return e;
             y = gu;
             for (const DMat& m : L.gu) {
-                if (const int e = mv(m, y); e) return e;
+                if (const int e = mv(m, xq, y); e) return e;
                 y += m.rows;
             }
-            if (const int e = silu_mul_q8(gu, gu + inter, nullptr, nullptr, xq, reinterpret_cast<float*>(xq + (inter / 32) * 8), inter, 1, stream_); e) return e;
-            if (const int e = mv(L.wd, t); e) return e;
+            if (const int e = silu_mul_q8(gu, gu + inter, nullptr, nullptr, xq_wd + wd_win.first_block * 8, xd_of(xq_wd, L.wd.k) + wd_win.first_block * 2,
+                                          inter, 1, stream_);
+                e)
+                return e;
+            po = partial_out();
+            if (const int e = mv(L.wd, xq_wd, po); e) return e;
             const float* next = l + 1 < layers.size() ? layers[l + 1].attn_norm : out_norm;
-            if (const int e = add_norm_q8_fast(x, t, next, xq, reinterpret_cast<float*>(xq + (hidden / 32) * 8), hidden, eps, stream_); e) return e;
+            if (const int e = add_norm(po, next, exchange); e) return e;
         }
-        if (const int e = mv(lm_head, logits); e) return e;
-        if (const int e = argmax_partial(logits, vocab, cand_v, cand_i, kCand, stream_); e) return e;
-        argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, tok_p, history, pos_p, max_ctx);
-        (void)kv;
+        float* my_logits = logits + static_cast<size_t>(tp.rank) * vocab;
+        if (const int e = mv(lm_head, xq, my_logits); e) return e;
+        if (const int e = argmax_partial(my_logits, vocab, cand_v, cand_i, kCand, stream_); e) return e;
+        if (tp.world == 1) {
+            argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, tok_p, history, pos_p, max_ctx);
+        } else {
+            TpCtx c = tp;
+            if (!exchange) {
+                c.world = 1, c.rank = 0;
+                c.cand_v[0] = cand_v, c.cand_i[0] = cand_i, c.flags[0] = tp.flags[tp.rank] + tp.rank;
+            }
+            tp_argmax_advance_kernel<<<1, 256, 0, stream_>>>(c, kCand, exchange ? vocab : 0, tok_p, history, pos_p, max_ctx);
+        }
         return launch_status();
     }
 
-    int hidden = 0, inter = 0, heads = 0, kv_heads = 0, hd = 0, vocab = 0, max_ctx = 0, neox = 0, qk_norm = 0, nsplit = 1;
+    // heads, kv_heads, inter and vocab are this rank's shares
+    int hidden = 0, inter = 0, heads = 0, kv_heads = 0, hd = 0, vocab = 0, vocab_total = 0, max_ctx = 0, neox = 0, qk_norm = 0, nsplit = 1;
+    TpCtx tp;
+    KWindow wo_win, wd_win;
+    int xchg_ = 0;  // exchanges recorded so far in the current step (parity picks the partial buffer)
     float eps = 1e-5f, log2_base = 0.f;
     std::vector<DLayer> layers;
-    DMat lm_head;
+    DMat lm_head, embed_w;
     float *out_norm = nullptr, *rope_ff = nullptr;
     float *x = nullptr, *t = nullptr, *qkv = nullptr, *attn = nullptr, *gu = nullptr, *logits = nullptr, *part = nullptr;
-    static constexpr int kCand = 296;
     float* cand_v = nullptr;
     int* cand_i = nullptr;
-    int *xq = nullptr, *state = nullptr, *forced = nullptr, *history = nullptr;
+    int *xq = nullptr, *xq_wo = nullptr, *xq_wd = nullptr, *state = nullptr, *forced = nullptr, *history = nullptr;
     cudaStream_t stream_ = nullptr;
     cudaGraph_t graph_ = nullptr;
     cudaGraphExec_t exec_ = nullptr;
@@ -633,6 +914,25 @@ int kcb_decoder_create(const kcb_model_desc* desc, void** out) {
     }
     *out = d;
     return kcb::KCB_SUCCESS;
+}
+size_t kcb_decoder_tp_shared_bytes(const kcb_model_desc* desc) { return desc && desc->hidden > 0 ? kcb::tp_shared_bytes(desc->hidden) : 0; }
+int kcb_decoder_create_tp(const kcb_model_desc* desc, int rank, int world, void* const* shared, void** out) {
+    if (!desc || !out || !desc->layers || desc->n_layers <= 0) return kcb::KCB_INVALID_VALUE;
+    *out = nullptr;
+    auto* d = new Decoder;
+    const int e = d->init(*desc, rank, world, shared);
+    if (e != kcb::KCB_SUCCESS) {
+        kcb::tl_err = d->err_;
+        delete d;
+        return e;
+    }
+    *out = d;
+    return kcb::KCB_SUCCESS;
+}
+unsigned kcb_decoder_tp_timeouts(void) {
+    unsigned v = 0;
+    cudaMemcpyFromSymbol(&v, kcb::g_tp_timeouts, sizeof v);
+    return v;
 }
 int kcb_decoder_set_prompt(void* h, const int* tokens, int n, int start_pos) {
     return h ? static_cast<Decoder*>(h)->set_prompt(tokens, n, start_pos) : kcb::KCB_INVALID_VALUE;

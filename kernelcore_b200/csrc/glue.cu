@@ -14,15 +14,6 @@
 namespace kcb {
 namespace {
 
-__device__ __forceinline__ float block_sum(float v, float* red) {  // red: >= 32 floats of shared memory
-    v = warp_sum(v);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-    __syncthreads();
-    if (lane == 0) red[warp] = v;
-    __syncthreads();
-    float t = lane < nw ? red[lane] : 0.0f;
-    return warp_sum(t);
-}
 __device__ __forceinline__ float block_max(float v, float* red) {
     v = warp_max(v);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
@@ -31,10 +22,6 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     __syncthreads();
     float t = lane < nw ? red[lane] : -INFINITY;
     return warp_max(t);
-}
-
-__device__ __forceinline__ float rinv_rms(float sumsq, int n, float eps) {  // 1 / sqrt(ss / n + eps)
-    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, static_cast<float>(n)), eps)));
 }
 
 __device__ __forceinline__ float swiglu(float g, float u) {  // g / (1 + 2^(-g log2 e)) * u

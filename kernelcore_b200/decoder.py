@@ -84,9 +84,12 @@ class FastDecoder:
     """The graph-replayed decoder (kcb_decoder_*): one captured CUDA graph replayed per token, position and
     token on the device, fp16 KV cache, greedy pick on the device."""
 
-    def __init__(self, shape: tm.Shape, model: dict):
+    def __init__(self, shape: tm.Shape, model: dict, tp=None):
+        """tp = (rank, world, exchange_ptrs): the tensor-parallel form; exchange_ptrs[r] is rank r's zero-filled
+        exchange area (tp_shared_bytes(shape) bytes) as mapped into this process."""
         L = lib.raw
         self.shape, self._keep = shape, []
+        self.rank, self.world = (tp[0], tp[1]) if tp else (0, 1)
         layers = (_Layer * shape.layers)()
         ms = tm.mat_shapes(shape)
         for l, src in enumerate(model["layers"]):
@@ -106,7 +109,11 @@ class FastDecoder:
         d.lm_head = _Mat(self._ptr(model["lm_head"]), shape.vocab, shape.hidden, 6)
         self._keep.append(layers)
         self.handle = C.c_void_p()
-        st = L.kcb_decoder_create(C.byref(d), C.byref(self.handle))
+        if tp:
+            ptrs = (C.c_void_p * self.world)(*[int(p) for p in tp[2]])
+            st = L.kcb_decoder_create_tp(C.byref(d), int(self.rank), int(self.world), ptrs, C.byref(self.handle))
+        else:
+            st = L.kcb_decoder_create(C.byref(d), C.byref(self.handle))
         if st != 0:
             L.kcb_decoder_last_error.restype = C.c_char_p
             raise RuntimeError(f"kcb_decoder_create: status {st}: {L.kcb_decoder_last_error().decode()}")
@@ -119,6 +126,23 @@ class FastDecoder:
         a = np.ascontiguousarray(a)
         self._keep.append(a)
         return a.ctypes.data
+
+    @staticmethod
+    def tp_shared_bytes(shape: tm.Shape) -> int:
+        d = _Desc()
+        d.hidden = shape.hidden
+        lib.raw.kcb_decoder_tp_shared_bytes.restype = C.c_size_t
+        return int(lib.raw.kcb_decoder_tp_shared_bytes(C.byref(d)))
+
+    @staticmethod
+    def tp_timeouts() -> int:
+        lib.raw.kcb_decoder_tp_timeouts.restype = C.c_uint
+        return int(lib.raw.kcb_decoder_tp_timeouts())
+
+    def local_rows(self):
+        """Rows of the logits this rank fills (all of them on one GPU)."""
+        per = self.shape.vocab // self.world
+        return self.rank * per, (self.rank + 1) * per
 
     def set_prompt(self, tokens, start_pos=0):
         t = np.ascontiguousarray(tokens, np.int32)

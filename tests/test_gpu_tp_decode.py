@@ -1,0 +1,95 @@
+"""Tensor-parallel graph decoder on 2 GPUs (one process per GPU) against the single-GPU decoder.
+
+Skipped on a single-GPU box.  The ranks shard heads, FFN rows and vocabulary rows; the partial hidden vectors of
+the K-split attention-output / FFN-down matvecs are summed inside the following norm kernel out of both ranks'
+memories.  Only the order of those fp32 additions differs from one GPU, so logits agree to the bound the
+single-GPU decoder test states for Q8 re-quantization (3e-2 of max|logit| at every position), and the ranks agree
+with each other exactly."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+STEPS, PROMPT = 24, 16
+
+
+def _shape():
+    from kernelcore_b200 import tiny_model as tm
+    # FFN share 384 = 1.5 super-blocks (a straddled K window), 8 query / 2 kv heads of 64
+    return tm.Shape("tp-tiny", 512, 768, 2, 8, 2, 64, 512, 48)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+    from kernelcore_b200 import decoder, tiny_model as tm
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    shape = _shape()
+    model = tm.build(shape, seed=11)
+    area = symm_mem.empty(decoder.FastDecoder.tp_shared_bytes(shape), dtype=torch.uint8, device=dev)
+    area.zero_()
+    handle = symm_mem.rendezvous(area, dist.group.WORLD.group_name)
+    torch.cuda.synchronize()
+    dist.barrier()
+    prompt = [int(t) for t in np.random.default_rng(2).integers(0, shape.vocab, PROMPT)]
+    with decoder.FastDecoder(shape, model, tp=(rank, world, list(handle.buffer_ptrs))) as dec:
+        dec.set_prompt(prompt)
+        dist.barrier()
+        per_step = []
+        for _ in range(STEPS):
+            dec.run(1)
+            logits, _, _ = dec.read(0)
+            r0, r1 = dec.local_rows()
+            per_step.append(logits[r0:r1].copy())
+        _, hist, pos = dec.read(STEPS)
+        out[rank] = (np.stack(per_step), hist.copy(), pos, decoder.FastDecoder.tp_timeouts())
+        dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_decoder_matches_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    sys.path.insert(0, ROOT)
+    from helpers import rel_diff
+    from kernelcore_b200 import decoder, tiny_model as tm
+    world = 2
+    with mp.Manager() as man:
+        out = man.dict()
+        mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+        res = dict(out)
+    assert res[0][3] == 0 and res[1][3] == 0                      # no wait gave up
+    assert res[0][2] == res[1][2] == STEPS
+    assert np.array_equal(res[0][1], res[1][1])                   # both ranks picked the same tokens
+    tp_logits = np.concatenate([res[0][0], res[1][0]], axis=1)   # [steps][vocab]
+    shape = _shape()
+    model = tm.build(shape, seed=11)
+    prompt = [int(t) for t in np.random.default_rng(2).integers(0, shape.vocab, PROMPT)]
+    # one GPU, forced to the tokens the two-rank run consumed, so every step sees the same inputs
+    consumed = prompt + [int(t) for t in res[0][1][PROMPT - 1:STEPS - 1]]
+    with decoder.FastDecoder(shape, model) as dec:
+        dec.set_prompt(consumed[:STEPS])
+        errs = []
+        for s in range(STEPS):
+            dec.run(1)
+            logits, _, _ = dec.read(0)
+            errs.append(rel_diff(tp_logits[s], logits))
+    assert max(errs) < 3e-2, errs
+    assert errs[0] < 1e-4, errs

@@ -57,3 +57,56 @@ def test_row_range_rules():
         shard.row_range(100, 0, 8)
     with pytest.raises(ValueError):
         shard.row_range(128, 2, 2)
+
+
+def _ksplit_worker(rank, world, port, rows, k, q6, out):
+    """K-split of one matrix (the attention-output / FFN-down split of tensor-parallel decode): every rank runs
+    the oracle on its window of whole super-blocks with the channels it does not own zeroed, the partial vectors
+    are gathered and added in rank order on every rank."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle
+    from kernelcore_b200 import shard, synth
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    w = synth.q6k_blocks(rows, k, 5) if q6 else synth.q4k_blocks(rows, k, 5)
+    x = synth.activations(k, 6)
+    share = k // world
+    sb0, nsb, first = shard.k_window(rank * share, share)
+    win = shard.k_slice_blocks(w, rows, k, 210 if q6 else 144, sb0, nsb)
+    xw = np.zeros(nsb * 256, np.float32)
+    xw[first * 32:first * 32 + share] = x[rank * share:(rank + 1) * share]
+    part = torch.from_numpy(oracle.matvec_q8(oracle.port, win, xw, rows, nsb * 256, q6))
+    parts = [torch.empty(rows, dtype=torch.float32) for _ in range(world)]
+    dist.all_gather(parts, part)
+    total = parts[0].clone()
+    for p in parts[1:]:
+        total += p
+    want = oracle.matvec_q8(oracle.port, w, x, rows, k, q6)
+    err = float(np.abs(total.numpy() - want).max() / np.abs(want).max())
+    out[rank] = (err, total.numpy().tobytes())
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("q6", [0, 1])
+def test_two_rank_k_split_with_straddled_super_block(q6):
+    world, rows, k = 2, 40, 768          # shares of 384 channels: 1.5 super-blocks each, block 1 read by both
+    with mp.Manager() as man:
+        out = man.dict()
+        mp.spawn(_ksplit_worker, args=(world, _free_port(), rows, k, q6, out), nprocs=world, join=True)
+        res = dict(out)
+    assert res[0][0] < 2e-6 and res[1][0] < 2e-6       # same products, only the order of fp32 additions differs
+    assert res[0][1] == res[1][1]                      # every rank holds the same bits
+
+
+def test_head_shares_and_k_windows():
+    sys.path.insert(0, ROOT)
+    from kernelcore_b200 import shard
+    q, kv = shard.head_shares(24, 8, 5, 8)
+    assert list(q) == [15, 16, 17] and list(kv) == [5]
+    assert shard.k_window(5 * 384, 384) == (7, 2, 4)    # channels 1920..2303: super-blocks 7-8, from Q8 block 4
+    assert shard.k_window(2 * 1024, 1024) == (8, 4, 0)
+    with pytest.raises(ValueError):
+        shard.head_shares(24, 8, 0, 3)
+    with pytest.raises(ValueError):
+        shard.k_window(100, 384)
