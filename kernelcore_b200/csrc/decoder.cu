@@ -354,6 +354,11 @@ __device__ __forceinline__ float ld_peer_f32(const float* p) {
     asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ float4 ld_peer_f32x4(const float* p) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ int ld_peer_s32(const int* p) {
     int v;
     asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -369,7 +374,6 @@ __device__ void tp_arrive_and_wait(const TpCtx& c) {
     const unsigned e = e_sh;
     if (threadIdx.x < static_cast<unsigned>(c.world)) {
         const int r = threadIdx.x;
-        __threadfence_system();
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(c.flags[r] + c.rank), "r"(e) : "memory");
         const unsigned limit = *reinterpret_cast<volatile unsigned*>(&g_tp_dead) ? 1u : (1u << 22);
         bool arrived = false;
@@ -394,17 +398,25 @@ __device__ void tp_arrive_and_wait(const TpCtx& c) {
 // add_norm_q8_fast_kernel does for one GPU.
 __global__ void __launch_bounds__(1024) tp_add_norm_q8_kernel(float* x, TpCtx c, int parity, const float* __restrict__ w, int* xq,
                                                                float* xd, int n, float eps) {
-    extern __shared__ float sh[];  // n floats
+    extern __shared__ __align__(16) float sh[];  // n floats
     __shared__ float red[32];
     tp_arrive_and_wait(c);
     float ss = 0.0f;
-    for (int j = threadIdx.x; j < n; j += blockDim.x) {
-        float t = ld_peer_f32(c.partial[0] + static_cast<size_t>(parity) * n + j);
-        for (int r = 1; r < c.world; ++r) t = __fadd_rn(t, ld_peer_f32(c.partial[r] + static_cast<size_t>(parity) * n + j));
-        const float v = __fadd_rn(x[j], t);
-        x[j] = v;
-        sh[j] = v;
-        ss += v * v;
+    for (int j = 4 * threadIdx.x; j < n; j += 4 * blockDim.x) {  // n is a multiple of 256
+        // all ranks' loads are issued before the first use: one NVLink round trip, not `world` of them
+        float4 p[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < c.world) p[r] = ld_peer_f32x4(c.partial[r] + static_cast<size_t>(parity) * n + j);
+        float4 t = p[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r)
+            if (r < c.world) t.x = __fadd_rn(t.x, p[r].x), t.y = __fadd_rn(t.y, p[r].y), t.z = __fadd_rn(t.z, p[r].z), t.w = __fadd_rn(t.w, p[r].w);
+        float4 v = *reinterpret_cast<const float4*>(x + j);
+        v.x = __fadd_rn(v.x, t.x), v.y = __fadd_rn(v.y, t.y), v.z = __fadd_rn(v.z, t.z), v.w = __fadd_rn(v.w, t.w);
+        *reinterpret_cast<float4*>(x + j) = v;
+        *reinterpret_cast<float4*>(sh + j) = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     const float r = rinv_rms(block_sum(ss, red), n, eps);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;

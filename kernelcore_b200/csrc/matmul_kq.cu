@@ -172,13 +172,14 @@ __global__ void __launch_bounds__(kThreads) matmul_kq_kernel(const uint8_t* __re
 // q6: Q6_K planes, else Q4_K blocks.  q8k: slots of 85*k/256 ints (per-256 scales), else 11*k/32.
 int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int ncols, int q6, int q8k, cudaStream_t s) {
     if (rows <= 0 || k <= 0 || k % 256 || k > 32768 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
-    // Q4_K with per-256 activation slots and whole 128-row tiles goes to the tensor cores (bit-identical results);
+    // Per-256 activation slots and whole 128-row tiles go to the tensor cores (bit-identical results);
     // KCB_MATMUL_TC=0 keeps everything on the CUDA-core kernel below.
     static const bool tc = [] {
         const char* e = getenv("KCB_MATMUL_TC");
         return !e || atoi(e) != 0;
     }();
-    if (tc && !q6 && q8k && rows % 128 == 0 && ncols >= 16) return matmul_q4k_q8k_tc(w, xq, y, rows, k, ncols, s);
+    if (tc && q8k && rows % 128 == 0 && ncols >= 16)
+        return q6 ? matmul_q6k_q8k_tc(w, xq, y, rows, k, ncols, s) : matmul_q4k_q8k_tc(w, xq, y, rows, k, ncols, s);
     const int nsb = k / 256, nb = nsb * 8;
     const int slot_ints = q8k ? nsb * 85 : nb * 11;
     const size_t col_bytes = static_cast<size_t>(nsb * 64 + nb * 2 + (q6 ? nb * 2 : 0)) * 4;

@@ -1,4 +1,4 @@
-// Q4_K x Q8_K-activation matmul on the 5th-generation tensor cores (tcgen05, int8 -> int32, TMEM).
+// Q4_K / Q6_K x Q8_K-activation matmuls on the 5th-generation tensor cores (tcgen05, int8 -> int32, TMEM).
 //
 // Replaces the reference's kernels/llm/matmul_q4k_q8kx4.cu:41 / matmul_q4k_q8kx8.cu:41-239 (prompt
 // processing; one thread per (row, 4 or 8 columns) with dp4a there).  Y[c*rows + r] = sum over super-blocks
@@ -229,6 +229,153 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const ui
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
 }
 
+// ---- Q6_K --------------------------------------------------------------------------------------------------
+// llm::ref::matvecQ6KQ8K (llm/llm_reference.cpp:564-596): per super-block
+//     acc += (d * dx_c) * float(is),   is = sum over 16-weight groups g of sc_g * (dot16(q_g, x_g) - 32 * B_g)
+// with q the raw 6-bit weights (0..63), sc the int8 group scale and B_g the activation sum of the group.  The
+// -32 offset folds into the weight: is = sum_k w'_k x_k with w' = sc * (q - 32), |w'| <= 4096.  w' is split as
+// w' = 64 a + b with a = w' >> 6 (arithmetic, -64..64) and b = w' & 63: two int8 planes, two accumulators,
+// is = 64 Da + Db -- the same integer, so every output is bit-identical to the reference's per-column mirror.
+// Weights are read from the device layout of Q6_K (four planes: ql | qh | scales | d).
+
+// q4: four 6-bit weights in bytes, scb = sc + 128 (0..255), crep = (8192 - 32 sc) in both 16-bit lanes.
+// Per 16-bit lane u = q * scb - 128 q + crep = sc * (q - 32) + 8192, in 4128..12288: never negative, no borrow
+// between lanes.  (u >> 6) - 128 == w' >> 6 and subtracting 128 from a byte is flipping its top bit.
+__device__ __forceinline__ void scale_split_q6(unsigned q4, unsigned scb, unsigned crep, unsigned& a, unsigned& b) {
+    const unsigned qe = q4 & 0x00FF00FFu, qo = (q4 >> 8) & 0x00FF00FFu;
+    const unsigned ue = qe * scb + crep - (qe << 7), uo = qo * scb + crep - (qo << 7);
+    a = (((ue >> 6) & 0x00FF00FFu) | (((uo >> 6) & 0x00FF00FFu) << 8)) ^ 0x80808080u;
+    b = (ue & 0x003F003Fu) | ((uo & 0x003F003Fu) << 8);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const uint8_t* __restrict__ w, const int* __restrict__ xq,
+                                                                         float* __restrict__ y, int rows, int nsb, int ncols) {
+    extern __shared__ __align__(1024) uint8_t sm[];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(sm + kOffBar);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kOffBar + 16);
+    float* dxs = reinterpret_cast<float*>(sm + kOffDx);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r_tile = blockIdx.x * TM, c_tile = blockIdx.y * TN;
+    const int slot_ints = nsb * 85;
+    const size_t nblk = static_cast<size_t>(rows) * nsb;
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        mbar_init_fence();
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    const int erow = 32 * (warp & 3) + lane, ecol0 = 64 * (warp >> 2);
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+    // unpack role: tile row tid / 2, half n = tid & 1 of the super-block (weights 128 n .. 128 n + 127, K-steps 4n .. 4n+3)
+    const int urow = tid >> 1, n = tid & 1;
+    const size_t ublk0 = static_cast<size_t>(r_tile + urow) * nsb, eblk0 = static_cast<size_t>(r_tile + erow) * nsb;
+    const uint32_t ubase = (urow >> 3) * 256 + (urow & 7) * 16;
+
+    bool failed = false;
+    for (int sb = 0; sb < nsb && !failed; ++sb) {
+        {
+            const size_t blk = ublk0 + sb;
+            uint4 lq[4], hq[2];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) lq[i] = ldg_stream(w + blk * 128 + 64 * n + 16 * i);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) hq[i] = ldg_stream(w + nblk * 128 + blk * 64 + 32 * n + 16 * i);
+            const uint2 scw = __ldg(reinterpret_cast<const uint2*>(w + nblk * 192 + blk * 16 + 8 * n));
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {      // K-step 4n + t: weights 128n + 32t .. +31
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {  // 16 weights sharing scale 2t + c
+                    const int si = 2 * t + c;
+                    const int sc = static_cast<int>(((si < 4 ? scw.x : scw.y) << (24 - 8 * (si & 3)))) >> 24;
+                    const unsigned scb = static_cast<unsigned>(sc + 128);
+                    const unsigned c16 = static_cast<unsigned>(8192 - 32 * sc), crep = c16 | (c16 << 16);
+                    const uint4 lv = lq[2 * (t & 1) + c], hv = hq[c];
+                    const unsigned lw[4] = {lv.x, lv.y, lv.z, lv.w}, hw[4] = {hv.x, hv.y, hv.z, hv.w};
+                    unsigned a[4], b[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const unsigned nib = (t >= 2 ? lw[i] >> 4 : lw[i]) & 0x0F0F0F0Fu;
+                        const unsigned q4 = nib | (((hw[i] >> (2 * t)) & 0x03030303u) << 4);
+                        scale_split_q6(q4, scb, crep, a[i], b[i]);
+                    }
+                    const int s = 4 * n + t;
+                    *reinterpret_cast<uint4*>(sm + kOffAa + s * kSlab + ubase + 128 * c) = make_uint4(a[0], a[1], a[2], a[3]);
+                    *reinterpret_cast<uint4*>(sm + kOffAb + s * kSlab + ubase + 128 * c) = make_uint4(b[0], b[1], b[2], b[3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int i = tid + kThreads * it, col = i >> 4, part = i & 15;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (c_tile + col < ncols) v = __ldg(reinterpret_cast<const uint4*>(xq + static_cast<size_t>(c_tile + col) * slot_ints + sb * 64 + part * 4));
+            *reinterpret_cast<uint4*>(sm + kOffBx + (part >> 1) * kSlab + (col >> 3) * 256 + (part & 1) * 128 + (col & 7) * 16) = v;
+        }
+        if (tid < TN) {
+            float dx = 0.0f;
+            if (c_tile + tid < ncols) dx = __int_as_float(__ldg(xq + static_cast<size_t>(c_tile + tid) * slot_ints + nsb * 64 + sb));
+            dxs[tid] = dx;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t base = smem_u32(sm);
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const uint64_t bd = smem_desc(base + kOffBx + s * kSlab);
+                mma_i8(tmem + 0, smem_desc(base + kOffAa + s * kSlab), bd, s > 0);
+                mma_i8(tmem + 128, smem_desc(base + kOffAb + s * kSlab), bd, s > 0);
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+        }
+        const bool ok = mbar_wait_bounded(bar, static_cast<uint32_t>(sb) & 1u);
+        if (__syncthreads_or(!ok)) {
+            failed = true;
+            break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(w + nblk * 208 + (eblk0 + sb) * 2)));
+        const uint32_t trow = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + ecol0;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+            int va[16], vb[16];
+            tmem_ld16(trow + 16 * ch, va);
+            tmem_ld16(trow + 128 + 16 * ch, vb);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int is = 64 * va[i] + vb[i];
+                acc[16 * ch + i] = __fadd_rn(acc[16 * ch + i], __fmul_rn(__fmul_rn(d, dxs[ecol0 + 16 * ch + i]), static_cast<float>(is)));
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+    }
+    if (failed) {
+        if (tid == 0) atomicAdd(&g_tc_timeouts, 1u);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+            const int c = c_tile + ecol0 + i;
+            if (c < ncols) y[static_cast<size_t>(c) * rows + r_tile + erow] = acc[i];
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+}
+
 }  // namespace
 
 unsigned tc_timeouts() {
@@ -248,6 +395,20 @@ int matmul_q4k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, i
     }
     const dim3 grid(rows / TM, (ncols + TN - 1) / TN);
     matmul_q4k_q8k_tc_kernel<<<grid, kThreads, kSmemBytes, s>>>(static_cast<const uint8_t*>(w), xq, y, rows, k / 256, ncols);
+    return launch_status();
+}
+
+// Tensor-core path for Q6_K weights (device planes) and per-256 activation slots; rows a multiple of 128.
+int matmul_q6k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s) {
+    if (rows <= 0 || rows % TM || k <= 0 || k % 256 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(matmul_q6k_q8k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return KCB_LAUNCH_FAILURE;
+        attr_set = true;
+    }
+    const dim3 grid(rows / TM, (ncols + TN - 1) / TN);
+    matmul_q6k_q8k_tc_kernel<<<grid, kThreads, kSmemBytes, s>>>(static_cast<const uint8_t*>(w), xq, y, rows, k / 256, ncols);
     return launch_status();
 }
 

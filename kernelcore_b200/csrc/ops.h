@@ -34,6 +34,7 @@ int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int nc
 
 // matmul_tc.cu
 int matmul_q4k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s);
+int matmul_q6k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s);
 unsigned tc_timeouts();
 
 // glue.cu

@@ -40,17 +40,19 @@ def test_golden_columns(golden, q6, q8k):
     assert rel_diff(y, g[tag + ("_Y_q8k" if q8k else "_Y_q8")]) < 1e-5
 
 
+@pytest.mark.parametrize("q6", [False, True])
 @pytest.mark.parametrize("ncols", [16, 17, 128, 130, 300])
-def test_tensor_core_q4k_q8k_bit_identical(ncols):
-    """Q4_K x per-256 activations on tcgen05: exact integer contractions and the reference's fp32 order, so
-    every output equals llm::ref::matvecQ4KQ8K bit for bit, including ragged column tiles."""
+def test_tensor_core_q8k_bit_identical(ncols, q6):
+    """Q4_K / Q6_K x per-256 activations on tcgen05: exact integer contractions and the reference's fp32 order,
+    so every output equals llm::ref::matvecQ4KQ8K / matvecQ6KQ8K bit for bit, including ragged column tiles.
+    raw_blocks draws every byte uniformly, so Q6_K scales reach -128 and 127 (the extremes of the plane split)."""
     rows, k = 256, 1024
     for gen in (synth.kquant_blocks, synth.raw_blocks):
-        w = gen(rows, k, ncols, False)
+        w = gen(rows, k, ncols, q6)
         X = np.random.default_rng(ncols).uniform(-3, 3, (ncols, k)).astype(np.float32)
         X[0, :256] = 0  # an all-zero super-block: scale 0
-        y = run(w, X, rows, k, False, True)
-        want = np.stack([oracle.matvec_q8k(port, w, X[c], rows, k, 0) for c in range(ncols)])
+        y = run(w, X, rows, k, q6, True)
+        want = np.stack([oracle.matvec_q8k(port, w, X[c], rows, k, int(q6)) for c in range(ncols)])
         assert bit_equal(y, want), (ncols, gen.__name__, rel_diff(y, want))
     assert lib.raw.kcb_tc_timeouts() == 0
 
