@@ -277,6 +277,12 @@ size_t kcb_decoder_tp_shared_bytes(const kcb_model_desc* desc);
 int kcb_decoder_create_tp(const kcb_model_desc* desc, int rank, int world, void* const* shared, void** decoder);
 unsigned kcb_decoder_tp_timeouts(void);
 int kcb_decoder_set_prompt(void* decoder, const int* tokens, int n, int start_pos);
+/* Batched prompt pass (single GPU): all n tokens through every layer together -- the reference's batched path in its
+ * ggml backend (integrations/llama.cpp/ggml/src/ggml-kernelcore/ggml-kernelcore.cpp:548-589 mul_mat with per-256
+ * activation slots, :502-522 fused norm, :663-697 attention over the fp16 cache) -- on the tensor-core matmuls.
+ * Leaves the decoder where n single steps would: KV rows filled, logits and greedy pick of the last prompt token,
+ * position start_pos + n; kcb_decoder_run then generates.  Returns after the pass has finished. */
+int kcb_decoder_prefill(void* decoder, const int* tokens, int n, int start_pos);
 int kcb_decoder_run(void* decoder, int steps);
 int kcb_decoder_sync(void* decoder);
 int kcb_decoder_read(void* decoder, float* logits_host, int* history_host, int n_history, int* pos_host);

@@ -28,6 +28,8 @@ __device__ __forceinline__ int sbyte_of(unsigned w, int i) { return static_cast<
 
 // x[hidden] = dequantised row `token` of a Q6_K (planes) or Q4_K matrix: the tied-embedding lookup
 // (llm/gguf_model.cpp:96-104), bit-exact with llm::ref::dequantRowQ6K / Q4K.
+__device__ __forceinline__ void embed_row(const uint8_t* __restrict__ w, size_t nblk, int nsb, int q6, int token, int t, float* __restrict__ x);
+
 __global__ void embed_kernel(const uint8_t* __restrict__ w, size_t nblk, int nsb, int q6, int vocab,
                              const int* __restrict__ token_p, const int* __restrict__ forced, const int* __restrict__ n_forced,
                              const int* __restrict__ pos_p, int* token_used, float* __restrict__ x) {
@@ -37,6 +39,17 @@ __global__ void embed_kernel(const uint8_t* __restrict__ w, size_t nblk, int nsb
     int token = pos < *n_forced ? forced[pos] : *token_p;
     token = min(max(token, 0), vocab - 1);
     if (t == 0) *token_used = token;
+    embed_row(w, nblk, nsb, q6, token, t, x);
+}
+// Prompt form: row blockIdx.y of x is the embedding of tokens[blockIdx.y].
+__global__ void embed_rows_kernel(const uint8_t* __restrict__ w, size_t nblk, int nsb, int q6, int vocab,
+                                  const int* __restrict__ tokens, float* __restrict__ x) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= nsb * 8) return;
+    const int token = min(max(tokens[blockIdx.y], 0), vocab - 1);
+    embed_row(w, nblk, nsb, q6, token, t, x + static_cast<size_t>(blockIdx.y) * nsb * 256);
+}
+__device__ __forceinline__ void embed_row(const uint8_t* __restrict__ w, size_t nblk, int nsb, int q6, int token, int t, float* __restrict__ x) {
     const size_t blk = static_cast<size_t>(token) * nsb + (t >> 3);
     const int c8 = t & 7;
     float* out = x + (t >> 3) * 256;
@@ -93,15 +106,20 @@ __global__ void embed_kernel(const uint8_t* __restrict__ w, size_t nblk, int nsb
 // RoPE of q and k (+ optional per-head RMSNorm first) at the device-side position, K and V appended to the
 // fp16 cache rows of that position.  One warp per head: q heads, then k heads, then v heads.
 // kernels/llm/rope.cu:4-17 / rope_ff.cu / rope_ggml.cu:21-44 for the rotation, set_rows_f16.cu for the cast.
-__global__ void rope_kv_f16_kernel(float* qkv, const int* __restrict__ pos_p, unsigned short* kc, unsigned short* vc,
-                                   const float* __restrict__ ff, const float* __restrict__ qn, const float* __restrict__ kn,
-                                   int heads, int kv_heads, int hd, float log2_base, int neox, float eps, int max_ctx) {
+// Token blockIdx.y (decode: one) sits at position *pos_p + pos0 + blockIdx.y; its q|k heads are row blockIdx.y of
+// qk (row stride qk_stride floats), its v heads row blockIdx.y of v.
+__global__ void rope_kv_f16_kernel(float* qk, float* v, int qk_stride, int v_stride, const int* __restrict__ pos_p, int pos0,
+                                   unsigned short* kc, unsigned short* vc, const float* __restrict__ ff,
+                                   const float* __restrict__ qn, const float* __restrict__ kn, int heads, int kv_heads, int hd,
+                                   float log2_base, int neox, float eps, int max_ctx) {
     const int lane = threadIdx.x & 31;
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (w >= heads + 2 * kv_heads) return;
-    const int pos = min(*pos_p, max_ctx - 1);
+    const int tok = blockIdx.y;
+    const int pos = min((pos_p ? *pos_p : 0) + pos0 + tok, max_ctx - 1);
     const int kvdim = kv_heads * hd;
-    float* base = qkv + static_cast<size_t>(w) * hd;
+    float* base = w < heads + kv_heads ? qk + static_cast<size_t>(tok) * qk_stride + static_cast<size_t>(w) * hd
+                                       : v + static_cast<size_t>(tok) * v_stride + static_cast<size_t>(w - heads - kv_heads) * hd;
     if (w >= heads + kv_heads) {  // v head: cast and store
         unsigned short* dst = vc + static_cast<size_t>(pos) * kvdim + static_cast<size_t>(w - heads - kv_heads) * hd;
         for (int i = lane; i < hd; i += 32) dst[i] = static_cast<unsigned short>(f32_to_f16_bits(base[i]));
@@ -148,20 +166,25 @@ __global__ void rope_kv_f16_kernel(float* qkv, const int* __restrict__ pos_p, un
 // per lane group, and the CTA merges its groups into one partial {m, l, acc[HD]} per query head.
 // Same quantities as kernels/llm/fa_scores.cu ... fa_values.cu: s = scale * q.k, p = 2^((s - max) log2 e),
 // out = sum p v / sum p.
+// Prompt form: blockIdx.z = token, whose query row is qkv + token * q_stride and whose position is
+// *pos_p + pos0 + token (causal: it attends to the cache rows up to its own); with `direct` set (nsplit == 1)
+// the normalised output goes straight to direct[token][heads * HD].
 template <int HD, int G>
 __global__ void __launch_bounds__(128) attn_partial_kernel(const float* __restrict__ qkv, const unsigned short* __restrict__ kc,
                                                             const unsigned short* __restrict__ vc, const int* __restrict__ pos_p,
                                                             float* __restrict__ part, int heads, int kv_heads, int nsplit,
-                                                            float scale, int max_ctx) {
+                                                            float scale, int max_ctx, int q_stride, int pos0, float* __restrict__ direct) {
     constexpr int DPL = HD / 8;  // channels per lane
     constexpr int NW = 4;
     extern __shared__ float sm[];  // [NW*4][G][HD + 2]
     const int kvh = blockIdx.x, sp = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, grp = lane >> 3, l8 = lane & 7;
-    const int ctx = min(*pos_p, max_ctx - 1) + 1;
+    const int tok = blockIdx.z;
+    const int ctx = min((pos_p ? *pos_p : 0) + pos0 + tok, max_ctx - 1) + 1;
     const int chunk = (ctx + nsplit - 1) / nsplit;
     const int t0 = sp * chunk, t1 = min(ctx, t0 + chunk);
     const int kvdim = kv_heads * HD;
+    qkv += static_cast<size_t>(tok) * q_stride;
 
     float q[G][DPL];
 #pragma unroll
@@ -242,6 +265,10 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float* __restri
             const float wgt = pp[HD] == -INFINITY ? 0.0f : exp2f((pp[HD] - mm) * 1.44269504f);
             ll += pp[HD + 1] * wgt;
             aa += pp[d] * wgt;
+        }
+        if (direct) {
+            direct[static_cast<size_t>(tok) * heads * HD + static_cast<size_t>(kvh * G + g) * HD + d] = __fdiv_rn(aa, ll);
+            continue;
         }
         float* dst = part + (static_cast<size_t>(kvh * G + g) * nsplit + sp) * (HD + 2);
         dst[d] = aa;
@@ -660,6 +687,83 @@ public:
         for (int i = 0; i < steps; ++i) CU(cudaGraphLaunch(exec_, stream_));
         return KCB_SUCCESS;
     }
+    // Batched prompt pass: the n tokens go through every layer together, in chunks of at most kPrefillChunk, with the
+    // arithmetic of the reference's batched (ggml) path -- per-256 activation slots (llm/llm_kernels.hpp:86-89),
+    // tensor-core K-quant matmuls, add + RMSNorm + quantize per row (kernels/llm/add_sumsq_f.cu, norm_mul_q8k_f.cu),
+    // causal attention over the fp16 cache -- and leave the decoder where n single steps would: KV rows
+    // [start_pos, start_pos + n) filled, logits and greedy pick of the last token, position start_pos + n.
+    int prefill(const int* tokens, int n, int start_pos) {
+        if (tp.world != 1) {
+            err_ = "batched prompt pass is single-GPU; feed the prompt through kcb_decoder_set_prompt + kcb_decoder_run";
+            return KCB_UNSUPPORTED_OPERATION;
+        }
+        if (n < 1 || start_pos < 0 || start_pos + n > max_ctx || !tokens) return KCB_INVALID_VALUE;
+        if (const int e = prefill_buffers(std::min(n, kPrefillChunk)); e) return e;
+        std::vector<int> f(static_cast<size_t>(max_ctx), 0);
+        for (int i = 0; i < n; ++i) f[static_cast<size_t>(start_pos + i)] = tokens[i];
+        CU(cudaMemcpyAsync(forced, f.data(), f.size() * 4, cudaMemcpyHostToDevice, stream_));
+        CU(cudaStreamSynchronize(stream_));  // f goes out of scope
+        const int qd = heads * hd, kv = kv_heads * hd, nsbh = hidden / 256;
+        for (int c0 = 0; c0 < n; c0 += kPrefillChunk) {
+            const int m = std::min(kPrefillChunk, n - c0), p0 = start_pos + c0;
+            const size_t nblk = static_cast<size_t>(embed_w.rows) * nsbh;
+            embed_rows_kernel<<<dim3((nsbh * 8 + 127) / 128, m), 128, 0, stream_>>>(embed_w.data, nblk, nsbh, embed_w.q6, vocab_total, forced + p0, pX);
+            if (const int e = launch_status(); e) return e;
+            for (size_t l = 0; l < layers.size(); ++l) {
+                const DLayer& L = layers[l];
+                // X (+= T of the previous layer), normalise, quantize
+                if (const int e = add_norm_q8(pX, l ? pT : nullptr, pX, L.attn_norm, nullptr, pSlots, pSq, hidden, m, eps, 3, 1, stream_); e) return e;
+                // q|k and v rows of every token: token-major outputs (the reference's column-major Y)
+                const bool fused_qkv = L.qkv.size() == 1;  // {q|k|v} when the three formats agree, else {q|k, v}
+                if (!(fused_qkv || (L.qkv.size() == 2 && L.qkv[0].rows == qd + kv)) || (L.gu.size() == 1 && L.gu[0].q6)) {
+                    err_ = "batched prompt pass supports q and k in one format (v either) and Q4_K gate/up, or split gate/up";
+                    return KCB_UNSUPPORTED_OPERATION;
+                }
+                float* outs[2] = {pQK, pV};
+                int which = 0;
+                for (const DMat& w : L.qkv)
+                    if (const int e = matmul_kq_q8(w.data, pSlots, outs[which++], w.rows, w.k, m, w.q6, 1, stream_); e) return e;
+                const int qk_stride = fused_qkv ? qd + 2 * kv : qd + kv;
+                float* vrows = fused_qkv ? pQK + qd + kv : pV;
+                const int v_stride = fused_qkv ? qk_stride : kv;
+                rope_kv_f16_kernel<<<dim3((heads + 2 * kv_heads + 3) / 4, m), 128, 0, stream_>>>(pQK, vrows, qk_stride, v_stride, nullptr, p0, L.kc, L.vc,
+                                                                                                  rope_ff, L.q_norm, L.k_norm, heads, kv_heads, hd,
+                                                                                                  log2_base, neox, eps, max_ctx);
+                if (const int e = launch_status(); e) return e;
+                if (const int e = hd == 128 ? attention<128>(L, pQK, qk_stride, m, p0, pA) : attention<64>(L, pQK, qk_stride, m, p0, pA); e) return e;
+                if (const int e = quantize_cols_k(pA, pSlots, qd, m, stream_); e) return e;
+                if (const int e = matmul_kq_q8(L.wo.data, pSlots, pT, L.wo.rows, L.wo.k, m, L.wo.q6, 1, stream_); e) return e;
+                if (const int e = add_norm_q8(pX, pT, pX, L.ffn_norm, nullptr, pSlots, pSq, hidden, m, eps, 3, 1, stream_); e) return e;
+                // gate and up separately so that each is a contiguous [m][inter] matrix for SwiGLU
+                float* go = pG;
+                for (const DMat& w : L.gu) {
+                    const size_t row_bytes = static_cast<size_t>(w.k / 256) * kQ4KBlock;
+                    if (w.rows == 2 * inter && !w.q6) {
+                        if (const int e = matmul_kq_q8(w.data, pSlots, pG, inter, w.k, m, 0, 1, stream_); e) return e;
+                        if (const int e = matmul_kq_q8(w.data + row_bytes * inter, pSlots, pU, inter, w.k, m, 0, 1, stream_); e) return e;
+                    } else {
+                        if (const int e = matmul_kq_q8(w.data, pSlots, go, w.rows, w.k, m, w.q6, 1, stream_); e) return e;
+                        go = pU;
+                    }
+                }
+                if (const int e = silu_mul(pG, pU, pG, static_cast<size_t>(m) * inter, stream_); e) return e;
+                if (const int e = quantize_cols_k(pG, pSlots, inter, m, stream_); e) return e;
+                if (const int e = matmul_kq_q8(L.wd.data, pSlots, pT, L.wd.rows, L.wd.k, m, L.wd.q6, 1, stream_); e) return e;
+            }
+            if (c0 + m < n) continue;
+            // last token: residual add, final norm, logits, greedy pick, position
+            const int st[4] = {start_pos + n - 1, 0, 0, 0};
+            CU(cudaMemcpyAsync(state, st, sizeof st, cudaMemcpyHostToDevice, stream_));
+            float* xl = pX + static_cast<size_t>(m - 1) * hidden;
+            if (const int e = add_norm_q8_fast(xl, pT + static_cast<size_t>(m - 1) * hidden, out_norm, xq, xd_of(xq, hidden), hidden, eps, stream_); e) return e;
+            if (const int e = mv(lm_head, xq, logits); e) return e;
+            if (const int e = argmax_partial(logits, vocab, cand_v, cand_i, kCand, stream_); e) return e;
+            argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, state + 1, history, state, max_ctx);
+            if (const int e = launch_status(); e) return e;
+        }
+        CU(cudaStreamSynchronize(stream_));
+        return KCB_SUCCESS;
+    }
     int sync() {
         CU(cudaStreamSynchronize(stream_));
         return KCB_SUCCESS;
@@ -676,6 +780,26 @@ public:
     long long weight_bytes = 0;
 
 private:
+    static constexpr int kPrefillChunk = 512;
+    // Scratch of the batched prompt pass for chunks of up to m tokens, allocated on first use.
+    int prefill_buffers(int m) {
+        if (m <= prefill_cap_) return KCB_SUCCESS;
+        const int cap = std::min(kPrefillChunk, std::max(m, 128));
+        const int qd = heads * hd, kv = kv_heads * hd;
+        const int maxk = std::max(std::max(hidden, inter), qd);
+        const size_t M = static_cast<size_t>(cap);
+        if (const int e = dev(reinterpret_cast<void**>(&pX), M * hidden * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&pT), M * hidden * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&pQK), M * (qd + 2 * kv) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&pV), M * kv * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&pA), M * qd * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&pG), M * inter * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&pU), M * inter * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&pSlots), M * 85 * (maxk / 256) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&pSq), M * 11 * (hidden / 32) * 4); e) return e;
+        prefill_cap_ = cap;
+        return KCB_SUCCESS;
+    }
     int dev(void** p, size_t bytes) {
         CU(cudaMalloc(p, bytes));
         owned_.push_back(*p);
@@ -810,15 +934,19 @@ private:
         return launch_status();
     }
     float* partial_out() { return tp.world == 1 ? t : tp.partial[tp.rank] + static_cast<size_t>(xchg_ & 1) * hidden; }
+    // Decode: one token at the device-side position, nsplit partials.  Prompt (direct != nullptr): n_tok query rows
+    // of stride q_stride at host-known positions pos0.., one CTA per (kv head, token), normalised output.
     template <int HD>
-    int attention(const DLayer& L) {
+    int attention(const DLayer& L, const float* q = nullptr, int q_stride = 0, int n_tok = 1, int pos0 = 0, float* direct = nullptr) {
         const int group = heads / kv_heads;
-        const dim3 grid(kv_heads, nsplit);
+        const int ns = direct ? 1 : nsplit;
+        const dim3 grid(kv_heads, ns, n_tok);
         const size_t smem = static_cast<size_t>(16) * group * (HD + 2) * 4;
         const float scale = 1.0f / std::sqrt(static_cast<float>(HD));
-        int* pos_p = state;
+        const int* pos_p = direct ? nullptr : state;
+        if (!q) q = qkv;
 #define KCB_ATTN(G_)                                                                                                        \
-    attn_partial_kernel<HD, G_><<<grid, 128, smem, stream_>>>(qkv, L.kc, L.vc, pos_p, part, heads, kv_heads, nsplit, scale, max_ctx)
+    attn_partial_kernel<HD, G_><<<grid, 128, smem, stream_>>>(q, L.kc, L.vc, pos_p, part, heads, kv_heads, ns, scale, max_ctx, q_stride, pos0, direct)
         switch (group) {
         case 1: KCB_ATTN(1); break;
         case 2: KCB_ATTN(2); break;
@@ -846,8 +974,8 @@ private:
                 if (const int e = mv(m, xq, y); e) return e;
                 y += m.rows;
             }
-            rope_kv_f16_kernel<<<(heads + 2 * kv_heads + 3) / 4, 128, 0, stream_>>>(qkv, pos_p, L.kc, L.vc, rope_ff, L.q_norm, L.k_norm, heads,
-                                                                                     kv_heads, hd, log2_base, neox, eps, max_ctx);
+            rope_kv_f16_kernel<<<(heads + 2 * kv_heads + 3) / 4, 128, 0, stream_>>>(qkv, qkv + qd + kv_heads * hd, 0, 0, pos_p, 0, L.kc, L.vc, rope_ff,
+                                                                                     L.q_norm, L.k_norm, heads, kv_heads, hd, log2_base, neox, eps, max_ctx);
             if (const int e = launch_status(); e) return e;
             if (const int e = hd == 128 ? attention<128>(L) : attention<64>(L); e) return e;
             attn_combine_q8_kernel<<<(qd / 32 + 3) / 4, 128, 0, stream_>>>(part, attn, xq_wo + wo_win.first_block * 8,
@@ -889,6 +1017,8 @@ private:
     // heads, kv_heads, inter and vocab are this rank's shares
     int hidden = 0, inter = 0, heads = 0, kv_heads = 0, hd = 0, vocab = 0, vocab_total = 0, max_ctx = 0, neox = 0, qk_norm = 0, nsplit = 1;
     TpCtx tp;
+    float *pX = nullptr, *pT = nullptr, *pQK = nullptr, *pV = nullptr, *pA = nullptr, *pG = nullptr, *pU = nullptr;
+    int *pSlots = nullptr, *pSq = nullptr, prefill_cap_ = 0;
     KWindow wo_win, wd_win;
     int xchg_ = 0;  // exchanges recorded so far in the current step (parity picks the partial buffer)
     float eps = 1e-5f, log2_base = 0.f;
@@ -948,6 +1078,13 @@ unsigned kcb_decoder_tp_timeouts(void) {
 }
 int kcb_decoder_set_prompt(void* h, const int* tokens, int n, int start_pos) {
     return h ? static_cast<Decoder*>(h)->set_prompt(tokens, n, start_pos) : kcb::KCB_INVALID_VALUE;
+}
+int kcb_decoder_prefill(void* h, const int* tokens, int n, int start_pos) {
+    if (!h) return kcb::KCB_INVALID_VALUE;
+    auto* d = static_cast<Decoder*>(h);
+    const int e = d->prefill(tokens, n, start_pos);
+    if (e != kcb::KCB_SUCCESS) kcb::tl_err = d->err_;
+    return e;
 }
 int kcb_decoder_run(void* h, int steps) { return h && steps >= 0 ? static_cast<Decoder*>(h)->run(steps) : kcb::KCB_INVALID_VALUE; }
 int kcb_decoder_sync(void* h) { return h ? static_cast<Decoder*>(h)->sync() : kcb::KCB_INVALID_VALUE; }

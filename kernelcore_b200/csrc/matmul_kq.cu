@@ -178,7 +178,8 @@ int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int nc
         const char* e = getenv("KCB_MATMUL_TC");
         return !e || atoi(e) != 0;
     }();
-    if (tc && q8k && rows % 128 == 0 && ncols >= 16)
+    // (16-byte loads of the 85 * nsb-int activation slots need nsb % 4 == 0)
+    if (tc && q8k && rows % 128 == 0 && ncols >= 16 && (k / 256) % 4 == 0)
         return q6 ? matmul_q6k_q8k_tc(w, xq, y, rows, k, ncols, s) : matmul_q4k_q8k_tc(w, xq, y, rows, k, ncols, s);
     const int nsb = k / 256, nb = nsb * 8;
     const int slot_ints = q8k ? nsb * 85 : nb * 11;

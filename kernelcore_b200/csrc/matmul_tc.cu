@@ -386,7 +386,8 @@ unsigned tc_timeouts() {
 
 // Tensor-core path for Q4_K weights and per-256 activation slots; rows must be a multiple of 128.
 int matmul_q4k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s) {
-    if (rows <= 0 || rows % TM || k <= 0 || k % 256 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
+    // k % 1024: a column's slot is 85 * k / 256 ints and is read with 16-byte loads
+    if (rows <= 0 || rows % TM || k <= 0 || k % 1024 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(matmul_q4k_q8k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
@@ -400,7 +401,8 @@ int matmul_q4k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, i
 
 // Tensor-core path for Q6_K weights (device planes) and per-256 activation slots; rows a multiple of 128.
 int matmul_q6k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s) {
-    if (rows <= 0 || rows % TM || k <= 0 || k % 256 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
+    // k % 1024: a column's slot is 85 * k / 256 ints and is read with 16-byte loads
+    if (rows <= 0 || rows % TM || k <= 0 || k % 1024 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(matmul_q6k_q8k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)

@@ -148,6 +148,14 @@ class FastDecoder:
         t = np.ascontiguousarray(tokens, np.int32)
         lib.check(lib.raw.kcb_decoder_set_prompt(self.handle, t.ctypes.data_as(C.c_void_p), int(t.size), int(start_pos)), "kcb_decoder_set_prompt")
 
+    def prefill(self, tokens, start_pos=0):
+        """Batched prompt pass (single GPU): returns once the KV cache holds the prompt and the first pick is made."""
+        t = np.ascontiguousarray(tokens, np.int32)
+        st = lib.raw.kcb_decoder_prefill(self.handle, t.ctypes.data_as(C.c_void_p), int(t.size), int(start_pos))
+        if st != 0:
+            lib.raw.kcb_decoder_last_error.restype = C.c_char_p
+            raise lib.KcbError("kcb_decoder_prefill", st, lib.raw.kcb_decoder_last_error().decode())
+
     def run(self, steps: int):
         lib.check(lib.raw.kcb_decoder_run(self.handle, int(steps)), "kcb_decoder_run")
 

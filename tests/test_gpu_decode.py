@@ -5,7 +5,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
-from helpers import OracleModel, rel_diff
+from helpers import OracleModel, oracle_prefill, rel_diff
 from kernelcore_b200 import decoder, lib, tiny_model as tm
 
 pytestmark = pytest.mark.gpu
@@ -87,3 +87,53 @@ def test_graph_decoder_against_oracle(shape_fn):
         assert int(logits_free.argmax()) == int(hist[11])
         with pytest.raises(lib.KcbError):
             d.set_prompt(list(range(49)))          # longer than the KV cache
+
+
+def _tc_shape(max_ctx):
+    # hidden and FFN multiples of 1024, matrix rows multiples of 128: every matmul of the prompt pass runs on tcgen05
+    return tm.Shape("tc-small", 1024, 2048, 2, 8, 2, 128, 512, max_ctx)
+
+
+@pytest.mark.parametrize("shape_fn,n_prompt,bound", [(tm.tiny, 3, 1e-5), (tm.tiny, 16, 1e-5), (tm.tiny_qwen, 8, 1e-5), (tm.tiny, 5, 3e-2),
+                                                     (tm.tiny, 40, 3e-2), (tm.tiny_qwen, 40, 3e-2), (tm.tiny, 530, 3e-2),
+                                                     (_tc_shape, 150, 3e-2)])
+def test_batched_prefill(shape_fn, n_prompt, bound):
+    """The batched prompt pass (per-256 activation slots, tensor-core matmuls from 16 columns up, causal attention
+    over the fp16 cache; 530 tokens = two chunks; the 256-wide models take the CUDA-core matmul because their
+    activation slots are not 16-byte multiples, the 1024-wide one the tensor cores).
+
+    Against the oracle's restatement of the same batched pipeline (helpers.oracle_prefill): same bound and
+    reasoning as the decoder test above -- a last-bit difference in the attention sums can flip one int8 of a
+    re-quantized activation, and on a 256-wide model with one scale per 256 values a single flip moves the logits
+    by 1e-2..2e-2 (prompt lengths 1, 2, 3, 8, 16 agree to 2e-7, length 5 has one such flip) -- so 3e-2 of
+    max|logit| always, and 1e-5 on the lengths without a flip.
+    Against feeding the prompt one token at a time: the two paths quantize activations differently (per 256 vs
+    per 32 values); the oracle's own two pipelines differ by 3.4e-2 on the 40-token case, so this comparison is
+    a sanity bound (1e-1) on the prompt's last logits and on steps generated on top of each cache."""
+    shape = shape_fn(max_ctx=n_prompt + 16)
+    model = tm.build(shape, seed=8)
+    prompt = [int(t) for t in np.random.default_rng(n_prompt).integers(0, shape.vocab, n_prompt)]
+    with decoder.FastDecoder(shape, model) as a, decoder.FastDecoder(shape, model) as b:
+        a.set_prompt(prompt)
+        a.run(n_prompt)
+        la, ha, pa = a.read(n_history=n_prompt)
+        b.prefill(prompt)
+        lb, hb, pb = b.read(n_history=n_prompt)
+        assert pa == pb == n_prompt
+        e_oracle = rel_diff(lb, oracle_prefill(shape, model, prompt))
+        print(f"prefill vs oracle: {e_oracle:.3e}; vs token-by-token: {rel_diff(lb, la):.3e}")
+        assert e_oracle < bound
+        assert rel_diff(lb, la) < 1e-1
+        assert int(hb[n_prompt - 1]) == int(lb.argmax())
+        # continue both from their own caches with the same forced tokens
+        cont = [int(t) for t in np.random.default_rng(1).integers(0, shape.vocab, 8)]
+        a.set_prompt(cont, start_pos=n_prompt)
+        b.set_prompt(cont, start_pos=n_prompt)
+        for _ in cont:
+            a.run(1)
+            b.run(1)
+            assert rel_diff(b.read()[0], a.read()[0]) < 1e-1
+    assert lib.raw.kcb_tc_timeouts() == 0
+    with decoder.FastDecoder(shape, model) as c:
+        with pytest.raises(lib.KcbError):
+            c.prefill(list(range(shape.max_ctx + 1)))
