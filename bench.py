@@ -469,15 +469,32 @@ def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b"):
 
     d.set_prompt(prompt)
     timed(min(4, n_prompt))
-    d.set_prompt(prompt)
-    ms_p, ms_g = timed(n_prompt), timed(n_gen)
+    prompt_mode = "token by token through the decode graph"
+    ms_tbt = None
+    if world == 1:
+        # batched prompt pass on the tensor-core matmuls; the token-by-token time is kept beside it
+        d.prefill(prompt)                                # warm-up: scratch allocation, lazy kernel loading
+        d.set_prompt(prompt)
+        ms_tbt = timed(n_prompt)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        d.prefill(prompt)
+        e1.record(stream)
+        d.sync()
+        ms_p = e0.elapsed_time(e1)
+        prompt_mode = "batched: Q8_K activation slots, tcgen05 K-quant matmuls, 512-token chunks"
+        ms_g = timed(n_gen)
+    else:
+        d.set_prompt(prompt)
+        ms_p, ms_g = timed(n_prompt), timed(n_gen)
     _, hist, _ = d.read(n_prompt + n_gen, want_logits=False)
     total_weight_bytes = tm.weight_bytes_per_token(shape)
     out = {"model": shape.name, "n_gpus": world, "prompt_tokens": n_prompt, "generated_tokens": n_gen, "prompt_tok_s": n_prompt / ms_p * 1e3,
            "decode_tok_s": n_gen / ms_g * 1e3, "us_per_token": ms_g / n_gen * 1e3, "launches_per_token": d.launches_per_token,
            "weight_bytes_per_token_this_rank": d.weight_bytes, "weight_bytes_per_token": total_weight_bytes,
            "frac_of_measured_hbm_weights_only": total_weight_bytes * (n_gen / ms_g * 1e3) / (peak * 1e9 * world),
-           "kv_cache": "fp16", "prompt_mode": "token by token through the decode graph",
+           "kv_cache": "fp16", "prompt_mode": prompt_mode,
+           "prompt_tok_s_token_by_token": (n_prompt / ms_tbt * 1e3) if ms_tbt else None,
            "picks_digest": int(np.asarray(hist, np.int64).sum() % 1000003),
            "sharding": "none" if world == 1 else f"tp{world}: heads / FFN rows / vocabulary rows; K-split wo, wd; in-kernel sum over peer loads",
            "exchange_timeouts": decoder.FastDecoder.tp_timeouts()}

@@ -199,30 +199,40 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float* __restri
 #pragma unroll
         for (int i = 0; i < DPL; ++i) acc[g][i] = 0.0f;
     }
+    // K/V rows are fetched one step ahead: the 16-byte loads of step i+1 are in flight while step i is scored
+    constexpr int NV = DPL / 8;  // 16-byte loads per lane and row
+    uint4 kn[NV], vn[NV];
+    auto fetch = [&](int t) {
+        if (t < t1) {
+            const unsigned short* kr = kc + static_cast<size_t>(t) * kvdim + kvh * HD + l8 * DPL;
+            const unsigned short* vr = vc + static_cast<size_t>(t) * kvdim + kvh * HD + l8 * DPL;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                kn[i] = *reinterpret_cast<const uint4*>(kr + 8 * i);
+                vn[i] = *reinterpret_cast<const uint4*>(vr + 8 * i);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) kn[i] = vn[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    fetch(t0 + warp * 4 + grp);
     for (int tb = t0 + warp * 4; tb < t1; tb += NW * 4) {  // warp-uniform trip count: every lane takes part in the shuffles
         const int t = tb + grp;
         const bool live = t < t1;
         float kf[DPL], vf[DPL];
-        if (live) {
-            const unsigned short* kr = kc + static_cast<size_t>(t) * kvdim + kvh * HD + l8 * DPL;
-            const unsigned short* vr = vc + static_cast<size_t>(t) * kvdim + kvh * HD + l8 * DPL;
 #pragma unroll
-            for (int i = 0; i < DPL; i += 8) {
-                const uint4 kw = *reinterpret_cast<const uint4*>(kr + i);
-                const uint4 vw = *reinterpret_cast<const uint4*>(vr + i);
-                const unsigned ku[4] = {kw.x, kw.y, kw.z, kw.w}, vu[4] = {vw.x, vw.y, vw.z, vw.w};
+        for (int i = 0; i < NV; ++i) {
+            const unsigned ku[4] = {kn[i].x, kn[i].y, kn[i].z, kn[i].w}, vu[4] = {vn[i].x, vn[i].y, vn[i].z, vn[i].w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    kf[i + 2 * j] = half_bits_to_float(ku[j] & 0xFFFFu);
-                    kf[i + 2 * j + 1] = half_bits_to_float(ku[j] >> 16);
-                    vf[i + 2 * j] = half_bits_to_float(vu[j] & 0xFFFFu);
-                    vf[i + 2 * j + 1] = half_bits_to_float(vu[j] >> 16);
-                }
+            for (int j = 0; j < 4; ++j) {
+                kf[8 * i + 2 * j] = half_bits_to_float(ku[j] & 0xFFFFu);
+                kf[8 * i + 2 * j + 1] = half_bits_to_float(ku[j] >> 16);
+                vf[8 * i + 2 * j] = half_bits_to_float(vu[j] & 0xFFFFu);
+                vf[8 * i + 2 * j + 1] = half_bits_to_float(vu[j] >> 16);
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) kf[i] = vf[i] = 0.0f;
         }
+        fetch(t + NW * 4);
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             float s = 0.0f;
