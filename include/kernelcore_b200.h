@@ -125,6 +125,16 @@ int kcb_matvec_q6k_f32(const void* planes_dev, const float* x_dev, float* y_dev,
  * llm::ref::matvecQ4KQ8K (llm/llm_reference.cpp:529-562); other cases on CUDA cores. */
 int kcb_matmul_kq_q8(const void* w_dev, const int32_t* slots_dev, float* y_dev, int rows, int k, int ncols, int q6, int q8k,
                      void* stream);
+/* The reference's synthetic weight formats and fp16 matmul (kernels/llm/matvec_q8.cu, matvec_q4.cu, matvec_q4x8.cu,
+ * matvec_q4x8_q8.cu / _q8x2.cu, matmul_f16.cu; layouts llm/llm_kernels.hpp:24-70, :284-296).  Bit-identical to
+ * llm::ref::matvecQ8 / matvecQ4 / matvecQ4x8 / matvecQ4x8Q8 / matmulF16.  `interleaved` selects the 8-row
+ * interleaved layout of llm::ref::repackQ4x8 (rows % 8 == 0); qw of kcb_matvec_q4x8_q8 is llm::ref::repackQ4x8Q8's
+ * stream, of kcb_matmul_f16 llm::ref::repackF16's. */
+int kcb_matvec_q8w(const int8_t* q_dev, const float* scales_dev, const float* x_dev, float* y_dev, int rows, int k, void* stream);
+int kcb_matvec_q4w(const uint8_t* qs_dev, const float* scales_dev, const float* x_dev, float* y_dev, int rows, int k, int interleaved,
+                   void* stream);
+int kcb_matvec_q4x8_q8(const int32_t* qw_dev, const int32_t* xq_dev, const float* xd_dev, float* y_dev, int rows, int k, void* stream);
+int kcb_matmul_f16(const int32_t* qw_dev, const float* x_dev, float* y_dev, int rows, int k, int ncols, void* stream);
 /* Bounded waits of the tensor-core kernel that expired since load (0 in a healthy process); synchronous. */
 unsigned kcb_tc_timeouts(void);
 

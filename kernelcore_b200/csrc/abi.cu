@@ -152,6 +152,18 @@ int kcb_matmul_kq_q8(const void* w, const int32_t* xq, float* y, int rows, int k
     return matmul_kq_q8(w, xq, y, rows, k, ncols, q6, q8k, st(s));
 }
 unsigned kcb_tc_timeouts(void) { return tc_timeouts(); }
+int kcb_matvec_q8w(const int8_t* q, const float* scales, const float* x, float* y, int rows, int k, void* s) {
+    return matvec_q8w(q, scales, x, y, rows, k, st(s));
+}
+int kcb_matvec_q4w(const uint8_t* qs, const float* scales, const float* x, float* y, int rows, int k, int interleaved, void* s) {
+    return matvec_q4w(qs, scales, x, y, rows, k, interleaved, st(s));
+}
+int kcb_matvec_q4x8_q8(const int32_t* qw, const int32_t* xq, const float* xd, float* y, int rows, int k, void* s) {
+    return matvec_q4x8_q8(qw, xq, xd, y, rows, k, st(s));
+}
+int kcb_matmul_f16(const int32_t* qw, const float* x, float* y, int rows, int k, int ncols, void* s) {
+    return matmul_f16(qw, x, y, rows, k, ncols, st(s));
+}
 int kcb_matvec_q6k_q8_gather(const void* w, const int32_t* xq, const float* xd, float* y_local, float* const* y_peers, int npeers,
                              int rows, int k, void* s) {
     return matvec_q6k_q8_gather(w, xq, xd, y_local, y_peers, npeers, rows, k, st(s));

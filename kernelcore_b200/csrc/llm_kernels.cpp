@@ -347,7 +347,52 @@ int k_fa_values(const void* p, const RangeChecker& rc, cudaStream_t s) {
     faDimsInts(d, dims);
     return fa_stage(3, nullptr, nullptr, a.v, nullptr, const_cast<float*>(a.p), nullptr, a.out, dims, 0.f, s);
 }
-int k_unbuilt(const void*, const RangeChecker&, cudaStream_t) { return KCB_UNSUPPORTED_OPERATION; }
+// The synthetic weight formats (llm/llm_kernels.cpp:110-262 of the reference validate the same extents).
+int k_matvec_q8w(const void* p, const RangeChecker& rc, cudaStream_t s) {
+    const auto& a = *static_cast<const MatvecQ8Args*>(p);
+    if (a.rows < 0 || a.k <= 0 || a.k % 32 || !fits(a.rows, a.k)) return KCB_INVALID_VALUE;
+    const long long nb = a.k / 32;
+    TRY(rc.check(a.q, static_cast<size_t>(a.rows) * a.k, "q"));
+    TRY(rc.check(a.scales, f32(a.rows * nb), "scales"));
+    TRY(rc.check(a.x, f32(a.k), "x"));
+    TRY(rc.check(a.y, f32(a.rows), "y"));
+    TRY(rc.check(a.dims, 2 * sizeof(int), "dims"));
+    return matvec_q8w(a.q, a.scales, a.x, a.y, a.rows, a.k, s);
+}
+template <bool kInterleaved>
+int k_matvec_q4w(const void* p, const RangeChecker& rc, cudaStream_t s) {
+    const auto& a = *static_cast<const MatvecQ4Args*>(p);
+    if (a.rows < 0 || (kInterleaved && a.rows % 8) || a.k <= 0 || a.k % 32 || !fits(a.rows, a.k)) return KCB_INVALID_VALUE;
+    const long long nb = a.k / 32;
+    TRY(rc.check(a.qs, static_cast<size_t>(a.rows) * (a.k / 2), "qs"));
+    TRY(rc.check(a.scales, f32(a.rows * nb), "scales"));
+    TRY(rc.check(a.x, f32(a.k), "x"));
+    TRY(rc.check(a.y, f32(a.rows), "y"));
+    TRY(rc.check(a.dims, 2 * sizeof(int), "dims"));
+    return matvec_q4w(a.qs, a.scales, a.x, a.y, a.rows, a.k, kInterleaved, s);
+}
+template <int kRowMult>  // matvec_q4x8_q8x2 is the same arithmetic with rows % 16 == 0
+int k_matvec_q4x8_q8(const void* p, const RangeChecker& rc, cudaStream_t s) {
+    const auto& a = *static_cast<const MatvecQ4Q8Args*>(p);
+    if (a.rows < 0 || a.rows % kRowMult || a.k <= 0 || a.k % 32 || !fits(a.rows, a.k)) return KCB_INVALID_VALUE;
+    const long long nb = a.k / 32;
+    TRY(rc.check(a.qw, static_cast<size_t>(a.rows) * a.k * 5 / 8, "qw"));
+    TRY(rc.check(a.xq, i32(nb * 8), "xq"));
+    TRY(rc.check(a.xd, f32(nb * 2), "xd"));
+    TRY(rc.check(a.y, f32(a.rows), "y"));
+    TRY(rc.check(a.dims, 2 * sizeof(int), "dims"));
+    return matvec_q4x8_q8(a.qw, a.xq, a.xd, a.y, a.rows, a.k, s);
+}
+int k_matmul_f16(const void* p, const RangeChecker& rc, cudaStream_t s) {  // llm/llm_kernels.cpp:835-850
+    const auto& a = *static_cast<const MatmulF16Args*>(p);
+    if (a.rows <= 0 || a.rows % 8 || a.k <= 0 || a.k % 2 || a.ncols <= 0 || !fits(a.rows, a.k) || !fits(a.k, a.ncols) || !fits(a.rows, a.ncols))
+        return KCB_INVALID_VALUE;
+    TRY(rc.check(a.qw, i32(static_cast<long long>(a.rows) * (a.k / 2)), "qw"));
+    TRY(rc.check(a.x, f32(static_cast<long long>(a.k) * a.ncols), "x"));
+    TRY(rc.check(a.y, f32(static_cast<long long>(a.rows) * a.ncols), "y"));
+    TRY(rc.check(a.dims, 3 * sizeof(int), "dims"));
+    return matmul_f16(a.qw, a.x, a.y, a.rows, a.k, a.ncols, s);
+}
 
 const KernelDesc kTable[] = {
     {"vector_add", &k_vector_add},
@@ -390,14 +435,12 @@ const KernelDesc kTable[] = {
     {"fa_max", &k_fa_max},
     {"fa_exp", &k_fa_exp},
     {"fa_values", &k_fa_values},
-    // Names of the reference's table that this build does not implement yet: launching them reports
-    // UnsupportedOperation instead of KernelNotFound.
-    {"matvec_q8", &k_unbuilt},
-    {"matvec_q4", &k_unbuilt},
-    {"matvec_q4x8", &k_unbuilt},
-    {"matvec_q4x8_q8", &k_unbuilt},
-    {"matvec_q4x8_q8x2", &k_unbuilt},
-    {"matmul_f16", &k_unbuilt},
+    {"matvec_q8", &k_matvec_q8w},
+    {"matvec_q4", &k_matvec_q4w<false>},
+    {"matvec_q4x8", &k_matvec_q4w<true>},
+    {"matvec_q4x8_q8", &k_matvec_q4x8_q8<8>},
+    {"matvec_q4x8_q8x2", &k_matvec_q4x8_q8<16>},
+    {"matmul_f16", &k_matmul_f16},
 
 };
 constexpr int kCount = sizeof(kTable) / sizeof(kTable[0]);

@@ -65,4 +65,10 @@ int flash_attn_f16(const float* q, const void* k, const void* v, const void* mas
 int fa_stage(int which, const float* q, const void* k, const void* v, const void* mask, float* s_buf, float* m_buf, float* out,
              const int* dims15, float scale, cudaStream_t s);
 
+// synthetic_formats.cu
+int matvec_q8w(const int8_t* q, const float* scales, const float* x, float* y, int rows, int k, cudaStream_t s);
+int matvec_q4w(const uint8_t* qs, const float* scales, const float* x, float* y, int rows, int k, int interleaved, cudaStream_t s);
+int matvec_q4x8_q8(const int* qw, const int* xq, const float* xd, float* y, int rows, int k, cudaStream_t s);
+int matmul_f16(const int* qw, const float* x, float* y, int rows, int k, int ncols, cudaStream_t s);
+
 }  // namespace kcb

@@ -23,6 +23,7 @@ _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
 _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 _u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
 _i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
+_i8p = np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS")
 
 
 class AttnDims(C.Structure):
@@ -87,6 +88,14 @@ def _sig(lib, prefix):
     f("norm_mul_q8k", None, _f32p, _f32p, _f32p, _i32p, _i32p, i, i, fl)
     f("silu_mul_q8f", None, _f32p, _f32p, _f32p, _i32p, i, i)
     f("silu_mul_q8k", None, _f32p, _f32p, _f32p, _i32p, i, i)
+    f("matvec_q8w", None, _i8p, _f32p, _f32p, _f32p, i, i)
+    f("matvec_q4w", None, _u8p, _f32p, _f32p, _f32p, i, i)
+    f("repack_q4x8", None, _u8p, _f32p, _u8p, _f32p, i, i)
+    f("matvec_q4x8", None, _u8p, _f32p, _f32p, _f32p, i, i)
+    f("repack_q4x8_q8", None, _u8p, _f32p, _i32p, i, i)
+    f("matvec_q4x8_q8", None, _i32p, _i32p, _f32p, _f32p, i, i)
+    f("repack_f16", None, _u16p, i, i, _i32p)
+    f("matmul_f16", None, _u16p, _f32p, _f32p, i, i, i)
     f("set_rows_f16", None, _f32p, _i64p, _u16p, i, i, i, i, i)
     f("flash_attn_f16", None, _f32p, _u16p, _u16p, _u16p, _f32p, C.POINTER(FaDims), fl)
 

@@ -647,6 +647,132 @@ void kqo_flash_attn_f16(const float* q, const uint16_t* k, const uint16_t* v, co
     free(s);
 }
 
+/* ---- synthetic 8-bit / 4-bit formats of the reference's own benchmark models and fp16 weights --------- */
+
+/* ref:10-23 -- int8 weights [rows][k], one float scale per 32. */
+void kqo_matvec_q8w(const int8_t* q, const float* scales, const float* x, float* y, int rows, int k) {
+    const int nb = k / 32;
+    for (int row = 0; row < rows; ++row) {
+        float acc = 0.0f;
+        for (int b = 0; b < nb; ++b) {
+            float s = 0.0f;
+            for (int j = 0; j < 32; ++j) s += (float)q[(size_t)row * k + (size_t)b * 32 + j] * x[(size_t)b * 32 + j];
+            acc += s * scales[(size_t)row * nb + b];
+        }
+        y[row] = acc;
+    }
+}
+
+/* ref:25-42 -- 4-bit weights, ggml Q4_0 nibble order with a float scale: byte j of a block holds weight j
+ * (low nibble) and j + 16 (high), each biased by 8. */
+void kqo_matvec_q4w(const uint8_t* qs, const float* scales, const float* x, float* y, int rows, int k) {
+    const int nb = k / 32;
+    for (int row = 0; row < rows; ++row) {
+        float acc = 0.0f;
+        for (int b = 0; b < nb; ++b) {
+            float s = 0.0f;
+            const uint8_t* qb = qs + (size_t)row * (k / 2) + (size_t)b * 16;
+            for (int j = 0; j < 16; ++j) {
+                s += (float)((qb[j] & 15) - 8) * x[(size_t)b * 32 + j];
+                s += (float)((qb[j] >> 4) - 8) * x[(size_t)b * 32 + j + 16];
+            }
+            acc += s * scales[(size_t)row * nb + b];
+        }
+        y[row] = acc;
+    }
+}
+
+/* ref:66-77 -- the same blocks interleaved over groups of 8 rows: byte j of row l of block (g, b) at
+ * qs8[((g*nb + b)*16 + j)*8 + l], its scale at scales8[(g*nb + b)*8 + l]. */
+void kqo_repack_q4x8(const uint8_t* qs, const float* scales, uint8_t* qs8, float* scales8, int rows, int k) {
+    const int nb = k / 32;
+    for (int row = 0; row < rows; ++row)
+        for (int b = 0; b < nb; ++b) {
+            const size_t blk = (size_t)(row / 8) * nb + b;
+            for (int j = 0; j < 16; ++j) qs8[(blk * 16 + j) * 8 + row % 8] = qs[(size_t)row * (k / 2) + (size_t)b * 16 + j];
+            scales8[blk * 8 + row % 8] = scales[(size_t)row * nb + b];
+        }
+}
+
+/* ref:44-64 -- four partial sums per block, combined as (s0 + s2) + (s1 + s3). */
+void kqo_matvec_q4x8(const uint8_t* qs8, const float* scales8, const float* x, float* y, int rows, int k) {
+    const int nb = k / 32;
+    for (int row = 0; row < rows; ++row) {
+        float acc = 0.0f;
+        for (int b = 0; b < nb; ++b) {
+            const size_t blk = (size_t)(row / 8) * nb + b;
+            const uint8_t* qb = qs8 + blk * 128 + row % 8;
+            const float* xb = x + (size_t)b * 32;
+            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+            for (int j = 0; j < 16; j += 2) {
+                const int v0 = qb[j * 8], v1 = qb[j * 8 + 8];
+                s0 += (float)((v0 & 15) - 8) * xb[j];
+                s1 += (float)((v0 >> 4) - 8) * xb[j + 16];
+                s2 += (float)((v1 & 15) - 8) * xb[j + 1];
+                s3 += (float)((v1 >> 4) - 8) * xb[j + 17];
+            }
+            acc += ((s0 + s2) + (s1 + s3)) * scales8[blk * 8 + row % 8];
+        }
+        y[row] = acc;
+    }
+}
+
+/* ref:137-152 -- 40 words per (8-row group, block): 4 x 8 quant words (word w of row l at [w*8 + l]), then the
+ * 8 float scales. */
+void kqo_repack_q4x8_q8(const uint8_t* qs, const float* scales, int32_t* qw, int rows, int k) {
+    const int nb = k / 32;
+    for (int row = 0; row < rows; ++row)
+        for (int b = 0; b < nb; ++b) {
+            int32_t* blk = qw + ((size_t)(row / 8) * nb + b) * 40;
+            const uint8_t* src = qs + (size_t)row * (k / 2) + (size_t)b * 16;
+            for (int w = 0; w < 4; ++w) blk[w * 8 + row % 8] = ld32(src + 4 * w);
+            memcpy(blk + 32 + row % 8, &scales[(size_t)row * nb + b], 4);
+        }
+}
+
+/* ref:114-135 -- integer dot against Q8 activations; the +8 bias leaves through the activation sum. */
+void kqo_matvec_q4x8_q8(const int32_t* qw, const int32_t* xq, const float* xd, float* y, int rows, int k) {
+    const int nb = k / 32;
+    for (int row = 0; row < rows; ++row) {
+        float acc = 0.0f;
+        for (int b = 0; b < nb; ++b) {
+            const int32_t* blk = qw + ((size_t)(row / 8) * nb + b) * 40;
+            int32_t lo = 0, hi = 0;
+            for (int w = 0; w < 4; ++w) {
+                const int32_t q = blk[w * 8 + row % 8];
+                lo = dot4_u8s8(q & 0x0F0F0F0F, xq[(size_t)b * 8 + w], lo);
+                hi = dot4_u8s8(asr(q, 4) & 0x0F0F0F0F, xq[(size_t)b * 8 + 4 + w], hi);
+            }
+            float sc;
+            memcpy(&sc, blk + 32 + row % 8, 4);
+            const int32_t dot = lo + hi - 8 * (int32_t)xd[(size_t)b * 2 + 1];
+            acc += (float)dot * (sc * xd[(size_t)b * 2]);
+        }
+        y[row] = acc;
+    }
+}
+
+/* ref:740-746 -- fp16 weights as 32-bit words (two halves), interleaved over groups of 8 rows. */
+void kqo_repack_f16(const uint16_t* w, int rows, int k, int32_t* out) {
+    const int kw = k / 2;
+    for (int r = 0; r < rows; ++r)
+        for (int j = 0; j < kw; ++j)
+            out[((size_t)(r / 8) * kw + j) * 8 + r % 8] =
+                (int32_t)((uint32_t)w[(size_t)r * k + 2 * j] | ((uint32_t)w[(size_t)r * k + 2 * j + 1] << 16));
+}
+
+/* ref:756-764 -- Y[c*rows + r] = sum over pairs of (w0 x0 + w1 x1), on the row-major fp16 matrix. */
+void kqo_matmul_f16(const uint16_t* w, const float* x, float* y, int rows, int k, int ncols) {
+    for (int c = 0; c < ncols; ++c)
+        for (int r = 0; r < rows; ++r) {
+            float a = 0.0f;
+            for (int j = 0; j < k; j += 2)
+                a += kqo_f16_to_f32(w[(size_t)r * k + j]) * x[(size_t)c * k + j] +
+                     kqo_f16_to_f32(w[(size_t)r * k + j + 1]) * x[(size_t)c * k + j + 1];
+            y[(size_t)c * rows + r] = a;
+        }
+}
+
 /* ---- decode step ---------------------------------------------------------------- */
 
 static int pad8(int n) { return (n + 7) / 8 * 8; }

@@ -91,6 +91,17 @@ void kqo_set_rows_f16(const float* src, const int64_t* idx, uint16_t* dst, int p
 void kqo_flash_attn_f16(const float* q, const uint16_t* k, const uint16_t* v, const uint16_t* mask, float* out,
                         const kqo_fa_dims* d, float scale);
 
+/* The reference's synthetic 8-bit / 4-bit benchmark formats and fp16 weights (llm_reference.cpp:10-77, :114-152,
+ * :740-764).  The *x8 layouts interleave 8 rows; kqo_repack_* build them from the row-major form. */
+void kqo_matvec_q8w(const int8_t* q, const float* scales, const float* x, float* y, int rows, int k);
+void kqo_matvec_q4w(const uint8_t* qs, const float* scales, const float* x, float* y, int rows, int k);
+void kqo_repack_q4x8(const uint8_t* qs, const float* scales, uint8_t* qs8, float* scales8, int rows, int k);
+void kqo_matvec_q4x8(const uint8_t* qs8, const float* scales8, const float* x, float* y, int rows, int k);
+void kqo_repack_q4x8_q8(const uint8_t* qs, const float* scales, int32_t* qw, int rows, int k);
+void kqo_matvec_q4x8_q8(const int32_t* qw, const int32_t* xq, const float* xd, float* y, int rows, int k);
+void kqo_repack_f16(const uint16_t* w, int rows, int k, int32_t* out);
+void kqo_matmul_f16(const uint16_t* w, const float* x, float* y, int rows, int k, int ncols);
+
 /* One matrix of a decode model: GGUF blocks, row-major.  fmt: 4 = Q4_K, 6 = Q6_K. */
 typedef struct {
     const uint8_t* blocks;

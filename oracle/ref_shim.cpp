@@ -110,6 +110,28 @@ void kcref_matvec_stream_q8k(const int32_t* qw, const int32_t* xq, float* y, int
     else llm::ref::matvecQ4KQ8K(qw, xq, y, rows, k);
 }
 
+void kcref_matvec_q8w(const int8_t* q, const float* scales, const float* x, float* y, int rows, int k) {
+    llm::ref::matvecQ8(q, scales, x, y, rows, k);
+}
+void kcref_matvec_q4w(const uint8_t* qs, const float* scales, const float* x, float* y, int rows, int k) {
+    llm::ref::matvecQ4(qs, scales, x, y, rows, k);
+}
+void kcref_repack_q4x8(const uint8_t* qs, const float* scales, uint8_t* qs8, float* scales8, int rows, int k) {
+    llm::ref::repackQ4x8(qs, scales, qs8, scales8, rows, k);
+}
+void kcref_matvec_q4x8(const uint8_t* qs8, const float* scales8, const float* x, float* y, int rows, int k) {
+    llm::ref::matvecQ4x8(qs8, scales8, x, y, rows, k);
+}
+void kcref_repack_q4x8_q8(const uint8_t* qs, const float* scales, int32_t* qw, int rows, int k) {
+    llm::ref::repackQ4x8Q8(qs, scales, qw, rows, k);
+}
+void kcref_matvec_q4x8_q8(const int32_t* qw, const int32_t* xq, const float* xd, float* y, int rows, int k) {
+    llm::ref::matvecQ4x8Q8(qw, xq, xd, y, rows, k);
+}
+void kcref_repack_f16(const uint16_t* w, int rows, int k, int32_t* out) { llm::ref::repackF16(w, rows, k, out); }
+void kcref_matmul_f16(const uint16_t* w, const float* x, float* y, int rows, int k, int ncols) {
+    llm::ref::matmulF16(w, x, y, rows, k, ncols);
+}
 void kcref_matvec_q4k_q8(const uint8_t* w, const int32_t* xq, const float* xd, float* y, int rows, int k) {
     llm::ref::matvecQ4KQ8(stream(w, rows, k, 0).data(), xq, xd, y, rows, k);
 }

@@ -10,7 +10,7 @@ import oracle
 
 def bits(a):
     a = np.ascontiguousarray(a)
-    return a.view({4: np.uint32, 2: np.uint16, 8: np.uint64}[a.dtype.itemsize])
+    return a.view({1: np.uint8, 4: np.uint32, 2: np.uint16, 8: np.uint64}[a.dtype.itemsize])
 
 
 def bit_equal(a, b) -> bool:

@@ -152,3 +152,39 @@ def test_port_equals_reference_library_on_fresh_inputs():
         xq, xd = oracle.quantize_q8x4(lib, x)
         assert xd[0] == 0 and (xq[:8] == 0).all()
     assert bit_equal(oracle.quantize_q8x4(port, x)[0], oracle.quantize_q8x4(ref, x)[0])
+
+
+def test_synthetic_formats_port_equals_reference():
+    """The reference's 8-bit / 4-bit benchmark formats and fp16 matmul (llm/llm_reference.cpp:10-77, :114-152,
+    :740-764): the restatement against the compiled reference, bit for bit, repacks included."""
+    rng = np.random.default_rng(21)
+    rows, k, nb = 24, 96, 3
+    x = rng.standard_normal(k).astype(np.float32)
+    scales = rng.uniform(0.01, 0.1, rows * nb).astype(np.float32)
+    q8 = rng.integers(-127, 128, rows * k, dtype=np.int8)
+    qs = rng.integers(0, 256, rows * k // 2, dtype=np.uint8)
+    out = {}
+    for name, L in (("port", oracle.port), ("ref", oracle.ref)):
+        y8, y4, y48, y48q = (np.zeros(rows, np.float32) for _ in range(4))
+        L.matvec_q8w(q8, scales, x, y8, rows, k)
+        L.matvec_q4w(qs, scales, x, y4, rows, k)
+        qs8, sc8 = np.zeros_like(qs), np.zeros_like(scales)
+        L.repack_q4x8(qs, scales, qs8, sc8, rows, k)
+        L.matvec_q4x8(qs8, sc8, x, y48, rows, k)
+        qw = np.zeros(rows * nb * 5, np.int32)
+        L.repack_q4x8_q8(qs, scales, qw, rows, k)
+        xq, xd = oracle.quantize_q8x4(L, x)
+        L.matvec_q4x8_q8(qw, xq, xd, y48q, rows, k)
+        rng = np.random.default_rng(22)      # the same fp16 matrix and X for both libraries
+        w16 = rng.integers(0, 0x7C00, rows * k).astype(np.uint16) | (rng.integers(0, 2, rows * k).astype(np.uint16) << 15)
+        X = rng.standard_normal((5, k)).astype(np.float32)
+        yf = np.zeros((5, rows), np.float32)
+        L.matmul_f16(w16, X, yf, rows, k, 5)
+        st = np.zeros(rows * k // 2, np.int32)
+        L.repack_f16(w16, rows, k, st)
+        out[name] = (y8, y4, qs8, sc8, y48, qw, y48q, yf, st)
+    for a, b in zip(out["port"], out["ref"]):
+        assert bit_equal(a, b)
+    # the interleaved forms compute what the row-major form does (different summation order for q4x8)
+    assert np.abs(out["port"][4] - out["port"][1]).max() < 1e-4 * np.abs(out["port"][1]).max()
+    assert np.abs(out["port"][6] - out["port"][1]).max() < 3e-2 * np.abs(out["port"][1]).max()
