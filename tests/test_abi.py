@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "kernelcore_b200.h")).read()
+    text = "".join(open(os.path.join(ROOT, "include", h)).read() for h in ("kernelcore_b200.h", "ggml-kernelcore-ops.h"))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(kcb_\w+)\s*\(", text)))
 
@@ -41,7 +41,7 @@ def test_error_codes_match_reference_numbering():
 def test_headers_compile_as_plain_cxx(tmp_path):
     """The public headers must compile with a host compiler alone (no CUDA), like the reference's."""
     src = tmp_path / "t.cpp"
-    src.write_text('#include <kernelcore/api.hpp>\n#include <llm_kernels.hpp>\n#include <llm_model.hpp>\n#include <kernelcore_b200.h>\n'
+    src.write_text('#include <kernelcore/api.hpp>\n#include <llm_kernels.hpp>\n#include <llm_model.hpp>\n#include <kernelcore_b200.h>\n#include <ggml-kernelcore-ops.h>\n'
                    'static_assert(sizeof(llm::MatvecQ4Q8Args) == 48, "");\nstatic_assert(sizeof(llm::AttnDims) == 28, "");\n'
                    'static_assert(llm::scratchInts(96) == 1056 && llm::scratchKInts(12) == 1020, "");\nint main() { return 0; }\n')
     inc = os.path.join(ROOT, "include")
