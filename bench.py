@@ -346,6 +346,7 @@ def run_ours(args):
         torch.cuda.empty_cache()
         line["extra"] = {"q4k_matvec_config0": q4k_config0(torch, kquant, synth, peak),
                          "q4k_matmul_config2": matmul_bench(),
+                         "q6k_matmul_ffn_down_3072x8192": matmul_bench((512,), q6=True),
                          "decode_llama32_3b": decode_bench(640, 512, 128, peak)[0]}
     print(json.dumps(line))
     if world > 1:
@@ -385,14 +386,15 @@ def q4k_config0(torch, kquant, synth, peak):
             "protocol": f"{n} launches in one CUDA graph over {nmat} rotating matrices, median of 5 replays"}
 
 
-def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5):
+def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5, q6=False):
     """BASELINE configs[2]: Y[M x 8192] = X[M x 3072] . W^T, W Q4_K; X quantized on the fly to per-256 int8 slots
-    (quantize_cols_k) and contracted on the tensor cores (tcgen05 int8).  One step = quantize + matmul."""
+    (quantize_cols_k) and contracted on the tensor cores (tcgen05 int8).  One step = quantize + matmul.
+    q6: the Q6_K kernel on the FFN-down shape of the same model, 3072 x 8192."""
     import torch
 
     from kernelcore_b200 import kquant, lib, synth
-    rows, k = 8192, 3072
-    w = kquant.KMatrix(synth.q4k_blocks(rows, k, 0), rows, k, False)
+    rows, k = (3072, 8192) if q6 else (8192, 3072)
+    w = kquant.KMatrix(synth.kquant_blocks(rows, k, 0, q6), rows, k, q6)
     peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
     bf16 = float(peaks.get("bf16_tflops", 1590.0))
     out = {}
@@ -403,7 +405,7 @@ def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5):
 
         def step():
             lib.call("quantize_cols_k", X, slots, k, M)
-            lib.call("matmul_kq_q8", w.data, slots, y, rows, k, M, 0, 1)
+            lib.call("matmul_kq_q8", w.data, slots, y, rows, k, M, int(q6), 1)
         for _ in range(3):
             step()
         torch.cuda.synchronize()
@@ -423,7 +425,7 @@ def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5):
     return out
 
 
-def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b"):
+def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b", lean=False):
     """BASELINE configs[3] (or [4] with model="qwen3_8b"): random-init model, Q4_K_M mix, batch 1, fp16 KV cache,
     greedy.  The prompt is processed token by token through the same graph (no batched prefill yet).
     Under torchrun (WORLD_SIZE > 1) the ranks run the tensor-parallel decoder: heads, FFN rows and vocabulary rows
@@ -474,8 +476,9 @@ def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b"):
     if world == 1:
         # batched prompt pass on the tensor-core matmuls; the token-by-token time is kept beside it
         d.prefill(prompt)                                # warm-up: scratch allocation, lazy kernel loading
-        d.set_prompt(prompt)
-        ms_tbt = timed(n_prompt)
+        if not lean:
+            d.set_prompt(prompt)
+            ms_tbt = timed(n_prompt)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         d.prefill(prompt)
@@ -507,7 +510,7 @@ def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b"):
 
 def run_decode(args):
     peak, _ = measured_peak()
-    out, rank = decode_bench(max(64, args.prompt + args.gen), args.prompt, args.gen, peak, args.model)
+    out, rank = decode_bench(max(64, args.prompt + args.gen), args.prompt, args.gen, peak, args.model, args.lean)
     if rank == 0:
         cfg = "configs[4]" if args.model == "qwen3_8b" else "configs[3]"
         print(json.dumps({"metric": f"{args.model}_decode_tok_s", "value": out["decode_tok_s"], "unit": "tokens/s", "n_gpus": out["n_gpus"],
@@ -526,6 +529,8 @@ def main():
                     help="lm_head: the benchmark line; decode: Llama-3.2-3B-shape decode only (profiling, quick checks)")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=128)
+    ap.add_argument("--q6", action="store_true", help="--workload matmul: the Q6_K tensor-core kernel (3072 x 8192) instead of Q4_K")
+    ap.add_argument("--lean", action="store_true", help="--workload decode: skip the token-by-token prompt timing (short launch lists for profiling)")
     ap.add_argument("--model", default="llama32_3b", choices=["llama32_3b", "qwen3_8b"], help="--workload decode: which architecture")
     ap.add_argument("--nccl-gather", action="store_true", help="N > 1: use an NCCL all-gather instead of the fused peer stores")
     ap.add_argument("--rows", type=int, default=ROWS, help="shrink the matrix (profiling captures only; the bench line is the default size)")
@@ -535,7 +540,8 @@ def main():
     if args.workload == "decode":
         run_decode(args)
     elif args.workload == "matmul":
-        print(json.dumps({"metric": "q4k_matmul_tflops", "unit": "TFLOP/s", "n_gpus": 1, "data": "synthetic", "detail": matmul_bench((args.prompt,), reps=2)}))
+        print(json.dumps({"metric": ("q6k" if args.q6 else "q4k") + "_matmul_tflops", "unit": "TFLOP/s", "n_gpus": 1, "data": "synthetic",
+                          "detail": matmul_bench((args.prompt,), reps=2, q6=args.q6)}))
     elif args.impl == "reference":
         run_reference(args)
     else:

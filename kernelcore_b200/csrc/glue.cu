@@ -70,16 +70,24 @@ __global__ void add_norm_q8_kernel(const float* __restrict__ a, const float* __r
     const float* ar = a + static_cast<size_t>(row) * n;
     float* orow = out ? out + static_cast<size_t>(row) * n : nullptr;
     if (phases & 1) {
-        for (int b = threadIdx.x; b < nb; b += blockDim.x) {
-            float s = 0.0f;
-            for (int i = 0; i < 32; ++i) {
-                float v = ar[b * 32 + i];
-                if (t) v = __fadd_rn(v, t[static_cast<size_t>(row) * n + b * 32 + i]);
-                if (orow) orow[b * 32 + i] = v;
-                s = __fadd_rn(s, __fmul_rn(v, v));
+        // a warp per block of 32: coalesced add and store, then one lane adds the 32 squares in index order
+        // out of shared memory (the reference's order; the other 31 lanes have nothing to add to it)
+        for (int b = warp; b < nb; b += nw) {
+            float v = ar[b * 32 + lane];
+            if (t) v = __fadd_rn(v, t[static_cast<size_t>(row) * n + b * 32 + lane]);
+            if (orow) orow[b * 32 + lane] = v;
+            sh[b * 32 + lane] = v;
+            __syncwarp();
+            if (lane == 0) {
+                float s = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float x = sh[b * 32 + i];
+                    s = __fadd_rn(s, __fmul_rn(x, x));
+                }
+                ss[b] = s;
+                part[b] = s;
             }
-            ss[b] = s;
-            part[b] = s;
         }
     } else {
         for (int b = threadIdx.x; b < nb; b += blockDim.x) part[b] = ss[b];

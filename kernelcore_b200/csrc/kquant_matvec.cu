@@ -865,11 +865,6 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
     }
 }
 
-int env_int(const char* name, int dflt) {
-    const char* e = getenv(name);
-    return e ? atoi(e) : dflt;
-}
-
 template <bool kQ6, int ITERS, int TR, int RPW>
 int launch_tma_cfg(const uint8_t* wb, const int* xq, const float* xd, float* y, int rows, int nsb, cudaStream_t s, const PeerOut& peers,
                    const float* xf32) {
@@ -877,8 +872,6 @@ int launch_tma_cfg(const uint8_t* wb, const int* xq, const float* xd, float* y, 
     const size_t stage_bytes = static_cast<size_t>(TR) * nsb * (kQ6 ? kQ6KBlock : kQ4KBlock);
     int stages = static_cast<int>((226 * 1024 - 128 - kProlBytes) / stage_bytes);  // 227 KB of shared memory per CTA on sm_100
     if (stages > kTmaMaxStages) stages = kTmaMaxStages;
-    static const int forced = env_int("KCB_TMA_STAGES", 0);
-    if (forced > 0 && forced < stages) stages = forced;
     if (stages < 2) return KCB_UNSUPPORTED_OPERATION;
     const size_t smem = 128 + kProlBytes + stages * stage_bytes;
     static bool attr_set = false;  // per instantiation
@@ -923,14 +916,6 @@ int ctas_per_sm(Kern kern, size_t smem) {
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem) != cudaSuccess || n < 1) n = 1;
     return n;
-}
-
-int env_variant() {
-    static const int v = [] {
-        const char* e = getenv("KCB_MATVEC_VARIANT");
-        return e ? atoi(e) : 0;
-    }();
-    return v;
 }
 
 template <class Kern>
@@ -1043,13 +1028,8 @@ unsigned tma_timeouts() {
 
 #define KCB_LAUNCH_REG(KERN, ITERS_)                                                                         \
     do {                                                                                                     \
-        if (pf) {                                                                                            \
-            auto kern = KERN<ITERS_, true>;                                                                  \
-            kern<<<grid_for(kern, rows, kWarps), kThreads, 0, s>>>(wb, xq, xd, y, rows, nsb);                \
-        } else {                                                                                             \
-            auto kern = KERN<ITERS_, false>;                                                                 \
-            kern<<<grid_for(kern, rows, kWarps), kThreads, 0, s>>>(wb, xq, xd, y, rows, nsb);                \
-        }                                                                                                    \
+        auto kern = KERN<ITERS_, true>;                                                                      \
+        kern<<<grid_for(kern, rows, kWarps), kThreads, 0, s>>>(wb, xq, xd, y, rows, nsb);                    \
     } while (0)
 
 int matvec_q4k_q8(const void* w, const int* xq, const float* xd, float* y, int rows, int k, cudaStream_t s) {
@@ -1057,9 +1037,8 @@ int matvec_q4k_q8(const void* w, const int* xq, const float* xd, float* y, int r
     if (rows == 0) return KCB_SUCCESS;
     const int nsb = k / 256, iters = (nsb + 3) / 4;
     const uint8_t* wb = static_cast<const uint8_t*>(w);
-    const bool pf = env_variant() != 1;
-    if (use_tma(rows, nsb) && env_variant() == 0) return launch_tma_iters<false>(wb, xq, xd, y, rows, nsb, s);
-    if (iters <= 4 && env_variant() != 2) {
+    if (use_tma(rows, nsb)) return launch_tma_iters<false>(wb, xq, xd, y, rows, nsb, s);
+    if (iters <= 4) {
         switch (iters) {
         case 1: KCB_LAUNCH_REG(matvec_q4k_q8_reg_kernel, 1); break;
         case 2: KCB_LAUNCH_REG(matvec_q4k_q8_reg_kernel, 2); break;
@@ -1081,9 +1060,8 @@ int matvec_q6k_q8(const void* w, const int* xq, const float* xd, float* y, int r
     if (rows == 0) return KCB_SUCCESS;
     const int nsb = k / 256, iters = (nsb + 3) / 4;
     const uint8_t* wb = static_cast<const uint8_t*>(w);
-    const bool pf = env_variant() != 1;
-    if (use_tma(rows, nsb) && env_variant() == 0) return launch_tma_iters<true>(wb, xq, xd, y, rows, nsb, s);
-    if (iters <= 4 && env_variant() != 2) {
+    if (use_tma(rows, nsb)) return launch_tma_iters<true>(wb, xq, xd, y, rows, nsb, s);
+    if (iters <= 4) {
         switch (iters) {
         case 1: KCB_LAUNCH_REG(matvec_q6k_q8_reg_kernel, 1); break;
         case 2: KCB_LAUNCH_REG(matvec_q6k_q8_reg_kernel, 2); break;

@@ -147,7 +147,10 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const ui
         // ---- activation bytes, sums and scales of this super-block ----
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
-            const int i = tid + kThreads * it, col = i >> 4, part = i & 15;  // part = 2 * K-step + 16-byte half
+            // part = 2 * K-step + 16-byte half.  Lanes: 8 neighbouring columns x 4 neighbouring parts, so a warp's
+            // global reads are 64-byte runs and its shared-memory stores collide 4 ways instead of 16
+            const int i = tid + kThreads * it;
+            const int col = (i & 7) + 8 * (i >> 7), part = ((i >> 3) & 3) + 4 * ((i >> 5) & 3);
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (c_tile + col < ncols) v = __ldg(reinterpret_cast<const uint4*>(xq + static_cast<size_t>(c_tile + col) * slot_ints + sb * 64 + part * 4));
             *reinterpret_cast<uint4*>(sm + kOffBx + (part >> 1) * kSlab + (col >> 3) * 256 + (part & 1) * 128 + (col & 7) * 16) = v;
@@ -316,7 +319,8 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const ui
         }
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
-            const int i = tid + kThreads * it, col = i >> 4, part = i & 15;
+            const int i = tid + kThreads * it;  // lane mapping as in the Q4_K kernel
+            const int col = (i & 7) + 8 * (i >> 7), part = ((i >> 3) & 3) + 4 * ((i >> 5) & 3);
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (c_tile + col < ncols) v = __ldg(reinterpret_cast<const uint4*>(xq + static_cast<size_t>(c_tile + col) * slot_ints + sb * 64 + part * 4));
             *reinterpret_cast<uint4*>(sm + kOffBx + (part >> 1) * kSlab + (col >> 3) * 256 + (part & 1) * 128 + (col & 7) * 16) = v;
