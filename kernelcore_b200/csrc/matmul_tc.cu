@@ -63,6 +63,32 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
                  : "r"(taddr));
 }
 
+// tcgen05.ld is asynchronous: its destination registers hold the data only after tcgen05.wait::ld.  The wait is an asm
+// statement without register operands, so nothing would stop the compiler from scheduling arithmetic on those
+// registers ahead of it; passing them through this empty asm (volatile asm statements keep their order) ties
+// every later use to a point after the wait.
+__device__ __forceinline__ void after_tmem_wait(int (&v)[16]) {
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+                      "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])::"memory");
+}
+
+// Packed fp32 pairs (sm_100 f32x2 arithmetic): each lane of a pair is rounded exactly as the scalar _rn operation.
+// Only the multiplies of the epilogues are packed: ptxas contracts mul.rn.f32x2 followed by sub / add.rn.f32x2 into
+// one fused operation (a single rounding, measured: 58 % of the results change in the last bits, -fmad=false
+// notwithstanding), which would break bit-identity with the reference, so subtraction and accumulation stay scalar
+// _rn intrinsics.
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
 // Two 16-bit lanes at a time: (four 4-bit values in bytes) * sc, split into (>> 5) and (& 31) byte planes.
 __device__ __forceinline__ void scale_split(unsigned nib4, unsigned sc, unsigned& a, unsigned& b) {
     const unsigned pe = (nib4 & 0x00FF00FFu) * sc, po = ((nib4 >> 8) & 0x00FF00FFu) * sc;
@@ -197,6 +223,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const ui
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned hdw = __ldg(reinterpret_cast<const unsigned*>(erow_blocks + static_cast<size_t>(sb) * kQ4KBlock));
         const float d = half_bits_to_float(hdw & 0xFFFFu), dmin = half_bits_to_float(hdw >> 16);
+        const f32x2 d2 = pack2(d, d), dmin2 = pack2(dmin, dmin);
         const uint32_t trow = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + ecol0;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
@@ -206,13 +233,18 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const ui
             tmem_ld16(trow + 256 + 16 * ch, vh);
             tmem_ld16(trow + 384 + 16 * ch, vl);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            after_tmem_wait(va), after_tmem_wait(vb), after_tmem_wait(vh), after_tmem_wait(vl);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float dx = dxs[ecol0 + 16 * ch + i];
-                const int is = 32 * va[i] + vb[i], im = 64 * vh[i] + vl[i];
-                const float t1 = __fmul_rn(__fmul_rn(d, dx), static_cast<float>(is));
-                const float t2 = __fmul_rn(__fmul_rn(dmin, dx), static_cast<float>(im));
-                acc[16 * ch + i] = __fadd_rn(acc[16 * ch + i], __fsub_rn(t1, t2));
+            for (int i = 0; i < 16; i += 2) {
+                const float2 dxp = *reinterpret_cast<const float2*>(dxs + ecol0 + 16 * ch + i);
+                const f32x2 dx2 = pack2(dxp.x, dxp.y);
+                const f32x2 is2 = pack2(static_cast<float>(32 * va[i] + vb[i]), static_cast<float>(32 * va[i + 1] + vb[i + 1]));
+                const f32x2 im2 = pack2(static_cast<float>(64 * vh[i] + vl[i]), static_cast<float>(64 * vh[i + 1] + vl[i + 1]));
+                float t1a, t1b, t2a, t2b;
+                unpack2(mul2(mul2(d2, dx2), is2), t1a, t1b);
+                unpack2(mul2(mul2(dmin2, dx2), im2), t2a, t2b);
+                acc[16 * ch + i] = __fadd_rn(acc[16 * ch + i], __fsub_rn(t1a, t2a));
+                acc[16 * ch + i + 1] = __fadd_rn(acc[16 * ch + i + 1], __fsub_rn(t1b, t2b));
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -350,6 +382,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const ui
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(w + nblk * 208 + (eblk0 + sb) * 2)));
+        const f32x2 d2 = pack2(d, d);
         const uint32_t trow = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + ecol0;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
@@ -357,10 +390,15 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const ui
             tmem_ld16(trow + 16 * ch, va);
             tmem_ld16(trow + 128 + 16 * ch, vb);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            after_tmem_wait(va), after_tmem_wait(vb);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int is = 64 * va[i] + vb[i];
-                acc[16 * ch + i] = __fadd_rn(acc[16 * ch + i], __fmul_rn(__fmul_rn(d, dxs[ecol0 + 16 * ch + i]), static_cast<float>(is)));
+            for (int i = 0; i < 16; i += 2) {
+                const float2 dxp = *reinterpret_cast<const float2*>(dxs + ecol0 + 16 * ch + i);
+                const f32x2 is2 = pack2(static_cast<float>(64 * va[i] + vb[i]), static_cast<float>(64 * va[i + 1] + vb[i + 1]));
+                float ta, tb;
+                unpack2(mul2(mul2(d2, pack2(dxp.x, dxp.y)), is2), ta, tb);
+                acc[16 * ch + i] = __fadd_rn(acc[16 * ch + i], ta);
+                acc[16 * ch + i + 1] = __fadd_rn(acc[16 * ch + i + 1], tb);
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

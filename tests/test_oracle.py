@@ -188,3 +188,20 @@ def test_synthetic_formats_port_equals_reference():
     # the interleaved forms compute what the row-major form does (different summation order for q4x8)
     assert np.abs(out["port"][4] - out["port"][1]).max() < 1e-4 * np.abs(out["port"][1]).max()
     assert np.abs(out["port"][6] - out["port"][1]).max() < 3e-2 * np.abs(out["port"][1]).max()
+
+
+def test_batched_pipeline_restatement_agrees_with_the_decode_loop():
+    """helpers.oracle_prefill strings the oracle's batched operators together (rope_ggml, set_rows_f16,
+    flash_attn_f16 with a causal mask, per-row add + norm).  With per-32 activations it must reproduce the oracle's
+    own token-by-token decode loop on an fp16 cache: same arithmetic, different plumbing."""
+    from helpers import OracleModel, oracle_prefill
+    from kernelcore_b200 import tiny_model as tm
+    for shape in (tm.tiny(max_ctx=16), tm.tiny_qwen(max_ctx=16)):
+        model = tm.build(shape, seed=8)
+        prompt = [int(t) for t in np.random.default_rng(5).integers(0, shape.vocab, 5)]
+        om = OracleModel(shape, model)
+        for pos, tok in enumerate(prompt):
+            want = om.decode_port(om.embed(tok), pos, kv_f16=True)
+        assert rel_diff(oracle_prefill(shape, model, prompt, q8k=False), want) < 1e-5
+        # per-256 activations: a different quantization of the same model, within the reference's Q8-vs-float bound
+        assert rel_diff(oracle_prefill(shape, model, prompt), want) < 5e-2
