@@ -157,7 +157,7 @@ unsigned kcb_peer_timeouts(void);
  * kcb_peer_barrier).  counters: two zero-initialised device words owned by this rank (epoch, finished CTAs); NULL
  * when world == 1.  ev_before / ev_after: optional cudaEvent_t recorded around the launch on `stream`.  With
  * npeers == 0 and world == 1 this is Backend::matvec for one Q6_K matrix (llm/llm_model.cpp:385-397) in a single
- * launch.  rows % 8 == 0, k <= 4096. */
+ * launch.  rows % 8 == 0, k <= 4096, x_dev 16-byte aligned. */
 int kcb_matvec_q6k_f32x_sharded(const void* planes_dev, const float* x_dev, float* y_local, float* const* y_peers, int npeers,
                                 unsigned* const* flags, unsigned* counters, int rank, int world, int rows, int k, void* ev_before,
                                 void* ev_after, void* stream);

@@ -89,6 +89,39 @@ __device__ __forceinline__ void quantize_block_warp(float v, int* xq, float* xd,
     }
 }
 
+// Four Q8 blocks per warp at once: lane l holds values 4*(l & 7) .. +3 of block b4 + (l >> 3) (so a warp covers 128
+// consecutive values with one 16-byte load per lane).  Same arithmetic as quantize_block_warp -- the maximum, the
+// scale, each rounding and the integer sum do not depend on how the 32 values are spread over lanes -- with three
+// shuffle steps per reduction instead of five and no shuffles to pack the words.
+__device__ __forceinline__ void quantize_4blocks_warp(float4 v, int* xq, float* xd, int b4, int lane) {
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    const float e[4] = {v.x, v.y, v.z, v.w};
+    unsigned word = 0;
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float t = __fmul_rn(e[i], id);
+        int q = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
+        q = max(-127, min(127, q));
+        sum += q;
+        word |= (static_cast<unsigned>(q) & 255u) << (8 * i);
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    const int b = b4 + (lane >> 3);
+    xq[b * 8 + (lane & 7)] = static_cast<int>(word);
+    if ((lane & 7) == 0) {
+        xd[b * 2] = d;
+        xd[b * 2 + 1] = static_cast<float>(sum);
+    }
+}
+
 // ---- block-wide sum and the RMSNorm factor ---------------------------------------------------------------
 __device__ __forceinline__ float block_sum(float v, float* red) {  // red: >= 32 floats of shared memory
     v = warp_sum(v);

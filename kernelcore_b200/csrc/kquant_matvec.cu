@@ -682,6 +682,17 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
         }
     };
 
+    // fp32 activations (quantized below): groups of four blocks (128 values), group gi = warp + i * NW, one 16-byte
+    // load per lane, all issued before anything else so their latency overlaps the barrier set-up
+    constexpr int kMaxPerWarp = (16 * 2 + NW - 1) / NW;  // nsb <= 16: at most 32 groups
+    float4 xv[kMaxPerWarp];
+    if (xf32) {
+#pragma unroll
+        for (int i = 0; i < kMaxPerWarp; ++i) {
+            const int gi = warp + i * NW;
+            xv[i] = gi < nsb * 2 ? __ldg(reinterpret_cast<const float4*>(xf32) + gi * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
         mbar_init_fence();
@@ -695,17 +706,10 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
     if (xf32) {
         int* sxq = reinterpret_cast<int*>(smem + 128);
         float* sxd = reinterpret_cast<float*>(sxq + nsb * 64);
-        constexpr int kMaxPerWarp = (16 * 8 + NW - 1) / NW;  // nsb <= 16
-        float xv[kMaxPerWarp];
-#pragma unroll
-        for (int i = 0; i < kMaxPerWarp; ++i) {  // all loads first: one memory latency, not one per block
-            const int b = warp + i * NW;
-            xv[i] = b < nsb * 8 ? __ldg(xf32 + b * 32 + lane) : 0.0f;
-        }
 #pragma unroll
         for (int i = 0; i < kMaxPerWarp; ++i) {
-            const int b = warp + i * NW;
-            if (b < nsb * 8) quantize_block_warp(xv[i], sxq, sxd, b, lane);
+            const int gi = warp + i * NW;
+            if (gi < nsb * 2) quantize_4blocks_warp(xv[i], sxq, sxd, gi * 4, lane);
         }
         __syncthreads();
         xq = sxq;
@@ -1004,7 +1008,8 @@ int matvec_q6k_q8_gather(const void* w, const int* xq, const float* xd, float* y
 // the other ranks' outputs and the cross-GPU step barrier (world > 1).
 int matvec_q6k_f32x_sharded(const void* w, const float* x, float* y_local, float* const* y_peers, int npeers, unsigned* const* flags,
                             unsigned* epoch_counter, unsigned* done_counter, int rank, int world, int rows, int k, cudaStream_t s) {
-    if (!shape_ok(rows, k) || !w || !x || !y_local || npeers < 0 || npeers > 7 || (npeers && !y_peers) || world < 1 || world > 8)
+    if (!shape_ok(rows, k) || !w || !x || !y_local || npeers < 0 || npeers > 7 || (npeers && !y_peers) || world < 1 || world > 8 ||
+        (reinterpret_cast<uintptr_t>(x) & 15))  // x is read with 16-byte loads
         return KCB_INVALID_VALUE;
     if (rows == 0) return KCB_SUCCESS;
     const int nsb = k / 256;
