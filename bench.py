@@ -38,7 +38,7 @@ METRIC, UNIT = "q6k_lm_head_matvec_hbm_gbs", "GB/s"
 # DRAM bytes per full-size launch of the matvec kernel (dram__bytes_read.sum + dram__bytes_write.sum):
 # the ncu capture summarised in profiles/matvec_q6k_q8_lm_head.md measured 161.65 MB + 5.0 MB on a 64128-row
 # case; traffic grows linearly with rows, so a 128256-row launch moves twice that.
-NCU_TRAFFIC_BYTES_PER_LAUNCH_FULL = 2 * (161_651_968 + 4_995_840)
+NCU_TRAFFIC_BYTES_PER_LAUNCH_FULL = 2 * (161_679_872 + 4_038_528)
 
 
 def algorithmic_bytes(rows: int) -> int:
