@@ -457,8 +457,13 @@ __global__ void __launch_bounds__(1024) tp_add_norm_q8_kernel(float* x, TpCtx c,
     }
     const float r = rinv_rms(block_sum(ss, red), n, eps);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int b = warp; b < n / 32; b += nw)
-        quantize_block_warp(__fmul_rn(__fmul_rn(sh[b * 32 + lane], r), w[b * 32 + lane]), xq, xd, b, lane);
+    for (int gi = warp; gi < n / 128; gi += nw) {  // four blocks of 32 per warp and step (n is a multiple of 256)
+        const float4 v = *reinterpret_cast<const float4*>(sh + gi * 128 + 4 * lane);
+        const float4 ww = *reinterpret_cast<const float4*>(w + gi * 128 + 4 * lane);
+        quantize_4blocks_warp(make_float4(__fmul_rn(__fmul_rn(v.x, r), ww.x), __fmul_rn(__fmul_rn(v.y, r), ww.y),
+                                          __fmul_rn(__fmul_rn(v.z, r), ww.z), __fmul_rn(__fmul_rn(v.w, r), ww.w)),
+                              xq, xd, gi * 4, lane);
+    }
 }
 
 // Greedy pick over every rank's candidates (rank r's indices are local to its vocab/world rows), first index

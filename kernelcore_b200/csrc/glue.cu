@@ -160,7 +160,7 @@ __global__ void add_norm_q8_kernel(const float* __restrict__ a, const float* __r
 // the sum of squares by a tree reduction.  x += t (t may be null), Q8 blocks of norm(x) * w into (xq, xd).
 __global__ void __launch_bounds__(1024) add_norm_q8_fast_kernel(float* x, const float* __restrict__ t, const float* __restrict__ w,
                                                                  int* xq, float* xd, int n, float eps) {
-    extern __shared__ float sh[];  // n floats
+    extern __shared__ __align__(16) float sh[];  // n floats
     __shared__ float red[32];
     float ss = 0.0f;
     for (int j = threadIdx.x; j < n; j += blockDim.x) {
@@ -174,7 +174,15 @@ __global__ void __launch_bounds__(1024) add_norm_q8_fast_kernel(float* x, const 
     }
     const float r = rinv_rms(block_sum(ss, red), n, eps);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int b = warp; b < n / 32; b += nw)
+    const int groups = n / 128;  // four blocks of 32 per warp and step
+    for (int gi = warp; gi < groups; gi += nw) {
+        const float4 v = *reinterpret_cast<const float4*>(sh + gi * 128 + 4 * lane);
+        const float4 ww = *reinterpret_cast<const float4*>(w + gi * 128 + 4 * lane);
+        quantize_4blocks_warp(make_float4(__fmul_rn(__fmul_rn(v.x, r), ww.x), __fmul_rn(__fmul_rn(v.y, r), ww.y),
+                                          __fmul_rn(__fmul_rn(v.z, r), ww.z), __fmul_rn(__fmul_rn(v.w, r), ww.w)),
+                              xq, xd, gi * 4, lane);
+    }
+    for (int b = groups * 4 + warp; b < n / 32; b += nw)  // n % 128 != 0: the last one to three blocks
         quantize_block_warp(__fmul_rn(__fmul_rn(sh[b * 32 + lane], r), w[b * 32 + lane]), xq, xd, b, lane);
 }
 

@@ -653,6 +653,7 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
                                                                              int stages, PeerOut peers,
                                                                              const float* __restrict__ xf32) {
     extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ float ytile[2][TR];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint8_t* buf = smem + 128 + kProlBytes;
     constexpr int kBlk = kQ6 ? kQ6KBlock : kQ4KBlock;
@@ -838,12 +839,15 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
             const int row = row0 + warp + r * NW;
             if (lane == 0 && row < rows) {
                 y[row] = v;
-                // fused all-gather: the same value into every other rank's gather buffer (plain peer stores)
-                for (int p = 0; p < peers.n; ++p) peers.y[p][row] = v;
+                ytile[i & 1][warp + r * NW] = v;
             }
         }
         __syncthreads();  // every warp is done with stage s
         if (threadIdx.x == 0 && i + stages < my_tiles) issue(i + stages);
+        // fused all-gather: warp p stores the tile's TR results to rank p's gather buffer as one coalesced line (an
+        // NVLink transaction per tile and peer instead of one per row).  ytile is double-buffered: tile i + 2 writes
+        // this buffer only after the barrier of tile i + 1, which these warps reach after their stores.
+        if (warp < peers.n && lane < TR && row0 + lane < rows) peers.y[warp][row0 + lane] = ytile[i & 1][lane];
     }
     // Step barrier across GPUs, run once per launch by whichever CTA finishes last: release this launch's epoch
     // into every rank's flag array, then wait (bounded) until every rank's epoch has arrived here.
