@@ -348,6 +348,9 @@ def run_ours(args):
                          "q4k_matmul_config2": matmul_bench(),
                          "q6k_matmul_ffn_down_3072x8192": matmul_bench((512,), q6=True),
                          "decode_llama32_3b": decode_bench(640, 512, 128, peak)[0]}
+        from kernelcore_b200 import tiny_model as tm
+        shape = tm.llama32_3b(16)
+        line["extra"]["decode_llama32_3b"]["cpu_baseline"] = cpu_decode_baseline(shape, tm.build(shape, seed=0))
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -508,9 +511,40 @@ def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b", lean=False)
     return out, rank
 
 
+def cpu_decode_baseline(shape, model, n_tokens=2):
+    """The reference's own decode loop (llm::decodeToken on its single-thread C++ backend, compiled in place from the
+    reference sources) on the same model, timed on one host core for a bounded sample of tokens."""
+    import ctypes as C
+
+    import oracle
+    if oracle.ref is None:
+        return None
+    bm = oracle.BoundModel(shape, model)
+    t0 = time.perf_counter()
+    h = oracle.ref.lib.kcref_model_open(C.byref(bm.c))
+    t_open = time.perf_counter() - t0
+    logits = np.zeros(shape.vocab, np.float32)
+    toks = [int(t) for t in np.random.default_rng(1).integers(0, shape.vocab, n_tokens)]
+    t0 = time.perf_counter()
+    for pos, tok in enumerate(toks):
+        if oracle.ref.lib.kcref_model_decode(h, bm.embed(tok), pos, logits) != 0:
+            oracle.ref.lib.kcref_model_close(h)
+            return None
+    dt = time.perf_counter() - t0
+    oracle.ref.lib.kcref_model_close(h)
+    return {"value": n_tokens / dt, "unit": "tokens/s", "cores": 1, "kind": "reference",
+            "sample": f"{n_tokens} tokens at positions 0..{n_tokens - 1}: llm::decodeToken on the reference's C++ backend "
+                      f"(weights repacked to its stream in {t_open:.1f} s, not timed)"}
+
+
 def run_decode(args):
     peak, _ = measured_peak()
     out, rank = decode_bench(max(64, args.prompt + args.gen), args.prompt, args.gen, peak, args.model, args.lean)
+    if rank == 0 and out["n_gpus"] == 1 and not args.lean and not args.skip_cpu_baseline:
+        from kernelcore_b200 import tiny_model as tm
+        shape = (tm.qwen3_8b if args.model == "qwen3_8b" else tm.llama32_3b)(16)
+        if not shape.qk_norm:   # the reference's decode loop has no per-head q/k norm (its ggml path does that in llama.cpp)
+            out["cpu_baseline"] = cpu_decode_baseline(shape, tm.build(shape, seed=0))
     if rank == 0:
         cfg = "configs[4]" if args.model == "qwen3_8b" else "configs[3]"
         print(json.dumps({"metric": f"{args.model}_decode_tok_s", "value": out["decode_tok_s"], "unit": "tokens/s", "n_gpus": out["n_gpus"],
