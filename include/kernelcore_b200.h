@@ -50,6 +50,10 @@ int kcb_register_kernel(const void* kernel_entry);    /* kcRegisterKernel, api.h
 /* kcLaunchKernel / kcLaunchKernelChunked, api.hpp:35-39: typed_args points at the kernel's llm::*Args
  * struct (llm/llm_kernels.hpp), host memory. */
 int kcb_launch_kernel(const char* name, const void* typed_args, void* stream);
+/* The built-in kernel table (every name of llm::registerKernels, llm/llm_kernels.cpp:1016-1062, plus vector_add and
+ * flash_attn_f16): number of entries and the name of entry i (NULL outside the range).  No device needed. */
+int kcb_kernel_count(void);
+const char* kcb_kernel_name(int i);
 int kcb_stream_create(void** stream);                 /* kcStreamCreate, api.hpp:42 */
 int kcb_stream_destroy(void* stream);                 /* kcStreamDestroy, api.hpp:43 */
 int kcb_stream_synchronize(void* stream);             /* kcStreamSynchronize, api.hpp:44 */

@@ -59,3 +59,21 @@ def test_runtime_refuses_without_a_device():
     assert lib.raw.kcb_malloc(C.byref(p), C.c_size_t(16)) == 1   # NotInitialized
     lib.raw.kcb_last_error_detail.restype = C.c_char_p
     assert b"kcInit" in lib.raw.kcb_last_error_detail()
+
+
+def test_every_kernel_name_of_the_reference_is_registered():
+    """The names llm::registerKernels puts in the reference's table (llm/llm_kernels.cpp:1016-1062) plus the runtime's
+    built-in vector_add: each must resolve here (launching needs a GPU; the table does not)."""
+    import ctypes as C
+
+    from kernelcore_b200 import lib
+    lib.raw.kcb_kernel_name.restype = C.c_char_p
+    have = {lib.raw.kcb_kernel_name(i).decode() for i in range(lib.raw.kcb_kernel_count())}
+    reference = """matvec_q8 matvec_q4 matvec_q4x8 quantize_q8x4 matvec_q4x8_q8 matvec_q4x8_q8x2 matvec_q4k_q8 matvec_q6k_q8
+        matmul_q4k_q8x4 matmul_q6k_q8x4 matmul_q4k_q8x8 matmul_q6k_q8x8 quantize_cols quantize_cols_k matmul_q4k_q8kx4
+        matmul_q6k_q8kx4 matmul_q4k_q8kx8 matmul_q6k_q8kx8 rope_ff mul_rows rope_ggml add_sumsq_f sumsq_part norm_mul_q8_f
+        silu_mul_q8x4f norm_mul_q8k_f silu_mul_q8kf add_rms_norm silu_mul_q8x4 add_sumsq norm_q8x4 rms_norm rope kv_append
+        attn_scores softmax attn_values silu_mul matmul_f16 set_rows_f16 fa_scores fa_max fa_exp fa_values vector_add""".split()
+    assert len(reference) == 45
+    assert not [n for n in reference if n not in have]
+    assert lib.raw.kcb_kernel_name(-1) is None and lib.raw.kcb_kernel_name(10 ** 6) is None
