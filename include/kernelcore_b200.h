@@ -268,6 +268,15 @@ int kcb_model_destroy(void* model);
  * decode loop reports failures as C++ exceptions, llm/llm_model.cpp:91-97). */
 const char* kcb_model_last_error(void);
 
+/* ---- GGUF files (llm/gguf.cpp:79-139 reader, llm/gguf_model.cpp:51-106 loader; POSIX mmap here) -----------------
+ * kcb_gguf_open maps a llama- or qwen3-architecture GGUF file (Q4_K / Q6_K matrices, f32 norms) and fills `desc`
+ * with pointers into the mapping, ready for kcb_model_create / kcb_decoder_create; the handle must stay open while
+ * they upload (kcb_model_* also reads embedding rows from it afterwards).  No device needed. */
+int kcb_gguf_open(const char* path, int max_ctx, void** gguf, kcb_model_desc* desc);
+long long kcb_gguf_weight_bytes(void* gguf);   /* bytes of the matrices a token reads */
+int kcb_gguf_close(void* gguf);
+const char* kcb_gguf_last_error(void);
+
 /* ---- graph-replayed decoder ---------------------------------------------------------------------------
  * The fast form of the decode loop (llm/llm_model.cpp:287-360; the reference's own CUDA comparison re-uses one
  * graph per token too, app/llm_bench.cpp:155-179): one CUDA graph captured at creation, replayed per token;
