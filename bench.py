@@ -427,7 +427,34 @@ def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5, q6=False):
         ms = statistics.median(ts)
         tf = 2.0 * M * rows * k / ms / 1e9
         out[f"M{M}"] = {"us": ms * 1e3, "tflops": tf, "frac_of_measured_bf16_burst": tf / bf16, "prompt_tok_s_one_matrix": M / ms * 1e3}
-    out["note"] = "int8 tcgen05 path; fraction quoted against the measured bf16 cuBLAS burst peak (no int8 peak was measured on this pool)"
+    # The denominator an int8 contraction deserves: cuBLASLt's own int8 GEMM (torch._int_mm, int8 x int8 -> int32) at
+    # 8192^3, timed here because the pool's peak file holds only a bf16 figure.
+    int8_peak = None
+    try:
+        n = 8192
+        a = torch.randint(-128, 127, (n, n), dtype=torch.int8, device="cuda")
+        b = torch.randint(-128, 127, (n, n), dtype=torch.int8, device="cuda")
+        for _ in range(3):
+            torch._int_mm(a, b)
+        best = 1e30
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        int8_peak = 2.0 * n ** 3 / best / 1e9
+        del a, b
+    except Exception as e:  # noqa: BLE001 - the library GEMM is only a yardstick
+        out["int8_peak_error"] = f"{type(e).__name__}: {e}"[:200]
+    if int8_peak:
+        out["int8_library_gemm_tflops_measured_here"] = int8_peak
+        for v in out.values():
+            if isinstance(v, dict) and "tflops" in v:
+                v["frac_of_measured_int8_library_gemm"] = v["tflops"] / int8_peak
+    out["note"] = ("int8 tcgen05 path; fractions against the pool's measured bf16 cuBLAS burst peak and against a cuBLASLt int8 GEMM "
+                   "(torch._int_mm, 8192^3) timed in this run")
     return out
 
 
