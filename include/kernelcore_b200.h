@@ -307,6 +307,15 @@ int kcb_decoder_set_prompt(void* decoder, const int* tokens, int n, int start_po
  * position start_pos + n; kcb_decoder_run then generates.  Returns after the pass has finished. */
 int kcb_decoder_prefill(void* decoder, const int* tokens, int n, int start_pos);
 int kcb_decoder_run(void* decoder, int steps);
+/* A batch of independent sequences decoded in lockstep on one GPU (BASELINE's batch-32 case; the reference's batched
+ * path is its ggml backend with several tokens per graph, ggml-kernelcore.cpp:548-603): begin allocates one fp16 KV
+ * cache per sequence; batch_prefill runs sequence `seq`'s prompt (all prompts the same length) and makes its first
+ * pick; batch_run advances every sequence by `steps` greedy tokens, reading the weights once per step for the whole
+ * batch; batch_read returns the last logits, the picks and the position of one sequence. */
+int kcb_decoder_batch_begin(void* decoder, int n_sequences);
+int kcb_decoder_batch_prefill(void* decoder, int seq, const int* tokens, int n);
+int kcb_decoder_batch_run(void* decoder, int steps);
+int kcb_decoder_batch_read(void* decoder, int seq, float* logits_host, int* history_host, int n_history, int* pos_host);
 int kcb_decoder_sync(void* decoder);
 int kcb_decoder_read(void* decoder, float* logits_host, int* history_host, int n_history, int* pos_host);
 int kcb_decoder_info(void* decoder, int* launches_per_token, long long* weight_bytes);

@@ -111,13 +111,17 @@ __device__ __forceinline__ void embed_row(const uint8_t* __restrict__ w, size_t 
 __global__ void rope_kv_f16_kernel(float* qk, float* v, int qk_stride, int v_stride, const int* __restrict__ pos_p, int pos0,
                                    unsigned short* kc, unsigned short* vc, const float* __restrict__ ff,
                                    const float* __restrict__ qn, const float* __restrict__ kn, int heads, int kv_heads, int hd,
-                                   float log2_base, int neox, float eps, int max_ctx) {
+                                   float log2_base, int neox, float eps, int max_ctx, int seq_rows = 0) {
     const int lane = threadIdx.x & 31;
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (w >= heads + 2 * kv_heads) return;
     const int tok = blockIdx.y;
-    const int pos = min((pos_p ? *pos_p : 0) + pos0 + tok, max_ctx - 1);
+    // seq_rows != 0: a batch of independent sequences, token `tok` belongs to sequence `tok`, whose cache starts
+    // seq_rows rows further on; all sequences stand at the same position
+    const int pos = min((pos_p ? *pos_p : 0) + pos0 + (seq_rows ? 0 : tok), max_ctx - 1);
     const int kvdim = kv_heads * hd;
+    kc += static_cast<size_t>(tok) * seq_rows * kvdim;
+    vc += static_cast<size_t>(tok) * seq_rows * kvdim;
     float* base = w < heads + kv_heads ? qk + static_cast<size_t>(tok) * qk_stride + static_cast<size_t>(w) * hd
                                        : v + static_cast<size_t>(tok) * v_stride + static_cast<size_t>(w - heads - kv_heads) * hd;
     if (w >= heads + kv_heads) {  // v head: cast and store
@@ -173,14 +177,18 @@ template <int HD, int G>
 __global__ void __launch_bounds__(128) attn_partial_kernel(const float* __restrict__ qkv, const unsigned short* __restrict__ kc,
                                                             const unsigned short* __restrict__ vc, const int* __restrict__ pos_p,
                                                             float* __restrict__ part, int heads, int kv_heads, int nsplit,
-                                                            float scale, int max_ctx, int q_stride, int pos0, float* __restrict__ direct) {
+                                                            float scale, int max_ctx, int q_stride, int pos0, float* __restrict__ direct,
+                                                            int seq_rows = 0) {
     constexpr int DPL = HD / 8;  // channels per lane
     constexpr int NW = 4;
     extern __shared__ float sm[];  // [NW*4][G][HD + 2]
     const int kvh = blockIdx.x, sp = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, grp = lane >> 3, l8 = lane & 7;
     const int tok = blockIdx.z;
-    const int ctx = min((pos_p ? *pos_p : 0) + pos0 + tok, max_ctx - 1) + 1;
+    const int ctx = min((pos_p ? *pos_p : 0) + pos0 + (seq_rows ? 0 : tok), max_ctx - 1) + 1;
+    kc += static_cast<size_t>(tok) * seq_rows * kv_heads * HD;  // batch of sequences: this token's own cache
+    vc += static_cast<size_t>(tok) * seq_rows * kv_heads * HD;
+    part += static_cast<size_t>(tok) * heads * nsplit * (HD + 2);
     const int chunk = (ctx + nsplit - 1) / nsplit;
     const int t0 = sp * chunk, t1 = min(ctx, t0 + chunk);
     const int kvdim = kv_heads * HD;
@@ -326,6 +334,61 @@ __global__ void attn_combine_q8_kernel(const float* __restrict__ part, float* __
         xd[b * 2 + 1] = static_cast<float>(sum);
     }
 }
+
+// Batched form of the merge: token blockIdx.y, normalised floats to out[token][heads * hd] (quantized per 256 afterwards).
+__global__ void attn_combine_rows_kernel(const float* __restrict__ part, float* __restrict__ out, int heads, int hd, int nsplit) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= heads * hd) return;
+    const int h = i / hd, d = i % hd, tok = blockIdx.y;
+    const float* ph = part + (static_cast<size_t>(tok) * heads + h) * nsplit * (hd + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, ph[s * (hd + 2) + hd]);
+    float ll = 0.0f, aa = 0.0f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float pm = ph[s * (hd + 2) + hd];
+        const float wgt = pm == -INFINITY ? 0.0f : exp2f((pm - mm) * 1.44269504f);
+        ll += ph[s * (hd + 2) + hd + 1] * wgt;
+        aa += ph[s * (hd + 2) + d] * wgt;
+    }
+    out[static_cast<size_t>(tok) * heads * hd + i] = __fdiv_rn(aa, ll);
+}
+
+// Greedy pick of every sequence of a batch: one CTA per row of logits, first maximum; the pick becomes the sequence's
+// next token and goes into its history at the common position.
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* tok, int* history,
+                                                           const int* __restrict__ pos_p, int max_ctx) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* row = logits + static_cast<size_t>(blockIdx.x) * vocab;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best) best = v, idx = i;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+    }
+    if (lane == 0) bv[warp] = best, bi[warp] = idx;
+    __syncthreads();
+    if (warp == 0) {
+        best = bv[lane], idx = bi[lane];  // 32 warps
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+        }
+        if (lane == 0) {
+            const int pos = *pos_p;
+            tok[blockIdx.x] = idx;
+            if (pos < max_ctx) history[static_cast<size_t>(blockIdx.x) * max_ctx + pos] = idx;
+        }
+    }
+}
+__global__ void advance_pos_kernel(int* pos_p) { *pos_p += 1; }
 
 // Greedy pick (first maximum, as a sequential scan would), token history, position advance.
 __global__ void argmax_advance_kernel(const float* __restrict__ cand_v, const int* __restrict__ cand_i, int ncand, int* token,
@@ -707,13 +770,15 @@ public:
     // tensor-core K-quant matmuls, add + RMSNorm + quantize per row (kernels/llm/add_sumsq_f.cu, norm_mul_q8k_f.cu),
     // causal attention over the fp16 cache -- and leave the decoder where n single steps would: KV rows
     // [start_pos, start_pos + n) filled, logits and greedy pick of the last token, position start_pos + n.
-    int prefill(const int* tokens, int n, int start_pos) {
+    // seq >= 0: the prompt of sequence `seq` of a batch (batch_begin): its own cache, first pick into the batch's token list.
+    int prefill(const int* tokens, int n, int start_pos, int seq = -1) {
         if (tp.world != 1) {
             err_ = "batched prompt pass is single-GPU; feed the prompt through kcb_decoder_set_prompt + kcb_decoder_run";
             return KCB_UNSUPPORTED_OPERATION;
         }
-        if (n < 1 || start_pos < 0 || start_pos + n > max_ctx || !tokens) return KCB_INVALID_VALUE;
+        if (n < 1 || start_pos < 0 || start_pos + n > max_ctx || !tokens || seq >= batch_) return KCB_INVALID_VALUE;
         if (const int e = prefill_buffers(std::min(n, kPrefillChunk)); e) return e;
+        const size_t seq_off = seq >= 0 ? static_cast<size_t>(seq) * max_ctx * kv_heads * hd : 0;
         std::vector<int> f(static_cast<size_t>(max_ctx), 0);
         for (int i = 0; i < n; ++i) f[static_cast<size_t>(start_pos + i)] = tokens[i];
         CU(cudaMemcpyAsync(forced, f.data(), f.size() * 4, cudaMemcpyHostToDevice, stream_));
@@ -741,11 +806,14 @@ public:
                 const int qk_stride = fused_qkv ? qd + 2 * kv : qd + kv;
                 float* vrows = fused_qkv ? pQK + qd + kv : pV;
                 const int v_stride = fused_qkv ? qk_stride : kv;
-                rope_kv_f16_kernel<<<dim3((heads + 2 * kv_heads + 3) / 4, m), 128, 0, stream_>>>(pQK, vrows, qk_stride, v_stride, nullptr, p0, L.kc, L.vc,
+                unsigned short* kc = seq >= 0 ? kcB[l] + seq_off : L.kc;
+                unsigned short* vc = seq >= 0 ? vcB[l] + seq_off : L.vc;
+                rope_kv_f16_kernel<<<dim3((heads + 2 * kv_heads + 3) / 4, m), 128, 0, stream_>>>(pQK, vrows, qk_stride, v_stride, nullptr, p0, kc, vc,
                                                                                                   rope_ff, L.q_norm, L.k_norm, heads, kv_heads, hd,
                                                                                                   log2_base, neox, eps, max_ctx);
                 if (const int e = launch_status(); e) return e;
-                if (const int e = hd == 128 ? attention<128>(L, pQK, qk_stride, m, p0, pA) : attention<64>(L, pQK, qk_stride, m, p0, pA); e) return e;
+                if (const int e = hd == 128 ? attention<128>(L, pQK, qk_stride, m, p0, pA, kc, vc) : attention<64>(L, pQK, qk_stride, m, p0, pA, kc, vc); e)
+                    return e;
                 if (const int e = quantize_cols_k(pA, pSlots, qd, m, stream_); e) return e;
                 if (const int e = matmul_kq_q8(L.wo.data, pSlots, pT, L.wo.rows, L.wo.k, m, L.wo.q6, 1, stream_); e) return e;
                 if (const int e = add_norm_q8(pX, pT, pX, L.ffn_norm, nullptr, pSlots, pSq, hidden, m, eps, 3, 1, stream_); e) return e;
@@ -768,15 +836,131 @@ public:
             if (c0 + m < n) continue;
             // last token: residual add, final norm, logits, greedy pick, position
             const int st[4] = {start_pos + n - 1, 0, 0, 0};
-            CU(cudaMemcpyAsync(state, st, sizeof st, cudaMemcpyHostToDevice, stream_));
+            int* pos_word = seq >= 0 ? seq_pos + seq : state;  // position word the pick advances
+            int* tok_word = seq >= 0 ? tokB + seq : state + 1;
+            int* hist = seq >= 0 ? historyB + static_cast<size_t>(seq) * max_ctx : history;
+            float* lg = seq >= 0 ? logitsB + static_cast<size_t>(seq) * vocab : logits;
+            if (seq >= 0) CU(cudaMemcpyAsync(pos_word, st, 4, cudaMemcpyHostToDevice, stream_));
+            else CU(cudaMemcpyAsync(state, st, sizeof st, cudaMemcpyHostToDevice, stream_));
             float* xl = pX + static_cast<size_t>(m - 1) * hidden;
             if (const int e = add_norm_q8_fast(xl, pT + static_cast<size_t>(m - 1) * hidden, out_norm, xq, xd_of(xq, hidden), hidden, eps, stream_); e) return e;
-            if (const int e = mv(lm_head, xq, logits); e) return e;
-            if (const int e = argmax_partial(logits, vocab, cand_v, cand_i, kCand, stream_); e) return e;
-            argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, state + 1, history, state, max_ctx);
+            if (const int e = mv(lm_head, xq, lg); e) return e;
+            if (const int e = argmax_partial(lg, vocab, cand_v, cand_i, kCand, stream_); e) return e;
+            argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, tok_word, hist, pos_word, max_ctx);
             if (const int e = launch_status(); e) return e;
         }
         CU(cudaStreamSynchronize(stream_));
+        return KCB_SUCCESS;
+    }
+    // ---- a batch of independent sequences decoded in lockstep (every sequence at the same position) ----------------
+    // One step feeds one token per sequence through every layer together: the weights are read once per step for the whole
+    // batch (per-256 activation slots + the tensor-core matmuls from 16 sequences up), each sequence attends to its own
+    // fp16 cache.  The arithmetic per sequence is that of the batched prompt pass with one row.
+    int batch_begin(int n_seq) {
+        if (tp.world != 1) {
+            err_ = "batched decoding is single-GPU";
+            return KCB_UNSUPPORTED_OPERATION;
+        }
+        if (n_seq < 1 || n_seq > kPrefillChunk || batch_ != 0) return KCB_INVALID_VALUE;
+        if (const int e = prefill_buffers(std::max(n_seq, 128)); e) return e;
+        const size_t cache = static_cast<size_t>(n_seq) * max_ctx * kv_heads * hd * 2;
+        for (size_t l = 0; l < layers.size(); ++l) {
+            unsigned short *k = nullptr, *v = nullptr;
+            if (const int e = dev(reinterpret_cast<void**>(&k), cache); e) return e;
+            if (const int e = dev(reinterpret_cast<void**>(&v), cache); e) return e;
+            kcB.push_back(k), vcB.push_back(v);
+        }
+        if (const int e = dev(reinterpret_cast<void**>(&tokB), static_cast<size_t>(n_seq) * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&seq_pos), static_cast<size_t>(n_seq) * 4 + 64); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&historyB), static_cast<size_t>(n_seq) * max_ctx * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&logitsB), static_cast<size_t>(n_seq) * vocab * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&partB), static_cast<size_t>(n_seq) * heads * nsplit * (hd + 2) * 4); e) return e;
+        CU(cudaMemsetAsync(historyB, 0, static_cast<size_t>(n_seq) * max_ctx * 4, stream_));
+        CU(cudaMemsetAsync(tokB, 0, static_cast<size_t>(n_seq) * 4, stream_));
+        bpos = seq_pos + n_seq;  // the batch's common position word
+        batch_ = n_seq, batch_pos_ = -1;
+        CU(cudaStreamSynchronize(stream_));
+        return KCB_SUCCESS;
+    }
+    int batch_prefill(int seq, const int* tokens, int n) {
+        if (seq < 0 || seq >= batch_ || (batch_pos_ >= 0 && n != batch_pos_)) {
+            err_ = "every sequence of a batch takes a prompt of the same length";
+            return KCB_INVALID_VALUE;
+        }
+        if (const int e = prefill(tokens, n, 0, seq); e) return e;
+        batch_pos_ = n;
+        CU(cudaMemcpyAsync(bpos, &batch_pos_, 4, cudaMemcpyHostToDevice, stream_));
+        CU(cudaStreamSynchronize(stream_));
+        return KCB_SUCCESS;
+    }
+    int batch_step() {
+        const int B = batch_, qd = heads * hd, kv = kv_heads * hd, nsbh = hidden / 256;
+        const size_t nblk = static_cast<size_t>(embed_w.rows) * nsbh;
+        embed_rows_kernel<<<dim3((nsbh * 8 + 127) / 128, B), 128, 0, stream_>>>(embed_w.data, nblk, nsbh, embed_w.q6, vocab_total, tokB, pX);
+        if (const int e = launch_status(); e) return e;
+        for (size_t l = 0; l < layers.size(); ++l) {
+            const DLayer& L = layers[l];
+            if (const int e = add_norm_q8(pX, l ? pT : nullptr, pX, L.attn_norm, nullptr, pSlots, pSq, hidden, B, eps, 3, 1, stream_); e) return e;
+            const bool fused_qkv = L.qkv.size() == 1;
+            if (!(fused_qkv || (L.qkv.size() == 2 && L.qkv[0].rows == qd + kv)) || (L.gu.size() == 1 && L.gu[0].q6)) {
+                err_ = "batched decoding supports q and k in one format (v either) and Q4_K gate/up, or split gate/up";
+                return KCB_UNSUPPORTED_OPERATION;
+            }
+            float* outs[2] = {pQK, pV};
+            int which = 0;
+            for (const DMat& w : L.qkv)
+                if (const int e = matmul_kq_q8(w.data, pSlots, outs[which++], w.rows, w.k, B, w.q6, 1, stream_); e) return e;
+            const int qk_stride = fused_qkv ? qd + 2 * kv : qd + kv;
+            float* vrows = fused_qkv ? pQK + qd + kv : pV;
+            const int v_stride = fused_qkv ? qk_stride : kv;
+            rope_kv_f16_kernel<<<dim3((heads + 2 * kv_heads + 3) / 4, B), 128, 0, stream_>>>(pQK, vrows, qk_stride, v_stride, bpos, 0, kcB[l], vcB[l],
+                                                                                              rope_ff, L.q_norm, L.k_norm, heads, kv_heads, hd,
+                                                                                              log2_base, neox, eps, max_ctx, max_ctx);
+            if (const int e = launch_status(); e) return e;
+            if (const int e = hd == 128 ? attention<128>(L, pQK, qk_stride, B, 0, nullptr, kcB[l], vcB[l], bpos, max_ctx, partB)
+                                        : attention<64>(L, pQK, qk_stride, B, 0, nullptr, kcB[l], vcB[l], bpos, max_ctx, partB);
+                e)
+                return e;
+            attn_combine_rows_kernel<<<dim3((qd + 127) / 128, B), 128, 0, stream_>>>(partB, pA, heads, hd, nsplit);
+            if (const int e = launch_status(); e) return e;
+            if (const int e = quantize_cols_k(pA, pSlots, qd, B, stream_); e) return e;
+            if (const int e = matmul_kq_q8(L.wo.data, pSlots, pT, L.wo.rows, L.wo.k, B, L.wo.q6, 1, stream_); e) return e;
+            if (const int e = add_norm_q8(pX, pT, pX, L.ffn_norm, nullptr, pSlots, pSq, hidden, B, eps, 3, 1, stream_); e) return e;
+            float* go = pG;
+            for (const DMat& w : L.gu) {
+                const size_t row_bytes = static_cast<size_t>(w.k / 256) * kQ4KBlock;
+                if (w.rows == 2 * inter && !w.q6) {
+                    if (const int e = matmul_kq_q8(w.data, pSlots, pG, inter, w.k, B, 0, 1, stream_); e) return e;
+                    if (const int e = matmul_kq_q8(w.data + row_bytes * inter, pSlots, pU, inter, w.k, B, 0, 1, stream_); e) return e;
+                } else {
+                    if (const int e = matmul_kq_q8(w.data, pSlots, go, w.rows, w.k, B, w.q6, 1, stream_); e) return e;
+                    go = pU;
+                }
+            }
+            if (const int e = silu_mul(pG, pU, pG, static_cast<size_t>(B) * inter, stream_); e) return e;
+            if (const int e = quantize_cols_k(pG, pSlots, inter, B, stream_); e) return e;
+            if (const int e = matmul_kq_q8(L.wd.data, pSlots, pT, L.wd.rows, L.wd.k, B, L.wd.q6, 1, stream_); e) return e;
+        }
+        if (const int e = add_norm_q8(pX, pT, pX, out_norm, nullptr, pSlots, pSq, hidden, B, eps, 3, 1, stream_); e) return e;
+        if (const int e = matmul_kq_q8(lm_head.data, pSlots, logitsB, lm_head.rows, lm_head.k, B, lm_head.q6, 1, stream_); e) return e;
+        argmax_rows_kernel<<<B, 1024, 0, stream_>>>(logitsB, vocab, tokB, historyB, bpos, max_ctx);
+        advance_pos_kernel<<<1, 1, 0, stream_>>>(bpos);
+        return launch_status();
+    }
+    int batch_run(int steps) {
+        if (batch_ == 0 || batch_pos_ < 0 || steps < 0 || batch_pos_ + steps > max_ctx) return KCB_INVALID_VALUE;
+        for (int i = 0; i < steps; ++i)
+            if (const int e = batch_step(); e) return e;
+        batch_pos_ += steps;
+        return KCB_SUCCESS;
+    }
+    int batch_read(int seq, float* logits_host, int* history_host, int n_hist, int* pos_host) {
+        if (seq < 0 || seq >= batch_) return KCB_INVALID_VALUE;
+        CU(cudaStreamSynchronize(stream_));
+        if (logits_host) CU(cudaMemcpy(logits_host, logitsB + static_cast<size_t>(seq) * vocab, static_cast<size_t>(vocab) * 4, cudaMemcpyDeviceToHost));
+        if (history_host && n_hist > 0)
+            CU(cudaMemcpy(history_host, historyB + static_cast<size_t>(seq) * max_ctx, static_cast<size_t>(std::min(n_hist, max_ctx)) * 4, cudaMemcpyDeviceToHost));
+        if (pos_host) *pos_host = batch_pos_;
         return KCB_SUCCESS;
     }
     int sync() {
@@ -951,17 +1135,23 @@ private:
     float* partial_out() { return tp.world == 1 ? t : tp.partial[tp.rank] + static_cast<size_t>(xchg_ & 1) * hidden; }
     // Decode: one token at the device-side position, nsplit partials.  Prompt (direct != nullptr): n_tok query rows
     // of stride q_stride at host-known positions pos0.., one CTA per (kv head, token), normalised output.
+    // Batch of sequences (seq_rows != 0): n_tok query rows, token i reads the cache of sequence i (kc, vc given, seq_rows
+    // rows apart) up to the common device-side position *pos_dev, nsplit partials per token into part_buf.
     template <int HD>
-    int attention(const DLayer& L, const float* q = nullptr, int q_stride = 0, int n_tok = 1, int pos0 = 0, float* direct = nullptr) {
+    int attention(const DLayer& L, const float* q = nullptr, int q_stride = 0, int n_tok = 1, int pos0 = 0, float* direct = nullptr,
+                  const unsigned short* kc = nullptr, const unsigned short* vc = nullptr, const int* pos_dev = nullptr, int seq_rows = 0,
+                  float* part_buf = nullptr) {
         const int group = heads / kv_heads;
         const int ns = direct ? 1 : nsplit;
         const dim3 grid(kv_heads, ns, n_tok);
         const size_t smem = static_cast<size_t>(16) * group * (HD + 2) * 4;
         const float scale = 1.0f / std::sqrt(static_cast<float>(HD));
-        const int* pos_p = direct ? nullptr : state;
+        const int* pos_p = pos_dev ? pos_dev : (direct ? nullptr : state);
         if (!q) q = qkv;
+        if (!kc) kc = L.kc, vc = L.vc;
+        float* pb = part_buf ? part_buf : part;
 #define KCB_ATTN(G_)                                                                                                        \
-    attn_partial_kernel<HD, G_><<<grid, 128, smem, stream_>>>(q, L.kc, L.vc, pos_p, part, heads, kv_heads, ns, scale, max_ctx, q_stride, pos0, direct)
+    attn_partial_kernel<HD, G_><<<grid, 128, smem, stream_>>>(q, kc, vc, pos_p, pb, heads, kv_heads, ns, scale, max_ctx, q_stride, pos0, direct, seq_rows)
         switch (group) {
         case 1: KCB_ATTN(1); break;
         case 2: KCB_ATTN(2); break;
@@ -1034,6 +1224,11 @@ private:
     TpCtx tp;
     float *pX = nullptr, *pT = nullptr, *pQK = nullptr, *pV = nullptr, *pA = nullptr, *pG = nullptr, *pU = nullptr;
     int *pSlots = nullptr, *pSq = nullptr, prefill_cap_ = 0;
+    // batch of sequences
+    int batch_ = 0, batch_pos_ = -1;
+    std::vector<unsigned short*> kcB, vcB;
+    int *tokB = nullptr, *seq_pos = nullptr, *bpos = nullptr, *historyB = nullptr;
+    float *logitsB = nullptr, *partB = nullptr;
     KWindow wo_win, wd_win;
     int xchg_ = 0;  // exchanges recorded so far in the current step (parity picks the partial buffer)
     float eps = 1e-5f, log2_base = 0.f;
@@ -1101,6 +1296,19 @@ int kcb_decoder_prefill(void* h, const int* tokens, int n, int start_pos) {
     if (e != kcb::KCB_SUCCESS) kcb::tl_err = d->err_;
     return e;
 }
+#define KCB_DEC_CALL(expr)                                   \
+    if (!h) return kcb::KCB_INVALID_VALUE;                   \
+    auto* d = static_cast<Decoder*>(h);                      \
+    const int e = (expr);                                    \
+    if (e != kcb::KCB_SUCCESS) kcb::tl_err = d->err_;        \
+    return e
+int kcb_decoder_batch_begin(void* h, int n_seq) { KCB_DEC_CALL(d->batch_begin(n_seq)); }
+int kcb_decoder_batch_prefill(void* h, int seq, const int* tokens, int n) { KCB_DEC_CALL(d->batch_prefill(seq, tokens, n)); }
+int kcb_decoder_batch_run(void* h, int steps) { KCB_DEC_CALL(d->batch_run(steps)); }
+int kcb_decoder_batch_read(void* h, int seq, float* logits_host, int* history_host, int n_history, int* pos_host) {
+    KCB_DEC_CALL(d->batch_read(seq, logits_host, history_host, n_history, pos_host));
+}
+#undef KCB_DEC_CALL
 int kcb_decoder_run(void* h, int steps) { return h && steps >= 0 ? static_cast<Decoder*>(h)->run(steps) : kcb::KCB_INVALID_VALUE; }
 int kcb_decoder_sync(void* h) { return h ? static_cast<Decoder*>(h)->sync() : kcb::KCB_INVALID_VALUE; }
 int kcb_decoder_read(void* h, float* logits_host, int* history_host, int n_history, int* pos_host) {

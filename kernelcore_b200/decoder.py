@@ -156,6 +156,30 @@ class FastDecoder:
             lib.raw.kcb_decoder_last_error.restype = C.c_char_p
             raise lib.KcbError("kcb_decoder_prefill", st, lib.raw.kcb_decoder_last_error().decode())
 
+    # ---- a batch of independent sequences in lockstep (single GPU) ----
+    def batch_begin(self, n_sequences: int):
+        self._batch_call(lib.raw.kcb_decoder_batch_begin(self.handle, int(n_sequences)), "kcb_decoder_batch_begin")
+
+    def batch_prefill(self, seq: int, tokens):
+        t = np.ascontiguousarray(tokens, np.int32)
+        self._batch_call(lib.raw.kcb_decoder_batch_prefill(self.handle, int(seq), t.ctypes.data_as(C.c_void_p), int(t.size)), "kcb_decoder_batch_prefill")
+
+    def batch_run(self, steps: int):
+        self._batch_call(lib.raw.kcb_decoder_batch_run(self.handle, int(steps)), "kcb_decoder_batch_run")
+
+    def batch_read(self, seq: int, n_history=0):
+        logits = np.zeros(self.shape.vocab, np.float32)
+        hist = np.zeros(max(n_history, 1), np.int32)
+        pos = C.c_int()
+        self._batch_call(lib.raw.kcb_decoder_batch_read(self.handle, int(seq), logits.ctypes.data_as(C.c_void_p), hist.ctypes.data_as(C.c_void_p),
+                                                        int(n_history), C.byref(pos)), "kcb_decoder_batch_read")
+        return logits, hist[:n_history], pos.value
+
+    def _batch_call(self, st, what):
+        if st != 0:
+            lib.raw.kcb_decoder_last_error.restype = C.c_char_p
+            raise lib.KcbError(what, st, lib.raw.kcb_decoder_last_error().decode())
+
     def run(self, steps: int):
         lib.check(lib.raw.kcb_decoder_run(self.handle, int(steps)), "kcb_decoder_run")
 

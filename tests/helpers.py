@@ -35,7 +35,7 @@ def pad8(n: int) -> int:
 OracleModel = oracle.BoundModel
 
 
-def oracle_prefill(shape, model, tokens, q8k=True):
+def oracle_prefill(shape, model, tokens, q8k=True, tail_q8k=False):
     """The batched prompt pass restated on the CPU oracle, op for op as the reference's batched (ggml) path runs
     it: add + partial sums of squares, RMSNorm * weight + per-256 quantization (add_sumsq_f / sumsq_part /
     norm_mul_q8k), K-quant matvecs on per-256 slots per token, per-head q/k RMSNorm and rope_ggml, fp16 KV rows
@@ -121,6 +121,14 @@ def oracle_prefill(shape, model, tokens, q8k=True):
         act, islots = np.zeros_like(g), np.zeros((n, 85 * (s.inter // 256)), np.int32)
         P.silu_mul_q8k(g, u, act, islots, s.inter, n)
         T = mm(L["wd"], islots if q8k else quant_rows(act, s.inter), "wd")
+    if tail_q8k:   # the batched decode step: add + norm + per-256 quantization of the row, K-quant matvec on the slot
+        xr, tr = np.ascontiguousarray(X[n - 1:n]), np.ascontiguousarray(T[n - 1:n])
+        sq, slot, yn = np.zeros((1, nb * 11), np.int32), np.zeros((1, 85 * nsbh), np.int32), np.zeros((1, s.hidden), np.float32)
+        P.add_sumsq_f(xr, tr, xr, sq, s.hidden, 1)
+        P.norm_mul_q8k(xr, np.ascontiguousarray(model["out_norm"], np.float32), yn, slot, sq, s.hidden, 1, s.eps)
+        out = np.zeros(s.vocab, np.float32)
+        P.matvec_q6k_q8k(np.ascontiguousarray(model["lm_head"], np.uint8).ravel(), slot[0], out, s.vocab, s.hidden)
+        return out
     x = X[n - 1] + T[n - 1]
     y = np.zeros(s.hidden, np.float32)
     P.rms_norm(x, np.ascontiguousarray(model["out_norm"], np.float32), y, s.hidden, 1, s.eps)

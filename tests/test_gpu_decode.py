@@ -137,3 +137,45 @@ def test_batched_prefill(shape_fn, n_prompt, bound):
     with decoder.FastDecoder(shape, model) as c:
         with pytest.raises(lib.KcbError):
             c.prefill(list(range(shape.max_ctx + 1)))
+
+
+@pytest.mark.parametrize("shape_fn", [tm.tiny, tm.tiny_qwen, _tc_shape])
+def test_batch_of_sequences_in_lockstep(shape_fn):
+    """Independent sequences decoded together: every sequence's logits and picks are bit-identical to decoding it
+    alone through the same entry points (columns of the batched matmuls do not interact), and the first batched step
+    agrees with the oracle's batched pipeline on prompt + first pick (bound as for the prompt pass)."""
+    shape = shape_fn(max_ctx=32)
+    model = tm.build(shape, seed=12)
+    n_prompt, steps = 6, 5
+    nseq = 3 if shape.hidden < 1024 else 17          # 17 sequences put the 1024-wide model on the tensor-core matmuls
+    rng = np.random.default_rng(3)
+    prompts = [[int(t) for t in rng.integers(0, shape.vocab, n_prompt)] for _ in range(nseq)]
+    with decoder.FastDecoder(shape, model) as d:
+        d.batch_begin(nseq)
+        for i, p in enumerate(prompts):
+            d.batch_prefill(i, p)
+        d.batch_run(1)
+        first = [d.batch_read(i, n_prompt + 1) for i in range(nseq)]
+        d.batch_run(steps - 1)
+        together = [d.batch_read(i, n_prompt + steps) for i in range(nseq)]
+        with pytest.raises(lib.KcbError):
+            d.batch_prefill(0, prompts[0][:3])       # prompts of one batch have one length
+    # the comparison run: the sequence alone -- or, for the tensor-core shape, as column 5 of another batch of 16 with
+    # different neighbours, so that both runs take the tensor-core matmuls (the CUDA-core matmul a single column gets
+    # sums in a different order: equal to 1e-5, not bit for bit)
+    other = 1 if nseq < 16 else 16
+    for i in (0, nseq - 1):
+        with decoder.FastDecoder(shape, model) as d:
+            d.batch_begin(other)
+            slot = 0 if other == 1 else 5
+            for j in range(other):
+                d.batch_prefill(j, prompts[i] if j == slot else prompts[(i + 1 + j) % nseq])
+            d.batch_run(steps)
+            lg, hist, pos = d.batch_read(slot, n_prompt + steps)
+        assert pos == together[i][2] == n_prompt + steps
+        assert (hist == together[i][1]).all() and (lg.view(np.uint32) == together[i][0].view(np.uint32)).all()
+    lg1, hist1, _ = first[0]
+    want = oracle_prefill(shape, model, prompts[0] + [int(hist1[n_prompt - 1])], tail_q8k=True)
+    assert rel_diff(lg1, want) < 3e-2
+    assert int(hist1[n_prompt]) == int(lg1.argmax())
+    assert lib.raw.kcb_tc_timeouts() == 0
