@@ -541,6 +541,40 @@ def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b", lean=False)
     return out, rank
 
 
+def batch_decode_bench(model_name, n_seq, n_prompt, n_gen):
+    """BASELINE configs[4] at batch > 1: n_seq independent sequences with random prompts of n_prompt tokens each,
+    decoded in lockstep for n_gen greedy tokens on one GPU; the aggregate rate counts every sequence's tokens."""
+    import torch
+
+    from kernelcore_b200 import decoder, tiny_model as tm
+    shape = (tm.qwen3_8b if model_name == "qwen3_8b" else tm.llama32_3b)(n_prompt + n_gen + 8)
+    d = decoder.FastDecoder(shape, tm.build(shape, seed=0))
+    stream = torch.cuda.ExternalStream(d.cuda_stream)
+    rng = np.random.default_rng(1)
+    d.batch_begin(n_seq)
+    t0 = time.perf_counter()
+    for i in range(n_seq):
+        d.batch_prefill(i, rng.integers(0, shape.vocab, n_prompt))
+    d.sync()
+    t_prompt = time.perf_counter() - t0
+    d.batch_run(2)   # warm-up steps (counted in the position, not in the time)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    d.batch_run(n_gen - 2)
+    e1.record(stream)
+    d.sync()
+    ms = e0.elapsed_time(e1)
+    steps = n_gen - 2
+    _, hist, pos = d.batch_read(0, n_prompt + n_gen)
+    out = {"model": shape.name, "sequences": n_seq, "prompt_tokens_each": n_prompt, "timed_steps": steps, "ms_per_step": ms / steps,
+           "aggregate_tok_s": n_seq * steps / ms * 1e3, "per_sequence_tok_s": steps / ms * 1e3,
+           "prompt_tok_s_batched_pass": n_seq * n_prompt / t_prompt, "position": pos,
+           "weight_bytes_per_step": d.weight_bytes, "frac_of_measured_hbm_weights_only": d.weight_bytes / (ms / steps * 1e-3) / (measured_peak()[0] * 1e9),
+           "kv_cache": "fp16, one per sequence", "picks_digest": int(np.asarray(hist, np.int64).sum() % 1000003)}
+    d.close()
+    return out
+
+
 def cpu_decode_baseline(shape, model, n_tokens=2):
     """The reference's own decode loop (llm::decodeToken on its single-thread C++ backend, compiled in place from the
     reference sources) on the same model, timed on one host core for a bounded sample of tokens."""
@@ -568,6 +602,13 @@ def cpu_decode_baseline(shape, model, n_tokens=2):
 
 
 def run_decode(args):
+    if args.batch > 1:
+        out = batch_decode_bench(args.model, args.batch, args.prompt, args.gen)
+        print(json.dumps({"metric": f"{args.model}_batch{args.batch}_decode_tok_s", "value": out["aggregate_tok_s"], "unit": "tokens/s", "n_gpus": 1,
+                          "higher_is_better": True, "data": "synthetic", "dtype": "int8 dot, fp32 accumulate",
+                          "config": {"workload": f"BASELINE configs[4]-style batch of {args.batch} independent sequences, lockstep decode"},
+                          "detail": out}))
+        return
     peak, _ = measured_peak()
     out, rank = decode_bench(max(64, args.prompt + args.gen), args.prompt, args.gen, peak, args.model, args.lean)
     if rank == 0 and out["n_gpus"] == 1 and not args.lean and not args.skip_cpu_baseline:
@@ -594,6 +635,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=128)
     ap.add_argument("--q6", action="store_true", help="--workload matmul: the Q6_K tensor-core kernel (3072 x 8192) instead of Q4_K")
+    ap.add_argument("--batch", type=int, default=1, help="--workload decode: this many independent sequences in lockstep (single GPU)")
     ap.add_argument("--lean", action="store_true", help="--workload decode: skip the token-by-token prompt timing (short launch lists for profiling)")
     ap.add_argument("--model", default="llama32_3b", choices=["llama32_3b", "qwen3_8b"], help="--workload decode: which architecture")
     ap.add_argument("--nccl-gather", action="store_true", help="N > 1: use an NCCL all-gather instead of the fused peer stores")
