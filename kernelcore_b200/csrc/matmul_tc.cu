@@ -23,7 +23,7 @@
 namespace kcb {
 namespace {
 
-constexpr int TM = 128, TN = 128;
+constexpr int TM = 128;  // rows per tile; the column tile TN (128 or 32) is a template parameter of the kernels
 constexpr int kSlab = 128 * 32;  // one K-step (32 bytes of K) of a 128-row operand
 constexpr int kThreads = 256;
 
@@ -47,9 +47,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
            (static_cast<uint64_t>(256 >> 4) << 32) | (static_cast<uint64_t>(1) << 46);
 }
 // int32 accumulate, signed 8-bit A and B, both K-major, N = 128, M = 128.
-constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TN >> 3) << 17) | (static_cast<uint32_t>(TM >> 4) << 24);
+template <int TN>
+constexpr uint32_t kIdescFor = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TN >> 3) << 17) | (static_cast<uint32_t>(TM >> 4) << 24);
 
+template <int TN>
 __device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    constexpr uint32_t kIdesc = kIdescFor<TN>;
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
@@ -96,7 +99,8 @@ __device__ __forceinline__ void scale_split(unsigned nib4, unsigned sc, unsigned
     b = (pe & 0x001F001Fu) | ((po & 0x001F001Fu) << 8);
 }
 
-__global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const uint8_t* __restrict__ w, const int* __restrict__ xq,
+template <int TN>
+__global__ void __launch_bounds__(kThreads, TN == 128 ? 1 : 2) matmul_q4k_q8k_tc_kernel(const uint8_t* __restrict__ w, const int* __restrict__ xq,
                                                                          float* __restrict__ y, int rows, int nsb, int ncols) {
     extern __shared__ __align__(1024) uint8_t sm[];
     uint64_t* bar = reinterpret_cast<uint64_t*>(sm + kOffBar);
@@ -107,7 +111,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const ui
     const int slot_ints = nsb * 85;
 
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(4 * TN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (tid == 0) {
@@ -119,11 +123,11 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const ui
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
-    // epilogue role: TMEM lane (= tile row) 32 * (warp & 3) + lane, columns [64 * (warp >> 2), +64)
-    const int erow = 32 * (warp & 3) + lane, ecol0 = 64 * (warp >> 2);
-    float acc[64];
+    // epilogue role: TMEM lane (= tile row) 32 * (warp & 3) + lane, columns [TN/2 * (warp >> 2), + TN/2)
+    const int erow = 32 * (warp & 3) + lane, ecol0 = (TN / 2) * (warp >> 2);
+    float acc[TN / 2];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < TN / 2; ++i) acc[i] = 0.0f;
     // unpack role: tile row tid / 2, quant chunks 2 * (tid & 1) and + 1 (sub-blocks 4 * hsel .. + 3)
     const int urow = tid >> 1, hsel = tid & 1;
     const uint8_t* urow_blocks = w + static_cast<size_t>(r_tile + urow) * nsb * kQ4KBlock;
@@ -172,7 +176,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const ui
         }
         // ---- activation bytes, sums and scales of this super-block ----
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
+        for (int it = 0; it < TN * 16 / kThreads; ++it) {
             // part = 2 * K-step + 16-byte half.  Lanes: 8 neighbouring columns x 4 neighbouring parts, so a warp's
             // global reads are 64-byte runs and its shared-memory stores collide 4 ways instead of 16
             const int i = tid + kThreads * it;
@@ -206,12 +210,12 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const ui
 #pragma unroll
             for (int s = 0; s < 8; ++s) {
                 const uint64_t bd = smem_desc(base + kOffBx + s * kSlab);
-                mma_i8(tmem + 0, smem_desc(base + kOffAa + s * kSlab), bd, s > 0);
-                mma_i8(tmem + 128, smem_desc(base + kOffAb + s * kSlab), bd, s > 0);
+                mma_i8<TN>(tmem + 0, smem_desc(base + kOffAa + s * kSlab), bd, s > 0);
+                mma_i8<TN>(tmem + TN, smem_desc(base + kOffAb + s * kSlab), bd, s > 0);
             }
             const uint64_t md = smem_desc(base + kOffAm);
-            mma_i8(tmem + 256, md, smem_desc(base + kOffBh), 0);
-            mma_i8(tmem + 384, md, smem_desc(base + kOffBl), 0);
+            mma_i8<TN>(tmem + 2 * TN, md, smem_desc(base + kOffBh), 0);
+            mma_i8<TN>(tmem + 3 * TN, md, smem_desc(base + kOffBl), 0);
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
         }
         // ---- epilogue: read the four accumulators, apply the reference's two scale products ----
@@ -226,12 +230,12 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const ui
         const f32x2 d2 = pack2(d, d), dmin2 = pack2(dmin, dmin);
         const uint32_t trow = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + ecol0;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < TN / 32; ++ch) {
             int va[16], vb[16], vh[16], vl[16];
             tmem_ld16(trow + 16 * ch, va);
-            tmem_ld16(trow + 128 + 16 * ch, vb);
-            tmem_ld16(trow + 256 + 16 * ch, vh);
-            tmem_ld16(trow + 384 + 16 * ch, vl);
+            tmem_ld16(trow + TN + 16 * ch, vb);
+            tmem_ld16(trow + 2 * TN + 16 * ch, vh);
+            tmem_ld16(trow + 3 * TN + 16 * ch, vl);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             after_tmem_wait(va), after_tmem_wait(vb), after_tmem_wait(vh), after_tmem_wait(vl);
 #pragma unroll
@@ -254,14 +258,14 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q4k_q8k_tc_kernel(const ui
         if (tid == 0) atomicAdd(&g_tc_timeouts, 1u);
     } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
+        for (int i = 0; i < TN / 2; ++i) {
             const int c = c_tile + ecol0 + i;
             if (c < ncols) y[static_cast<size_t>(c) * rows + r_tile + erow] = acc[i];
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(4 * TN) : "memory");
 }
 
 // ---- Q6_K --------------------------------------------------------------------------------------------------
@@ -283,7 +287,8 @@ __device__ __forceinline__ void scale_split_q6(unsigned q4, unsigned scb, unsign
     b = (ue & 0x003F003Fu) | ((uo & 0x003F003Fu) << 8);
 }
 
-__global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const uint8_t* __restrict__ w, const int* __restrict__ xq,
+template <int TN>
+__global__ void __launch_bounds__(kThreads, TN == 128 ? 1 : 2) matmul_q6k_q8k_tc_kernel(const uint8_t* __restrict__ w, const int* __restrict__ xq,
                                                                          float* __restrict__ y, int rows, int nsb, int ncols) {
     extern __shared__ __align__(1024) uint8_t sm[];
     uint64_t* bar = reinterpret_cast<uint64_t*>(sm + kOffBar);
@@ -295,7 +300,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const ui
     const size_t nblk = static_cast<size_t>(rows) * nsb;
 
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * TN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (tid == 0) {
@@ -307,10 +312,10 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const ui
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
-    const int erow = 32 * (warp & 3) + lane, ecol0 = 64 * (warp >> 2);
-    float acc[64];
+    const int erow = 32 * (warp & 3) + lane, ecol0 = (TN / 2) * (warp >> 2);
+    float acc[TN / 2];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < TN / 2; ++i) acc[i] = 0.0f;
     // unpack role: tile row tid / 2, half n = tid & 1 of the super-block (weights 128 n .. 128 n + 127, K-steps 4n .. 4n+3)
     const int urow = tid >> 1, n = tid & 1;
     const size_t ublk0 = static_cast<size_t>(r_tile + urow) * nsb, eblk0 = static_cast<size_t>(r_tile + erow) * nsb;
@@ -350,7 +355,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const ui
             }
         }
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
+        for (int it = 0; it < TN * 16 / kThreads; ++it) {
             const int i = tid + kThreads * it;  // lane mapping as in the Q4_K kernel
             const int col = (i & 7) + 8 * (i >> 7), part = ((i >> 3) & 3) + 4 * ((i >> 5) & 3);
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -370,8 +375,8 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const ui
 #pragma unroll
             for (int s = 0; s < 8; ++s) {
                 const uint64_t bd = smem_desc(base + kOffBx + s * kSlab);
-                mma_i8(tmem + 0, smem_desc(base + kOffAa + s * kSlab), bd, s > 0);
-                mma_i8(tmem + 128, smem_desc(base + kOffAb + s * kSlab), bd, s > 0);
+                mma_i8<TN>(tmem + 0, smem_desc(base + kOffAa + s * kSlab), bd, s > 0);
+                mma_i8<TN>(tmem + TN, smem_desc(base + kOffAb + s * kSlab), bd, s > 0);
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
         }
@@ -385,10 +390,10 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const ui
         const f32x2 d2 = pack2(d, d);
         const uint32_t trow = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + ecol0;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < TN / 32; ++ch) {
             int va[16], vb[16];
             tmem_ld16(trow + 16 * ch, va);
-            tmem_ld16(trow + 128 + 16 * ch, vb);
+            tmem_ld16(trow + TN + 16 * ch, vb);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             after_tmem_wait(va), after_tmem_wait(vb);
 #pragma unroll
@@ -408,16 +413,38 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_q6k_q8k_tc_kernel(const ui
         if (tid == 0) atomicAdd(&g_tc_timeouts, 1u);
     } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
+        for (int i = 0; i < TN / 2; ++i) {
             const int c = c_tile + ecol0 + i;
             if (c < ncols) y[static_cast<size_t>(c) * rows + r_tile + erow] = acc[i];
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * TN) : "memory");
 }
 
+}  // namespace
+
+namespace {
+// Up to 64 columns (a batch of sequences decoding in lockstep) take 32-column tiles: a quarter of the epilogue and
+// copy work per super-block, a quarter of the TMEM, so two CTAs share an SM and one's unpacking overlaps the other's
+// MMAs; wider batches take 128-column tiles, which unpack each weight tile once per 128 columns.
+template <bool kQ6, int TN>
+int launch_tc_tn(const uint8_t* w, const int* xq, float* y, int rows, int nsb, int ncols, cudaStream_t s) {
+    auto kern = kQ6 ? matmul_q6k_q8k_tc_kernel<TN> : matmul_q4k_q8k_tc_kernel<TN>;
+    static bool attr_set = false;  // per instantiation
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return KCB_LAUNCH_FAILURE;
+        attr_set = true;
+    }
+    const dim3 grid(rows / TM, (ncols + TN - 1) / TN);
+    kern<<<grid, kThreads, kSmemBytes, s>>>(w, xq, y, rows, nsb, ncols);
+    return launch_status();
+}
+template <bool kQ6>
+int launch_tc(const uint8_t* w, const int* xq, float* y, int rows, int nsb, int ncols, cudaStream_t s) {
+    return ncols <= 64 ? launch_tc_tn<kQ6, 32>(w, xq, y, rows, nsb, ncols, s) : launch_tc_tn<kQ6, 128>(w, xq, y, rows, nsb, ncols, s);
+}
 }  // namespace
 
 unsigned tc_timeouts() {
@@ -430,30 +457,14 @@ unsigned tc_timeouts() {
 int matmul_q4k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s) {
     // k % 1024: a column's slot is 85 * k / 256 ints and is read with 16-byte loads
     if (rows <= 0 || rows % TM || k <= 0 || k % 1024 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(matmul_q4k_q8k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-            return KCB_LAUNCH_FAILURE;
-        attr_set = true;
-    }
-    const dim3 grid(rows / TM, (ncols + TN - 1) / TN);
-    matmul_q4k_q8k_tc_kernel<<<grid, kThreads, kSmemBytes, s>>>(static_cast<const uint8_t*>(w), xq, y, rows, k / 256, ncols);
-    return launch_status();
+    return launch_tc<false>(static_cast<const uint8_t*>(w), xq, y, rows, k / 256, ncols, s);
 }
 
 // Tensor-core path for Q6_K weights (device planes) and per-256 activation slots; rows a multiple of 128.
 int matmul_q6k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s) {
     // k % 1024: a column's slot is 85 * k / 256 ints and is read with 16-byte loads
     if (rows <= 0 || rows % TM || k <= 0 || k % 1024 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(matmul_q6k_q8k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-            return KCB_LAUNCH_FAILURE;
-        attr_set = true;
-    }
-    const dim3 grid(rows / TM, (ncols + TN - 1) / TN);
-    matmul_q6k_q8k_tc_kernel<<<grid, kThreads, kSmemBytes, s>>>(static_cast<const uint8_t*>(w), xq, y, rows, k / 256, ncols);
-    return launch_status();
+    return launch_tc<true>(static_cast<const uint8_t*>(w), xq, y, rows, k / 256, ncols, s);
 }
 
 }  // namespace kcb

@@ -41,7 +41,7 @@ def test_golden_columns(golden, q6, q8k):
 
 
 @pytest.mark.parametrize("q6", [False, True])
-@pytest.mark.parametrize("ncols", [16, 17, 128, 130, 300])
+@pytest.mark.parametrize("ncols", [16, 17, 33, 64, 65, 128, 130, 300])
 def test_tensor_core_q8k_bit_identical(ncols, q6):
     """Q4_K / Q6_K x per-256 activations on tcgen05: exact integer contractions and the reference's fp32 order,
     so every output equals llm::ref::matvecQ4KQ8K / matvecQ6KQ8K bit for bit, including ragged column tiles.
