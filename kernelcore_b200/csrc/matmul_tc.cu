@@ -10,11 +10,11 @@
 //     accumulators, is = 32 Da + Db, each a K = 256 contraction per super-block on the tensor core;
 //   * the min term is a K = 8 contraction of the mins with the activation sums; the reference already stores
 //     the sums as two bytes (B >> 6, B & 63), so im = 64 Dh + Dl with two more accumulators.
-// One CTA owns a 128-row x 128-column output tile: per super-block it unpacks the weight planes into shared
-// memory (no-swizzle K-major core-matrix layout), copies the activation bytes, one thread issues 18
-// tcgen05.mma (M 128, N 128, K 32) into four TMEM accumulators, and all 8 warps read them back with tcgen05.ld
-// and apply the two fp32 scale products in the reference's order -- so every output is bit-identical to the
-// reference's per-column mirror.  Accumulators across super-blocks stay in registers (64 per thread).
+// One CTA owns a 128-row x TN-column output tile (TN = 128, or 32 for narrow batches): per super-block it unpacks
+// the weight planes into shared memory (no-swizzle K-major core-matrix layout), copies the activation bytes, one
+// thread issues 18 tcgen05.mma (M 128, N TN, K 32) into four TMEM accumulators, and all 8 warps read them back with
+// tcgen05.ld and apply the two fp32 scale products in the reference's order -- so every output is bit-identical to
+// the reference's per-column mirror.  Accumulators across super-blocks stay in registers (TN / 2 per thread).
 // Every wait on the MMA-completion mbarrier is bounded; on expiry the CTA records it, frees its TMEM and leaves.
 
 #include "common.cuh"
