@@ -179,3 +179,31 @@ def test_batch_of_sequences_in_lockstep(shape_fn):
     assert rel_diff(lg1, want) < 3e-2
     assert int(hist1[n_prompt]) == int(lg1.argmax())
     assert lib.raw.kcb_tc_timeouts() == 0
+
+
+def test_full_size_model_properties():
+    """BASELINE configs[3] at its real shapes (random-init Llama-3.2-3B architecture, 28 layers): properties that
+    need no CPU oracle run.  Free-running greedy decode and the teacher-forced replay of its own picks give the same
+    logits and picks bit for bit; the batched prompt pass and the token-by-token prompt agree within the bound the
+    two activation quantizations allow; nothing timed out."""
+    shape = tm.llama32_3b(96)
+    model = tm.build(shape, seed=0)
+    prompt = [int(t) for t in np.random.default_rng(9).integers(0, shape.vocab, 48)]
+    with decoder.FastDecoder(shape, model) as d:
+        assert d.weight_bytes == 2113026048                      # the per-token weight bytes BASELINE states
+        d.set_prompt(prompt)
+        d.run(56)                                                # 48 forced + 8 free
+        free_logits, hist, pos = d.read(n_history=56)
+        assert pos == 56
+        d.set_prompt(prompt + [int(t) for t in hist[47:55]])
+        d.run(56)
+        forced_logits, hist2, _ = d.read(n_history=56)
+        assert (hist == hist2).all() and (free_logits.view(np.uint32) == forced_logits.view(np.uint32)).all()
+        d.set_prompt(prompt)
+        d.run(48)
+        step_logits, _, _ = d.read()
+        d.prefill(prompt)
+        batch_logits, _, p = d.read()
+        assert p == 48 and np.isfinite(batch_logits).all()
+        assert 0 < rel_diff(batch_logits, step_logits) < 1e-1
+    assert lib.raw.kcb_tc_timeouts() == 0 and lib.raw.kcb_tma_timeouts() == 0

@@ -20,10 +20,12 @@ pytestmark = pytest.mark.gpu
 STEPS, PROMPT = 24, 16
 
 
-def _shape():
+def _shape(which=0):
     from kernelcore_b200 import tiny_model as tm
-    # FFN share 384 = 1.5 super-blocks (a straddled K window), 8 query / 2 kv heads of 64
-    return tm.Shape("tp-tiny", 512, 768, 2, 8, 2, 64, 512, 48)
+    if which == 0:   # FFN share 384 = 1.5 super-blocks (a straddled K window), 8 query / 2 kv heads of 64
+        return tm.Shape("tp-tiny", 512, 768, 2, 8, 2, 64, 512, 48)
+    # attention-output share 384 channels as well (12 heads of 64 over 2 ranks): both K windows straddle a super-block
+    return tm.Shape("tp-straddle", 768, 768, 2, 12, 4, 64, 512, 48)
 
 
 def _free_port():
@@ -32,7 +34,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, which, out):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import torch.distributed as dist
@@ -41,7 +43,7 @@ def _worker(rank, world, port, out):
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    shape = _shape()
+    shape = _shape(which)
     model = tm.build(shape, seed=11)
     area = symm_mem.empty(decoder.FastDecoder.tp_shared_bytes(shape), dtype=torch.uint8, device=dev)
     area.zero_()
@@ -64,7 +66,8 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_two_rank_decoder_matches_single_gpu():
+@pytest.mark.parametrize("which", [0, 1])
+def test_two_rank_decoder_matches_single_gpu(which):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     sys.path.insert(0, ROOT)
@@ -73,13 +76,13 @@ def test_two_rank_decoder_matches_single_gpu():
     world = 2
     with mp.Manager() as man:
         out = man.dict()
-        mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), which, out), nprocs=world, join=True)
         res = dict(out)
     assert res[0][3] == 0 and res[1][3] == 0                      # no wait gave up
     assert res[0][2] == res[1][2] == STEPS
     assert np.array_equal(res[0][1], res[1][1])                   # both ranks picked the same tokens
     tp_logits = np.concatenate([res[0][0], res[1][0]], axis=1)   # [steps][vocab]
-    shape = _shape()
+    shape = _shape(which)
     model = tm.build(shape, seed=11)
     prompt = [int(t) for t in np.random.default_rng(2).integers(0, shape.vocab, PROMPT)]
     # one GPU, forced to the tokens the two-rank run consumed, so every step sees the same inputs
