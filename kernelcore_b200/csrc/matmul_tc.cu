@@ -20,6 +20,10 @@
 #include "common.cuh"
 #include "ops.h"
 
+#include <algorithm>
+#include <map>
+#include <mutex>
+
 namespace kcb {
 namespace {
 
@@ -101,7 +105,7 @@ __device__ __forceinline__ void scale_split(unsigned nib4, unsigned sc, unsigned
 
 template <int TN>
 __global__ void __launch_bounds__(kThreads, TN == 128 ? 1 : 2) matmul_q4k_q8k_tc_kernel(const uint8_t* __restrict__ w, const int* __restrict__ xq,
-                                                                         float* __restrict__ y, int rows, int nsb, int ncols) {
+                                                                         float* __restrict__ y, int rows, int nsb, int ncols, int sb_per_split, float* __restrict__ partial) {
     extern __shared__ __align__(1024) uint8_t sm[];
     uint64_t* bar = reinterpret_cast<uint64_t*>(sm + kOffBar);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kOffBar + 16);
@@ -135,7 +139,9 @@ __global__ void __launch_bounds__(kThreads, TN == 128 ? 1 : 2) matmul_q4k_q8k_tc
     const uint32_t ubase = (urow >> 3) * 256 + (urow & 7) * 16;
 
     bool failed = false;
-    for (int sb = 0; sb < nsb && !failed; ++sb) {
+    // split K (partial != nullptr): this CTA contracts super-blocks [sb0, sb1) and leaves its sum in slice blockIdx.z
+    const int sb0 = blockIdx.z * sb_per_split, sb1 = min(nsb, sb0 + sb_per_split);
+    for (int sb = sb0; sb < sb1 && !failed; ++sb) {
         // ---- weight planes ----
         {
             const uint8_t* blk = urow_blocks + static_cast<size_t>(sb) * kQ4KBlock;
@@ -219,7 +225,7 @@ __global__ void __launch_bounds__(kThreads, TN == 128 ? 1 : 2) matmul_q4k_q8k_tc
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
         }
         // ---- epilogue: read the four accumulators, apply the reference's two scale products ----
-        const bool ok = mbar_wait_bounded(bar, static_cast<uint32_t>(sb) & 1u);
+        const bool ok = mbar_wait_bounded(bar, static_cast<uint32_t>(sb - sb0) & 1u);
         if (__syncthreads_or(!ok)) {
             failed = true;
             break;
@@ -254,13 +260,14 @@ __global__ void __launch_bounds__(kThreads, TN == 128 ? 1 : 2) matmul_q4k_q8k_tc
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();  // TMEM and the operand slabs are free for the next super-block
     }
+    float* out = partial ? partial + static_cast<size_t>(blockIdx.z) * ncols * rows : y;
     if (failed) {
         if (tid == 0) atomicAdd(&g_tc_timeouts, 1u);
     } else {
 #pragma unroll
         for (int i = 0; i < TN / 2; ++i) {
             const int c = c_tile + ecol0 + i;
-            if (c < ncols) y[static_cast<size_t>(c) * rows + r_tile + erow] = acc[i];
+            if (c < ncols) out[static_cast<size_t>(c) * rows + r_tile + erow] = acc[i];
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -289,7 +296,7 @@ __device__ __forceinline__ void scale_split_q6(unsigned q4, unsigned scb, unsign
 
 template <int TN>
 __global__ void __launch_bounds__(kThreads, TN == 128 ? 1 : 2) matmul_q6k_q8k_tc_kernel(const uint8_t* __restrict__ w, const int* __restrict__ xq,
-                                                                         float* __restrict__ y, int rows, int nsb, int ncols) {
+                                                                         float* __restrict__ y, int rows, int nsb, int ncols, int sb_per_split, float* __restrict__ partial) {
     extern __shared__ __align__(1024) uint8_t sm[];
     uint64_t* bar = reinterpret_cast<uint64_t*>(sm + kOffBar);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kOffBar + 16);
@@ -322,7 +329,9 @@ __global__ void __launch_bounds__(kThreads, TN == 128 ? 1 : 2) matmul_q6k_q8k_tc
     const uint32_t ubase = (urow >> 3) * 256 + (urow & 7) * 16;
 
     bool failed = false;
-    for (int sb = 0; sb < nsb && !failed; ++sb) {
+    // split K (partial != nullptr): this CTA contracts super-blocks [sb0, sb1) and leaves its sum in slice blockIdx.z
+    const int sb0 = blockIdx.z * sb_per_split, sb1 = min(nsb, sb0 + sb_per_split);
+    for (int sb = sb0; sb < sb1 && !failed; ++sb) {
         {
             const size_t blk = ublk0 + sb;
             uint4 lq[4], hq[2];
@@ -380,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, TN == 128 ? 1 : 2) matmul_q6k_q8k_tc
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
         }
-        const bool ok = mbar_wait_bounded(bar, static_cast<uint32_t>(sb) & 1u);
+        const bool ok = mbar_wait_bounded(bar, static_cast<uint32_t>(sb - sb0) & 1u);
         if (__syncthreads_or(!ok)) {
             failed = true;
             break;
@@ -409,13 +418,14 @@ __global__ void __launch_bounds__(kThreads, TN == 128 ? 1 : 2) matmul_q6k_q8k_tc
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
     }
+    float* out = partial ? partial + static_cast<size_t>(blockIdx.z) * ncols * rows : y;
     if (failed) {
         if (tid == 0) atomicAdd(&g_tc_timeouts, 1u);
     } else {
 #pragma unroll
         for (int i = 0; i < TN / 2; ++i) {
             const int c = c_tile + ecol0 + i;
-            if (c < ncols) y[static_cast<size_t>(c) * rows + r_tile + erow] = acc[i];
+            if (c < ncols) out[static_cast<size_t>(c) * rows + r_tile + erow] = acc[i];
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -429,6 +439,35 @@ namespace {
 // Up to 64 columns (a batch of sequences decoding in lockstep) take 32-column tiles: a quarter of the epilogue and
 // copy work per super-block, a quarter of the TMEM, so two CTAs share an SM and one's unpacking overlaps the other's
 // MMAs; wider batches take 128-column tiles, which unpack each weight tile once per 128 columns.
+// y[i] = ((p_0[i] + p_1[i]) + p_2[i]) + ...: the K slices of a split contraction, added in slice order.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ y, size_t n, int splits) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float a = partial[i];
+    for (int z = 1; z < splits; ++z) a = __fadd_rn(a, partial[static_cast<size_t>(z) * n + i]);
+    y[i] = a;
+}
+
+// Scratch for the K slices, one buffer per stream (calls on different streams may overlap), grown on demand and
+// kept for the life of the process.
+float* splitk_scratch(cudaStream_t s, size_t floats) {
+    static std::mutex m;
+    static std::map<cudaStream_t, std::pair<float*, size_t>> bufs;
+    std::lock_guard<std::mutex> lock(m);
+    auto& b = bufs[s];
+    if (b.second < floats) {
+        if (b.first) {
+            cudaStreamSynchronize(s);
+            cudaFree(b.first);
+        }
+        b = {nullptr, 0};
+        void* p = nullptr;
+        if (cudaMalloc(&p, floats * sizeof(float)) != cudaSuccess) return nullptr;
+        b = {static_cast<float*>(p), floats};
+    }
+    return b.first;
+}
+
 template <bool kQ6, int TN>
 int launch_tc_tn(const uint8_t* w, const int* xq, float* y, int rows, int nsb, int ncols, cudaStream_t s) {
     auto kern = kQ6 ? matmul_q6k_q8k_tc_kernel<TN> : matmul_q4k_q8k_tc_kernel<TN>;
@@ -437,8 +476,33 @@ int launch_tc_tn(const uint8_t* w, const int* xq, float* y, int rows, int nsb, i
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return KCB_LAUNCH_FAILURE;
         attr_set = true;
     }
-    const dim3 grid(rows / TM, (ncols + TN - 1) / TN);
-    kern<<<grid, kThreads, kSmemBytes, s>>>(w, xq, y, rows, nsb, ncols);
+    const int tiles = (rows / TM) * ((ncols + TN - 1) / TN);
+    // Narrow batches leave most SMs without a tile and every CTA with a long serial chain over the super-blocks: split K
+    // so that about two CTAs per SM exist, each contracting at least two super-blocks; the slices are added in slice
+    // order by a second kernel (deterministic; differs from the one-pass result only in where the fp32 sum is
+    // associated, so outputs agree with the reference's mirror to ~1e-6 instead of bit for bit).  Not under stream
+    // capture, where the scratch cannot be allocated.
+    int splits = 1, per = nsb;
+    if (TN == 32 && nsb >= 4 && tiles < kSmCount) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(s, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
+            const int want = std::min(nsb / 2, std::max(1, 2 * kSmCount / tiles));
+            per = (nsb + want - 1) / want;
+            splits = (nsb + per - 1) / per;
+        }
+    }
+    float* partial = nullptr;
+    if (splits > 1) {
+        partial = splitk_scratch(s, static_cast<size_t>(splits) * ncols * rows);
+        if (!partial) return KCB_OUT_OF_MEMORY;
+    } else {
+        per = nsb;
+    }
+    const dim3 grid(rows / TM, (ncols + TN - 1) / TN, splits);
+    kern<<<grid, kThreads, kSmemBytes, s>>>(w, xq, y, rows, nsb, ncols, per, partial);
+    if (const int e = launch_status(); e != KCB_SUCCESS || splits == 1) return e;
+    const size_t n = static_cast<size_t>(ncols) * rows;
+    splitk_reduce_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(partial, y, n, splits);
     return launch_status();
 }
 template <bool kQ6>

@@ -42,10 +42,12 @@ def test_golden_columns(golden, q6, q8k):
 
 @pytest.mark.parametrize("q6", [False, True])
 @pytest.mark.parametrize("ncols", [16, 17, 33, 64, 65, 128, 130, 300])
-def test_tensor_core_q8k_bit_identical(ncols, q6):
-    """Q4_K / Q6_K x per-256 activations on tcgen05: exact integer contractions and the reference's fp32 order,
-    so every output equals llm::ref::matvecQ4KQ8K / matvecQ6KQ8K bit for bit, including ragged column tiles.
-    raw_blocks draws every byte uniformly, so Q6_K scales reach -128 and 127 (the extremes of the plane split)."""
+def test_tensor_core_q8k_against_the_mirror(ncols, q6):
+    """Q4_K / Q6_K x per-256 activations on tcgen05: exact integer contractions and the reference's fp32 order, so
+    every output equals llm::ref::matvecQ4KQ8K / matvecQ6KQ8K bit for bit, including ragged column tiles.
+    raw_blocks draws every byte uniformly, so Q6_K scales reach -128 and 127 (the extremes of the plane split).
+    Up to 64 columns with few row tiles the contraction is split along K and the slices are added afterwards: the same
+    exact integers and products, one differently associated fp32 sum -- 1e-6 instead of bit identity."""
     rows, k = 256, 1024
     for gen in (synth.kquant_blocks, synth.raw_blocks):
         w = gen(rows, k, ncols, q6)
@@ -53,8 +55,22 @@ def test_tensor_core_q8k_bit_identical(ncols, q6):
         X[0, :256] = 0  # an all-zero super-block: scale 0
         y = run(w, X, rows, k, q6, True)
         want = np.stack([oracle.matvec_q8k(port, w, X[c], rows, k, int(q6)) for c in range(ncols)])
-        assert bit_equal(y, want), (ncols, gen.__name__, rel_diff(y, want))
+        if ncols > 64:
+            assert bit_equal(y, want), (ncols, gen.__name__, rel_diff(y, want))
+        else:
+            assert rel_diff(y, want) < 2e-6, (ncols, gen.__name__)
     assert lib.raw.kcb_tc_timeouts() == 0
+
+
+@pytest.mark.parametrize("q6", [False, True])
+def test_narrow_tiles_without_k_split_are_bit_identical(q6):
+    """148 row tiles give every SM a tile, so the 32-column kernel runs in one pass: bit identity again."""
+    rows, k, ncols = 128 * 148, 1024, 17
+    w = synth.raw_blocks(rows, k, 5, q6)
+    X = np.random.default_rng(5).uniform(-3, 3, (ncols, k)).astype(np.float32)
+    y = run(w, X, rows, k, q6, True)
+    want = np.stack([oracle.matvec_q8k(port, w, X[c], rows, k, int(q6)) for c in range(ncols)])
+    assert bit_equal(y, want)
 
 
 def test_config2_shape_against_cuda_core_path():
