@@ -477,16 +477,16 @@ int launch_tc_tn(const uint8_t* w, const int* xq, float* y, int rows, int nsb, i
         attr_set = true;
     }
     const int tiles = (rows / TM) * ((ncols + TN - 1) / TN);
-    // Narrow batches leave most SMs without a tile and every CTA with a long serial chain over the super-blocks: split K
+    // Few tiles leave most SMs without one and every CTA with a long serial chain over the super-blocks: split K
     // so that about two CTAs per SM exist, each contracting at least two super-blocks; the slices are added in slice
     // order by a second kernel (deterministic; differs from the one-pass result only in where the fp32 sum is
     // associated, so outputs agree with the reference's mirror to ~1e-6 instead of bit for bit).  Not under stream
     // capture, where the scratch cannot be allocated.
     int splits = 1, per = nsb;
-    if (TN == 32 && nsb >= 4 && tiles < kSmCount) {
+    if (nsb >= 4 && 2 * tiles <= kSmCount * (TN == 32 ? 2 : 1)) {
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
         if (cudaStreamIsCapturing(s, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
-            const int want = std::min(nsb / 2, std::max(1, 2 * kSmCount / tiles));
+            const int want = std::min(nsb / 2, std::max(1, (TN == 32 ? 2 : 1) * kSmCount / tiles));  // CTAs an SM holds: 2 / 1
             per = (nsb + want - 1) / want;
             splits = (nsb + per - 1) / per;
         }
