@@ -684,7 +684,7 @@ public:
             if (const int e = up(rope_ff, d.rope_ff, hd / 2); e) return e;
         const int kv = kv_heads * hd;
         const int maxk = hidden;
-        nsplit = std::max(1, std::min(16, (kSmCount + kv_heads - 1) / kv_heads));
+        nsplit = std::max(1, std::min(32, (2 * kSmCount + kv_heads - 1) / kv_heads));
         nsplit = std::min(nsplit, std::max(1, max_ctx / 64));
         if (const int e = dev(reinterpret_cast<void**>(&x), hidden * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&t), hidden * 4); e) return e;
