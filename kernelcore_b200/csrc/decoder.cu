@@ -182,7 +182,8 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float* __restri
     constexpr int DPL = HD / 8;  // channels per lane
     constexpr int NW = 4;
     extern __shared__ float sm[];  // [NW*4][G][HD + 2]
-    const int kvh = blockIdx.x, sp = blockIdx.y;
+    // blockIdx.x counts groups of G query heads; G == heads / kv_heads: one CTA per kv head, G == 1: one per query head
+    const int h0 = blockIdx.x * G, kvh = h0 / (heads / kv_heads), sp = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, grp = lane >> 3, l8 = lane & 7;
     const int tok = blockIdx.z;
     const int ctx = min((pos_p ? *pos_p : 0) + pos0 + (seq_rows ? 0 : tok), max_ctx - 1) + 1;
@@ -198,7 +199,7 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float* __restri
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) q[g][i] = qkv[static_cast<size_t>(kvh * G + g) * HD + l8 * DPL + i];
+        for (int i = 0; i < DPL; ++i) q[g][i] = qkv[static_cast<size_t>(h0 + g) * HD + l8 * DPL + i];
     float m[G], l[G], acc[G][DPL];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -285,10 +286,10 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float* __restri
             aa += pp[d] * wgt;
         }
         if (direct) {
-            direct[static_cast<size_t>(tok) * heads * HD + static_cast<size_t>(kvh * G + g) * HD + d] = __fdiv_rn(aa, ll);
+            direct[static_cast<size_t>(tok) * heads * HD + static_cast<size_t>(h0 + g) * HD + d] = __fdiv_rn(aa, ll);
             continue;
         }
-        float* dst = part + (static_cast<size_t>(kvh * G + g) * nsplit + sp) * (HD + 2);
+        float* dst = part + (static_cast<size_t>(h0 + g) * nsplit + sp) * (HD + 2);
         dst[d] = aa;
         if (d == 0) {
             dst[HD] = mm;
@@ -1141,9 +1142,11 @@ private:
     int attention(const DLayer& L, const float* q = nullptr, int q_stride = 0, int n_tok = 1, int pos0 = 0, float* direct = nullptr,
                   const unsigned short* kc = nullptr, const unsigned short* vc = nullptr, const int* pos_dev = nullptr, int seq_rows = 0,
                   float* part_buf = nullptr) {
-        const int group = heads / kv_heads;
+        // one CTA per kv head and its group of query heads; the prompt pass (many tokens, no split) takes one CTA per
+        // query head instead: a quarter of the registers, so four times the warps hide the cache-read latency
+        const int group = direct ? 1 : heads / kv_heads;
         const int ns = direct ? 1 : nsplit;
-        const dim3 grid(kv_heads, ns, n_tok);
+        const dim3 grid(heads / group, ns, n_tok);
         const size_t smem = static_cast<size_t>(16) * group * (HD + 2) * 4;
         const float scale = 1.0f / std::sqrt(static_cast<float>(HD));
         const int* pos_p = pos_dev ? pos_dev : (direct ? nullptr : state);
