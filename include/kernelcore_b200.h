@@ -268,6 +268,18 @@ int kcb_model_destroy(void* model);
  * decode loop reports failures as C++ exceptions, llm/llm_model.cpp:91-97). */
 const char* kcb_model_last_error(void);
 
+/* ---- host-buffer matvec pipe ------------------------------------------------------------------------------
+ * For callers whose activations and results stay in host memory, as everything does in the reference
+ * (Backend::matvec, llm/llm_model.cpp:385-397, reads x and writes y in process memory).  submit() enqueues
+ * x_host -> device, the single-launch Q6_K matvec and y -> y_host on two internal streams and returns at once; the
+ * read-back of one call overlaps the kernel of the next (two slots).  y_host of a call is complete after
+ * kcb_host_matvec_sync, or once the second following submit has returned.  Pin the host buffers.  rows % 8 == 0,
+ * k <= 4096; planes_dev may differ from call to call (same shape). */
+int kcb_host_matvec_create(int rows, int k, void** pipe);
+int kcb_host_matvec_submit(void* pipe, const void* planes_dev, const float* x_host, float* y_host);
+int kcb_host_matvec_sync(void* pipe);
+int kcb_host_matvec_destroy(void* pipe);
+
 /* ---- GGUF files (llm/gguf.cpp:79-139 reader, llm/gguf_model.cpp:51-106 loader; POSIX mmap here) -----------------
  * kcb_gguf_open maps a llama- or qwen3-architecture GGUF file (Q4_K / Q6_K matrices, f32 norms) and fills `desc`
  * with pointers into the mapping, ready for kcb_model_create / kcb_decoder_create; the handle must stay open while
