@@ -851,24 +851,30 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
     }
     // Step barrier across GPUs, run once per launch by whichever CTA finishes last: release this launch's epoch
     // into every rank's flag array, then wait (bounded) until every rank's epoch has arrived here.
-    if (peers.world > 1 && threadIdx.x == 0) {
-        __threadfence_system();  // this CTA's peer stores before its arrival
-        if (atomicAdd(peers.done_counter, 1u) == gridDim.x - 1) {
-            atomicExch(peers.done_counter, 0u);
-            const unsigned epoch = atomicAdd(peers.epoch_counter, 1u) + 1u;
-            __threadfence_system();
-            for (int r = 0; r < peers.world; ++r)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[r] + peers.rank), "r"(epoch) : "memory");
-            for (int r = 0; r < peers.world; ++r) {
-                bool arrived = false;
-                for (int it = 0; it < (1 << 22) && !arrived; ++it) {
-                    unsigned v;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(peers.flags[peers.rank] + r) : "memory");
-                    arrived = static_cast<int>(v - epoch) >= 0;
-                    if (!arrived) __nanosleep(64);
-                }
-                if (!arrived) atomicAdd(&g_tma_timeouts, 1u);
+    if (peers.world > 1) {
+        __shared__ unsigned s_epoch;  // 0: another CTA finishes last
+        if (threadIdx.x == 0) {
+            __threadfence_system();  // this CTA's peer stores before its arrival
+            unsigned e = 0;
+            if (atomicAdd(peers.done_counter, 1u) == gridDim.x - 1) {
+                atomicExch(peers.done_counter, 0u);
+                e = atomicAdd(peers.epoch_counter, 1u) + 1u;  // epochs start at 1
             }
+            s_epoch = e;
+        }
+        __syncthreads();
+        const unsigned epoch = s_epoch;
+        if (epoch != 0 && threadIdx.x < static_cast<unsigned>(peers.world)) {  // one thread per rank: announce and wait in parallel
+            const int r = threadIdx.x;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[r] + peers.rank), "r"(epoch) : "memory");
+            bool arrived = false;
+            for (int it = 0; it < (1 << 22) && !arrived; ++it) {
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(peers.flags[peers.rank] + r) : "memory");
+                arrived = static_cast<int>(v - epoch) >= 0;
+                if (!arrived) __nanosleep(64);
+            }
+            if (!arrived) atomicAdd(&g_tma_timeouts, 1u);
         }
     }
 }
