@@ -311,6 +311,8 @@ std::string tokenText(const std::vector<std::string>& vocab, int id) {
 
 // ---- C view ----------------------------------------------------------------------------------------------------
 namespace {
+// status codes of the C ABI (kc::Error values, include/kernelcore/api.hpp); this file is plain host code
+constexpr int kSuccess = 0, kInvalidValue = 2, kInternalError = 15;
 struct OpenGguf {
     std::unique_ptr<llm::gguf::File> file;
     llm::HostModel host;
@@ -323,7 +325,7 @@ kcb_mat c_mat(const llm::HostMat& m) { return kcb_mat{m.blocks, m.rows, m.k, m.q
 extern "C" {
 
 int kcb_gguf_open(const char* path, int max_ctx, void** out, kcb_model_desc* desc) {
-    if (!path || !out || !desc) return 2;
+    if (!path || !out || !desc) return kInvalidValue;
     *out = nullptr;
     try {
         auto g = std::make_unique<OpenGguf>();
@@ -341,14 +343,14 @@ int kcb_gguf_open(const char* path, int max_ctx, void** out, kcb_model_desc* des
         *out = g.release();
     } catch (const std::exception& e) {
         tl_gguf_err = e.what();
-        return 15;
+        return kInternalError;
     }
-    return 0;
+    return kSuccess;
 }
 long long kcb_gguf_weight_bytes(void* h) { return h ? static_cast<OpenGguf*>(h)->host.cfg.file_weight_bytes : 0; }
 int kcb_gguf_close(void* h) {
     delete static_cast<OpenGguf*>(h);
-    return 0;
+    return kSuccess;
 }
 const char* kcb_gguf_last_error(void) { return tl_gguf_err.c_str(); }
 
