@@ -136,6 +136,48 @@ __device__ __forceinline__ float rinv_rms(float sumsq, int n, float eps) {  // 1
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, static_cast<float>(n)), eps)));
 }
 
+// Residual add + RMSNorm + Q8 blocks by one whole CTA: x += t (t may be null), then blocks of norm(x) * w into
+// (xq, xd).  n % 128 == 0 and n <= 128 * MAXIT * warps of the CTA; x, t and w 16-byte aligned; gsum holds n / 128
+// floats of shared memory.  The sum of squares is taken per 128 values (a warp's butterfly over four products per
+// lane) and the group sums are added 32 apart in order, so the result does not depend on the CTA's size.
+template <int MAXIT>
+__device__ __forceinline__ void add_norm_q8_cta(float* x, const float* t, const float* __restrict__ w, int* xq, float* xd, int n,
+                                                float eps, float* gsum) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int groups = n / 128;
+    float4 v[MAXIT];
+#pragma unroll
+    for (int i = 0; i < MAXIT; ++i) {
+        const int gi = warp + i * nw;
+        if (gi < groups) {
+            float4* px = reinterpret_cast<float4*>(x + gi * 128) + lane;
+            float4 a = *px;
+            if (t) {
+                const float4 b = *(reinterpret_cast<const float4*>(t + gi * 128) + lane);
+                a = make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
+                *px = a;
+            }
+            v[i] = a;
+            const float p = __fadd_rn(__fadd_rn(__fmul_rn(a.x, a.x), __fmul_rn(a.y, a.y)), __fadd_rn(__fmul_rn(a.z, a.z), __fmul_rn(a.w, a.w)));
+            const float s = warp_sum(p);
+            if (lane == 0) gsum[gi] = s;
+        }
+    }
+    __syncthreads();
+    float tot = 0.0f;  // every warp takes the same total, so no second barrier
+    for (int g = lane; g < groups; g += 32) tot = __fadd_rn(tot, gsum[g]);
+    const float r = rinv_rms(warp_sum(tot), n, eps);
+#pragma unroll
+    for (int i = 0; i < MAXIT; ++i) {
+        const int gi = warp + i * nw;
+        if (gi < groups) {
+            const float4 ww = __ldg(reinterpret_cast<const float4*>(w + gi * 128) + lane);
+            quantize_4blocks_warp(make_float4(__fmul_rn(__fmul_rn(v[i].x, r), ww.x), __fmul_rn(__fmul_rn(v[i].y, r), ww.y),
+                                              __fmul_rn(__fmul_rn(v[i].z, r), ww.z), __fmul_rn(__fmul_rn(v[i].w, r), ww.w)),
+                                  xq, xd, gi * 4, lane);
+        }
+    }
+}
 
 // ---- mbarrier + bulk-copy (TMA) primitives ---------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }

@@ -157,9 +157,16 @@ __global__ void add_norm_q8_kernel(const float* __restrict__ a, const float* __r
 }
 
 // The same operation for the graph decoder, where latency matters more than summation order: one CTA,
-// the sum of squares by a tree reduction.  x += t (t may be null), Q8 blocks of norm(x) * w into (xq, xd).
-__global__ void __launch_bounds__(1024) add_norm_q8_fast_kernel(float* x, const float* __restrict__ t, const float* __restrict__ w,
+// the sum of squares by groups of 128 (add_norm_q8_cta; the same arithmetic runs as the tail of the matvec
+// launches of the decoder).  x += t (t may be null), Q8 blocks of norm(x) * w into (xq, xd).
+__global__ void __launch_bounds__(1024) add_norm_q8_fast_kernel(float* x, const float* t, const float* __restrict__ w,
                                                                  int* xq, float* xd, int n, float eps) {
+    __shared__ float gsum[11264 / 128];
+    add_norm_q8_cta<3>(x, t, w, xq, xd, n, eps, gsum);
+}
+// n % 32 == 0 but not a multiple of 128: values staged in shared memory, tree reduction, the last blocks one by one.
+__global__ void __launch_bounds__(1024) add_norm_q8_odd_kernel(float* x, const float* t, const float* __restrict__ w,
+                                                                int* xq, float* xd, int n, float eps) {
     extern __shared__ __align__(16) float sh[];  // n floats
     __shared__ float red[32];
     float ss = 0.0f;
@@ -174,15 +181,7 @@ __global__ void __launch_bounds__(1024) add_norm_q8_fast_kernel(float* x, const 
     }
     const float r = rinv_rms(block_sum(ss, red), n, eps);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const int groups = n / 128;  // four blocks of 32 per warp and step
-    for (int gi = warp; gi < groups; gi += nw) {
-        const float4 v = *reinterpret_cast<const float4*>(sh + gi * 128 + 4 * lane);
-        const float4 ww = *reinterpret_cast<const float4*>(w + gi * 128 + 4 * lane);
-        quantize_4blocks_warp(make_float4(__fmul_rn(__fmul_rn(v.x, r), ww.x), __fmul_rn(__fmul_rn(v.y, r), ww.y),
-                                          __fmul_rn(__fmul_rn(v.z, r), ww.z), __fmul_rn(__fmul_rn(v.w, r), ww.w)),
-                              xq, xd, gi * 4, lane);
-    }
-    for (int b = groups * 4 + warp; b < n / 32; b += nw)  // n % 128 != 0: the last one to three blocks
+    for (int b = warp; b < n / 32; b += nw)
         quantize_block_warp(__fmul_rn(__fmul_rn(sh[b * 32 + lane], r), w[b * 32 + lane]), xq, xd, b, lane);
 }
 
@@ -475,7 +474,10 @@ int add_norm_q8(const float* a, const float* t, float* out, const float* w, floa
 }
 int add_norm_q8_fast(float* x, const float* t, const float* w, int* xq, float* xd, int n, float eps, cudaStream_t s) {
     if (n <= 0 || n % 32 || n > 11264 || !x || !w || !xq || !xd) return KCB_INVALID_VALUE;
-    add_norm_q8_fast_kernel<<<1, 1024, static_cast<size_t>(n) * sizeof(float), s>>>(x, t, w, xq, xd, n, eps);
+    if (n % 128 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(t) | reinterpret_cast<uintptr_t>(w)) & 15) == 0)
+        add_norm_q8_fast_kernel<<<1, 1024, 0, s>>>(x, t, w, xq, xd, n, eps);
+    else
+        add_norm_q8_odd_kernel<<<1, 1024, static_cast<size_t>(n) * sizeof(float), s>>>(x, t, w, xq, xd, n, eps);
     return launch_status();
 }
 int argmax_partial(const float* logits, int vocab, float* cand_v, int* cand_i, int ncand, cudaStream_t s) {
