@@ -477,18 +477,33 @@ int launch_tc_tn(const uint8_t* w, const int* xq, float* y, int rows, int nsb, i
         attr_set = true;
     }
     const int tiles = (rows / TM) * ((ncols + TN - 1) / TN);
-    // Few tiles leave most SMs without one and every CTA with a long serial chain over the super-blocks: split K
-    // so that about two CTAs per SM exist, each contracting at least two super-blocks; the slices are added in slice
-    // order by a second kernel (deterministic; differs from the one-pass result only in where the fp32 sum is
-    // associated, so outputs agree with the reference's mirror to ~1e-6 instead of bit for bit).  Not under stream
-    // capture, where the scratch cannot be allocated.
+    // Few tiles leave SMs without one (or the last wave mostly empty) and every CTA with a long serial chain over the
+    // super-blocks: split K where a wave model says it pays.  A launch of `c` CTAs runs in ceil(c / slots) waves, a CTA
+    // costs its super-blocks plus ~1.5 super-block times of set-up and store, and the second kernel that adds the
+    // slices (in slice order: deterministic, but the fp32 sum is associated differently from the one-pass result, so
+    // outputs agree with the reference's mirror to ~1e-6 instead of bit for bit) costs about as much again.  The
+    // split must win by 10 %, contract at least two super-blocks per CTA and keep the slices within 64 MB.  Not
+    // under stream capture, where the scratch cannot be allocated.
     int splits = 1, per = nsb;
-    if (nsb >= 4 && 2 * tiles <= kSmCount * (TN == 32 ? 2 : 1)) {
+    if (nsb >= 4) {
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
         if (cudaStreamIsCapturing(s, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
-            const int want = std::min(nsb / 2, std::max(1, (TN == 32 ? 2 : 1) * kSmCount / tiles));  // CTAs an SM holds: 2 / 1
-            per = (nsb + want - 1) / want;
-            splits = (nsb + per - 1) / per;
+            const int slots = kSmCount * (TN == 32 ? 2 : 1);  // CTAs the machine holds at once
+            const auto cost = [&](int n_splits) {
+                const int p = (nsb + n_splits - 1) / n_splits;
+                const int waves = (tiles * n_splits + slots - 1) / slots;
+                return waves * (2 * p + 3) + (n_splits > 1 ? 3 : 0);  // in half super-block times
+            };
+            int best = 1, best_cost = cost(1);
+            for (int c = 2; c <= nsb / 2; ++c) {
+                if ((nsb + c - 1) / c * (c - 1) >= nsb) continue;  // the last slice would be empty
+                if (static_cast<size_t>(c) * ncols * rows * sizeof(float) > (64u << 20)) break;
+                if (cost(c) < best_cost) best = c, best_cost = cost(c);
+            }
+            if (best > 1 && 10 * best_cost <= 9 * cost(1)) {
+                per = (nsb + best - 1) / best;
+                splits = (nsb + per - 1) / per;
+            }
         }
     }
     float* partial = nullptr;

@@ -46,9 +46,9 @@ def test_tensor_core_q8k_against_the_mirror(ncols, q6):
     """Q4_K / Q6_K x per-256 activations on tcgen05: exact integer contractions and the reference's fp32 order, so
     every output equals llm::ref::matvecQ4KQ8K / matvecQ6KQ8K bit for bit, including ragged column tiles.
     raw_blocks draws every byte uniformly, so Q6_K scales reach -128 and 127 (the extremes of the plane split).
-    With so few tiles (256 rows) the contraction is split along K and the slices are added afterwards: the same exact
-    integers and products, one differently associated fp32 sum -- 1e-6 here, bit identity in the two tests below,
-    whose tile counts fill the machine."""
+    Where the launch splits the contraction along K (few tiles, many super-blocks) the slices are added afterwards: the
+    same exact integers and products, one differently associated fp32 sum -- hence 1e-6 here; bit identity is asserted
+    in the tests below on shapes that run in one pass."""
     rows, k = 256, 1024
     for gen in (synth.kquant_blocks, synth.raw_blocks):
         w = gen(rows, k, ncols, q6)
@@ -56,7 +56,7 @@ def test_tensor_core_q8k_against_the_mirror(ncols, q6):
         X[0, :256] = 0  # an all-zero super-block: scale 0
         y = run(w, X, rows, k, q6, True)
         want = np.stack([oracle.matvec_q8k(port, w, X[c], rows, k, int(q6)) for c in range(ncols)])
-        assert rel_diff(y, want) < 2e-6, (ncols, gen.__name__)   # 2 to 6 tiles on 148 SMs: always the K-split route
+        assert rel_diff(y, want) < 2e-6, (ncols, gen.__name__)   # 2 to 6 tiles on 148 SMs: one pass or K-split as the launch's wave model decides
     assert lib.raw.kcb_tc_timeouts() == 0
 
 
@@ -71,6 +71,20 @@ def test_one_pass_tiles_are_bit_identical(q6, ncols):
     y = run(w, X, rows, k, q6, True)
     want = np.stack([oracle.matvec_q8k(port, w, X[c], rows, k, int(q6)) for c in range(ncols)])
     assert bit_equal(y, want)
+
+
+def test_ffn_down_shape_splits_k_three_ways():
+    """Llama-3.2-3B's FFN-down at a 512-token prompt chunk: Q6_K 3072 x 8192, 96 tiles of 32 super-blocks on 148 SMs.
+    The launch contracts it as three K slices (two full waves of 11 super-blocks instead of one of 32 on two thirds of
+    the machine); columns against the oracle to 2e-6, and exact doubling under doubled activations."""
+    rows, k, M = 3072, 8192, 512
+    w = synth.raw_blocks(rows, k, 11, True)
+    X = np.random.default_rng(2).standard_normal((M, k)).astype(np.float32)
+    y = run(w, X, rows, k, True, True)
+    for c in (0, 255, M - 1):
+        assert rel_diff(y[c], oracle.matvec_q8k(port, w, X[c], rows, k, 1)) < 2e-6
+    assert bit_equal(run(w, X * 2, rows, k, True, True), y * 2)
+    assert lib.raw.kcb_tc_timeouts() == 0
 
 
 def test_config2_shape_against_cuda_core_path():
