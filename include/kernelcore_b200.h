@@ -116,6 +116,12 @@ int kcb_matvec_q4k_q8(const void* w_dev, const int32_t* xq_dev, const float* xd_
                       void* stream);
 int kcb_matvec_q6k_q8(const void* planes_dev, const int32_t* xq_dev, const float* xd_dev, float* y_dev, int rows,
                       int k, void* stream);
+/* Both of the above on the same activations in one launch: y4 = W4 x (Q4_K), y6 = W6 x (Q6_K planes) -- the q|k and
+ * v projections of a Q4_K_M layer (llm_model.cpp's three Backend::matvec calls on the attention input), each output
+ * bit-identical to its own launch.  k <= 4096 and at most 6144 rows each; beyond that KCB_UNSUPPORTED_OPERATION (7),
+ * and the caller launches them separately (larger matrices stream better through the bulk-copy kernel). */
+int kcb_matvec_q4k_q6k_pair_q8(const void* w4_dev, float* y4_dev, int rows4, const void* planes6_dev, float* y6_dev, int rows6,
+                               const int32_t* xq_dev, const float* xd_dev, int k, void* stream);
 /* The same product on fp32 activations: y = dequant(W) x with fp32 accumulation, the quantity the
  * reference's tests call "dequantized floats" (tests/test_llm_kernels.cpp:228-236).  k <= 12288. */
 int kcb_matvec_q4k_f32(const void* w_dev, const float* x_dev, float* y_dev, int rows, int k, void* stream);

@@ -57,6 +57,10 @@ int kcb_matvec_q4k_q8(const void* w, const int32_t* xq, const float* xd, float* 
 int kcb_matvec_q6k_q8(const void* w, const int32_t* xq, const float* xd, float* y, int rows, int k, void* s) {
     return matvec_q6k_q8(w, xq, xd, y, rows, k, st(s));
 }
+int kcb_matvec_q4k_q6k_pair_q8(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, const int32_t* xq, const float* xd,
+                               int k, void* s) {
+    return matvec_q4k_q6k_pair_q8(w4, y4, rows4, w6, y6, rows6, xq, xd, k, st(s));
+}
 int kcb_matvec_q4k_f32(const void* w, const float* x, float* y, int rows, int k, void* s) { return matvec_q4k_f32(w, x, y, rows, k, st(s)); }
 int kcb_matvec_q6k_f32(const void* w, const float* x, float* y, int rows, int k, void* s) { return matvec_q6k_f32(w, x, y, rows, k, st(s)); }
 

@@ -1178,10 +1178,17 @@ private:
         for (size_t l = 0; l < layers.size(); ++l) {
             const DLayer& L = layers[l];
             float* y = qkv;
-            for (const DMat& m : L.qkv) {
-                if (const int e = mv(m, xq, y); e) return e;
-                y += m.rows;
-            }
+            // Q4_K_M mix: q|k in Q4_K and v in Q6_K take one launch where both fit the register-resident kernels
+            int paired = KCB_UNSUPPORTED_OPERATION;
+            if (L.qkv.size() == 2 && !L.qkv[0].q6 && L.qkv[1].q6 && L.qkv[0].k == L.qkv[1].k)
+                paired = matvec_q4k_q6k_pair_q8(L.qkv[0].data, y, L.qkv[0].rows, L.qkv[1].data, y + L.qkv[0].rows, L.qkv[1].rows, xq,
+                                                xd_of(xq, hidden), L.qkv[0].k, stream_);
+            if (paired != KCB_SUCCESS && paired != KCB_UNSUPPORTED_OPERATION) return paired;
+            if (paired == KCB_UNSUPPORTED_OPERATION)
+                for (const DMat& m : L.qkv) {
+                    if (const int e = mv(m, xq, y); e) return e;
+                    y += m.rows;
+                }
             rope_kv_f16_kernel<<<(heads + 2 * kv_heads + 3) / 4, 128, 0, stream_>>>(qkv, qkv + qd + kv_heads * hd, 0, 0, pos_p, 0, L.kc, L.vc, rope_ff,
                                                                                      L.q_norm, L.k_norm, heads, kv_heads, hd, log2_base, neox, eps, max_ctx);
             if (const int e = launch_status(); e) return e;

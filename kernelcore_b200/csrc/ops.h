@@ -10,6 +10,9 @@ namespace kcb {
 // kquant_matvec.cu
 int matvec_q4k_q8(const void* w, const int* xq, const float* xd, float* y, int rows, int k, cudaStream_t s);
 int matvec_q6k_q8(const void* w, const int* xq, const float* xd, float* y, int rows, int k, cudaStream_t s);
+// Both products in one launch (k <= 4096 and at most 6144 rows each, else KCB_UNSUPPORTED_OPERATION).
+int matvec_q4k_q6k_pair_q8(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, const int* xq, const float* xd, int k,
+                           cudaStream_t s);
 int matvec_q4k_f32(const void* w, const float* x, float* y, int rows, int k, cudaStream_t s);
 int matvec_q6k_f32(const void* w, const float* x, float* y, int rows, int k, cudaStream_t s);
 int dequant_q4k(const void* w, float* out, int rows, int k, cudaStream_t s);

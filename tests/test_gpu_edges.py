@@ -98,3 +98,29 @@ def test_attention_over_a_single_position():
              dims.ctypes.data_as(C.c_void_p), C.c_float(0.125))
     want = np.repeat(v16.astype(np.float32).reshape(Hkv, D), H // Hkv, axis=0)
     assert bit_equal(out.cpu().numpy().reshape(H, D), want)
+
+
+@pytest.mark.parametrize("rows4,rows6,k", [(4096, 1024, 3072), (8, 8, 256), (5120, 1024, 4096), (6144, 3000, 4096), (520, 4000, 1024)])
+def test_q4k_and_q6k_matvec_in_one_launch_equal_their_own_launches(rows4, rows6, k):
+    """The q|k (Q4_K) and v (Q6_K) projections of a Q4_K_M layer share their input; the pair launch gives each output
+    bit for bit what its own launch gives, whether the grid holds every CTA at once or is shared out by bytes."""
+    w4 = kquant.KMatrix(synth.raw_blocks(rows4, k, 21, False), rows4, k, False)
+    w6 = kquant.KMatrix(synth.raw_blocks(rows6, k, 22, True), rows6, k, True)
+    nb = k // 32
+    xq, xd = torch.zeros(nb * 8, dtype=torch.int32, device="cuda"), torch.zeros(nb * 2, device="cuda")
+    lib.call("quantize_q8x4", dev(synth.activations(k, 9)), xq, xd, nb)
+    a4, a6 = torch.zeros(rows4, device="cuda"), torch.zeros(rows6, device="cuda")
+    lib.call("matvec_q4k_q8", w4.data, xq, xd, a4, rows4, k)
+    lib.call("matvec_q6k_q8", w6.data, xq, xd, a6, rows6, k)
+    b4, b6 = torch.zeros(rows4, device="cuda"), torch.zeros(rows6, device="cuda")
+    lib.call("matvec_q4k_q6k_pair_q8", w4.data, b4, rows4, w6.data, b6, rows6, xq, xd, k)
+    assert bit_equal(a4.cpu().numpy(), b4.cpu().numpy()) and bit_equal(a6.cpu().numpy(), b6.cpu().numpy())
+
+
+def test_pair_launch_declines_what_the_bulk_copy_kernel_takes():
+    """More than 6144 rows belongs to the bulk-copy kernel, k > 4096 to the staged one: UnsupportedOperation (7) and
+    nothing launched; a bad shape is InvalidValue (2)."""
+    buf = torch.zeros(1 << 16, device="cuda")
+    for rows4, rows6, k, want in ((6152, 1024, 4096, 7), (1024, 6152, 3072, 7), (1024, 1024, 4096 + 256, 7), (1024, 0, 1024, 7),
+                                  (1024, 1024, 100, 2)):
+        assert lib.call("matvec_q4k_q6k_pair_q8", buf, buf, rows4, buf, buf, rows6, buf, buf, k, raise_on_error=False) == want
