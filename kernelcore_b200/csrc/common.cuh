@@ -145,11 +145,13 @@ __device__ __forceinline__ void add_norm_q8_cta(float* x, const float* t, const 
                                                 float eps, float* gsum) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int groups = n / 128;
-    float4 v[MAXIT];
+    float4 v[MAXIT], ww[MAXIT];
 #pragma unroll
     for (int i = 0; i < MAXIT; ++i) {
         const int gi = warp + i * nw;
+        v[i] = ww[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (gi < groups) {
+            ww[i] = __ldg(reinterpret_cast<const float4*>(w + gi * 128) + lane);  // needed last, asked for first
             float4* px = reinterpret_cast<float4*>(x + gi * 128) + lane;
             float4 a = *px;
             if (t) {
@@ -171,9 +173,8 @@ __device__ __forceinline__ void add_norm_q8_cta(float* x, const float* t, const 
     for (int i = 0; i < MAXIT; ++i) {
         const int gi = warp + i * nw;
         if (gi < groups) {
-            const float4 ww = __ldg(reinterpret_cast<const float4*>(w + gi * 128) + lane);
-            quantize_4blocks_warp(make_float4(__fmul_rn(__fmul_rn(v[i].x, r), ww.x), __fmul_rn(__fmul_rn(v[i].y, r), ww.y),
-                                              __fmul_rn(__fmul_rn(v[i].z, r), ww.z), __fmul_rn(__fmul_rn(v[i].w, r), ww.w)),
+            quantize_4blocks_warp(make_float4(__fmul_rn(__fmul_rn(v[i].x, r), ww[i].x), __fmul_rn(__fmul_rn(v[i].y, r), ww[i].y),
+                                              __fmul_rn(__fmul_rn(v[i].z, r), ww[i].z), __fmul_rn(__fmul_rn(v[i].w, r), ww[i].w)),
                                   xq, xd, gi * 4, lane);
         }
     }
