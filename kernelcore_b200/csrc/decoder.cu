@@ -307,14 +307,34 @@ __global__ void attn_combine_q8_kernel(const float* __restrict__ part, float* __
     if (b >= heads * hd / 32) return;
     const int h = b * 32 / hd, d = (b * 32) % hd + lane;
     const float* ph = part + static_cast<size_t>(h) * nsplit * (hd + 2);
-    float mm = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, ph[s * (hd + 2) + hd]);
     float ll = 0.0f, aa = 0.0f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float pm = ph[s * (hd + 2) + hd];
-        const float wgt = pm == -INFINITY ? 0.0f : exp2f((pm - mm) * 1.44269504f);
-        ll += ph[s * (hd + 2) + hd + 1] * wgt;
-        aa += ph[s * (hd + 2) + d] * wgt;
+    if (nsplit <= 32) {
+        // one round trip: lane s asks for split s's {max, sum}, every lane for its channel of all splits; the weights
+        // are computed once per split and handed round by shuffles; the sums run in split order as in the loop below
+        float pv[32];
+#pragma unroll
+        for (int s = 0; s < 32; ++s) pv[s] = s < nsplit ? ph[s * (hd + 2) + d] : 0.0f;
+        const float pm = lane < nsplit ? ph[lane * (hd + 2) + hd] : -INFINITY;
+        const float pl = lane < nsplit ? ph[lane * (hd + 2) + hd + 1] : 0.0f;
+        const float mm = warp_max(pm);
+        const float wl = pm == -INFINITY ? 0.0f : exp2f((pm - mm) * 1.44269504f);
+#pragma unroll
+        for (int s = 0; s < 32; ++s) {
+            const float wgt = __shfl_sync(0xffffffffu, wl, s), ls = __shfl_sync(0xffffffffu, pl, s);
+            if (s < nsplit) {
+                ll = __fmaf_rn(ls, wgt, ll);
+                aa = __fmaf_rn(pv[s], wgt, aa);
+            }
+        }
+    } else {
+        float mm = -INFINITY;
+        for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, ph[s * (hd + 2) + hd]);
+        for (int s = 0; s < nsplit; ++s) {
+            const float pm = ph[s * (hd + 2) + hd];
+            const float wgt = pm == -INFINITY ? 0.0f : exp2f((pm - mm) * 1.44269504f);
+            ll = __fmaf_rn(ph[s * (hd + 2) + hd + 1], wgt, ll);
+            aa = __fmaf_rn(ph[s * (hd + 2) + d], wgt, aa);
+        }
     }
     const float v = __fdiv_rn(aa, ll);
     attn[b * 32 + lane] = v;
