@@ -147,6 +147,10 @@ int kcb_matvec_q4x8_q8(const int32_t* qw_dev, const int32_t* xq_dev, const float
 int kcb_matmul_f16(const int32_t* qw_dev, const float* x_dev, float* y_dev, int rows, int k, int ncols, void* stream);
 /* Bounded waits of the tensor-core kernel that expired since load (0 in a healthy process); synchronous. */
 unsigned kcb_tc_timeouts(void);
+/* How many K slices the tensor-core matmul of this shape is contracted in (outside stream capture): 1 = one pass,
+ * outputs bit-identical to llm::ref::matvecQ4KQ8K / matvecQ6KQ8K; more = slices added in order by a second kernel,
+ * outputs within ~1e-6.  0 for shapes that path does not take (rows % 128, k % 1024).  Pure host arithmetic. */
+int kcb_matmul_tc_k_slices(int rows, int k, int ncols);
 
 /* ---- row-sharded matvec across GPUs (no counterpart in the reference, which is single-device) -------------
  * One process per GPU, rank r owning `rows` consecutive rows of a Q6_K matrix (its own planes).  The kernel

@@ -157,6 +157,7 @@ int kcb_matmul_kq_q8(const void* w, const int32_t* xq, float* y, int rows, int k
     return matmul_kq_q8(w, xq, y, rows, k, ncols, q6, q8k, st(s));
 }
 unsigned kcb_tc_timeouts(void) { return tc_timeouts(); }
+int kcb_matmul_tc_k_slices(int rows, int k, int ncols) { return matmul_tc_k_slices(rows, k, ncols); }
 int kcb_kernel_count(void) { return kernel_count(); }
 const char* kcb_kernel_name(int i) { return kernel_name(i); }
 int kcb_matvec_q8w(const int8_t* q, const float* scales, const float* x, float* y, int rows, int k, void* s) {

@@ -468,6 +468,32 @@ float* splitk_scratch(cudaStream_t s, size_t floats) {
     return b.first;
 }
 
+// Super-blocks per K slice of a launch (nsb: one pass).  Few tiles leave SMs without one (or the last wave mostly
+// empty) and every CTA with a long serial chain over the super-blocks: split K where a wave model says it pays.  A
+// launch of `c` CTAs runs in ceil(c / slots) waves, a CTA costs its super-blocks plus ~1.5 super-block times of set-up
+// and store, and the second kernel that adds the slices (in slice order: deterministic, but the fp32 sum is
+// associated differently from the one-pass result, so outputs agree with the reference's mirror to ~1e-6 instead of
+// bit for bit) costs about as much again.  The split must win by 10 %, contract at least two super-blocks per CTA
+// and keep the slices within 64 MB.
+int super_blocks_per_slice(int rows, int nsb, int ncols, int tn) {
+    if (nsb < 4) return nsb;
+    const int tiles = (rows / TM) * ((ncols + tn - 1) / tn);
+    const int slots = kSmCount * (tn == 32 ? 2 : 1);  // CTAs the machine holds at once
+    const auto cost = [&](int n_splits) {
+        const int p = (nsb + n_splits - 1) / n_splits;
+        const int waves = (tiles * n_splits + slots - 1) / slots;
+        return waves * (2 * p + 3) + (n_splits > 1 ? 3 : 0);  // in half super-block times
+    };
+    int best = 1, best_cost = cost(1);
+    for (int c = 2; c <= nsb / 2; ++c) {
+        if ((nsb + c - 1) / c * (c - 1) >= nsb) continue;  // the last slice would be empty
+        if (static_cast<size_t>(c) * ncols * rows * sizeof(float) > (64u << 20)) break;
+        if (cost(c) < best_cost) best = c, best_cost = cost(c);
+    }
+    return best > 1 && 10 * best_cost <= 9 * cost(1) ? (nsb + best - 1) / best : nsb;
+}
+constexpr int tile_columns(int ncols) { return ncols <= 64 ? 32 : 128; }
+
 template <bool kQ6, int TN>
 int launch_tc_tn(const uint8_t* w, const int* xq, float* y, int rows, int nsb, int ncols, cudaStream_t s) {
     auto kern = kQ6 ? matmul_q6k_q8k_tc_kernel<TN> : matmul_q4k_q8k_tc_kernel<TN>;
@@ -476,36 +502,11 @@ int launch_tc_tn(const uint8_t* w, const int* xq, float* y, int rows, int nsb, i
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return KCB_LAUNCH_FAILURE;
         attr_set = true;
     }
-    const int tiles = (rows / TM) * ((ncols + TN - 1) / TN);
-    // Few tiles leave SMs without one (or the last wave mostly empty) and every CTA with a long serial chain over the
-    // super-blocks: split K where a wave model says it pays.  A launch of `c` CTAs runs in ceil(c / slots) waves, a CTA
-    // costs its super-blocks plus ~1.5 super-block times of set-up and store, and the second kernel that adds the
-    // slices (in slice order: deterministic, but the fp32 sum is associated differently from the one-pass result, so
-    // outputs agree with the reference's mirror to ~1e-6 instead of bit for bit) costs about as much again.  The
-    // split must win by 10 %, contract at least two super-blocks per CTA and keep the slices within 64 MB.  Not
-    // under stream capture, where the scratch cannot be allocated.
-    int splits = 1, per = nsb;
-    if (nsb >= 4) {
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        if (cudaStreamIsCapturing(s, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
-            const int slots = kSmCount * (TN == 32 ? 2 : 1);  // CTAs the machine holds at once
-            const auto cost = [&](int n_splits) {
-                const int p = (nsb + n_splits - 1) / n_splits;
-                const int waves = (tiles * n_splits + slots - 1) / slots;
-                return waves * (2 * p + 3) + (n_splits > 1 ? 3 : 0);  // in half super-block times
-            };
-            int best = 1, best_cost = cost(1);
-            for (int c = 2; c <= nsb / 2; ++c) {
-                if ((nsb + c - 1) / c * (c - 1) >= nsb) continue;  // the last slice would be empty
-                if (static_cast<size_t>(c) * ncols * rows * sizeof(float) > (64u << 20)) break;
-                if (cost(c) < best_cost) best = c, best_cost = cost(c);
-            }
-            if (best > 1 && 10 * best_cost <= 9 * cost(1)) {
-                per = (nsb + best - 1) / best;
-                splits = (nsb + per - 1) / per;
-            }
-        }
-    }
+    // K slices only outside stream capture, where the scratch can be allocated
+    int per = nsb;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) per = super_blocks_per_slice(rows, nsb, ncols, TN);
+    const int splits = (nsb + per - 1) / per;
     float* partial = nullptr;
     if (splits > 1) {
         partial = splitk_scratch(s, static_cast<size_t>(splits) * ncols * rows);
@@ -522,9 +523,17 @@ int launch_tc_tn(const uint8_t* w, const int* xq, float* y, int rows, int nsb, i
 }
 template <bool kQ6>
 int launch_tc(const uint8_t* w, const int* xq, float* y, int rows, int nsb, int ncols, cudaStream_t s) {
-    return ncols <= 64 ? launch_tc_tn<kQ6, 32>(w, xq, y, rows, nsb, ncols, s) : launch_tc_tn<kQ6, 128>(w, xq, y, rows, nsb, ncols, s);
+    return tile_columns(ncols) == 32 ? launch_tc_tn<kQ6, 32>(w, xq, y, rows, nsb, ncols, s) : launch_tc_tn<kQ6, 128>(w, xq, y, rows, nsb, ncols, s);
 }
 }  // namespace
+
+// K slices a tensor-core launch of this shape takes outside stream capture (1: one pass, outputs bit-identical to the
+// reference's mirror); 0 for shapes the tensor-core path does not take.
+int matmul_tc_k_slices(int rows, int k, int ncols) {
+    if (rows <= 0 || rows % TM || k <= 0 || k % 1024 || ncols <= 0) return 0;
+    const int nsb = k / 256, per = super_blocks_per_slice(rows, nsb, ncols, tile_columns(ncols));
+    return (nsb + per - 1) / per;
+}
 
 unsigned tc_timeouts() {
     unsigned v = 0;

@@ -39,6 +39,7 @@ int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int nc
 int matmul_q4k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s);
 int matmul_q6k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s);
 unsigned tc_timeouts();
+int matmul_tc_k_slices(int rows, int k, int ncols);
 
 // glue.cu
 int rms_norm(const float* x, const float* w, float* y, int n, int rows, float eps, cudaStream_t s);
