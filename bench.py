@@ -350,7 +350,7 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps_timed, "warmup": max(args.warmup, 3) + 3 * NMAT,
         "ms_per_step": total_ms / steps_timed, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 dot, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"Q6_K lm_head matvec {ROWS}x{K} (BASELINE configs[1]): Backend::matvec = Q8 quantize + matvec_q6k_q8 in one launch"
+        "config": {"workload": f"Q6_K lm_head matvec {ROWS}x{K} (benchmark spec configs[1]): Backend::matvec = Q8 quantize + matvec_q6k_q8 in one launch"
                                + (f", rows sharded over {world} GPUs + all-gather of the logits" if world > 1 else ""),
                    "rows": ROWS, "k": K, "rows_per_gpu": rows, "all_gather": gather_mode, "gather_identical_on_all_ranks": gather_ok,
                    "l2": f"inputs larger than L2: {NMAT} rotating {rows * NSB * 210 / 1e6:.0f} MB weight matrices"},
@@ -393,7 +393,7 @@ def run_ours(args):
 
 
 def q4k_config0(torch, kquant, synth, peak):
-    """BASELINE configs[0]: Q4_K matvec 8192 x 3072.  The 14 MB matrix fits L2 many times over, so 40 distinct
+    """Benchmark spec configs[0]: Q4_K matvec 8192 x 3072.  The 14 MB matrix fits L2 many times over, so 40 distinct
     copies rotate; 80 launches are timed inside one CUDA graph (the kernel is shorter than a launch)."""
     rows, k, nmat, n = 8192, 3072, 40, 80
     base = synth.q4k_blocks(rows, k, 0)
@@ -426,7 +426,7 @@ def q4k_config0(torch, kquant, synth, peak):
 
 
 def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5, q6=False):
-    """BASELINE configs[2]: Y[M x 8192] = X[M x 3072] . W^T, W Q4_K; X quantized on the fly to per-256 int8 slots
+    """Benchmark spec configs[2]: Y[M x 8192] = X[M x 3072] . W^T, W Q4_K; X quantized on the fly to per-256 int8 slots
     (quantize_cols_k) and contracted on the tensor cores (tcgen05 int8).  One step = quantize + matmul.
     q6: the Q6_K kernel on the FFN-down shape of the same model, 3072 x 8192."""
     import torch
@@ -492,7 +492,7 @@ def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5, q6=False):
 
 
 def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b", lean=False):
-    """BASELINE configs[3] (or [4] with model="qwen3_8b"): random-init model, Q4_K_M mix, batch 1, fp16 KV cache,
+    """Benchmark spec configs[3] (or [4] with model="qwen3_8b"): random-init model, Q4_K_M mix, batch 1, fp16 KV cache,
     greedy.  The prompt is processed token by token through the same graph (no batched prefill yet).
     Under torchrun (WORLD_SIZE > 1) the ranks run the tensor-parallel decoder: heads, FFN rows and vocabulary rows
     sharded, partial hidden vectors summed inside the norm kernels over NVLink peer loads; times are the max over
@@ -575,7 +575,7 @@ def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b", lean=False)
 
 
 def batch_decode_bench(model_name, n_seq, n_prompt, n_gen):
-    """BASELINE configs[4] at batch > 1: n_seq independent sequences with random prompts of n_prompt tokens each,
+    """Benchmark spec configs[4] at batch > 1: n_seq independent sequences with random prompts of n_prompt tokens each,
     decoded in lockstep for n_gen greedy tokens on one GPU; the aggregate rate counts every sequence's tokens."""
     import torch
 
@@ -639,7 +639,7 @@ def run_decode(args):
         out = batch_decode_bench(args.model, args.batch, args.prompt, args.gen)
         print(json.dumps({"metric": f"{args.model}_batch{args.batch}_decode_tok_s", "value": out["aggregate_tok_s"], "unit": "tokens/s", "n_gpus": 1,
                           "higher_is_better": True, "data": "synthetic", "dtype": "int8 dot, fp32 accumulate",
-                          "config": {"workload": f"BASELINE configs[4]-style batch of {args.batch} independent sequences, lockstep decode"},
+                          "config": {"workload": f"benchmark spec configs[4]-style batch of {args.batch} independent sequences, lockstep decode"},
                           "detail": out}))
         return
     peak, _ = measured_peak()
@@ -653,7 +653,7 @@ def run_decode(args):
         cfg = "configs[4]" if args.model == "qwen3_8b" else "configs[3]"
         print(json.dumps({"metric": f"{args.model}_decode_tok_s", "value": out["decode_tok_s"], "unit": "tokens/s", "n_gpus": out["n_gpus"],
                           "higher_is_better": True, "scaling": "strong", "data": "synthetic", "dtype": "int8 dot, fp32 accumulate",
-                          "config": {"workload": f"BASELINE {cfg} decode, graph-replayed decoder"}, "detail": out}))
+                          "config": {"workload": f"benchmark spec {cfg} decode, graph-replayed decoder"}, "detail": out}))
 
 
 def main():

@@ -329,7 +329,7 @@ int kcb_decoder_set_prompt(void* decoder, const int* tokens, int n, int start_po
  * position start_pos + n; kcb_decoder_run then generates.  Returns after the pass has finished. */
 int kcb_decoder_prefill(void* decoder, const int* tokens, int n, int start_pos);
 int kcb_decoder_run(void* decoder, int steps);
-/* A batch of independent sequences decoded in lockstep on one GPU (BASELINE's batch-32 case; the reference's batched
+/* A batch of independent sequences decoded in lockstep on one GPU (the benchmark spec's batch-32 case; the reference's batched
  * path is its ggml backend with several tokens per graph, ggml-kernelcore.cpp:548-603): begin allocates one fp16 KV
  * cache per sequence; batch_prefill runs sequence `seq`'s prompt (all prompts the same length) and makes its first
  * pick; batch_run advances every sequence by `steps` greedy tokens, reading the weights once per step for the whole

@@ -23,7 +23,7 @@ def test_library_exports_every_declared_symbol():
     missing = [n for n in names if not hasattr(lib.raw, n)]
     assert not missing, missing
     assert lib.raw.kcb_build_arch() == b"sm_100a"
-    assert lib.raw.kcb_kquant_bytes(8192, 3072, 0) == 14155776      # BASELINE config 0 weight bytes
+    assert lib.raw.kcb_kquant_bytes(8192, 3072, 0) == 14155776      # weight bytes of the Q4_K 8192 x 3072 benchmark matrix
     assert lib.raw.kcb_kquant_bytes(128256, 3072, 1) == 323205120   # config 1
     assert lib.raw.kcb_error_string(2) == b"invalid value"
 
@@ -85,7 +85,7 @@ def test_tensor_core_k_slices_follow_the_wave_model():
     with the reference's mirror and more slices mean ~1e-6."""
     from kernelcore_b200 import lib
     ks = lib.raw.kcb_matmul_tc_k_slices
-    assert ks(8192, 3072, 512) == 1 and ks(8192, 3072, 2048) == 1      # BASELINE configs[2]: 256 / 1024 tiles
+    assert ks(8192, 3072, 512) == 1 and ks(8192, 3072, 2048) == 1      # the Q4_K 8192 x 3072 benchmark matmul: 256 / 1024 tiles
     assert ks(8192, 3072, 128) == 2 and ks(8192, 3072, 32) == 4        # 64 tiles of 128 / 32 columns
     assert ks(3072, 8192, 512) == 3                                    # Llama-3.2-3B FFN-down: 96 tiles of 32 super-blocks
     assert ks(3072, 3072, 512) == 1 and ks(4096, 3072, 512) == 1      # wo, q|k: a split would gain < 10 %

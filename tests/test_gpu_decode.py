@@ -182,7 +182,7 @@ def test_batch_of_sequences_in_lockstep(shape_fn):
 
 
 def test_full_size_model_properties():
-    """BASELINE configs[3] at its real shapes (random-init Llama-3.2-3B architecture, 28 layers): properties that
+    """The Llama-3.2-3B decode benchmark at its real shapes (random-init Llama-3.2-3B architecture, 28 layers): properties that
     need no CPU oracle run.  Free-running greedy decode and the teacher-forced replay of its own picks give the same
     logits and picks bit for bit; the batched prompt pass and the token-by-token prompt agree within the bound the
     two activation quantizations allow; nothing timed out."""
@@ -190,7 +190,7 @@ def test_full_size_model_properties():
     model = tm.build(shape, seed=0)
     prompt = [int(t) for t in np.random.default_rng(9).integers(0, shape.vocab, 48)]
     with decoder.FastDecoder(shape, model) as d:
-        assert d.weight_bytes == 2113026048                      # the per-token weight bytes BASELINE states
+        assert d.weight_bytes == 2113026048                      # the per-token weight bytes the benchmark spec states
         d.set_prompt(prompt)
         d.run(56)                                                # 48 forced + 8 free
         free_logits, hist, pos = d.read(n_history=56)

@@ -83,7 +83,7 @@ def test_matvec_f32_against_dequant_dot(q6):
 
 
 def test_config0_and_lm_head_slice_full_k():
-    """BASELINE shapes: the whole 8192x3072 Q4_K matvec and a 16032-row slice (the 8-GPU shard) of
+    """Benchmark shapes: the whole 8192x3072 Q4_K matvec and a 16032-row slice (the 8-GPU shard) of
     the 128256x3072 Q6_K lm_head, against the oracle."""
     sc = kquant.Q8Scratch(3072)
     for rows, k, q6 in ((8192, 3072, False), (16032, 3072, True)):

@@ -93,7 +93,7 @@ def test_ffn_down_shape_splits_k_three_ways():
 
 
 def test_config2_shape_against_cuda_core_path():
-    """BASELINE configs[2] at M = 128 and 512: 8192 x 3072 Q4_K; spot-check columns against the oracle and the
+    """The Q4_K benchmark matmul at M = 128 and 512: 8192 x 3072 Q4_K; spot-check columns against the oracle and the
     linearity property on the rest (activations scaled by 2 give exactly doubled outputs)."""
     rows, k = 8192, 3072
     w = synth.q4k_blocks(rows, k, 0)
