@@ -130,11 +130,18 @@ int kcb_matvec_q6k_f32(const void* planes_dev, const float* x_dev, float* y_dev,
 /* ---- prompt matmul -------------------------------------------------------------------------------- */
 /* kernels "matmul_q4k_q8x4/x8", "matmul_q6k_q8x4/x8" (q8k = 0: per-32 slots of 11*k/32 ints per column) and
  * "matmul_q4k_q8kx4/x8", "matmul_q6k_q8kx4/x8" (q8k = 1: per-256 slots of 85*k/256 ints), llm::MatmulKQ8Args
- * (llm/llm_kernels.hpp:255-271): Y[c*rows + r] for ncols activation columns.  Q4_K with per-256 slots and
- * rows % 128 == 0 runs on the tensor cores (tcgen05, int8), bit-identical per column to
- * llm::ref::matvecQ4KQ8K (llm/llm_reference.cpp:529-562); other cases on CUDA cores. */
+ * (llm/llm_kernels.hpp:255-271): Y[c*rows + r] for ncols activation columns.  Per-256 slots with rows % 128 == 0,
+ * k % 1024 == 0 and at least 16 columns run on the tensor cores (tcgen05, int8) in one pass, every output
+ * bit-identical to llm::ref::matvecQ4KQ8K / matvecQ6KQ8K (llm/llm_reference.cpp:529-596); other cases on CUDA cores. */
 int kcb_matmul_kq_q8(const void* w_dev, const int32_t* slots_dev, float* y_dev, int rows, int k, int ncols, int q6, int q8k,
                      void* stream);
+/* The same with a caller-owned device workspace of kcb_matmul_tc_workspace_bytes(rows, k, ncols) bytes: where few
+ * tiles would leave SMs idle, the tensor-core launch then contracts K in kcb_matmul_tc_k_slices slices that a second
+ * kernel adds in slice order (outputs within ~1e-6 of the one-pass result, deterministic).  A null or smaller
+ * workspace means one pass.  Nothing is allocated by either call, inside or outside stream capture. */
+int kcb_matmul_kq_q8_ws(const void* w_dev, const int32_t* slots_dev, float* y_dev, int rows, int k, int ncols, int q6, int q8k,
+                        void* workspace_dev, size_t workspace_bytes, void* stream);
+size_t kcb_matmul_tc_workspace_bytes(int rows, int k, int ncols);
 /* The reference's synthetic weight formats and fp16 matmul (kernels/llm/matvec_q8.cu, matvec_q4.cu, matvec_q4x8.cu,
  * matvec_q4x8_q8.cu / _q8x2.cu, matmul_f16.cu; layouts llm/llm_kernels.hpp:24-70, :284-296).  Bit-identical to
  * llm::ref::matvecQ8 / matvecQ4 / matvecQ4x8 / matvecQ4x8Q8 / matmulF16.  `interleaved` selects the 8-row
@@ -147,9 +154,9 @@ int kcb_matvec_q4x8_q8(const int32_t* qw_dev, const int32_t* xq_dev, const float
 int kcb_matmul_f16(const int32_t* qw_dev, const float* x_dev, float* y_dev, int rows, int k, int ncols, void* stream);
 /* Bounded waits of the tensor-core kernel that expired since load (0 in a healthy process); synchronous. */
 unsigned kcb_tc_timeouts(void);
-/* How many K slices the tensor-core matmul of this shape is contracted in (outside stream capture): 1 = one pass,
- * outputs bit-identical to llm::ref::matvecQ4KQ8K / matvecQ6KQ8K; more = slices added in order by a second kernel,
- * outputs within ~1e-6.  0 for shapes that path does not take (rows % 128, k % 1024).  Pure host arithmetic. */
+/* How many K slices kcb_matmul_kq_q8_ws contracts a tensor-core shape in when given its workspace: 1 = one pass,
+ * more = slices added in order by a second kernel.  0 for shapes that path does not take (rows % 128, k % 1024).
+ * Pure host arithmetic. */
 int kcb_matmul_tc_k_slices(int rows, int k, int ncols);
 
 /* ---- row-sharded matvec across GPUs (no counterpart in the reference, which is single-device) -------------

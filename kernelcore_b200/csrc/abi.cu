@@ -156,8 +156,13 @@ int kcb_flash_attn_f16(const float* q, const void* k, const void* v, const void*
 int kcb_matmul_kq_q8(const void* w, const int32_t* xq, float* y, int rows, int k, int ncols, int q6, int q8k, void* s) {
     return matmul_kq_q8(w, xq, y, rows, k, ncols, q6, q8k, st(s));
 }
-unsigned kcb_tc_timeouts(void) { return tc_timeouts(); }
-int kcb_matmul_tc_k_slices(int rows, int k, int ncols) { return matmul_tc_k_slices(rows, k, ncols); }
+int kcb_matmul_kq_q8_ws(const void* w, const int32_t* xq, float* y, int rows, int k, int ncols, int q6, int q8k, void* workspace,
+                        size_t workspace_bytes, void* s) {
+    return matmul_kq_q8(w, xq, y, rows, k, ncols, q6, q8k, st(s), workspace, workspace_bytes);
+}
+size_t kcb_matmul_tc_workspace_bytes(int rows, int k, int ncols) { return matmul_tc_workspace_bytes(rows, k, ncols); }
+unsigned kcb_tc_timeouts(void) { return tc_timeouts() + tc_pipe_timeouts(); }
+int kcb_matmul_tc_k_slices(int rows, int k, int ncols) { return matmul_tc_pipe_k_slices(rows, k, ncols); }
 int kcb_kernel_count(void) { return kernel_count(); }
 const char* kcb_kernel_name(int i) { return kernel_name(i); }
 int kcb_matvec_q8w(const int8_t* q, const float* scales, const float* x, float* y, int rows, int k, void* s) {

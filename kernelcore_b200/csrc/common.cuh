@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace kcb {
 
 // Status codes returned across the C ABI: the integer values of the reference's kc::Error
@@ -219,6 +221,27 @@ __device__ __forceinline__ int prmt_sbyte(unsigned w, unsigned sel) {
     asm("prmt.b32 %0, %1, 0, %2;" : "=r"(r) : "r"(w), "r"(sel));
     return r;
 }
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is a setting of one device, and a process may drive several
+// (kcSetDevice selects one per thread): the "already raised" flag is kept per device, not per process.
+constexpr int kMaxDevices = 64;
+struct PerDeviceFlag {
+    std::atomic<bool> set[kMaxDevices] = {};
+};
+template <class Kern>
+inline bool raise_dynamic_smem(Kern kern, int bytes, PerDeviceFlag& f) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return false;
+    if (f.set[dev].load(std::memory_order_acquire)) return true;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    f.set[dev].store(true, std::memory_order_release);
+    return true;
+}
+
+// Host-side alignment test made by the launchers before anything is enqueued: the kernels read weights and Q8
+// scratch with 16-byte loads and bulk copies, so a pointer that is valid for the reference (any interior address)
+// but misaligned gets KCB_INVALID_POINTER here instead of a device-side misaligned-address fault.
+inline bool misaligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
 
 // Launch-error to status code; never synchronises.
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? KCB_SUCCESS : KCB_LAUNCH_FAILURE; }

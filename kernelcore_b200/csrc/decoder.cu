@@ -823,7 +823,7 @@ public:
                 float* outs[2] = {pQK, pV};
                 int which = 0;
                 for (const DMat& w : L.qkv)
-                    if (const int e = matmul_kq_q8(w.data, pSlots, outs[which++], w.rows, w.k, m, w.q6, 1, stream_); e) return e;
+                    if (const int e = matmul_kq_q8(w.data, pSlots, outs[which++], w.rows, w.k, m, w.q6, 1, stream_, pWs, kWsBytes); e) return e;
                 const int qk_stride = fused_qkv ? qd + 2 * kv : qd + kv;
                 float* vrows = fused_qkv ? pQK + qd + kv : pV;
                 const int v_stride = fused_qkv ? qk_stride : kv;
@@ -836,23 +836,23 @@ public:
                 if (const int e = hd == 128 ? attention<128>(L, pQK, qk_stride, m, p0, pA, kc, vc) : attention<64>(L, pQK, qk_stride, m, p0, pA, kc, vc); e)
                     return e;
                 if (const int e = quantize_cols_k(pA, pSlots, qd, m, stream_); e) return e;
-                if (const int e = matmul_kq_q8(L.wo.data, pSlots, pT, L.wo.rows, L.wo.k, m, L.wo.q6, 1, stream_); e) return e;
+                if (const int e = matmul_kq_q8(L.wo.data, pSlots, pT, L.wo.rows, L.wo.k, m, L.wo.q6, 1, stream_, pWs, kWsBytes); e) return e;
                 if (const int e = add_norm_q8(pX, pT, pX, L.ffn_norm, nullptr, pSlots, pSq, hidden, m, eps, 3, 1, stream_); e) return e;
                 // gate and up separately so that each is a contiguous [m][inter] matrix for SwiGLU
                 float* go = pG;
                 for (const DMat& w : L.gu) {
                     const size_t row_bytes = static_cast<size_t>(w.k / 256) * kQ4KBlock;
                     if (w.rows == 2 * inter && !w.q6) {
-                        if (const int e = matmul_kq_q8(w.data, pSlots, pG, inter, w.k, m, 0, 1, stream_); e) return e;
-                        if (const int e = matmul_kq_q8(w.data + row_bytes * inter, pSlots, pU, inter, w.k, m, 0, 1, stream_); e) return e;
+                        if (const int e = matmul_kq_q8(w.data, pSlots, pG, inter, w.k, m, 0, 1, stream_, pWs, kWsBytes); e) return e;
+                        if (const int e = matmul_kq_q8(w.data + row_bytes * inter, pSlots, pU, inter, w.k, m, 0, 1, stream_, pWs, kWsBytes); e) return e;
                     } else {
-                        if (const int e = matmul_kq_q8(w.data, pSlots, go, w.rows, w.k, m, w.q6, 1, stream_); e) return e;
+                        if (const int e = matmul_kq_q8(w.data, pSlots, go, w.rows, w.k, m, w.q6, 1, stream_, pWs, kWsBytes); e) return e;
                         go = pU;
                     }
                 }
                 if (const int e = silu_mul(pG, pU, pG, static_cast<size_t>(m) * inter, stream_); e) return e;
                 if (const int e = quantize_cols_k(pG, pSlots, inter, m, stream_); e) return e;
-                if (const int e = matmul_kq_q8(L.wd.data, pSlots, pT, L.wd.rows, L.wd.k, m, L.wd.q6, 1, stream_); e) return e;
+                if (const int e = matmul_kq_q8(L.wd.data, pSlots, pT, L.wd.rows, L.wd.k, m, L.wd.q6, 1, stream_, pWs, kWsBytes); e) return e;
             }
             if (c0 + m < n) continue;
             // last token: residual add, final norm, logits, greedy pick, position
@@ -930,7 +930,7 @@ public:
             float* outs[2] = {pQK, pV};
             int which = 0;
             for (const DMat& w : L.qkv)
-                if (const int e = matmul_kq_q8(w.data, pSlots, outs[which++], w.rows, w.k, B, w.q6, 1, stream_); e) return e;
+                if (const int e = matmul_kq_q8(w.data, pSlots, outs[which++], w.rows, w.k, B, w.q6, 1, stream_, pWs, kWsBytes); e) return e;
             const int qk_stride = fused_qkv ? qd + 2 * kv : qd + kv;
             float* vrows = fused_qkv ? pQK + qd + kv : pV;
             const int v_stride = fused_qkv ? qk_stride : kv;
@@ -945,25 +945,25 @@ public:
             attn_combine_rows_kernel<<<dim3((qd + 127) / 128, B), 128, 0, stream_>>>(partB, pA, heads, hd, nsplit);
             if (const int e = launch_status(); e) return e;
             if (const int e = quantize_cols_k(pA, pSlots, qd, B, stream_); e) return e;
-            if (const int e = matmul_kq_q8(L.wo.data, pSlots, pT, L.wo.rows, L.wo.k, B, L.wo.q6, 1, stream_); e) return e;
+            if (const int e = matmul_kq_q8(L.wo.data, pSlots, pT, L.wo.rows, L.wo.k, B, L.wo.q6, 1, stream_, pWs, kWsBytes); e) return e;
             if (const int e = add_norm_q8(pX, pT, pX, L.ffn_norm, nullptr, pSlots, pSq, hidden, B, eps, 3, 1, stream_); e) return e;
             float* go = pG;
             for (const DMat& w : L.gu) {
                 const size_t row_bytes = static_cast<size_t>(w.k / 256) * kQ4KBlock;
                 if (w.rows == 2 * inter && !w.q6) {
-                    if (const int e = matmul_kq_q8(w.data, pSlots, pG, inter, w.k, B, 0, 1, stream_); e) return e;
-                    if (const int e = matmul_kq_q8(w.data + row_bytes * inter, pSlots, pU, inter, w.k, B, 0, 1, stream_); e) return e;
+                    if (const int e = matmul_kq_q8(w.data, pSlots, pG, inter, w.k, B, 0, 1, stream_, pWs, kWsBytes); e) return e;
+                    if (const int e = matmul_kq_q8(w.data + row_bytes * inter, pSlots, pU, inter, w.k, B, 0, 1, stream_, pWs, kWsBytes); e) return e;
                 } else {
-                    if (const int e = matmul_kq_q8(w.data, pSlots, go, w.rows, w.k, B, w.q6, 1, stream_); e) return e;
+                    if (const int e = matmul_kq_q8(w.data, pSlots, go, w.rows, w.k, B, w.q6, 1, stream_, pWs, kWsBytes); e) return e;
                     go = pU;
                 }
             }
             if (const int e = silu_mul(pG, pU, pG, static_cast<size_t>(B) * inter, stream_); e) return e;
             if (const int e = quantize_cols_k(pG, pSlots, inter, B, stream_); e) return e;
-            if (const int e = matmul_kq_q8(L.wd.data, pSlots, pT, L.wd.rows, L.wd.k, B, L.wd.q6, 1, stream_); e) return e;
+            if (const int e = matmul_kq_q8(L.wd.data, pSlots, pT, L.wd.rows, L.wd.k, B, L.wd.q6, 1, stream_, pWs, kWsBytes); e) return e;
         }
         if (const int e = add_norm_q8(pX, pT, pX, out_norm, nullptr, pSlots, pSq, hidden, B, eps, 3, 1, stream_); e) return e;
-        if (const int e = matmul_kq_q8(lm_head.data, pSlots, logitsB, lm_head.rows, lm_head.k, B, lm_head.q6, 1, stream_); e) return e;
+        if (const int e = matmul_kq_q8(lm_head.data, pSlots, logitsB, lm_head.rows, lm_head.k, B, lm_head.q6, 1, stream_, pWs, kWsBytes); e) return e;
         argmax_rows_kernel<<<B, 1024, 0, stream_>>>(logitsB, vocab, tokB, historyB, bpos, max_ctx);
         advance_pos_kernel<<<1, 1, 0, stream_>>>(bpos);
         return launch_status();
@@ -1017,6 +1017,8 @@ private:
         if (const int e = dev(reinterpret_cast<void**>(&pU), M * inter * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&pSlots), M * 85 * (maxk / 256) * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&pSq), M * 11 * (hidden / 32) * 4); e) return e;
+        if (!pWs)  // K slices of the tensor-core matmuls (the launches keep them within this size)
+            if (const int e = dev(&pWs, kWsBytes); e) return e;
         prefill_cap_ = cap;
         return KCB_SUCCESS;
     }
@@ -1254,6 +1256,8 @@ private:
     TpCtx tp;
     float *pX = nullptr, *pT = nullptr, *pQK = nullptr, *pV = nullptr, *pA = nullptr, *pG = nullptr, *pU = nullptr;
     int *pSlots = nullptr, *pSq = nullptr, prefill_cap_ = 0;
+    void* pWs = nullptr;
+    static constexpr size_t kWsBytes = 64u << 20;
     // batch of sequences
     int batch_ = 0, batch_pos_ = -1;
     std::vector<unsigned short*> kcB, vcB;

@@ -451,14 +451,22 @@ inline unsigned blocks_for(size_t n, int per) { return static_cast<unsigned>((n 
 
 }  // namespace
 
+// True if any of the (possibly null) pointers is not 4-byte aligned: the glue kernels read and write 32-bit words.
+template <class... P>
+inline bool any_misaligned4(P... p) {
+    return (... || misaligned(p, 4));
+}
+
 int rms_norm(const float* x, const float* w, float* y, int n, int rows, float eps, cudaStream_t s) {
     if (n <= 0 || rows < 0 || !x || !w || !y) return KCB_INVALID_VALUE;
+    if (any_misaligned4(x, w, y)) return KCB_INVALID_POINTER;
     if (rows == 0) return KCB_SUCCESS;
     rms_norm_kernel<<<rows, n >= 1024 ? 256 : 64, 0, s>>>(const_cast<float*>(x), nullptr, w, y, n, eps);
     return launch_status();
 }
 int add_rms_norm(float* x, const float* t, const float* w, float* y, int n, float eps, cudaStream_t s) {
     if (n <= 0 || !x || !t || !w || !y) return KCB_INVALID_VALUE;
+    if (any_misaligned4(x, t, w, y)) return KCB_INVALID_POINTER;
     rms_norm_kernel<<<1, 1024, 0, s>>>(x, t, w, y, n, eps);
     return launch_status();
 }
@@ -466,6 +474,7 @@ int add_rms_norm(float* x, const float* t, const float* w, float* y, int n, floa
 int add_norm_q8(const float* a, const float* t, float* out, const float* w, float* y, int* q, int* sq, int n, int rows,
                 float eps, int phases, int kq, cudaStream_t s) {
     if (n <= 0 || n % (kq ? 256 : 32) || rows < 0 || !a || !q || (kq && !sq) || ((phases & 2) && !w)) return KCB_INVALID_VALUE;
+    if (any_misaligned4(a, t, out, w, y, q, sq)) return KCB_INVALID_POINTER;
     if (rows == 0) return KCB_SUCCESS;
     const size_t smem = (static_cast<size_t>(n) + n / 32) * sizeof(float);
     if (smem > 48 * 1024) return KCB_INVALID_VALUE;
@@ -474,6 +483,7 @@ int add_norm_q8(const float* a, const float* t, float* out, const float* w, floa
 }
 int add_norm_q8_fast(float* x, const float* t, const float* w, int* xq, float* xd, int n, float eps, cudaStream_t s) {
     if (n <= 0 || n % 32 || n > 11264 || !x || !w || !xq || !xd) return KCB_INVALID_VALUE;
+    if (any_misaligned4(x, t, w, xq, xd)) return KCB_INVALID_POINTER;
     if (n % 128 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(t) | reinterpret_cast<uintptr_t>(w)) & 15) == 0)
         add_norm_q8_fast_kernel<<<1, 1024, 0, s>>>(x, t, w, xq, xd, n, eps);
     else
@@ -482,17 +492,20 @@ int add_norm_q8_fast(float* x, const float* t, const float* w, int* xq, float* x
 }
 int argmax_partial(const float* logits, int vocab, float* cand_v, int* cand_i, int ncand, cudaStream_t s) {
     if (vocab <= 0 || ncand <= 0 || !logits || !cand_v || !cand_i) return KCB_INVALID_VALUE;
+    if (any_misaligned4(logits, cand_v, cand_i)) return KCB_INVALID_POINTER;
     argmax_partial_kernel<<<ncand, 256, 0, s>>>(logits, vocab, cand_v, cand_i);
     return launch_status();
 }
 int silu_mul(const float* g, const float* u, float* out, size_t count, cudaStream_t s) {
     if (!g || !u || !out) return KCB_INVALID_VALUE;
+    if (any_misaligned4(g, u, out)) return KCB_INVALID_POINTER;
     if (count == 0) return KCB_SUCCESS;
     silu_mul_kernel<<<blocks_for(count, 256), 256, 0, s>>>(g, u, out, count);
     return launch_status();
 }
 int silu_mul_q8(const float* g, const float* u, float* y, int* q, int* xq, float* xd, int n, int cols, cudaStream_t s) {
     if (n <= 0 || n % 32 || cols < 0 || !g || !u || (!q && !(xq && xd))) return KCB_INVALID_VALUE;
+    if (any_misaligned4(g, u, y, q, xq, xd)) return KCB_INVALID_POINTER;
     if (cols == 0) return KCB_SUCCESS;
     const size_t warps = static_cast<size_t>(n / 32) * cols;
     silu_mul_q8_kernel<<<blocks_for(warps, 8), 256, 0, s>>>(g, u, y, q, n / 32, cols, xq, xd);
@@ -500,18 +513,21 @@ int silu_mul_q8(const float* g, const float* u, float* y, int* q, int* xq, float
 }
 int mul_rows(const float* x, const float* w, float* y, int n, size_t count, cudaStream_t s) {
     if (n <= 0 || !x || !w || !y) return KCB_INVALID_VALUE;
+    if (any_misaligned4(x, w, y)) return KCB_INVALID_POINTER;
     if (count == 0) return KCB_SUCCESS;
     mul_rows_kernel<<<blocks_for(count, 256), 256, 0, s>>>(x, w, y, n, count);
     return launch_status();
 }
 int vector_add(const float* a, const float* b, float* out, size_t count, cudaStream_t s) {
     if (!a || !b || !out) return KCB_INVALID_VALUE;
+    if (any_misaligned4(a, b, out)) return KCB_INVALID_POINTER;
     if (count == 0) return KCB_SUCCESS;
     vector_add_kernel<<<blocks_for(count, 256), 256, 0, s>>>(a, b, out, count);
     return launch_status();
 }
 int rope(float* x, const float* ff, int pairs, int pos, int count, float log2_base, cudaStream_t s) {
     if (pairs <= 0 || count < 0 || pos < 0 || !x) return KCB_INVALID_VALUE;
+    if (any_misaligned4(x, ff)) return KCB_INVALID_POINTER;
     if (count == 0) return KCB_SUCCESS;
     rope_kernel<<<blocks_for(count, 128), 128, 0, s>>>(x, ff, pairs, pos, count, log2_base);
     return launch_status();
@@ -519,6 +535,7 @@ int rope(float* x, const float* ff, int pairs, int pos, int count, float log2_ba
 int rope_ggml(const float* x, float* y, const int* pos, const float* ff, int head_dim, int n_head, int n_tokens,
               float log2_base, int neox, cudaStream_t s) {
     if (head_dim <= 0 || head_dim % 2 || n_head < 0 || n_tokens < 0 || !x || !y || !pos) return KCB_INVALID_VALUE;
+    if (any_misaligned4(x, y, pos, ff)) return KCB_INVALID_POINTER;
     const size_t count = static_cast<size_t>(head_dim / 2) * n_head * n_tokens;
     if (count == 0) return KCB_SUCCESS;
     rope_ggml_kernel<<<blocks_for(count, 128), 128, 0, s>>>(x, y, pos, ff, head_dim, n_head, n_tokens, log2_base, neox);
@@ -526,18 +543,21 @@ int rope_ggml(const float* x, float* y, const int* pos, const float* ff, int hea
 }
 int kv_append(const float* k, const float* v, float* kt, float* vc, int n, int k_stride, int pos, cudaStream_t s) {
     if (n <= 0 || pos < 0 || pos >= k_stride || !k || !v || !kt || !vc) return KCB_INVALID_VALUE;
+    if (any_misaligned4(k, v, kt, vc)) return KCB_INVALID_POINTER;
     kv_append_kernel<<<blocks_for(n, 128), 128, 0, s>>>(k, v, kt, vc, n, k_stride, pos);
     return launch_status();
 }
 int attn_scores(const float* q, const float* kt, float* scores, int n_heads, int ctx, int head_dim, int group,
                 int ctx_pad, int k_stride, float scale, cudaStream_t s) {
     if (n_heads <= 0 || ctx <= 0 || head_dim <= 0 || group <= 0 || !q || !kt || !scores) return KCB_INVALID_VALUE;
+    if (any_misaligned4(q, kt, scores)) return KCB_INVALID_POINTER;
     const dim3 grid(blocks_for(ctx, 128), n_heads);
     attn_scores_kernel<<<grid, 128, head_dim * sizeof(float), s>>>(q, kt, scores, n_heads, ctx, head_dim, group, ctx_pad, k_stride, scale);
     return launch_status();
 }
 int softmax(float* x, int n, int stride, int rows, cudaStream_t s) {
     if (n <= 0 || stride < n || rows < 0 || !x) return KCB_INVALID_VALUE;
+    if (any_misaligned4(x)) return KCB_INVALID_POINTER;
     if (rows == 0) return KCB_SUCCESS;
     softmax_kernel<<<rows, n >= 1024 ? 256 : 64, 0, s>>>(x, n, stride);
     return launch_status();
@@ -545,12 +565,14 @@ int softmax(float* x, int n, int stride, int rows, cudaStream_t s) {
 int attn_values(const float* p, const float* v, float* out, int n_heads, int ctx, int head_dim, int kv_stride, int group,
                 int ctx_pad, cudaStream_t s) {
     if (n_heads <= 0 || ctx <= 0 || head_dim <= 0 || group <= 0 || !p || !v || !out) return KCB_INVALID_VALUE;
+    if (any_misaligned4(p, v, out)) return KCB_INVALID_POINTER;
     attn_values_kernel<<<blocks_for(static_cast<size_t>(n_heads) * head_dim, 64), 64, 0, s>>>(p, v, out, n_heads, ctx, head_dim, kv_stride, group, ctx_pad);
     return launch_status();
 }
 int set_rows_f16(const float* src, const long long* idx, void* dst, int pairs, int rows, int src_row, int dst_row,
                  int dst_rows, cudaStream_t s) {
     if (pairs <= 0 || rows < 0 || dst_rows < 0 || !src || !idx || !dst) return KCB_INVALID_VALUE;
+    if (misaligned(src, 8) || (src_row & 1) || misaligned(idx, 8) || misaligned(dst, 4)) return KCB_INVALID_POINTER;  // float pairs in, half pairs out
     if (rows == 0) return KCB_SUCCESS;
     set_rows_f16_kernel<<<blocks_for(static_cast<size_t>(pairs) * rows, 256), 256, 0, s>>>(src, idx, static_cast<unsigned*>(dst), pairs, rows, src_row, dst_row, dst_rows);
     return launch_status();
@@ -558,6 +580,7 @@ int set_rows_f16(const float* src, const long long* idx, void* dst, int pairs, i
 int flash_attn_f16(const float* q, const void* k, const void* v, const void* mask, float* out, const int* dims15,
                    float scale, cudaStream_t s) {
     if (!q || !k || !v || !out || !dims15) return KCB_INVALID_VALUE;
+    if (any_misaligned4(q, k, v, mask, out)) return KCB_INVALID_POINTER;
     FaParams d;
     int* f = reinterpret_cast<int*>(&d);
     for (int i = 0; i < 15; ++i) f[i] = dims15[i];
@@ -565,10 +588,8 @@ int flash_attn_f16(const float* q, const void* k, const void* v, const void* mas
     const size_t smem = (static_cast<size_t>(d.T) + d.D) * sizeof(float);
     if (smem > 200 * 1024) return KCB_UNSUPPORTED_OPERATION;
     if (smem > 48 * 1024) {
-        static bool raised = false;
-        if (!raised && cudaFuncSetAttribute(flash_attn_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
-            return KCB_LAUNCH_FAILURE;
-        raised = true;
+        static PerDeviceFlag raised;
+        if (!raise_dynamic_smem(flash_attn_f16_kernel, 200 * 1024, raised)) return KCB_LAUNCH_FAILURE;
     }
     flash_attn_f16_kernel<<<d.N * d.H, 256, smem, s>>>(q, static_cast<const unsigned*>(k), static_cast<const unsigned*>(v),
                                                          static_cast<const unsigned*>(mask), out, d, scale);

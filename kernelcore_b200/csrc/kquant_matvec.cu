@@ -23,8 +23,10 @@
 #include "ops.h"
 
 #include <algorithm>
-
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 namespace kcb {
 namespace {
@@ -845,7 +847,16 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
         if (!mbar_wait_bounded(&full[s], parity)) {
             if (lane == 0) atomicAdd(&g_tma_timeouts, 1u);
             for (int t = 0; t < 1000; ++t) __nanosleep(1000);  // bounded grace for copies still in flight
-            return;  // data never arrived: leave without touching y
+            // data never arrived: leave without touching y.  The CTA still counts as finished (once, by thread 0) so
+            // that the last-CTA detection of this and every later launch stays right; it announces without waiting.
+            if (threadIdx.x == 0 && peers.world > 1 && atomicAdd(peers.done_counter, 1u) == gridDim.x - 1) {
+                atomicExch(peers.done_counter, 0u);
+                const unsigned e = atomicAdd(peers.epoch_counter, 1u) + 1u;
+                __threadfence_system();
+                for (int r = 0; r < peers.world; ++r)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[r] + peers.rank), "r"(e) : "memory");
+            }
+            return;
         }
         const int row0 = (blockIdx.x + i * gridDim.x) * TR;
         const uint8_t* st = buf + static_cast<size_t>(s) * stage_bytes;
@@ -881,6 +892,11 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
     // into every rank's flag array, then wait (bounded) until every rank's epoch has arrived here.
     if (peers.world > 1) {
         __shared__ unsigned s_epoch;  // 0: another CTA finishes last
+        // The last tile's peer stores are made by warps 0 .. peers.n - 1 after the loop's final barrier: this barrier
+        // orders them before thread 0, whose system-scope fence is then cumulative over them -- a peer that sees the
+        // new epoch sees every row of this CTA.
+        if (threadIdx.x == 32) s_epoch = 0;  // thread 0 may have left on a timeout (it has then done the accounting)
+        __syncthreads();
         if (threadIdx.x == 0) {
             __threadfence_system();  // this CTA's peer stores before its arrival
             unsigned e = 0;
@@ -916,12 +932,8 @@ int launch_tma_cfg(const uint8_t* wb, const int* xq, const float* xd, float* y, 
     if (stages > kTmaMaxStages) stages = kTmaMaxStages;
     if (stages < 2) return KCB_UNSUPPORTED_OPERATION;
     const size_t smem = 128 + kProlBytes + stages * stage_bytes;
-    static bool attr_set = false;  // per instantiation
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess)
-            return KCB_LAUNCH_FAILURE;
-        attr_set = true;
-    }
+    static PerDeviceFlag raised;  // per instantiation and device
+    if (!raise_dynamic_smem(kern, 226 * 1024, raised)) return KCB_LAUNCH_FAILURE;
     const int ntiles = (rows + TR - 1) / TR;
     const int grid = ntiles < kSmCount ? ntiles : kSmCount;
     kern<<<grid, TR / RPW * 32, smem, s>>>(wb, xq, xd, y, rows, nsb, stages, peers, xf32);
@@ -952,11 +964,20 @@ int launch_tma_iters(const uint8_t* wb, const int* xq, const float* xd, float* y
 // every SM work.
 bool use_tma(int rows, int nsb) { return rows % 8 == 0 && nsb <= 16 && rows >= 32 * kSmCount; }
 
-// Resident CTAs per SM of a kernel, asked of the driver once per kernel and device.
+// Resident CTAs per SM of a kernel: asked of the driver once per (kernel, shared-memory size, device), then cached.
 template <class Kern>
 int ctas_per_sm(Kern kern, size_t smem) {
+    static std::mutex m;
+    static std::map<std::tuple<const void*, size_t, int>, int> cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const auto key = std::make_tuple(reinterpret_cast<const void*>(kern), smem, dev);
+    std::lock_guard<std::mutex> lock(m);
+    const auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem) != cudaSuccess || n < 1) n = 1;
+    cache[key] = n;
     return n;
 }
 
@@ -1030,6 +1051,7 @@ int peer_barrier(unsigned* const* flags, int rank, int world, unsigned epoch, un
 int matvec_q6k_q8_gather(const void* w, const int* xq, const float* xd, float* y_local, float* const* y_peers, int npeers, int rows,
                          int k, cudaStream_t s) {
     if (!shape_ok(rows, k) || !w || !xq || !xd || !y_local || npeers < 0 || npeers > 7 || (npeers && !y_peers)) return KCB_INVALID_VALUE;
+    if (misaligned(w, 16) || misaligned(xq, 16) || misaligned(xd, 16) || misaligned(y_local, 4)) return KCB_INVALID_POINTER;
     if (rows == 0) return KCB_SUCCESS;
     const int nsb = k / 256;
     if (!(rows % 8 == 0 && nsb <= 16)) return KCB_UNSUPPORTED_OPERATION;
@@ -1047,8 +1069,9 @@ int matvec_q6k_q8_gather(const void* w, const int* xq, const float* xd, float* y
 int matvec_q6k_f32x_sharded(const void* w, const float* x, float* y_local, float* const* y_peers, int npeers, unsigned* const* flags,
                             unsigned* epoch_counter, unsigned* done_counter, int rank, int world, int rows, int k, cudaStream_t s) {
     if (!shape_ok(rows, k) || !w || !x || !y_local || npeers < 0 || npeers > 7 || (npeers && !y_peers) || world < 1 || world > 8 ||
-        (reinterpret_cast<uintptr_t>(x) & 15))  // x is read with 16-byte loads
+        false)
         return KCB_INVALID_VALUE;
+    if (misaligned(w, 16) || misaligned(x, 16) || misaligned(y_local, 4)) return KCB_INVALID_POINTER;  // x is read with 16-byte loads
     if (rows == 0) return KCB_SUCCESS;
     const int nsb = k / 256;
     if (!(rows % 8 == 0 && nsb <= 16)) return KCB_UNSUPPORTED_OPERATION;
@@ -1077,6 +1100,7 @@ unsigned tma_timeouts() {
 
 int matvec_q4k_q8(const void* w, const int* xq, const float* xd, float* y, int rows, int k, cudaStream_t s) {
     if (!shape_ok(rows, k) || !w || !xq || !xd || !y) return KCB_INVALID_VALUE;
+    if (misaligned(w, 16) || misaligned(xq, 16) || misaligned(xd, 16) || misaligned(y, 4)) return KCB_INVALID_POINTER;
     if (rows == 0) return KCB_SUCCESS;
     const int nsb = k / 256, iters = (nsb + 3) / 4;
     const uint8_t* wb = static_cast<const uint8_t*>(w);
@@ -1100,6 +1124,7 @@ int matvec_q4k_q8(const void* w, const int* xq, const float* xd, float* y, int r
 
 int matvec_q6k_q8(const void* w, const int* xq, const float* xd, float* y, int rows, int k, cudaStream_t s) {
     if (!shape_ok(rows, k) || !w || !xq || !xd || !y) return KCB_INVALID_VALUE;
+    if (misaligned(w, 16) || misaligned(xq, 16) || misaligned(xd, 16) || misaligned(y, 4)) return KCB_INVALID_POINTER;
     if (rows == 0) return KCB_SUCCESS;
     const int nsb = k / 256, iters = (nsb + 3) / 4;
     const uint8_t* wb = static_cast<const uint8_t*>(w);
@@ -1127,6 +1152,8 @@ int matvec_q6k_q8(const void* w, const int* xq, const float* xd, float* y, int r
 int matvec_q4k_q6k_pair_q8(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, const int* xq, const float* xd, int k,
                            cudaStream_t s) {
     if (!shape_ok(rows4, k) || !shape_ok(rows6, k) || !w4 || !w6 || !y4 || !y6 || !xq || !xd) return KCB_INVALID_VALUE;
+    if (misaligned(w4, 16) || misaligned(w6, 16) || misaligned(xq, 16) || misaligned(xd, 16) || misaligned(y4, 4) || misaligned(y6, 4))
+        return KCB_INVALID_POINTER;
     const int nsb = k / 256, iters = (nsb + 3) / 4;
     // up to kPairMaxRows the launch saved is worth more than the bulk-copy kernel's better streaming (measured on a
     // 5120 x 4096 + 1024 x 4096 pair: +3.5 % tokens/s on the whole decode step)
@@ -1159,6 +1186,7 @@ int matvec_q4k_q6k_pair_q8(const void* w4, float* y4, int rows4, const void* w6,
 
 int matvec_q4k_f32(const void* w, const float* x, float* y, int rows, int k, cudaStream_t s) {
     if (!shape_ok(rows, k) || k > 12288 || !w || !x || !y) return KCB_INVALID_VALUE;
+    if (misaligned(w, 16) || misaligned(x, 4) || misaligned(y, 4)) return KCB_INVALID_POINTER;
     if (rows == 0) return KCB_SUCCESS;
     matvec_q4k_f32_kernel<<<grid_for_rows(rows, 1), kThreads, static_cast<size_t>(k) * 4, s>>>(static_cast<const uint8_t*>(w), x, y, rows, k / 256);
     return launch_status();
@@ -1166,6 +1194,7 @@ int matvec_q4k_f32(const void* w, const float* x, float* y, int rows, int k, cud
 
 int matvec_q6k_f32(const void* w, const float* x, float* y, int rows, int k, cudaStream_t s) {
     if (!shape_ok(rows, k) || k > 12288 || !w || !x || !y) return KCB_INVALID_VALUE;
+    if (misaligned(w, 16) || misaligned(x, 4) || misaligned(y, 4)) return KCB_INVALID_POINTER;
     if (rows == 0) return KCB_SUCCESS;
     matvec_q6k_f32_kernel<<<grid_for_rows(rows, 1), kThreads, static_cast<size_t>(k) * 4, s>>>(static_cast<const uint8_t*>(w), x, y, rows, k / 256, rows);
     return launch_status();
@@ -1173,6 +1202,7 @@ int matvec_q6k_f32(const void* w, const float* x, float* y, int rows, int k, cud
 
 int dequant_q4k(const void* w, float* out, int rows, int k, cudaStream_t s) {
     if (!shape_ok(rows, k) || !w || !out) return KCB_INVALID_VALUE;
+    if (misaligned(w, 16) || misaligned(out, 4)) return KCB_INVALID_POINTER;
     const size_t nblk = static_cast<size_t>(rows) * (k / 256);
     if (nblk == 0) return KCB_SUCCESS;
     dequant_q4k_kernel<<<static_cast<unsigned>((nblk * 8 + 255) / 256), 256, 0, s>>>(static_cast<const uint8_t*>(w), out, nblk);
@@ -1181,6 +1211,7 @@ int dequant_q4k(const void* w, float* out, int rows, int k, cudaStream_t s) {
 
 int dequant_q6k(const void* w, float* out, int rows, int k, cudaStream_t s) {
     if (!shape_ok(rows, k) || !w || !out) return KCB_INVALID_VALUE;
+    if (misaligned(w, 16) || misaligned(out, 4)) return KCB_INVALID_POINTER;
     const size_t nblk = static_cast<size_t>(rows) * (k / 256);
     if (nblk == 0) return KCB_SUCCESS;
     dequant_q6k_kernel<<<static_cast<unsigned>((nblk * 8 + 255) / 256), 256, 0, s>>>(static_cast<const uint8_t*>(w), out, nblk);
@@ -1189,6 +1220,7 @@ int dequant_q6k(const void* w, float* out, int rows, int k, cudaStream_t s) {
 
 int q6k_convert(const void* src, void* dst, int rows, int k, int to_planes, cudaStream_t s) {
     if (!shape_ok(rows, k) || !src || !dst) return KCB_INVALID_VALUE;
+    if (misaligned(src, 2) || misaligned(dst, 2)) return KCB_INVALID_POINTER;  // moved two bytes at a time
     const size_t nblk = static_cast<size_t>(rows) * (k / 256);
     if (nblk == 0) return KCB_SUCCESS;
     q6k_planes_kernel<<<static_cast<unsigned>((nblk * 105 + 255) / 256), 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), nblk, to_planes);

@@ -170,17 +170,24 @@ __global__ void __launch_bounds__(kThreads) matmul_kq_kernel(const uint8_t* __re
 }  // namespace
 
 // q6: Q6_K planes, else Q4_K blocks.  q8k: slots of 85*k/256 ints (per-256 scales), else 11*k/32.
-int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int ncols, int q6, int q8k, cudaStream_t s) {
+// workspace (device memory, may be null): room for the K slices of a tensor-core launch (matmul_tc_workspace_bytes);
+// without it every launch is one pass.
+int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int ncols, int q6, int q8k, cudaStream_t s, void* workspace,
+                 size_t workspace_bytes) {
     if (rows <= 0 || k <= 0 || k % 256 || k > 32768 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
+    if (misaligned(w, 16) || misaligned(xq, 16) || misaligned(y, 4)) return KCB_INVALID_POINTER;
     // Per-256 activation slots and whole 128-row tiles go to the tensor cores (bit-identical results);
-    // KCB_MATMUL_TC=0 keeps everything on the CUDA-core kernel below.
-    static const bool tc = [] {
+    // KCB_MATMUL_TC=0 keeps everything on the CUDA-core kernel below, KCB_MATMUL_TC=1 selects the earlier
+    // one-CTA-per-tile tensor-core kernels instead of the pipelined ones (kept for comparison measurements).
+    static const int tc = [] {
         const char* e = getenv("KCB_MATMUL_TC");
-        return !e || atoi(e) != 0;
+        return e ? atoi(e) : 2;
     }();
-    // (16-byte loads of the 85 * nsb-int activation slots need nsb % 4 == 0)
-    if (tc && q8k && rows % 128 == 0 && ncols >= 16 && (k / 256) % 4 == 0)
-        return q6 ? matmul_q6k_q8k_tc(w, xq, y, rows, k, ncols, s) : matmul_q4k_q8k_tc(w, xq, y, rows, k, ncols, s);
+    // (the activation slots of 85 * nsb ints are read in 16-byte pieces: nsb % 4 == 0)
+    if (tc && q8k && rows % 128 == 0 && ncols >= 16 && (k / 256) % 4 == 0) {
+        if (tc == 1) return q6 ? matmul_q6k_q8k_tc(w, xq, y, rows, k, ncols, s) : matmul_q4k_q8k_tc(w, xq, y, rows, k, ncols, s);
+        return matmul_kq_q8k_tc_pipe(w, xq, y, rows, k, ncols, q6, workspace, workspace_bytes, s);
+    }
     const int nsb = k / 256, nb = nsb * 8;
     const int slot_ints = q8k ? nsb * 85 : nb * 11;
     const size_t col_bytes = static_cast<size_t>(nsb * 64 + nb * 2 + (q6 ? nb * 2 : 0)) * 4;

@@ -33,13 +33,21 @@ int quantize_cols_k(const float* x, int* q, int k, int ncols, cudaStream_t s);
 
 
 // matmul_kq.cu
-int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int ncols, int q6, int q8k, cudaStream_t s);
+int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int ncols, int q6, int q8k, cudaStream_t s, void* workspace = nullptr,
+                 size_t workspace_bytes = 0);
 
 // matmul_tc.cu
 int matmul_q4k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s);
 int matmul_q6k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s);
 unsigned tc_timeouts();
 int matmul_tc_k_slices(int rows, int k, int ncols);
+
+// matmul_tc_pipe.cu: the warp-specialised tensor-core kernels.  `workspace` (device, may be null) allows K slices.
+int matmul_kq_q8k_tc_pipe(const void* w, const int* xq, float* y, int rows, int k, int ncols, int q6, void* workspace, size_t workspace_bytes,
+                          cudaStream_t s);
+int matmul_tc_pipe_k_slices(int rows, int k, int ncols);
+size_t matmul_tc_workspace_bytes(int rows, int k, int ncols);
+unsigned tc_pipe_timeouts();
 
 // glue.cu
 int rms_norm(const float* x, const float* w, float* y, int n, int rows, float eps, cudaStream_t s);

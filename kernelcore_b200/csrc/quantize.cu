@@ -87,6 +87,7 @@ __global__ void quantize_q8k_kernel(const float* __restrict__ x, int* __restrict
 
 int quantize_q8x4(const float* x, int* xq, float* xd, int count, cudaStream_t s) {
     if (count < 0 || !x || !xq || !xd) return KCB_INVALID_VALUE;
+    if (misaligned(x, 4) || misaligned(xq, 4) || misaligned(xd, 4)) return KCB_INVALID_POINTER;
     if (count == 0) return KCB_SUCCESS;
     quantize_q8x4_kernel<<<(count + 7) / 8, 256, 0, s>>>(x, nullptr, count, 1, count * 32, 0, xq, xd);
     return launch_status();
@@ -94,6 +95,7 @@ int quantize_q8x4(const float* x, int* xq, float* xd, int count, cudaStream_t s)
 
 int quantize_cols(const float* x, int* q, int k, int ncols, cudaStream_t s) {
     if (k <= 0 || k % 32 || ncols < 0 || !x || !q) return KCB_INVALID_VALUE;
+    if (misaligned(x, 4) || misaligned(q, 4)) return KCB_INVALID_POINTER;
     if (ncols == 0) return KCB_SUCCESS;
     const int nb = k / 32;
     const long long warps = static_cast<long long>(nb) * ncols;
@@ -103,6 +105,7 @@ int quantize_cols(const float* x, int* q, int k, int ncols, cudaStream_t s) {
 
 int quantize_cols_k(const float* x, int* q, int k, int ncols, cudaStream_t s) {
     if (k <= 0 || k % 256 || ncols < 0 || !x || !q) return KCB_INVALID_VALUE;
+    if (misaligned(x, 16) || misaligned(q, 4)) return KCB_INVALID_POINTER;  // x is read with 16-byte loads
     if (ncols == 0) return KCB_SUCCESS;
     const long long warps = static_cast<long long>(k / 256) * ncols;
     quantize_q8k_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, s>>>(x, q, k / 256, ncols, k);

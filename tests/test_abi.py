@@ -80,18 +80,22 @@ def test_every_kernel_name_of_the_reference_is_registered():
 
 
 def test_tensor_core_k_slices_follow_the_wave_model():
-    """The number of K slices of a tensor-core matmul is pure host arithmetic (CTAs / SM slots rounded up x super-blocks
-    per CTA): pinned here on the shapes the GPU tests and the benchmark rely on, because one pass means bit identity
-    with the reference's mirror and more slices mean ~1e-6."""
+    """The number of K slices of a tensor-core matmul given a workspace is pure host arithmetic (units per persistent
+    CTA x (super-blocks per unit + 1), plus the adding kernel): pinned here on the shapes the GPU tests and the benchmark
+    rely on, because one pass means bit identity with the reference's mirror and more slices mean ~1e-6."""
+    import ctypes as C
     from kernelcore_b200 import lib
     ks = lib.raw.kcb_matmul_tc_k_slices
+    ws = lib.raw.kcb_matmul_tc_workspace_bytes
+    ws.restype = C.c_size_t
     assert ks(8192, 3072, 512) == 1 and ks(8192, 3072, 2048) == 1      # the Q4_K 8192 x 3072 benchmark matmul: 256 / 1024 tiles
-    assert ks(8192, 3072, 128) == 2 and ks(8192, 3072, 32) == 4        # 64 tiles of 128 / 32 columns
+    assert ks(8192, 3072, 128) == 2 and ks(8192, 3072, 32) == 2        # 64 tiles
     assert ks(3072, 8192, 512) == 3                                    # Llama-3.2-3B FFN-down: 96 tiles of 32 super-blocks
     assert ks(3072, 3072, 512) == 1 and ks(4096, 3072, 512) == 1      # wo, q|k: a split would gain < 10 %
     assert ks(1024, 3072, 512) == 4                                    # v: 32 tiles
-    assert ks(16384, 3072, 512) == 1                                   # gate|up: slices would exceed 64 MB / not pay
+    assert ks(16384, 3072, 512) == 1                                   # gate|up
     assert ks(128 * 150, 1024, 128) == 1 and ks(128 * 150, 1024, 64) == 1 and ks(128 * 150, 1024, 16) == 1
     assert ks(4096, 12288, 512) == 1                                   # Qwen3-8B FFN-down: 128 tiles fill 86 % of the SMs
-    assert ks(3072, 8192, 32) == 11                                    # 24 tiles x 32 super-blocks in 3-block slices
+    assert ks(3072, 8192, 32) == 6                                     # 24 tiles x 32 super-blocks
     assert ks(100, 1024, 16) == 0 and ks(128, 768, 16) == 0            # not tensor-core shapes
+    assert ws(8192, 3072, 512) == 0 and ws(3072, 8192, 512) == 3 * 512 * 3072 * 4 and ws(100, 1024, 16) == 0

@@ -1,4 +1,6 @@
 """K-quant matmuls (prompt path) against the oracle's per-column mirror, through the C ABI."""
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
@@ -23,10 +25,19 @@ def slots_for(X, q8k):
     return s
 
 
-def run(w, X, rows, k, q6, q8k):
+def run(w, X, rows, k, q6, q8k, workspace=False):
+    """One pass (kcb_matmul_kq_q8) or, with workspace=True, the route that may contract K in slices
+    (kcb_matmul_kq_q8_ws with a caller buffer of kcb_matmul_tc_workspace_bytes)."""
     m = kquant.KMatrix(w, rows, k, q6)
-    y = torch.full((X.shape[0], rows), float("nan"), device="cuda")
-    lib.call("matmul_kq_q8", m.data, slots_for(X, q8k), y, rows, k, X.shape[0], int(q6), int(q8k))
+    ncols = X.shape[0]
+    y = torch.full((ncols, rows), float("nan"), device="cuda")
+    if not workspace:
+        lib.call("matmul_kq_q8", m.data, slots_for(X, q8k), y, rows, k, ncols, int(q6), int(q8k))
+    else:
+        lib.raw.kcb_matmul_tc_workspace_bytes.restype = C.c_size_t
+        nbytes = lib.raw.kcb_matmul_tc_workspace_bytes(rows, k, ncols)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+        lib.call("matmul_kq_q8_ws", m.data, slots_for(X, q8k), y, rows, k, ncols, int(q6), int(q8k), ws, C.c_size_t(nbytes))
     return y.cpu().numpy()
 
 
@@ -44,11 +55,9 @@ def test_golden_columns(golden, q6, q8k):
 @pytest.mark.parametrize("ncols", [16, 17, 33, 64, 65, 128, 130, 300])
 def test_tensor_core_q8k_against_the_mirror(ncols, q6):
     """Q4_K / Q6_K x per-256 activations on tcgen05: exact integer contractions and the reference's fp32 order, so
-    every output equals llm::ref::matvecQ4KQ8K / matvecQ6KQ8K bit for bit, including ragged column tiles.
-    raw_blocks draws every byte uniformly, so Q6_K scales reach -128 and 127 (the extremes of the plane split).
-    Where the launch splits the contraction along K (few tiles, many super-blocks) the slices are added afterwards: the
-    same exact integers and products, one differently associated fp32 sum -- hence 1e-6 here; bit identity is asserted
-    in the tests below on shapes that run in one pass."""
+    every output equals llm::ref::matvecQ4KQ8K / matvecQ6KQ8K bit for bit, including ragged column tiles (a last
+    tile of 1..64 columns uses one accumulator half only).  raw_blocks draws every byte uniformly, so Q6_K scales reach
+    -128 and 127 (the extremes of the plane split) and Q4_K scales and mins 0 and 63."""
     rows, k = 256, 1024
     for gen in (synth.kquant_blocks, synth.raw_blocks):
         w = gen(rows, k, ncols, q6)
@@ -56,51 +65,71 @@ def test_tensor_core_q8k_against_the_mirror(ncols, q6):
         X[0, :256] = 0  # an all-zero super-block: scale 0
         y = run(w, X, rows, k, q6, True)
         want = np.stack([oracle.matvec_q8k(port, w, X[c], rows, k, int(q6)) for c in range(ncols)])
-        if lib.raw.kcb_matmul_tc_k_slices(rows, k, ncols) == 1:   # one pass: the reference's own order of fp32 operations
-            assert bit_equal(y, want), (ncols, gen.__name__)
-        else:
-            assert rel_diff(y, want) < 2e-6, (ncols, gen.__name__)
+        assert bit_equal(y, want), (ncols, gen.__name__)
     assert lib.raw.kcb_tc_timeouts() == 0
 
 
 @pytest.mark.parametrize("q6", [False, True])
 @pytest.mark.parametrize("ncols", [17, 130])
 def test_one_pass_tiles_are_bit_identical(q6, ncols):
-    """150 row tiles are more than half of what the SMs hold at once, so the 32- and 128-column kernels run in one pass: every output equals the
-    reference mirror bit for bit, ragged column tiles included."""
+    """150 row tiles: every persistent CTA walks more than one tile (the pipeline runs across tile boundaries); every
+    output equals the reference mirror bit for bit, ragged column tiles included, with and without a workspace (this
+    shape takes one pass either way)."""
     rows, k = 128 * 150, 1024
     assert lib.raw.kcb_matmul_tc_k_slices(rows, k, ncols) == 1
     w = synth.raw_blocks(rows, k, 5, q6)
     X = np.random.default_rng(5).uniform(-3, 3, (ncols, k)).astype(np.float32)
-    y = run(w, X, rows, k, q6, True)
     want = np.stack([oracle.matvec_q8k(port, w, X[c], rows, k, int(q6)) for c in range(ncols)])
-    assert bit_equal(y, want)
+    assert bit_equal(run(w, X, rows, k, q6, True), want)
+    assert bit_equal(run(w, X, rows, k, q6, True, workspace=True), want)
 
 
 def test_ffn_down_shape_splits_k_three_ways():
     """Llama-3.2-3B's FFN-down at a 512-token prompt chunk: Q6_K 3072 x 8192, 96 tiles of 32 super-blocks on 148 SMs.
-    The launch contracts it as three K slices (two full waves of 11 super-blocks instead of one of 32 on two thirds of
-    the machine); columns against the oracle to 2e-6, and exact doubling under doubled activations."""
+    Given a workspace the launch contracts it as three K slices (288 units of 11 super-blocks instead of 96 of 32 on
+    two thirds of the machine): columns against the oracle to 2e-6, exact doubling under doubled activations.  Without
+    a workspace the same call is one pass and bit-identical to the mirror."""
     rows, k, M = 3072, 8192, 512
     assert lib.raw.kcb_matmul_tc_k_slices(rows, k, M) == 3
     w = synth.raw_blocks(rows, k, 11, True)
     X = np.random.default_rng(2).standard_normal((M, k)).astype(np.float32)
-    y = run(w, X, rows, k, True, True)
+    y = run(w, X, rows, k, True, True, workspace=True)
+    y1 = run(w, X, rows, k, True, True)
     for c in (0, 255, M - 1):
-        assert rel_diff(y[c], oracle.matvec_q8k(port, w, X[c], rows, k, 1)) < 2e-6
-    assert bit_equal(run(w, X * 2, rows, k, True, True), y * 2)
+        want = oracle.matvec_q8k(port, w, X[c], rows, k, 1)
+        assert rel_diff(y[c], want) < 2e-6
+        assert bit_equal(y1[c], want)
+    assert bit_equal(run(w, X * 2, rows, k, True, True, workspace=True), y * 2)
     assert lib.raw.kcb_tc_timeouts() == 0
 
 
 def test_config2_shape_against_cuda_core_path():
-    """The Q4_K benchmark matmul at M = 128 and 512: 8192 x 3072 Q4_K; spot-check columns against the oracle and the
-    linearity property on the rest (activations scaled by 2 give exactly doubled outputs)."""
+    """The Q4_K benchmark matmul at M = 32, 128, 512 and 2048: 8192 x 3072 Q4_K; spot-check columns against the oracle
+    (one pass: bit for bit; M = 128 with a workspace: two K slices, 2e-6) and the linearity property on the rest
+    (activations scaled by 2 give exactly doubled outputs)."""
     rows, k = 8192, 3072
     w = synth.q4k_blocks(rows, k, 0)
-    for M in (128, 512):   # 64 tiles: K split, 1e-6; 256 tiles: one pass, bit for bit
+    for M in (32, 128, 512, 2048):
         X = np.random.default_rng(1).standard_normal((M, k)).astype(np.float32)
         y = run(w, X, rows, k, False, True)
-        for c in (0, 77, M - 1):
-            want = oracle.matvec_q8k(port, w, X[c], rows, k, 0)
-            assert bit_equal(y[c], want) if M == 512 else rel_diff(y[c], want) < 2e-6
+        for c in (0, 17, M - 1):
+            assert bit_equal(y[c], oracle.matvec_q8k(port, w, X[c], rows, k, 0))
         assert bit_equal(run(w, X * 2, rows, k, False, True), y * 2)
+        if M == 128:
+            assert lib.raw.kcb_matmul_tc_k_slices(rows, k, M) == 2
+            ys = run(w, X, rows, k, False, True, workspace=True)
+            assert 0 < rel_diff(ys, y) < 2e-6 or bit_equal(ys, y)
+    assert lib.raw.kcb_tc_timeouts() == 0
+
+
+@pytest.mark.parametrize("q6", [False, True])
+def test_tensor_cores_agree_with_the_cuda_core_matmul(q6):
+    """The tensor-core kernels against the CUDA-core dp4a matmul of the same library, which shares no code with them:
+    per-256 slots, 40 columns; 264 rows (not a multiple of 128) take the dp4a route, their first 256 the tensor cores.
+    Same integers, fp32 sums in a different order: 1e-5."""
+    rows, k, ncols = 264, 1024, 40
+    w = synth.raw_blocks(rows, k, 21, q6)
+    X = np.random.default_rng(21).uniform(-2, 2, (ncols, k)).astype(np.float32)
+    y_cc = run(w, X, rows, k, q6, True)
+    y_tc = run(np.ascontiguousarray(w[:256]), X, 256, k, q6, True)
+    assert rel_diff(y_tc, y_cc[:, :256]) < 1e-5
