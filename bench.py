@@ -441,10 +441,13 @@ def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5, q6=False):
         X = torch.randn(M, k, device="cuda")
         slots = torch.zeros((M, 85 * k // 256), dtype=torch.int32, device="cuda")
         y = torch.empty((M, rows), device="cuda")
+        lib.raw.kcb_matmul_tc_workspace_bytes.restype = C.c_size_t
+        ws_bytes = lib.raw.kcb_matmul_tc_workspace_bytes(rows, k, M)   # > 0 where the launch contracts K in slices
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")
 
         def step():
             lib.call("quantize_cols_k", X, slots, k, M)
-            lib.call("matmul_kq_q8", w.data, slots, y, rows, k, M, int(q6), 1)
+            lib.call("matmul_kq_q8_ws", w.data, slots, y, rows, k, M, int(q6), 1, ws, C.c_size_t(ws_bytes))
         for _ in range(3):
             step()
         torch.cuda.synchronize()

@@ -14,14 +14,21 @@
 // The epilogue applies the reference's fp32 products in its order, so one-pass outputs are bit-identical to the
 // reference's per-column mirror.
 //
+// Orientation: the ACTIVATIONS are the M operand (128 columns of the batch = 128 TMEM lanes) and the weight planes the
+// N operand: one MMA of N = 128 covers plane a and plane b of 64 weight rows, so the activation slab is read from
+// shared memory once for both planes, and an epilogue thread (= one activation column) finds Da and Db of a weight
+// row side by side in its own lane.  The 128 weight rows of a tile are two halves of 64 with their own TMEM
+// accumulators: the epilogue of one half runs while the tensor core works on the other and on the next super-block.
+//
 // One persistent CTA per SM walks a static list of (128-row x 128-column tile, super-block range) units:
 //   * producer warps: one weight row (Q6_K: half a row) per thread; the next super-block's bytes are requested before
 //     this one is unpacked; planes go to shared memory in the no-swizzle K-major core-matrix layout (conflict-free
-//     512-byte stores per warp).  Producer thread 0 also issues the bulk tensor copies (TMA, no multicast) of the
-//     activation bytes (128-byte-swizzled K-major tiles), the activation sums and the activation scales;
-//   * one thread issues the MMAs: the 128 columns are two halves of 64 with their own TMEM accumulators, so the
-//     epilogue of one half runs while the tensor core works on the other and on the next super-block;
-//   * eight epilogue warps read TMEM (tcgen05.ld), combine the planes and accumulate in registers.
+//     512-byte stores per warp), the row's fp16 scales as floats into a small ring.  Producer thread 0 also issues
+//     the bulk tensor copies (TMA, no multicast) of the activation bytes (128-byte-swizzled K-major tiles) and the
+//     activation sums;
+//   * one thread issues the MMAs (18 per super-block for Q4_K, 16 for Q6_K);
+//   * eight epilogue warps read TMEM (tcgen05.ld, the next four rows requested while these four are combined) and
+//     accumulate in registers; a thread's activation scale is a scalar per super-block.
 // Operand slabs are double-buffered (full / empty mbarriers), accumulators are handed over with tmem_full / tmem_empty
 // mbarriers.  Every wait is bounded: on expiry the CTA raises a flag that the other roles poll, waits a bounded grace
 // period for copies in flight, counts the event, frees its TMEM and returns.
@@ -37,33 +44,39 @@
 namespace kcb {
 namespace {
 
-constexpr int TM = 128, TN = 128, HN = 64;  // tile rows, tile columns, columns per accumulator half
+constexpr int TM = 128, TN = 128, HR = 64;  // weight rows per tile, activation columns per tile, weight rows per accumulator half
 constexpr int kEpiWarps = 8;
-constexpr int kChunk = TM * 16;   // one 16-byte K chunk of a 128-row operand: [row][16 B]
+constexpr int kChunk = 128 * 16;  // one 16-byte K chunk of a 128-row operand: [row][16 B]
 constexpr int kAtom = 128 * 128;  // 128 rows x 128 K bytes in the 128-byte-swizzle layout
-constexpr int kDxSlots = 4;
+constexpr int kRing = 4;          // slots of the per-row scale ring
 
 template <bool kQ6>
 struct Cfg {
     static constexpr int kProdWarps = kQ6 ? 8 : 4;
     static constexpr int kProducers = 32 * kProdWarps;
-    static constexpr int kThreads = 32 * (kEpiWarps + 1) + kProducers;
-    static constexpr int kAccs = kQ6 ? 2 : 4;          // TMEM accumulators per half
-    static constexpr int kHalfCols = kAccs * HN;        // TMEM columns of one half
-    static constexpr int kTmemCols = 2 * kHalfCols;     // 512 (Q4_K) / 256 (Q6_K)
+    // warps: 8 epilogue (two warpgroups) | kProdWarps producers (whole warpgroups) | one warpgroup holding the MMA
+    // warp and three idle warps, which exists to hand its registers to the epilogue warpgroups (setmaxnreg below)
+    static constexpr int kMmaWarp = kEpiWarps + kProdWarps;
+    static constexpr int kThreads = 32 * (kMmaWarp + 4);
+    static constexpr int kRegsLaunch = kQ6 ? 96 : 128;   // what kThreads allows: 65536 / 640, 65536 / 512
+    static constexpr int kRegsEpi = kQ6 ? 120 : 168;     // epilogue warps after the hand-over
+    static constexpr int kRegsMma = 40;                   // the MMA warpgroup keeps this much
+    static_assert(8 * 32 * (kRegsEpi - kRegsLaunch) <= 4 * 32 * (kRegsLaunch - kRegsMma), "the epilogue takes what the MMA warpgroup gives up");
+    static constexpr int kHalfCols = kQ6 ? 128 : 256;   // TMEM columns of one half: Da | Db (| Dh | Dl), 64 each
+    static constexpr int kTmemCols = 2 * kHalfCols;      // 512 (Q4_K) / 256 (Q6_K)
     // one operand stage
-    static constexpr int kOffAa = 0;                    // plane a: 8 K-steps x 2 chunks
-    static constexpr int kOffAb = 16 * kChunk;          // plane b
-    static constexpr int kOffAm = 32 * kChunk;          // Q4_K: mins in K bytes 0..7 | mins in K bytes 8..15
-    static constexpr int kOffBx = kOffAm + (kQ6 ? 0 : 2 * kChunk);  // two swizzled atoms (1024-byte aligned)
-    static constexpr int kOffBs = kOffBx + 2 * kAtom;   // Q4_K: activation sums, one chunk
-    static constexpr int kStage = kOffBs + (kQ6 ? 0 : kChunk);
+    static constexpr int kOffW = 0;                      // [half][K-step][chunk][plane a rows 0..63 | plane b rows 0..63][16 B]
+    static constexpr int kOffWm = 32 * kChunk;           // Q4_K: [half][mins in K bytes 0..7 (64 rows) | mins in K bytes 8..15 (64 rows)]
+    static constexpr int kOffX = kOffWm + (kQ6 ? 0 : 2 * kChunk);  // two swizzled atoms (1024-byte aligned)
+    static constexpr int kOffXs = kOffX + 2 * kAtom;     // Q4_K: activation sums, one chunk
+    static constexpr int kStage = kOffXs + (kQ6 ? 0 : kChunk);
     // behind the two stages
-    static constexpr int kOffZero = 2 * kStage;         // Q4_K: a chunk of zeros (second K chunk of the min MMAs)
-    static constexpr int kOffDx = kOffZero + (kQ6 ? 0 : kChunk);  // ring of kDxSlots chunks: [column][4 floats]
-    static constexpr int kOffBar = kOffDx + kDxSlots * kChunk;
-    static constexpr int kSmem = kOffBar + 256 + 1024;  // + room to align the base to 1024 bytes
-    static_assert(kOffBx % 1024 == 0 && kStage % 1024 == 0, "swizzled atoms need 1024-byte alignment");
+    static constexpr int kOffZero = 2 * kStage;          // Q4_K: a chunk of zeros (second K chunk of the min MMAs)
+    static constexpr int kOffDd = kOffZero + (kQ6 ? 0 : kChunk);  // ring: per row pair {d, d', dmin, dmin'} (Q6_K: {d, d'})
+    static constexpr int kDdSlot = kQ6 ? 512 : 1024;
+    static constexpr int kOffBar = kOffDd + kRing * kDdSlot;
+    static constexpr int kSmem = kOffBar + 256 + 1024;   // + room to align the base to 1024 bytes
+    static_assert(kOffX % 1024 == 0 && kStage % 1024 == 0, "swizzled atoms need 1024-byte alignment");
 };
 
 __device__ unsigned g_tcp_timeouts = 0;
@@ -81,8 +94,8 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t addr) {
     return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) |
            (static_cast<uint64_t>(2) << 61);
 }
-// int32 accumulate, signed 8-bit A and B, both K-major, M = 128, N = 64.
-constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(HN >> 3) << 17) | (static_cast<uint32_t>(TM >> 4) << 24);
+// int32 accumulate, signed 8-bit A and B, both K-major, M = 128, N = 128.
+constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(128 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
 
 __device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
     asm volatile(
@@ -140,7 +153,38 @@ __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
     return r;
 }
 
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 pack2i(int a, int b) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a), "r"(b));
+    return r;
+}
+// Exact int32 -> fp32 without the conversion unit (which issues at a sixteenth of the fp32 rate and was what the
+// epilogue waited for).  For |v| < 2^22 the bit pattern 0x4B400000 + v is the float 1.5 * 2^23 + v, so subtracting
+// 1.5 * 2^23 gives float(v) exactly; with the exponent raised by s (0x4B400000 + (s << 23)) the same pattern is
+// 1.5 * 2^(23 + s) + 2^s v.  A value F a + b with |a|, |b| < 2^22 and F = 2^s is therefore converted as
+// (2^s a exactly) + (b exactly) in ONE fp32 addition, which rounds the exact integer once, to nearest even -- the
+// result of converting the integer F a + b itself, for every input.
+template <int S>
+__device__ __forceinline__ f32x2 planes_to_float2(int a0, int a1, int b0, int b1) {
+    constexpr int kMagicA = 0x4B400000 + (S << 23), kMagicB = 0x4B400000;
+    const float ca = -__int_as_float(kMagicA), cb = -12582912.0f;
+    const f32x2 fa = add2(pack2i(a0 + kMagicA, a1 + kMagicA), pack2(ca, ca));
+    const f32x2 fb = add2(pack2i(b0 + kMagicB, b1 + kMagicB), pack2(cb, cb));
+    return add2(fa, fb);
+}
+// |v| < 2^22 (the min sums: at most 8 * 63 * 4064).
+__device__ __forceinline__ f32x2 small_to_float2(int v0, int v1) {
+    return add2(pack2i(v0 + 0x4B400000, v1 + 0x4B400000), pack2(-12582912.0f, -12582912.0f));
+}
+
 // ---- weight blocks in registers and their unpacking ------------------------------------------------------------
+// `wb` points at the half's weight operand: [K-step][chunk][128 rows: plane a of the half's 64 weight rows, then plane
+// b][16 B]; `lr` is the row's index inside the half.
 struct Q4Blk {
     uint4 hd, q[8];
 };
@@ -150,14 +194,13 @@ __device__ __forceinline__ void load_blk(Q4Blk& b, const uint8_t* w, size_t /*nb
 #pragma unroll
     for (int i = 0; i < 8; ++i) b.q[i] = __ldg(p + 1 + i);
 }
-// One row of one super-block: planes a = (sc >> 3) * q and b = (sc & 7) * q for the eight K-steps (sub-blocks), the mins
-// as K bytes 0..7 of one chunk and 8..15 of the other.
-template <class C>
-__device__ __forceinline__ void unpack_blk(const Q4Blk& b, uint8_t* stage, int row, int /*n*/) {
+// One row of one super-block: planes a = (sc >> 3) * q and b = (sc & 7) * q for the eight K-steps (sub-blocks); the mins
+// as K bytes 0..7 (rows 0..63 of the min operand) and as K bytes 8..15 (rows 64..127); d and dmin into `dd`.
+__device__ __forceinline__ void unpack_blk(const Q4Blk& b, uint8_t* wb, uint8_t* wm, float* dd, int lr, int /*n*/) {
     const unsigned sclo = b.hd.y & 0x3F3F3F3Fu, schi = (b.hd.w & 0x0F0F0F0Fu) | ((b.hd.y >> 2) & 0x30303030u);
     const unsigned mlo = b.hd.z & 0x3F3F3F3Fu, mhi = ((b.hd.w >> 4) & 0x0F0F0F0Fu) | ((b.hd.z >> 2) & 0x30303030u);
-    uint8_t* pa = stage + C::kOffAa + row * 16;
-    uint8_t* pb = stage + C::kOffAb + row * 16;
+    uint8_t* pa = wb + lr * 16;
+    uint8_t* pb = pa + HR * 16;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {  // 32 quant bytes: low nibbles = sub-block 2g, high nibbles = sub-block 2g + 1
         const unsigned scw = (g < 2 ? sclo : schi) >> (16 * (g & 1));
@@ -175,13 +218,17 @@ __device__ __forceinline__ void unpack_blk(const Q4Blk& b, uint8_t* stage, int r
             *reinterpret_cast<uint4*>(pb + khi) = make_uint4(hx * sh0, hy * sh0, hz * sh0, hw * sh0);
         }
     }
-    *reinterpret_cast<uint4*>(stage + C::kOffAm + row * 16) = make_uint4(mlo, mhi, 0u, 0u);
-    *reinterpret_cast<uint4*>(stage + C::kOffAm + kChunk + row * 16) = make_uint4(0u, 0u, mlo, mhi);
+    *reinterpret_cast<uint4*>(wm + lr * 16) = make_uint4(mlo, mhi, 0u, 0u);
+    *reinterpret_cast<uint4*>(wm + (HR + lr) * 16) = make_uint4(0u, 0u, mlo, mhi);
+    // {d_r, d_r+1, dmin_r, dmin_r+1} per row pair: the epilogue reads a pair's scales as two packed operands
+    dd[(lr >> 1) * 4 + (lr & 1)] = half_bits_to_float(b.hd.x & 0xFFFFu);
+    dd[(lr >> 1) * 4 + 2 + (lr & 1)] = half_bits_to_float(b.hd.x >> 16);
 }
 
 struct Q6Blk {
     uint4 lq[4], hq[2];
     uint2 sc;
+    unsigned d;
 };
 // Half n of a block (weights 128 n .. 128 n + 127) out of the device planes ql | qh | scales | d.
 __device__ __forceinline__ void load_blk(Q6Blk& b, const uint8_t* w, size_t nblk, size_t blk, int n) {
@@ -190,6 +237,7 @@ __device__ __forceinline__ void load_blk(Q6Blk& b, const uint8_t* w, size_t nblk
 #pragma unroll
     for (int i = 0; i < 2; ++i) b.hq[i] = __ldg(reinterpret_cast<const uint4*>(w + nblk * 128 + blk * 64 + 32 * n + 16 * i));
     b.sc = __ldg(reinterpret_cast<const uint2*>(w + nblk * 192 + blk * 16 + 8 * n));
+    b.d = __ldg(reinterpret_cast<const unsigned short*>(w + nblk * 208 + blk * 2));
 }
 // q4: four 6-bit weights in bytes, scb = sc + 128 (0..255), crep = (8192 - 32 sc) in both 16-bit lanes.
 // Per 16-bit lane u = q * scb - 128 q + crep = sc * (q - 32) + 8192, in 4128..12288: never negative, no borrow
@@ -200,8 +248,7 @@ __device__ __forceinline__ void scale_split_q6(unsigned q4, unsigned scb, unsign
     a = (((ue >> 6) & 0x00FF00FFu) | (((uo >> 6) & 0x00FF00FFu) << 8)) ^ 0x80808080u;
     b = (ue & 0x003F003Fu) | ((uo & 0x003F003Fu) << 8);
 }
-template <class C>
-__device__ __forceinline__ void unpack_blk(const Q6Blk& blk, uint8_t* stage, int row, int n) {
+__device__ __forceinline__ void unpack_blk(const Q6Blk& blk, uint8_t* wb, uint8_t* /*wm*/, float* dd, int lr, int n) {
 #pragma unroll
     for (int t = 0; t < 4; ++t) {      // K-step 4n + t: weights 128n + 32t .. +31
 #pragma unroll
@@ -219,11 +266,12 @@ __device__ __forceinline__ void unpack_blk(const Q6Blk& blk, uint8_t* stage, int
                 const unsigned q4 = nib | (((hw[i] >> (2 * t)) & 0x03030303u) << 4);
                 scale_split_q6(q4, scb, crep, a[i], b[i]);
             }
-            const int ko = (2 * (4 * n + t) + c) * kChunk + row * 16;
-            *reinterpret_cast<uint4*>(stage + C::kOffAa + ko) = make_uint4(a[0], a[1], a[2], a[3]);
-            *reinterpret_cast<uint4*>(stage + C::kOffAb + ko) = make_uint4(b[0], b[1], b[2], b[3]);
+            uint8_t* pa = wb + (2 * (4 * n + t) + c) * kChunk + lr * 16;
+            *reinterpret_cast<uint4*>(pa) = make_uint4(a[0], a[1], a[2], a[3]);
+            *reinterpret_cast<uint4*>(pa + HR * 16) = make_uint4(b[0], b[1], b[2], b[3]);
         }
     }
+    if (n == 0) dd[lr] = half_bits_to_float(blk.d);
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------------------
@@ -231,38 +279,37 @@ __device__ __forceinline__ void unpack_blk(const Q6Blk& blk, uint8_t* stage, int
 // [z * per, min(nsb, (z + 1) * per)) and stores into y (one slice) or into slice z of `partial`.
 template <bool kQ6>
 __global__ void __launch_bounds__(Cfg<kQ6>::kThreads, 1)
-    matmul_kq_q8k_pipe_kernel(const uint8_t* __restrict__ w, const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_s,
-                              float* __restrict__ y, int rows, int nsb, int ncols, int per, int n_rt, int n_ct, int units,
-                              float* __restrict__ partial) {
+    matmul_kq_q8k_pipe_kernel(const uint8_t* __restrict__ w, const int* __restrict__ xq, const __grid_constant__ CUtensorMap map_x,
+                              const __grid_constant__ CUtensorMap map_s, float* __restrict__ y, int rows, int nsb, int ncols, int per, int n_rt,
+                              int n_ct, int units, float* __restrict__ partial) {
     using C = Cfg<kQ6>;
     using Blk = typename std::conditional<kQ6, Q6Blk, Q4Blk>::type;
     extern __shared__ uint8_t sm_raw[];
     uint8_t* sm = sm_raw + ((1024u - (smem_u32(sm_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(sm + C::kOffBar);
-    uint64_t* full = bars;            // [2] operands of a stage written (producers + tensor copies)
-    uint64_t* empty = bars + 2;       // [2] the MMAs reading a stage have completed
-    uint64_t* tfull = bars + 4;       // [2] accumulators of a half complete
-    uint64_t* tempty = bars + 6;      // [2] accumulators of a half read back
-    uint64_t* dxfull = bars + 8;      // [kDxSlots] activation scales of an item landed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
-    volatile int* fail = reinterpret_cast<volatile int*>(bars + 13);
+    uint64_t* full = bars;        // [2] operands of a stage written (producers + tensor copies)
+    uint64_t* empty = bars + 2;   // [2] the MMAs reading a stage have completed
+    uint64_t* tfull = bars + 4;   // [2] accumulators of a half complete
+    uint64_t* tempty = bars + 6;  // [2] accumulators of a half read back
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* fail = reinterpret_cast<volatile int*>(bars + 9);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t nblk = static_cast<size_t>(rows) * nsb;
+    const int slot_ints = nsb * 85;
 
     if (tid == 0) {
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&full[s], C::kProducers + 1);
+            mbar_init(&full[s], C::kProdWarps + 1);  // one arrival per producer warp + the tensor copies' expect_tx
             mbar_init(&empty[s], 1);
             mbar_init(&tfull[s], 1);
             mbar_init(&tempty[s], kEpiWarps);
         }
-        for (int s = 0; s < kDxSlots; ++s) mbar_init(&dxfull[s], 1);
         *fail = 0;
         mbar_init_fence();
     }
     if (!kQ6)  // zeros behind the min operands, written once
         for (int i = tid; i < kChunk / 16; i += C::kThreads) *reinterpret_cast<uint4*>(sm + C::kOffZero + i * 16) = make_uint4(0u, 0u, 0u, 0u);
-    if (warp == kEpiWarps) {
+    if (warp == C::kMmaWarp) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -282,74 +329,73 @@ __global__ void __launch_bounds__(Cfg<kQ6>::kThreads, 1)
     };
 
     if (warp < kEpiWarps) {
-        // ================= epilogue: TMEM lanes 32 * (warp & 3) .. + 31, columns 32 * (warp >> 2) .. + 31 of each half
-        const int erow = 32 * (warp & 3) + lane, cs = warp >> 2;
-        const uint32_t tlane = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + 32 * cs;
-        int it = 0, use[2] = {0, 0};  // items so far; uses of each accumulator half (a ragged last column tile skips half 1)
+        // ================= epilogue: activation column 32 * (warp & 3) + lane of the tile (its TMEM lane), weight rows
+        // 32 * (warp >> 2) .. + 31 of each half
+        // The CTA's registers are shared out at launch by thread count (128 / 96 per thread); the MMA warpgroup needs few
+        // and releases the rest, which these two warpgroups pick up: their 64 accumulators plus the rows in flight need
+        // the room to keep several rows' dependency chains interleaved.  The request waits until the release has happened.
+        if (kQ6) asm volatile("setmaxnreg.inc.sync.aligned.u32 120;");
+        else asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+        const int ecol = 32 * (warp & 3) + lane, rs = warp >> 2;
+        const uint32_t tlane = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + 32 * rs;
+        int it = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
             int rt, ct, sb0, sb1;
             unit_of(u, rt, ct, sb0, sb1);
-            const int c_tile = ct * TN, nh = ncols - c_tile > HN ? 2 : 1;
-            const size_t eblk = static_cast<size_t>(rt * TM + erow) * nsb;
+            const int col = ct * TN + ecol;
+            const bool warp_live = ct * TN + 32 * (warp & 3) < ncols;  // a ragged last column tile leaves whole warps idle
+            const int* slot = xq + static_cast<size_t>(min(col, ncols - 1)) * slot_ints + nsb * 64;  // this column's scales
             float acc[2 * 32];
 #pragma unroll
             for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+            float dx_next = __int_as_float(__ldg(slot + sb0));
             for (int sb = sb0; sb < sb1 && ok; ++sb, ++it) {
-                float d, dmin = 0.0f;
-                if (kQ6) {
-                    d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(w + nblk * 208 + (eblk + sb) * 2)));
-                } else {
-                    const unsigned hdw = __ldg(reinterpret_cast<const unsigned*>(w + (eblk + sb) * kQ4KBlock));
-                    d = half_bits_to_float(hdw & 0xFFFFu), dmin = half_bits_to_float(hdw >> 16);
-                }
-                const f32x2 d2 = pack2(d, d), dmin2 = pack2(dmin, dmin);
-                const int slot = it & (kDxSlots - 1);
-                ok = wait_or_fail(&dxfull[slot], static_cast<uint32_t>(it / kDxSlots) & 1u, fail);
-                if (!ok) break;
-                const float* dxs = reinterpret_cast<const float*>(sm + C::kOffDx + slot * kChunk) + (sb & 3);
+                const float dx = dx_next;
+                if (sb + 1 < sb1) dx_next = __int_as_float(__ldg(slot + sb + 1));
+                const f32x2 dx2 = pack2(dx, dx);
+                const uint8_t* ddslot = sm + C::kOffDd + (it & (kRing - 1)) * C::kDdSlot;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    if (h >= nh) break;
-                    ok = wait_or_fail(&tfull[h], static_cast<uint32_t>(use[h]++) & 1u, fail);
+                    ok = wait_or_fail(&tfull[h], static_cast<uint32_t>(it) & 1u, fail);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t t0 = tlane + h * C::kHalfCols;
+                    if (warp_live) {
+                        const uint32_t t0 = tlane + h * C::kHalfCols;
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {  // 8 columns at a time
-                        const int col0 = HN * h + 32 * cs + 8 * ch;
-                        if (c_tile + col0 >= ncols) continue;
-                        int va[8], vb[8];
-                        tmem_ld8(t0 + 8 * ch, va);
-                        tmem_ld8(t0 + HN + 8 * ch, vb);
-                        if (kQ6) {
+                        for (int ch = 0; ch < 4; ++ch) {  // eight weight rows at a time
+                            const int lr0 = 32 * rs + 8 * ch;  // first of them inside the half
+                            int va[8], vb[8], vh[8], vl[8];
+                            tmem_ld8(t0 + 8 * ch, va);
+                            tmem_ld8(t0 + HR + 8 * ch, vb);
+                            if (!kQ6) {
+                                tmem_ld8(t0 + 2 * HR + 8 * ch, vh);
+                                tmem_ld8(t0 + 3 * HR + 8 * ch, vl);
+                            }
                             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                             after_tmem_wait(va), after_tmem_wait(vb);
+                            if (!kQ6) after_tmem_wait(vh), after_tmem_wait(vl);
 #pragma unroll
-                            for (int i = 0; i < 8; i += 2) {
-                                const f32x2 dx2 = pack2(dxs[(col0 + i) * 4], dxs[(col0 + i + 1) * 4]);
-                                const f32x2 is2 = pack2(static_cast<float>(64 * va[i] + vb[i]), static_cast<float>(64 * va[i + 1] + vb[i + 1]));
-                                float ta, tb;
-                                unpack2(mul2(mul2(d2, dx2), is2), ta, tb);
-                                acc[32 * h + 8 * ch + i] = __fadd_rn(acc[32 * h + 8 * ch + i], ta);
-                                acc[32 * h + 8 * ch + i + 1] = __fadd_rn(acc[32 * h + 8 * ch + i + 1], tb);
-                            }
-                        } else {
-                            int vh[8], vl[8];
-                            tmem_ld8(t0 + 2 * HN + 8 * ch, vh);
-                            tmem_ld8(t0 + 3 * HN + 8 * ch, vl);
-                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                            after_tmem_wait(va), after_tmem_wait(vb), after_tmem_wait(vh), after_tmem_wait(vl);
-#pragma unroll
-                            for (int i = 0; i < 8; i += 2) {
-                                const f32x2 dx2 = pack2(dxs[(col0 + i) * 4], dxs[(col0 + i + 1) * 4]);
-                                const f32x2 is2 = pack2(static_cast<float>(8 * va[i] + vb[i]), static_cast<float>(8 * va[i + 1] + vb[i + 1]));
-                                const f32x2 im2 = pack2(static_cast<float>(64 * vh[i] + vl[i]), static_cast<float>(64 * vh[i + 1] + vl[i + 1]));
-                                float t1a, t1b, t2a, t2b;
-                                unpack2(mul2(mul2(d2, dx2), is2), t1a, t1b);
-                                unpack2(mul2(mul2(dmin2, dx2), im2), t2a, t2b);
-                                acc[32 * h + 8 * ch + i] = __fadd_rn(acc[32 * h + 8 * ch + i], __fsub_rn(t1a, t2a));
-                                acc[32 * h + 8 * ch + i + 1] = __fadd_rn(acc[32 * h + 8 * ch + i + 1], __fsub_rn(t1b, t2b));
+                            for (int pr = 0; pr < 4; ++pr) {
+                                const int rp = (HR * h + lr0) / 2 + pr;  // row pair inside the tile
+                                float* a0 = &acc[32 * h + 8 * ch + 2 * pr];
+                                if (kQ6) {
+                                    const f32x2 d2 = *reinterpret_cast<const f32x2*>(ddslot + rp * 8);
+                                    const f32x2 is2 = planes_to_float2<6>(va[2 * pr], va[2 * pr + 1], vb[2 * pr], vb[2 * pr + 1]);
+                                    float ta, tb;
+                                    unpack2(mul2(mul2(d2, dx2), is2), ta, tb);
+                                    a0[0] = __fadd_rn(a0[0], ta);
+                                    a0[1] = __fadd_rn(a0[1], tb);
+                                } else {
+                                    const ulonglong2 dq = *reinterpret_cast<const ulonglong2*>(ddslot + rp * 16);  // {d, d'}, {dmin, dmin'}
+                                    const f32x2 is2 = planes_to_float2<3>(va[2 * pr], va[2 * pr + 1], vb[2 * pr], vb[2 * pr + 1]);
+                                    const f32x2 im2 = small_to_float2(64 * vh[2 * pr] + vl[2 * pr], 64 * vh[2 * pr + 1] + vl[2 * pr + 1]);
+                                    float t1a, t1b, t2a, t2b;
+                                    unpack2(mul2(mul2(dq.x, dx2), is2), t1a, t1b);
+                                    unpack2(mul2(mul2(dq.y, dx2), im2), t2a, t2b);
+                                    a0[0] = __fadd_rn(a0[0], __fsub_rn(t1a, t2a));
+                                    a0[1] = __fadd_rn(a0[1], __fsub_rn(t1b, t2b));
+                                }
                             }
                         }
                     }
@@ -359,51 +405,44 @@ __global__ void __launch_bounds__(Cfg<kQ6>::kThreads, 1)
                     if (lane == 0) mbar_arrive(&tempty[h]);
                 }
             }
-            if (ok) {
-                float* out = (partial ? partial + static_cast<size_t>(sb0 / per) * ncols * rows : y) + rt * TM + erow;
+            if (ok && col < ncols) {  // 2 x 32 consecutive rows of column `col`
+                float* out = (partial ? partial + static_cast<size_t>(sb0 / per) * ncols * rows : y) + static_cast<size_t>(col) * rows + rt * TM + 32 * rs;
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int c = c_tile + HN * h + 32 * cs + j;
-                        if (c < ncols) out[static_cast<size_t>(c) * rows] = acc[32 * h + j];
-                    }
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4*>(out + HR * h + j) = make_float4(acc[32 * h + j], acc[32 * h + j + 1], acc[32 * h + j + 2], acc[32 * h + j + 3]);
             }
         }
-    } else if (warp == kEpiWarps) {
-        // ================= MMA issue: one thread
-        if (lane == 0) {
-            int it = 0, use[2] = {0, 0};
+    } else if (warp >= C::kMmaWarp) {
+        // ================= MMA issue: one thread of this warpgroup (the other three warps only release registers)
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == C::kMmaWarp && lane == 0) {
+            int it = 0;
             bool ok = true;
             const uint32_t base = smem_u32(sm);
+            const uint32_t zero = base + C::kOffZero;
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
                 int rt, ct, sb0, sb1;
                 unit_of(u, rt, ct, sb0, sb1);
-                const int nh = ncols - ct * TN > HN ? 2 : 1;
                 for (int sb = sb0; sb < sb1 && ok; ++sb, ++it) {
                     const int s = it & 1;
-                    const uint32_t ph = static_cast<uint32_t>(it >> 1) & 1u;
-                    ok = wait_or_fail(&full[s], ph, fail);
+                    ok = wait_or_fail(&full[s], static_cast<uint32_t>(it >> 1) & 1u, fail);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = base + s * C::kStage;
-                    for (int h = 0; h < nh && ok; ++h) {
-                        ok = wait_or_fail(&tempty[h], (static_cast<uint32_t>(use[h]++) & 1u) ^ 1u, fail);
+                    for (int h = 0; h < 2 && ok; ++h) {
+                        ok = wait_or_fail(&tempty[h], (static_cast<uint32_t>(it) & 1u) ^ 1u, fail);
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint32_t td = tmem + h * C::kHalfCols;
+                        const uint32_t wb = st + C::kOffW + h * (16 * kChunk);
 #pragma unroll
-                        for (int ks = 0; ks < 8; ++ks) {
-                            const uint64_t bd = desc_sw128(st + C::kOffBx + (ks >> 2) * kAtom + h * (HN * 128) + (ks & 3) * 32);
-                            mma_i8(td, desc_nosw(st + C::kOffAa + 2 * ks * kChunk, kChunk, 128), bd, ks > 0);
-                            mma_i8(td + HN, desc_nosw(st + C::kOffAb + 2 * ks * kChunk, kChunk, 128), bd, ks > 0);
-                        }
-                        if (!kQ6) {
-                            const uint32_t zero = base + C::kOffZero;
-                            const uint32_t am = st + C::kOffAm, bs = st + C::kOffBs + h * (HN * 16);
-                            const uint64_t sd = desc_nosw(bs, zero - bs, 128);
-                            mma_i8(td + 2 * HN, desc_nosw(am, zero - am, 128), sd, 0);
-                            mma_i8(td + 3 * HN, desc_nosw(am + kChunk, zero - (am + kChunk), 128), sd, 0);
+                        for (int ks = 0; ks < 8; ++ks)  // M = 128 activation columns, N = plane a | plane b of 64 weight rows
+                            mma_i8(td, desc_sw128(st + C::kOffX + (ks >> 2) * kAtom + (ks & 3) * 32), desc_nosw(wb + 2 * ks * kChunk, kChunk, 128), ks > 0);
+                        if (!kQ6) {  // N = Dh | Dl: the sums chunk against the mins in K bytes 0..7 / 8..15
+                            const uint32_t xs = st + C::kOffXs, wm = st + C::kOffWm + h * kChunk;
+                            mma_i8(td + 2 * HR, desc_nosw(xs, zero - xs, 128), desc_nosw(wm, zero - wm, 128), 0);
                         }
                         mma_commit(&tfull[h]);
                     }
@@ -412,9 +451,9 @@ __global__ void __launch_bounds__(Cfg<kQ6>::kThreads, 1)
             }
         }
     } else {
-        // ================= producers: weight planes (all) and the tensor copies of the activations (thread 0)
-        const int p = tid - 32 * (kEpiWarps + 1);
-        const int row = p & (TM - 1), n = p >> 7;
+        // ================= producers: weight planes and row scales (all), tensor copies of the activations (thread 0)
+        const int p = tid - 32 * kEpiWarps;
+        const int row = p & (TM - 1), n = p >> 7, half = row >> 6, lr = row & (HR - 1);
         int it = 0;
         bool ok = true;
         Blk cur, nxt;
@@ -447,16 +486,18 @@ __global__ void __launch_bounds__(Cfg<kQ6>::kThreads, 1)
                 if (p == 0) {
                     const int c_tile = ct * TN;
                     mbar_expect_tx(&full[s], 2 * kAtom + (kQ6 ? 0 : kChunk));
-                    tma_2d(st + C::kOffBx, &map_x, sb * 256, c_tile, &full[s]);
-                    tma_2d(st + C::kOffBx + kAtom, &map_x, sb * 256 + 128, c_tile, &full[s]);
-                    if (!kQ6) tma_2d(st + C::kOffBs, &map_s, nsb * 324 + sb * 16, c_tile, &full[s]);
-                    const int slot = it & (kDxSlots - 1);
-                    mbar_expect_tx(&dxfull[slot], kChunk);
-                    tma_2d(sm + C::kOffDx + slot * kChunk, &map_s, nsb * 256 + (sb >> 2) * 16, c_tile, &dxfull[slot]);
+                    tma_2d(st + C::kOffX, &map_x, sb * 256, c_tile, &full[s]);
+                    tma_2d(st + C::kOffX + kAtom, &map_x, sb * 256 + 128, c_tile, &full[s]);
+                    if (!kQ6) tma_2d(st + C::kOffXs, &map_s, nsb * 324 + sb * 16, c_tile, &full[s]);
                 }
-                unpack_blk<C>(cur, st, row, n);
+                // The scale ring slot of item `it` was last read by the epilogue of item it - 4, which finished before
+                // the MMAs of item it - 2 could start (they waited for the accumulators of item it - 3 to be read back),
+                // and this thread has just seen those MMAs complete.
+                float* dd = reinterpret_cast<float*>(sm + C::kOffDd + (it & (kRing - 1)) * C::kDdSlot) + half * (C::kDdSlot / 8);
+                unpack_blk(cur, st + C::kOffW + half * (16 * kChunk), st + C::kOffWm + half * kChunk, dd, lr, n);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
-                mbar_arrive(&full[s]);
+                __syncwarp();  // every lane's stores and fence before the warp's one arrival
+                if (lane == 0) mbar_arrive(&full[s]);
                 cur = nxt;
             }
         }
@@ -468,7 +509,7 @@ __global__ void __launch_bounds__(Cfg<kQ6>::kThreads, 1)
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (tid == 0 && *fail) atomicAdd(&g_tcp_timeouts, 1u);
-    if (warp == kEpiWarps) {
+    if (warp == C::kMmaWarp) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
     }
@@ -542,7 +583,7 @@ int launch_pipe(const uint8_t* w, const int* xq, float* y, int rows, int nsb, in
     if (splits > 1 && (!workspace || workspace_bytes < static_cast<size_t>(splits) * ncols * rows * sizeof(float))) per = nsb, splits = 1;
     const int n_rt = rows / TM, n_ct = (ncols + TN - 1) / TN, units = n_rt * n_ct * splits;
     const int grid = std::min(units, kSmCount);
-    kern<<<grid, C::kThreads, C::kSmem, s>>>(w, map_x, map_s, y, rows, nsb, ncols, per, n_rt, n_ct, units, splits > 1 ? workspace : nullptr);
+    kern<<<grid, C::kThreads, C::kSmem, s>>>(w, xq, map_x, map_s, y, rows, nsb, ncols, per, n_rt, n_ct, units, splits > 1 ? workspace : nullptr);
     if (const int e = launch_status(); e != KCB_SUCCESS || splits == 1) return e;
     const size_t n = static_cast<size_t>(ncols) * rows;
     splitk_sum_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(workspace, y, n, splits);
@@ -574,7 +615,7 @@ size_t matmul_tc_workspace_bytes(int rows, int k, int ncols) {
 int matmul_kq_q8k_tc_pipe(const void* w, const int* xq, float* y, int rows, int k, int ncols, int q6, void* workspace, size_t workspace_bytes,
                           cudaStream_t s) {
     if (rows <= 0 || rows % TM || k <= 0 || k % 1024 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
-    if (misaligned(w, 16) || misaligned(xq, 16) || misaligned(y, 4) || misaligned(workspace, 4)) return KCB_INVALID_POINTER;
+    if (misaligned(w, 16) || misaligned(xq, 16) || misaligned(y, 16) || misaligned(workspace, 16)) return KCB_INVALID_POINTER;  // y is stored four rows at a time
     return q6 ? launch_pipe<true>(static_cast<const uint8_t*>(w), xq, y, rows, k / 256, ncols, static_cast<float*>(workspace), workspace_bytes, s)
               : launch_pipe<false>(static_cast<const uint8_t*>(w), xq, y, rows, k / 256, ncols, static_cast<float*>(workspace), workspace_bytes, s);
 }
