@@ -45,6 +45,8 @@ int kcb_ggml_ctx_create(void* stream, void** ctx);
 /* Start of a graph: forget which inputs are quantized, reuse the scratch from its beginning.  Waits for the
  * stream first, since earlier launches may still read the scratch. */
 int kcb_ggml_ctx_begin_graph(void* ctx);
+/* Waits for everything launched through this context (a synchronous graph_compute ends with it). */
+int kcb_ggml_ctx_sync(void* ctx);
 int kcb_ggml_ctx_destroy(void* ctx);
 
 /* Bytes a weight tensor of this type occupies on the device, and the upload + layout conversion. */

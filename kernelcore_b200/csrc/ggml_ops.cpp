@@ -144,6 +144,10 @@ int kcb_ggml_ctx_begin_graph(void* h) {
     c->chunk = 0, c->used = 0;
     return KCB_SUCCESS;
 }
+int kcb_ggml_ctx_sync(void* h) {
+    if (!h) return KCB_INVALID_VALUE;
+    return cudaStreamSynchronize(static_cast<Ctx*>(h)->stream) == cudaSuccess ? KCB_SUCCESS : KCB_INTERNAL_ERROR;
+}
 int kcb_ggml_ctx_destroy(void* h) {
     if (h) {
         auto* c = static_cast<Ctx*>(h);

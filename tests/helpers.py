@@ -35,7 +35,7 @@ def pad8(n: int) -> int:
 OracleModel = oracle.BoundModel
 
 
-def oracle_prefill(shape, model, tokens, q8k=True, tail_q8k=False):
+def oracle_prefill(shape, model, tokens, q8k=True, tail_q8k=False, tail_ggml=False):
     """The batched prompt pass restated on the CPU oracle, op for op as the reference's batched (ggml) path runs
     it: add + partial sums of squares, RMSNorm * weight + per-256 quantization (add_sumsq_f / sumsq_part /
     norm_mul_q8k), K-quant matvecs on per-256 slots per token, per-head q/k RMSNorm and rope_ggml, fp16 KV rows
@@ -128,6 +128,15 @@ def oracle_prefill(shape, model, tokens, q8k=True, tail_q8k=False):
         P.norm_mul_q8k(xr, np.ascontiguousarray(model["out_norm"], np.float32), yn, slot, sq, s.hidden, 1, s.eps)
         out = np.zeros(s.vocab, np.float32)
         P.matvec_q6k_q8k(np.ascontiguousarray(model["lm_head"], np.uint8).ravel(), slot[0], out, s.vocab, s.hidden)
+        return out
+    if tail_ggml:  # the ggml graph's last row: ADD + RMS_NORM + MUL fused with per-32 quantization, then the matvec on it
+        xr, tr = np.ascontiguousarray(X[n - 1:n]), np.ascontiguousarray(T[n - 1:n])
+        slot, yn = np.zeros((1, nb * 11), np.int32), np.zeros((1, s.hidden), np.float32)
+        P.add_sumsq_f(xr, tr, xr, slot, s.hidden, 1)
+        P.norm_mul_q8(xr, np.ascontiguousarray(model["out_norm"], np.float32), yn, slot, s.hidden, 1, s.eps)
+        out = np.zeros(s.vocab, np.float32)
+        P.matvec_q6k_q8(np.ascontiguousarray(model["lm_head"], np.uint8).ravel(), slot[0, :nb * 8], slot[0, nb * 8:nb * 10].view(np.float32), out,
+                        s.vocab, s.hidden)
         return out
     x = X[n - 1] + T[n - 1]
     y = np.zeros(s.hidden, np.float32)
