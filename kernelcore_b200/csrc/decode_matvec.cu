@@ -1,0 +1,555 @@
+// Matvecs of the single-sequence decode step with their producers folded in.
+//
+// A decode step of the reference (llm/llm_model.cpp:287-360) alternates small vector kernels (residual add + RMSNorm +
+// quantize, SwiGLU + quantize, the merge of the attention partials + quantize) with the K-quant matvecs that consume
+// their output (kernels/llm/matvec_q4k_q8.cu, matvec_q6k_q8.cu).  On a B200 every one of those launches is shorter than
+// its own ramp, so here the vector kernel becomes the PROLOGUE of the matvec that reads it: every CTA recomputes the
+// few-KB activation vector out of L2 straight into shared memory (same arithmetic, bit for bit, as the stand-alone
+// kernels) and then streams its rows of the matrix.  Three more things make the chain of launches cheap:
+//   * weights do not depend on the step's data, so each CTA requests its first weight tiles (bulk copies into a
+//     shared-memory ring) BEFORE it waits for the preceding kernel (programmatic dependent launch): the matrix is
+//     already arriving while the previous kernel drains;
+//   * each kernel releases its dependents as soon as its own prologue is done;
+//   * rows are dealt in tiles to one persistent CTA of 8 warps per SM, small enough (registers, shared memory) for the
+//     next kernel's CTA to sit beside it; wide matrices (k = 8192) split a row's super-blocks over two warps so that a
+//     lane's activation slice still fits in registers.
+// The per-row arithmetic is that of the bulk-copy matvec in kquant_matvec.cu (integer dot products, the reference's
+// fp32 scale products, one shuffle tree per row).  Every mbarrier wait is bounded; on expiry the CTA counts the event
+// and leaves.
+
+#include "common.cuh"
+#include "ops.h"
+
+#include <algorithm>
+#include <cstdlib>
+
+namespace kcb {
+namespace {
+
+constexpr unsigned kLo4 = 0x0F0F0F0Fu;
+constexpr unsigned kHi2 = 0x30303030u;
+constexpr int kWarps = 16, kThreads = 32 * kWarps;  // 256 threads, <= 128 registers, <= ~110 KB: CTAs of two consecutive kernels share an SM
+constexpr int kMaxStages = 6;
+constexpr int kSmemBudget = 224 * 1024;  // per CTA, so that the next kernel's CTA fits beside it
+constexpr int kBarBytes = 128;
+
+__device__ unsigned g_dmv_timeouts = 0;
+
+
+struct DmvMat {
+    const uint8_t* w = nullptr;  // Q4_K blocks or Q6_K planes of `rows` rows
+    float* y = nullptr;
+    int rows = 0;
+};
+
+// ---- prologues: the activation vector as Q8 blocks of 32 in shared memory ------------------------------------------
+// Whatever the preceding kernels of the step produce is read with ordinary loads through pointers that are NOT declared
+// const __restrict__: under a programmatic dependency this kernel is already running while its predecessor writes, and
+// the read-only data path (ld.global.nc, which the compiler also picks for const __restrict__ pointers) is only defined
+// for data that does not change during the kernel's lifetime.  Weights and norm vectors may use it.
+// x_out = x_in + t (t may be null), then blocks of RMSNorm(x_out) * w.  The arithmetic of add_norm_q8_cta (common.cuh):
+// sums of squares per 128 values by a warp butterfly, group sums added 32 apart in order, so the result does not depend
+// on the CTA's size.  Only the CTA with `store` set writes x_out (all compute the same values).
+template <int MAXIT>
+__device__ __forceinline__ void pro_add_norm(const float* x_in, const float* t, float* x_out, bool store, const float* __restrict__ w, int* xq,
+                                             float* xd, int n, float eps, float* gsum) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int groups = n / 128;
+    float4 v[MAXIT], ww[MAXIT];
+#pragma unroll
+    for (int i = 0; i < MAXIT; ++i) {
+        const int gi = warp + i * kWarps;
+        v[i] = ww[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (gi < groups) {
+            ww[i] = __ldg(reinterpret_cast<const float4*>(w + gi * 128) + lane);
+            float4 a = *(reinterpret_cast<const float4*>(x_in + gi * 128) + lane);
+            if (t) {
+                const float4 b = *(reinterpret_cast<const float4*>(t + gi * 128) + lane);
+                a = make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
+            }
+            if (store) *(reinterpret_cast<float4*>(x_out + gi * 128) + lane) = a;
+            v[i] = a;
+            const float p = __fadd_rn(__fadd_rn(__fmul_rn(a.x, a.x), __fmul_rn(a.y, a.y)), __fadd_rn(__fmul_rn(a.z, a.z), __fmul_rn(a.w, a.w)));
+            const float s = warp_sum(p);
+            if (lane == 0) gsum[gi] = s;
+        }
+    }
+    __syncthreads();
+    float tot = 0.0f;
+    for (int g = lane; g < groups; g += 32) tot = __fadd_rn(tot, gsum[g]);
+    const float r = rinv_rms(warp_sum(tot), n, eps);
+#pragma unroll
+    for (int i = 0; i < MAXIT; ++i) {
+        const int gi = warp + i * kWarps;
+        if (gi < groups)
+            quantize_4blocks_warp(make_float4(__fmul_rn(__fmul_rn(v[i].x, r), ww[i].x), __fmul_rn(__fmul_rn(v[i].y, r), ww[i].y),
+                                              __fmul_rn(__fmul_rn(v[i].z, r), ww[i].z), __fmul_rn(__fmul_rn(v[i].w, r), ww[i].w)),
+                                  xq, xd, gi * 4, lane);
+    }
+}
+
+// SwiGLU g / (1 + 2^(-g log2 e)) * u quantized per 32 (kernels/llm/silu_mul_q8x4.cu): one warp per block of 32, all of
+// a lane's inputs requested before the first is used (one round trip to L2, not one per block).  n <= 32 * kWarps * MAXB.
+template <int MAXB>
+__device__ __forceinline__ void pro_swiglu(const float* g, const float* u, int* xq, float* xd, int n) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nb = n / 32;
+    float gv[MAXB], uv[MAXB];
+#pragma unroll
+    for (int i = 0; i < MAXB; ++i) {
+        const int b = warp + i * kWarps;
+        gv[i] = b < nb ? g[b * 32 + lane] : 0.0f;  // (plain loads: see the note on the read-only path above)
+        uv[i] = b < nb ? u[b * 32 + lane] : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < MAXB; ++i) {
+        const int b = warp + i * kWarps;
+        if (b < nb) {
+            const float e = exp2f(__fmul_rn(-gv[i], 1.44269504f));
+            quantize_block_warp(__fmul_rn(__fdiv_rn(gv[i], __fadd_rn(1.0f, e)), uv[i]), xq, xd, b, lane);
+        }
+    }
+}
+
+// Merge of the split-KV attention partials {acc[hd], max, sum} per head and split, normalised and quantized per 32
+// channels: one warp per block of 32 channels, weights 2^((max_s - max) log2 e) and sums in split order.
+__device__ __forceinline__ void pro_combine(const float* part, int* xq, float* xd, int heads, int hd, int nsplit) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int b = warp; b < heads * hd / 32; b += kWarps) {
+        const int h = b * 32 / hd, d = (b * 32) % hd + lane;
+        const float* ph = part + static_cast<size_t>(h) * nsplit * (hd + 2);
+        float ll = 0.0f, aa = 0.0f;
+        if (nsplit <= 32) {
+            float pv[32];
+#pragma unroll
+            for (int s = 0; s < 32; ++s) pv[s] = s < nsplit ? ph[s * (hd + 2) + d] : 0.0f;
+            const float pm = lane < nsplit ? ph[lane * (hd + 2) + hd] : -INFINITY;
+            const float pl = lane < nsplit ? ph[lane * (hd + 2) + hd + 1] : 0.0f;
+            const float mm = warp_max(pm);
+            const float wl = pm == -INFINITY ? 0.0f : exp2f((pm - mm) * 1.44269504f);
+#pragma unroll
+            for (int s = 0; s < 32; ++s) {
+                const float wgt = __shfl_sync(0xffffffffu, wl, s), ls = __shfl_sync(0xffffffffu, pl, s);
+                if (s < nsplit) {
+                    ll = __fmaf_rn(ls, wgt, ll);
+                    aa = __fmaf_rn(pv[s], wgt, aa);
+                }
+            }
+        } else {
+            float mm = -INFINITY;
+            for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, ph[s * (hd + 2) + hd]);
+            for (int s = 0; s < nsplit; ++s) {
+                const float pm = ph[s * (hd + 2) + hd];
+                const float wgt = pm == -INFINITY ? 0.0f : exp2f((pm - mm) * 1.44269504f);
+                ll = __fmaf_rn(ph[s * (hd + 2) + hd + 1], wgt, ll);
+                aa = __fmaf_rn(ph[s * (hd + 2) + d], wgt, aa);
+            }
+        }
+        quantize_block_warp(__fdiv_rn(aa, ll), xq, xd, b, lane);
+    }
+}
+
+// ---- the matvec body --------------------------------------------------------------------------------------------------
+// CTA `cta` of `nctas` takes tiles cta, cta + nctas, ... of TR rows.  KSPLIT warps share a row: warp w works on tile
+// row (w % (kWarps / KSPLIT)) [+ multiples of that], super-blocks [ks * nsb / KSPLIT, (ks + 1) * nsb / KSPLIT) with
+// ks = w / (kWarps / KSPLIT).  ITERS = ceil(nsb / KSPLIT / 4).
+template <bool kQ6, int ITERS, int TR, int KSPLIT>
+__device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq, const float* sxd, uint64_t* full, uint8_t* buf, int stages, int cta,
+                                         int nctas, float (*ytile)[TR * KSPLIT]) {
+    constexpr int kBlk = kQ6 ? kQ6KBlock : kQ4KBlock;
+    constexpr int NR = kWarps / KSPLIT;  // rows worked on at once
+    constexpr int RPW = TR / NR;         // rows per warp and tile
+    static_assert(TR % NR == 0 && RPW >= 1, "tile rows must be a multiple of the rows worked on at once");
+    const int rows = m.rows;
+    const uint32_t stage_bytes = static_cast<uint32_t>(TR) * nsb * kBlk;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 3, c8 = lane & 7;
+    const int wr = warp % NR, ks = warp / NR;
+    const int nsb_w = nsb / KSPLIT, sb_base = ks * nsb_w;
+    const int ntiles = (rows + TR - 1) / TR;
+    const int my_tiles = cta < ntiles ? (ntiles - 1 - cta) / nctas + 1 : 0;
+    const size_t nblk = static_cast<size_t>(rows) * nsb;
+
+    auto issue = [&](int i) {  // thread 0 only; the kernel has already requested tiles 0 .. stages - 1
+        const int s = i % stages;
+        const int r0 = (cta + i * nctas) * TR;
+        const int nr = min(TR, rows - r0);
+        uint8_t* dst = buf + static_cast<size_t>(s) * stage_bytes;
+        const size_t b0 = static_cast<size_t>(r0) * nsb;
+        const uint32_t nb = static_cast<uint32_t>(nr) * nsb;
+        mbar_expect_tx(&full[s], nb * kBlk);
+        if (kQ6) {
+            bulk_g2s(dst, m.w + b0 * 128, nb * 128, &full[s]);
+            bulk_g2s(dst + TR * nsb * 128, m.w + nblk * 128 + b0 * 64, nb * 64, &full[s]);
+            bulk_g2s(dst + TR * nsb * 192, m.w + nblk * 192 + b0 * 16, nb * 16, &full[s]);
+            bulk_g2s(dst + TR * nsb * 208, m.w + nblk * 208 + b0 * 2, nb * 2, &full[s]);
+        } else {
+            bulk_g2s(dst, m.w + b0 * kQ4KBlock, nb * kQ4KBlock, &full[s]);
+        }
+    };
+    // ---- this lane's slice of the activations, in registers ----
+    uint4 xa[ITERS], xb[ITERS];
+    float4 dd[ITERS];
+    int sa[ITERS], sb2[ITERS];
+    bool ok[ITERS];
+    const int j = c8 >> 1, h = c8 & 1, sh = 16 * (j & 1);   // Q4_K lane roles
+    const int n = c8 >> 2, a = (c8 >> 1) & 1;               // Q6_K lane roles
+    const int shl = 4 - 2 * a, shr = 2 * a;
+    const unsigned sel = static_cast<unsigned>(2 * a + h) * 0x1111u | 0x8880u;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int sbl = 4 * it + g;
+        ok[it] = sbl < nsb_w;
+        xa[it] = xb[it] = make_uint4(0, 0, 0, 0);
+        dd[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+        sa[it] = sb2[it] = 0;
+        if (!ok[it]) continue;
+        const int sb = sb_base + sbl;
+        if (kQ6) {
+            const int b = sb * 8 + 4 * n + a;
+            xa[it] = *reinterpret_cast<const uint4*>(sxq + b * 8 + 4 * h);
+            xb[it] = *reinterpret_cast<const uint4*>(sxq + (b + 2) * 8 + 4 * h);
+            dd[it].x = sxd[2 * b];
+            dd[it].z = sxd[2 * (b + 2)];
+            int s0 = 0, s1 = 0;
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].x), s0);
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].y), s0);
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].z), s0);
+            s0 = __dp4a(0x01010101, static_cast<int>(xa[it].w), s0);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].x), s1);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].y), s1);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].z), s1);
+            s1 = __dp4a(0x01010101, static_cast<int>(xb[it].w), s1);
+            sa[it] = 32 * s0;  // the -32 weight offset, applied through the activation sums
+            sb2[it] = 32 * s1;
+        } else {
+            const int b = sb * 8 + 2 * j;
+            xa[it] = *reinterpret_cast<const uint4*>(sxq + b * 8 + 4 * h);
+            xb[it] = *reinterpret_cast<const uint4*>(sxq + b * 8 + 8 + 4 * h);
+            const float4 t = *reinterpret_cast<const float4*>(sxd + 2 * b);
+            dd[it] = make_float4(t.x, h == 0 ? __fmul_rn(t.x, t.y) : 0.f, t.z, h == 0 ? __fmul_rn(t.z, t.w) : 0.f);
+        }
+    }
+
+    auto q6_step = [&](const uint8_t* st, int rl, int it) -> float {
+        const size_t blk = static_cast<size_t>(rl) * nsb + sb_base + g + 4 * it;
+        const uint4 l = *reinterpret_cast<const uint4*>(st + blk * 128 + 16 * c8);
+        const uint4 hq = *reinterpret_cast<const uint4*>(st + TR * nsb * 128 + blk * 64 + 32 * n + 16 * h);
+        const uint2 sc = *reinterpret_cast<const uint2*>(st + TR * nsb * 192 + blk * 16 + 8 * n);
+        const unsigned dq = *reinterpret_cast<const unsigned short*>(st + TR * nsb * 208 + blk * 2);
+        int dl0 = 0, dl1 = 0, dh0 = 0, dh1 = 0;
+        dl0 = __dp4a(static_cast<int>((l.x & kLo4) | ((hq.x << shl) & kHi2)), static_cast<int>(xa[it].x), dl0);
+        dl1 = __dp4a(static_cast<int>((l.y & kLo4) | ((hq.y << shl) & kHi2)), static_cast<int>(xa[it].y), dl1);
+        dl0 = __dp4a(static_cast<int>((l.z & kLo4) | ((hq.z << shl) & kHi2)), static_cast<int>(xa[it].z), dl0);
+        dl1 = __dp4a(static_cast<int>((l.w & kLo4) | ((hq.w << shl) & kHi2)), static_cast<int>(xa[it].w), dl1);
+        dh0 = __dp4a(static_cast<int>(((l.x >> 4) & kLo4) | ((hq.x >> shr) & kHi2)), static_cast<int>(xb[it].x), dh0);
+        dh1 = __dp4a(static_cast<int>(((l.y >> 4) & kLo4) | ((hq.y >> shr) & kHi2)), static_cast<int>(xb[it].y), dh1);
+        dh0 = __dp4a(static_cast<int>(((l.z >> 4) & kLo4) | ((hq.z >> shr) & kHi2)), static_cast<int>(xb[it].z), dh0);
+        dh1 = __dp4a(static_cast<int>(((l.w >> 4) & kLo4) | ((hq.w >> shr) & kHi2)), static_cast<int>(xb[it].w), dh1);
+        const int tl = prmt_sbyte(sc.x, sel) * (dl0 + dl1 - sa[it]);
+        const int th = prmt_sbyte(sc.y, sel) * (dh0 + dh1 - sb2[it]);
+        return half_bits_to_float(dq) * (static_cast<float>(tl) * dd[it].x + static_cast<float>(th) * dd[it].z);
+    };
+    auto q4_step = [&](const uint8_t* st, int rl, int it) -> float {
+        const uint8_t* pb = st + (static_cast<size_t>(rl) * nsb + sb_base + g + 4 * it) * kQ4KBlock;
+        const uint4 hd = *reinterpret_cast<const uint4*>(pb);
+        const uint4 q = *reinterpret_cast<const uint4*>(pb + 16 + 16 * c8);
+        int da0 = 0, da1 = 0, db0 = 0, db1 = 0;
+        da0 = __dp4a(static_cast<int>(q.x & kLo4), static_cast<int>(xa[it].x), da0);
+        da1 = __dp4a(static_cast<int>(q.y & kLo4), static_cast<int>(xa[it].y), da1);
+        da0 = __dp4a(static_cast<int>(q.z & kLo4), static_cast<int>(xa[it].z), da0);
+        da1 = __dp4a(static_cast<int>(q.w & kLo4), static_cast<int>(xa[it].w), da1);
+        db0 = __dp4a(static_cast<int>((q.x >> 4) & kLo4), static_cast<int>(xb[it].x), db0);
+        db1 = __dp4a(static_cast<int>((q.y >> 4) & kLo4), static_cast<int>(xb[it].y), db1);
+        db0 = __dp4a(static_cast<int>((q.z >> 4) & kLo4), static_cast<int>(xb[it].z), db0);
+        db1 = __dp4a(static_cast<int>((q.w >> 4) & kLo4), static_cast<int>(xb[it].w), db1);
+        unsigned scw, mw;
+        if (j < 2) {
+            scw = hd.y & 0x3F3F3F3Fu;
+            mw = hd.z & 0x3F3F3F3Fu;
+        } else {
+            scw = (hd.w & kLo4) | ((hd.y >> 2) & kHi2);
+            mw = ((hd.w >> 4) & kLo4) | ((hd.z >> 2) & kHi2);
+        }
+        const int sca = (scw >> sh) & 255, scb = (scw >> (sh + 8)) & 255;
+        const int ma = (mw >> sh) & 255, mb = (mw >> (sh + 8)) & 255;
+        const float d = half_bits_to_float(hd.x & 0xFFFFu), dmin = half_bits_to_float(hd.x >> 16);
+        const float t1 = static_cast<float>(sca * (da0 + da1)) * dd[it].x + static_cast<float>(scb * (db0 + db1)) * dd[it].z;
+        const float t2 = static_cast<float>(ma) * dd[it].y + static_cast<float>(mb) * dd[it].w;
+        return d * t1 - dmin * t2;
+    };
+
+    for (int i = 0; i < my_tiles; ++i) {
+        const int s = i % stages;
+        const uint32_t parity = static_cast<uint32_t>(i / stages) & 1u;
+        if (!mbar_wait_bounded(&full[s], parity)) {
+            if (lane == 0) atomicAdd(&g_dmv_timeouts, 1u);
+            for (int t = 0; t < 1000; ++t) __nanosleep(1000);  // bounded grace for copies still in flight
+            return;  // data never arrived: leave without touching y
+        }
+        const int row0 = (cta + i * nctas) * TR;
+        const uint8_t* st = buf + static_cast<size_t>(s) * stage_bytes;
+        float acc[RPW];
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) acc[r] = 0.0f;
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            if (!ok[it]) continue;
+#pragma unroll
+            for (int r = 0; r < RPW; ++r) {
+                const int rl = wr + r * NR;
+                if (row0 + rl < rows) acc[r] += kQ6 ? q6_step(st, rl, it) : q4_step(st, rl, it);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            const float v = warp_sum(acc[r]);
+            const int rl = wr + r * NR;
+            if (KSPLIT == 1) {
+                if (lane == 0 && row0 + rl < rows) m.y[row0 + rl] = v;
+            } else if (lane == 0) {
+                ytile[i & 1][ks * TR + rl] = v;  // double-buffered: tile i + 2 writes it only after the barrier of tile i + 1
+            }
+        }
+        __syncthreads();  // every warp is done with stage s (and the K shares of the tile's rows are in ytile)
+        if (threadIdx.x == 0 && i + stages < my_tiles) issue(i + stages);
+        if (KSPLIT > 1 && threadIdx.x < TR && row0 + static_cast<int>(threadIdx.x) < rows) {
+            float v = ytile[i & 1][threadIdx.x];
+#pragma unroll
+            for (int q = 1; q < KSPLIT; ++q) v = __fadd_rn(v, ytile[i & 1][q * TR + threadIdx.x]);  // shares added in K order
+            m.y[row0 + threadIdx.x] = v;
+        }
+    }
+}
+
+struct DmvPro {
+    // PRO 0: Q8 blocks given
+    const int* xq = nullptr;
+    const float* xd = nullptr;
+    // PRO 1: x_out = x_in + t (t may be null), RMSNorm * wn
+    const float* x_in = nullptr;
+    const float* t = nullptr;
+    float* x_out = nullptr;
+    const float* wn = nullptr;
+    float eps = 0.0f;
+    // PRO 2: SwiGLU of g, u
+    const float* g = nullptr;
+    const float* u = nullptr;
+    // PRO 3: merge of attention partials
+    const float* part = nullptr;
+    int heads = 0, hd = 0, nsplit = 0;
+};
+
+// One launch: matrix m4 (Q4_K) on CTAs [0, c4) and, when c6 > 0, matrix m6 (Q6_K planes) on CTAs [c4, c4 + c6), both on
+// the same activations.  kQ6First: a single Q6_K matrix (m6 only, c4 == 0).
+template <int ITERS, int TR, int KSPLIT, int PRO, bool kHas4, bool kHas6>
+__global__ void __launch_bounds__(kThreads, 1) dmv_kernel(const DmvMat m4, const DmvMat m6, int c4, int nsb, const DmvPro pro, int stages4, int stages6) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ float ytile[2][TR * KSPLIT];
+    __shared__ float gsum[64];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    int* sxq = reinterpret_cast<int*>(smem + kBarBytes);
+    float* sxd = reinterpret_cast<float*>(sxq + nsb * 64);
+    uint8_t* buf = smem + kBarBytes + ((nsb * 320 + 127) / 128) * 128;
+    const bool is4 = kHas4 && (!kHas6 || static_cast<int>(blockIdx.x) < c4);
+    const int cta = is4 ? blockIdx.x : blockIdx.x - c4;
+    const int nctas = is4 ? (kHas6 ? c4 : gridDim.x) : gridDim.x - c4;
+    const int stages = is4 ? stages4 : stages6;
+
+    // weights first: they do not depend on anything the preceding kernels write
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMaxStages; ++s) mbar_init(&full[s], 1);
+        mbar_init_fence();
+        const DmvMat& m = is4 ? m4 : m6;
+        const int blkb = is4 ? kQ4KBlock : kQ6KBlock;
+        const int ntiles = (m.rows + TR - 1) / TR;
+        const int my_tiles = cta < ntiles ? (ntiles - 1 - cta) / nctas + 1 : 0;
+        const uint32_t stage_bytes = static_cast<uint32_t>(TR) * nsb * blkb;
+        const size_t nblk = static_cast<size_t>(m.rows) * nsb;
+        for (int i = 0; i < stages && i < my_tiles; ++i) {
+            const int r0 = (cta + i * nctas) * TR;
+            const int nr = min(TR, m.rows - r0);
+            uint8_t* dst = buf + static_cast<size_t>(i) * stage_bytes;
+            const size_t b0 = static_cast<size_t>(r0) * nsb;
+            const uint32_t nb = static_cast<uint32_t>(nr) * nsb;
+            mbar_expect_tx(&full[i], nb * blkb);
+            if (!is4) {
+                bulk_g2s(dst, m.w + b0 * 128, nb * 128, &full[i]);
+                bulk_g2s(dst + TR * nsb * 128, m.w + nblk * 128 + b0 * 64, nb * 64, &full[i]);
+                bulk_g2s(dst + TR * nsb * 192, m.w + nblk * 192 + b0 * 16, nb * 16, &full[i]);
+                bulk_g2s(dst + TR * nsb * 208, m.w + nblk * 208 + b0 * 2, nb * 2, &full[i]);
+            } else {
+                bulk_g2s(dst, m.w + b0 * kQ4KBlock, nb * kQ4KBlock, &full[i]);
+            }
+        }
+    }
+    // from here on the preceding kernels' results are complete and visible (a no-op without a programmatic dependency)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    if (PRO == 0) {
+        for (int i = threadIdx.x; i < nsb * 64; i += kThreads) sxq[i] = pro.xq[i];
+        for (int i = threadIdx.x; i < nsb * 16; i += kThreads) sxd[i] = pro.xd[i];
+    } else if (PRO == 1) {
+        pro_add_norm<4>(pro.x_in, pro.t, pro.x_out, blockIdx.x == 0, pro.wn, sxq, sxd, nsb * 256, pro.eps, gsum);
+    } else if (PRO == 2) {
+        pro_swiglu<16>(pro.g, pro.u, sxq, sxd, nsb * 256);
+    } else {
+        pro_combine(pro.part, sxq, sxd, pro.heads, pro.hd, pro.nsplit);
+    }
+    __syncthreads();
+    // this kernel's inputs are consumed: the next kernel may come up and request its weights
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (is4) {
+        if (kHas4) dmv_body<false, ITERS, TR, KSPLIT>(m4, nsb, sxq, sxd, full, buf, stages, cta, nctas, ytile);
+    } else {
+        if (kHas6) dmv_body<true, ITERS, TR, KSPLIT>(m6, nsb, sxq, sxd, full, buf, stages, cta, nctas, ytile);
+    }
+}
+
+template <class Kern>
+int launch_dmv(Kern kern, int grid, size_t smem, bool pdl, cudaStream_t s, const DmvMat& m4, const DmvMat& m6, int c4, int nsb, const DmvPro& pro, int st4,
+               int st6, PerDeviceFlag& raised) {
+    if (!raise_dynamic_smem(kern, kSmemBudget, raised)) return KCB_LAUNCH_FAILURE;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, m4, m6, c4, nsb, pro, st4, st6) == cudaSuccess ? KCB_SUCCESS : KCB_LAUNCH_FAILURE;
+}
+
+int stages_for(int tiles_per_cta, size_t stage_bytes, size_t fixed) {
+    int st = static_cast<int>((kSmemBudget - fixed) / stage_bytes);
+    st = std::min(st, kMaxStages);
+    return std::min(st, std::max(tiles_per_cta, 1));
+}
+
+// CTAs for the two matrices of a launch: the SMs shared in proportion to the bytes each streams.
+void share_ctas(int t4, int t6, int rows4, int rows6, int& c4, int& c6) {
+    c4 = c6 = 0;
+    if (t4 && t6) {
+        const double f4 = static_cast<double>(rows4) * kQ4KBlock, f6 = static_cast<double>(rows6) * kQ6KBlock;
+        c4 = std::max(1, std::min(t4, static_cast<int>(kSmCount * f4 / (f4 + f6))));
+        c6 = std::max(1, std::min(t6, kSmCount - c4));
+    } else if (t4) {
+        c4 = std::min(t4, kSmCount);
+    } else {
+        c6 = std::min(t6, kSmCount);
+    }
+}
+
+// k <= 4096: TR-row tiles, one warp per TR / 8 rows, ITERS = ceil(nsb / 4).
+template <int PRO, int TR>
+int dmv_launch_narrow(const DmvMat& m4, const DmvMat& m6, int nsb, const DmvPro& pro, bool pdl, cudaStream_t s) {
+    const size_t fixed = kBarBytes + static_cast<size_t>((nsb * 320 + 127) / 128) * 128;
+    const bool has4 = m4.rows > 0, has6 = m6.rows > 0;
+    const int t4 = (m4.rows + TR - 1) / TR, t6 = (m6.rows + TR - 1) / TR;
+    int c4, c6;
+    share_ctas(t4, t6, m4.rows, m6.rows, c4, c6);
+    const int st4 = has4 ? stages_for((t4 + c4 - 1) / c4, static_cast<size_t>(TR) * nsb * kQ4KBlock, fixed) : 1;
+    const int st6 = has6 ? stages_for((t6 + c6 - 1) / c6, static_cast<size_t>(TR) * nsb * kQ6KBlock, fixed) : 1;
+    if (st4 < 1 || st6 < 1) return KCB_UNSUPPORTED_OPERATION;
+    const size_t smem = fixed + std::max(has4 ? static_cast<size_t>(st4) * TR * nsb * kQ4KBlock : 0, has6 ? static_cast<size_t>(st6) * TR * nsb * kQ6KBlock : 0);
+#define KCB_DMV(ITERS_, H4, H6)                                                                                                   \
+    do {                                                                                                                          \
+        static PerDeviceFlag raised;                                                                                              \
+        return launch_dmv(dmv_kernel<ITERS_, TR, 1, PRO, H4, H6>, c4 + c6, smem, pdl, s, m4, m6, c4, nsb, pro, st4, st6, raised); \
+    } while (0)
+#define KCB_DMV_IT(H4, H6)          \
+    switch ((nsb + 3) / 4) {        \
+    case 1: KCB_DMV(1, H4, H6);     \
+    case 2: KCB_DMV(2, H4, H6);     \
+    case 3: KCB_DMV(3, H4, H6);     \
+    default: KCB_DMV(4, H4, H6);    \
+    }
+    if (has4 && has6) { KCB_DMV_IT(true, true) }
+    if (has4) { KCB_DMV_IT(true, false) }
+    KCB_DMV_IT(false, true)
+#undef KCB_DMV_IT
+#undef KCB_DMV
+}
+
+// Row-times of a launch with TR-row tiles: rounds of the busiest CTA x rows per tile.
+int row_times(int rows4, int rows6, int tr) {
+    const int t4 = (rows4 + tr - 1) / tr, t6 = (rows6 + tr - 1) / tr;
+    int c4, c6;
+    share_ctas(t4, t6, rows4, rows6, c4, c6);
+    const int r4 = t4 ? (t4 + c4 - 1) / c4 : 0, r6 = t6 ? (t6 + c6 - 1) / c6 : 0;
+    return std::max(r4, r6) * tr;
+}
+
+template <int PRO>
+int dmv_dispatch(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const DmvPro& pro, bool pdl, cudaStream_t s) {
+    const int nsb = k / 256;
+    DmvMat m4{static_cast<const uint8_t*>(w4), y4, rows4}, m6{static_cast<const uint8_t*>(w6), y6, rows6};
+    if (nsb <= 16)  // 8-row tiles where they balance the SMs better (few tiles per CTA), else two rows per warp
+        return row_times(rows4, rows6, 16) < row_times(rows4, rows6, 32) ? dmv_launch_narrow<PRO, 16>(m4, m6, nsb, pro, pdl, s)
+                                                                          : dmv_launch_narrow<PRO, 32>(m4, m6, nsb, pro, pdl, s);
+    // k up to 8192: 4-row tiles, two warps per row (16 super-blocks each at most)
+    const bool has4 = rows4 > 0;
+    if (nsb > 32 || nsb % 2 || (rows4 > 0 && rows6 > 0)) return KCB_UNSUPPORTED_OPERATION;
+    constexpr int TR = 8;
+    const size_t fixed = kBarBytes + static_cast<size_t>((nsb * 320 + 127) / 128) * 128;
+    const int rows = has4 ? rows4 : rows6;
+    const int tiles = (rows + TR - 1) / TR, c = std::min(tiles, kSmCount);
+    const size_t stage_bytes = static_cast<size_t>(TR) * nsb * (has4 ? kQ4KBlock : kQ6KBlock);
+    const int st = stages_for((tiles + c - 1) / c, stage_bytes, fixed);
+    if (st < 1) return KCB_UNSUPPORTED_OPERATION;
+    const size_t smem = fixed + static_cast<size_t>(st) * stage_bytes;
+    static PerDeviceFlag raised4, raised6;
+    if (has4) return launch_dmv(dmv_kernel<4, TR, 2, PRO, true, false>, c, smem, pdl, s, m4, m6, c, nsb, pro, st, 1, raised4);
+    return launch_dmv(dmv_kernel<4, TR, 2, PRO, false, true>, c, smem, pdl, s, m4, m6, 0, nsb, pro, 1, st, raised6);
+}
+
+}  // namespace
+
+unsigned decode_matvec_timeouts() {
+    unsigned v = 0;
+    cudaMemcpyFromSymbol(&v, g_dmv_timeouts, sizeof v);
+    return v;
+}
+
+bool decode_matvec_shape_ok(int rows4, int rows6, int k) {
+    if (k <= 0 || k % 256 || rows4 < 0 || rows6 < 0 || rows4 % 8 || rows6 % 8 || rows4 + rows6 == 0) return false;
+    // (rows % 8 and an even number of super-blocks keep every Q6_K plane of a 4- or 8-row tile 16-byte aligned)
+    const int nsb = k / 256;
+    if (nsb <= 16) return true;
+    return nsb <= 32 && nsb % 2 == 0 && !(rows4 && rows6);
+}
+
+// y4 = W4 a, y6 = W6 a (either may be absent: rows 0) with the activation vector a produced by the prologue:
+//   Q8 blocks given | x_out = x_in + t, RMSNorm(x_out) * wn | SwiGLU(g, u) | merge of attention partials.
+// pdl: launch with a programmatic dependency on the preceding kernel of the stream.
+int decode_matvec_q8(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const int* xq, const float* xd, bool pdl,
+                     cudaStream_t s) {
+    if (!decode_matvec_shape_ok(rows4, rows6, k) || !xq || !xd) return KCB_INVALID_VALUE;
+    DmvPro p;
+    p.xq = xq, p.xd = xd;
+    return dmv_dispatch<0>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
+}
+int decode_matvec_norm(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* x_in, const float* t, float* x_out,
+                       const float* wn, float eps, bool pdl, cudaStream_t s) {
+    if (!decode_matvec_shape_ok(rows4, rows6, k) || k % 128 || k > 8192 || !x_in || !x_out || !wn) return KCB_INVALID_VALUE;
+    if (misaligned(x_in, 16) || misaligned(t, 16) || misaligned(x_out, 16) || misaligned(wn, 16)) return KCB_INVALID_POINTER;
+    DmvPro p;
+    p.x_in = x_in, p.t = t, p.x_out = x_out, p.wn = wn, p.eps = eps;
+    return dmv_dispatch<1>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
+}
+int decode_matvec_swiglu(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* g, const float* u, bool pdl,
+                         cudaStream_t s) {
+    if (!decode_matvec_shape_ok(rows4, rows6, k) || !g || !u) return KCB_INVALID_VALUE;
+    DmvPro p;
+    p.g = g, p.u = u;
+    return dmv_dispatch<2>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
+}
+int decode_matvec_combine(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* part, int heads, int hd,
+                          int nsplit, bool pdl, cudaStream_t s) {
+    if (!decode_matvec_shape_ok(rows4, rows6, k) || !part || heads * hd != k || hd % 32 || nsplit < 1) return KCB_INVALID_VALUE;
+    DmvPro p;
+    p.part = part, p.heads = heads, p.hd = hd, p.nsplit = nsplit;
+    return dmv_dispatch<3>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
+}
+
+}  // namespace kcb

@@ -17,6 +17,7 @@
 #include "ops.h"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -108,10 +109,14 @@ __device__ __forceinline__ void embed_row(const uint8_t* __restrict__ w, size_t 
 // kernels/llm/rope.cu:4-17 / rope_ff.cu / rope_ggml.cu:21-44 for the rotation, set_rows_f16.cu for the cast.
 // Token blockIdx.y (decode: one) sits at position *pos_p + pos0 + blockIdx.y; its q|k heads are row blockIdx.y of
 // qk (row stride qk_stride floats), its v heads row blockIdx.y of v.
-__global__ void rope_kv_f16_kernel(float* qk, float* v, int qk_stride, int v_stride, const int* __restrict__ pos_p, int pos0,
+__global__ void rope_kv_f16_kernel(float* qk, float* v, int qk_stride, int v_stride, const int* pos_p, int pos0,
                                    unsigned short* kc, unsigned short* vc, const float* __restrict__ ff,
                                    const float* __restrict__ qn, const float* __restrict__ kn, int heads, int kv_heads, int hd,
                                    float log2_base, int neox, float eps, int max_ctx, int seq_rows = 0) {
+    // programmatic dependent launch (a no-op for ordinary launches): results of the preceding kernel from here on,
+    // and the next kernel may come up and fetch what does not depend on this one
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (w >= heads + 2 * kv_heads) return;
@@ -174,14 +179,17 @@ __global__ void rope_kv_f16_kernel(float* qk, float* v, int qk_stride, int v_str
 // *pos_p + pos0 + token (causal: it attends to the cache rows up to its own); with `direct` set (nsplit == 1)
 // the normalised output goes straight to direct[token][heads * HD].
 template <int HD, int G>
-__global__ void __launch_bounds__(128) attn_partial_kernel(const float* __restrict__ qkv, const unsigned short* __restrict__ kc,
-                                                            const unsigned short* __restrict__ vc, const int* __restrict__ pos_p,
-                                                            float* __restrict__ part, int heads, int kv_heads, int nsplit,
+// (qkv, the cache and the position are written by preceding kernels of the same step, which may still be running when
+// this one starts under a programmatic dependency: no const __restrict__, i.e. no read-only data path, on them)
+__global__ void __launch_bounds__(128) attn_partial_kernel(const float* qkv, const unsigned short* kc, const unsigned short* vc, const int* pos_p,
+                                                            float* part, int heads, int kv_heads, int nsplit,
                                                             float scale, int max_ctx, int q_stride, int pos0, float* __restrict__ direct,
                                                             int seq_rows = 0) {
     constexpr int DPL = HD / 8;  // channels per lane
     constexpr int NW = 4;
     extern __shared__ float sm[];  // [NW*4][G][HD + 2]
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // (see rope_kv_f16_kernel)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // blockIdx.x counts groups of G query heads; G == heads / kv_heads: one CTA per kv head, G == 1: one per query head
     const int h0 = blockIdx.x * G, kvh = h0 / (heads / kv_heads), sp = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, grp = lane >> 3, l8 = lane & 7;
@@ -300,8 +308,10 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float* __restri
 
 // Merges the nsplit partials of every head, normalises, and writes attn[heads*HD] together with its Q8
 // quantization (the wo matvec's input): one warp per block of 32 output channels.
-__global__ void attn_combine_q8_kernel(const float* __restrict__ part, float* __restrict__ attn, int* xq, float* xd, int heads,
+__global__ void attn_combine_q8_kernel(const float* part, float* attn, int* xq, float* xd, int heads,
                                        int hd, int nsplit) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // (see rope_kv_f16_kernel)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const int b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;  // block of 32 channels
     if (b >= heads * hd / 32) return;
@@ -708,6 +718,7 @@ public:
         nsplit = std::max(1, std::min(32, (2 * kSmCount + kv_heads - 1) / kv_heads));
         nsplit = std::min(nsplit, std::max(1, max_ctx / 64));
         if (const int e = dev(reinterpret_cast<void**>(&x), hidden * 4); e) return e;
+        if (const int e = dev(reinterpret_cast<void**>(&x2), hidden * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&t), hidden * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&qkv), (qd + 2 * kv) * 4); e) return e;
         if (const int e = dev(reinterpret_cast<void**>(&attn), qd * 4); e) return e;
@@ -1187,8 +1198,120 @@ private:
 #undef KCB_ATTN
         return launch_status();
     }
+    // The step with the small vector kernels folded into the matvecs that read them (decode_matvec.cu): per layer
+    //   [add + norm + quantize | q|k (+ v)]  rope + cache append  attention partials  merge + quantize  wo
+    //   [add + norm + quantize | gate|up]  [SwiGLU + quantize | down]
+    // chained by programmatic dependent launches, so each kernel's weights are requested while its predecessor still runs.
+    // Single GPU; matrices whose shapes the fused kernels do not take keep the step on the unfused path (record()).
+    bool fused_ok() const {
+        if (tp.world != 1 || hidden % 128 || hidden > 4096) return false;
+        if (const char* e = getenv("KCB_DECODE_FUSED"); e && atoi(e) == 0) return false;
+        const auto one_or_pair = [](const std::vector<DMat>& v) {
+            return v.size() == 1 || (v.size() == 2 && !v[0].q6 && v[1].q6 && v[0].k == v[1].k);
+        };
+        for (const DLayer& L : layers) {
+            if (!one_or_pair(L.qkv) || !one_or_pair(L.gu)) return false;
+            if (!decode_matvec_shape_ok(L.wo.q6 ? 0 : L.wo.rows, L.wo.q6 ? L.wo.rows : 0, L.wo.k)) return false;
+            if (!decode_matvec_shape_ok(L.wd.q6 ? 0 : L.wd.rows, L.wd.q6 ? L.wd.rows : 0, L.wd.k)) return false;
+        }
+        return true;
+    }
+    struct Pair {
+        const void* w4 = nullptr;
+        float* y4 = nullptr;
+        int rows4 = 0;
+        const void* w6 = nullptr;
+        float* y6 = nullptr;
+        int rows6 = 0;
+    };
+    static Pair pair_of(const std::vector<DMat>& v, float* y) {
+        Pair p;
+        for (const DMat& m : v) {
+            if (m.q6) p.w6 = m.data, p.y6 = y, p.rows6 = m.rows;
+            else p.w4 = m.data, p.y4 = y, p.rows4 = m.rows;
+            y += m.rows;
+        }
+        return p;
+    }
+    static Pair pair_of(const DMat& m, float* y) { return pair_of(std::vector<DMat>{m}, y); }
+    template <class Kern, class... Args>
+    int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, bool pdl, Args... args) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream_;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr, cfg.numAttrs = pdl ? 1 : 0;
+        return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess ? KCB_SUCCESS : KCB_LAUNCH_FAILURE;
+    }
+    template <int HD>
+    int attention_pdl(const DLayer& L, bool pdl) {
+        const int group = heads / kv_heads;
+        const dim3 grid(heads / group, nsplit, 1);
+        const size_t smem = static_cast<size_t>(16) * group * (HD + 2) * 4;
+        const float scale = 1.0f / std::sqrt(static_cast<float>(HD));
+        const float* q = qkv;
+        const unsigned short *kc = L.kc, *vc = L.vc;
+        const int* pos_p = state;
+        float* direct = nullptr;
+#define KCB_ATTN(G_) return launch_pdl(attn_partial_kernel<HD, G_>, grid, dim3(128), smem, pdl, q, kc, vc, pos_p, part, heads, kv_heads, nsplit, scale, max_ctx, 0, 0, direct, 0)
+        switch (group) {
+        case 1: KCB_ATTN(1);
+        case 2: KCB_ATTN(2);
+        case 3: KCB_ATTN(3);
+        case 4: KCB_ATTN(4);
+        default: KCB_ATTN(8);
+        }
+#undef KCB_ATTN
+    }
+    int record_fused() {
+        const int qd = heads * hd;
+        int *pos_p = state, *tok_p = state + 1, *nforced_p = state + 2, *used_p = state + 3;
+        const bool pdl = !(getenv("KCB_DECODE_PDL") && atoi(getenv("KCB_DECODE_PDL")) == 0);
+        const size_t nblk = static_cast<size_t>(embed_w.rows) * (hidden / 256);
+        embed_kernel<<<(hidden / 256 * 8 + 127) / 128, 128, 0, stream_>>>(embed_w.data, nblk, hidden / 256, embed_w.q6, vocab_total, tok_p, forced,
+                                                                          nforced_p, pos_p, used_p, x);
+        if (const int e = launch_status(); e) return e;
+        float *cur = x, *other = x2;  // the residual stream ping-pongs: every CTA of a norm prologue reads cur, one writes other
+        const float* add = nullptr;   // what the next norm prologue adds to the residual stream first
+        for (size_t l = 0; l < layers.size(); ++l) {
+            const DLayer& L = layers[l];
+            const Pair a = pair_of(L.qkv, qkv);
+            if (const int e = decode_matvec_norm(a.w4, a.y4, a.rows4, a.w6, a.y6, a.rows6, hidden, cur, add, other, L.attn_norm, eps, pdl, stream_); e) return e;
+            std::swap(cur, other);
+            float* vrows = qkv + qd + kv_heads * hd;
+            const float *ff = rope_ff, *qn = L.q_norm, *kn = L.k_norm;
+            if (const int e = launch_pdl(rope_kv_f16_kernel, dim3((heads + 2 * kv_heads + 3) / 4), dim3(128), 0, pdl, qkv, vrows, 0, 0, const_cast<const int*>(pos_p),
+                                         0, L.kc, L.vc, ff, qn, kn, heads, kv_heads, hd, log2_base, neox, eps, max_ctx, 0);
+                e)
+                return e;
+            if (const int e = hd == 128 ? attention_pdl<128>(L, pdl) : attention_pdl<64>(L, pdl); e) return e;
+            // the merge of the partials stays a launch of its own: a block of 32 channels per warp over 24 CTAs is one
+            // round trip to L2, where every CTA of the wo launch redoing all 96 blocks took six
+            if (const int e = launch_pdl(attn_combine_q8_kernel, dim3((qd / 32 + 3) / 4), dim3(128), 0, pdl, const_cast<const float*>(part), attn, xq_wo,
+                                         xd_of(xq_wo, L.wo.k), heads, hd, nsplit);
+                e)
+                return e;
+            const Pair o = pair_of(L.wo, t);
+            if (const int e = decode_matvec_q8(o.w4, o.y4, o.rows4, o.w6, o.y6, o.rows6, L.wo.k, xq_wo, xd_of(xq_wo, L.wo.k), pdl, stream_); e) return e;
+            const Pair gup = pair_of(L.gu, gu);
+            if (const int e = decode_matvec_norm(gup.w4, gup.y4, gup.rows4, gup.w6, gup.y6, gup.rows6, hidden, cur, t, other, L.ffn_norm, eps, pdl, stream_); e)
+                return e;
+            std::swap(cur, other);
+            const Pair dn = pair_of(L.wd, t);
+            if (const int e = decode_matvec_swiglu(dn.w4, dn.y4, dn.rows4, dn.w6, dn.y6, dn.rows6, L.wd.k, gu, gu + inter, pdl, stream_); e) return e;
+            add = t;
+        }
+        const Pair lm = pair_of(lm_head, logits);
+        if (const int e = decode_matvec_norm(lm.w4, lm.y4, lm.rows4, lm.w6, lm.y6, lm.rows6, hidden, cur, add, other, out_norm, eps, pdl, stream_); e) return e;
+        if (const int e = argmax_partial(logits, vocab, cand_v, cand_i, kCand, stream_); e) return e;
+        argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, tok_p, history, pos_p, max_ctx);
+        return launch_status();
+    }
+
     // Enqueues one decode step on stream_.
     int record(bool exchange) {
+        if (fused_ok()) return record_fused();
         const int qd = heads * hd;
         int *pos_p = state, *tok_p = state + 1, *nforced_p = state + 2, *used_p = state + 3;
         xchg_ = 0;
@@ -1269,7 +1392,7 @@ private:
     std::vector<DLayer> layers;
     DMat lm_head, embed_w;
     float *out_norm = nullptr, *rope_ff = nullptr;
-    float *x = nullptr, *t = nullptr, *qkv = nullptr, *attn = nullptr, *gu = nullptr, *logits = nullptr, *part = nullptr;
+    float *x = nullptr, *x2 = nullptr, *t = nullptr, *qkv = nullptr, *attn = nullptr, *gu = nullptr, *logits = nullptr, *part = nullptr;
     float* cand_v = nullptr;
     int* cand_i = nullptr;
     int *xq = nullptr, *xq_wo = nullptr, *xq_wd = nullptr, *state = nullptr, *forced = nullptr, *history = nullptr;

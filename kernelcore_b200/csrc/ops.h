@@ -49,6 +49,18 @@ int matmul_tc_pipe_k_slices(int rows, int k, int ncols);
 size_t matmul_tc_workspace_bytes(int rows, int k, int ncols);
 unsigned tc_pipe_timeouts();
 
+// decode_matvec.cu: the decode step's matvecs with their producers as prologues (see the file header)
+bool decode_matvec_shape_ok(int rows4, int rows6, int k);
+int decode_matvec_q8(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const int* xq, const float* xd, bool pdl,
+                     cudaStream_t s);
+int decode_matvec_norm(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* x_in, const float* t, float* x_out,
+                       const float* wn, float eps, bool pdl, cudaStream_t s);
+int decode_matvec_swiglu(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* g, const float* u, bool pdl,
+                         cudaStream_t s);
+int decode_matvec_combine(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* part, int heads, int hd,
+                          int nsplit, bool pdl, cudaStream_t s);
+unsigned decode_matvec_timeouts();
+
 // glue.cu
 int rms_norm(const float* x, const float* w, float* y, int n, int rows, float eps, cudaStream_t s);
 int add_rms_norm(float* x, const float* t, const float* w, float* y, int n, float eps, cudaStream_t s);
