@@ -35,10 +35,16 @@ ROWS, K = 128256, 3072
 NSB = K // 256
 NMAT = 4
 METRIC, UNIT = "q6k_lm_head_matvec_hbm_gbs", "GB/s"
-# DRAM bytes per full-size launch of the matvec kernel (dram__bytes_read.sum + dram__bytes_write.sum):
-# the ncu capture summarised in profiles/matvec_q6k_q8_lm_head.md measured 161.65 MB + 5.0 MB on a 64128-row
-# case; traffic grows linearly with rows, so a 128256-row launch moves twice that.
+# DRAM bytes per full-size launch of the matvec kernel (dram__bytes_read.sum + dram__bytes_write.sum), from one
+# `ncu --set full` capture of this kernel on a 64128-row matrix (half the rows, so that the capture stays small):
+# 161,679,872 B read + 4,038,528 B written.  Traffic grows linearly with the rows, so a 128256-row launch moves twice that.
 NCU_TRAFFIC_BYTES_PER_LAUNCH_FULL = 2 * (161_679_872 + 4_038_528)
+WORKLOAD = f"Q6_K lm_head matvec {ROWS}x{K} (benchmark spec configs[1]): y = W x, fp32 x quantized to Q8 blocks of 32, fp32 logits"
+
+
+def bench_config():
+    """The same `config` on both arms: what is computed, not how."""
+    return {"workload": WORKLOAD, "rows": ROWS, "k": K, "l2": f"inputs larger than L2: {ROWS * NSB * 210 / 1e6:.0f} MB of weights per matvec"}
 
 
 def algorithmic_bytes(rows: int) -> int:
@@ -148,7 +154,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 dot, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"Q6_K lm_head matvec {ROWS}x{K}, reference CPU kernels on host cores", "rows": ROWS, "k": K},
+        "config": bench_config(), "impl_detail": "the reference's AVX2 kernels (generated by its own tool) on all host threads" if kind == "reference"
+        else "scalar C restatement of the reference's kernels",
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -336,6 +343,15 @@ def run_ours(args):
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         gather_ok = bool(torch.equal(lo, hi)) and lib.raw.kcb_peer_timeouts() == 0
+    dec_tp = None
+    if world > 1 and not args.skip_cpu_baseline:
+        # the other half of the metric at N > 1: tensor-parallel decode of the Llama-3.2-3B-shape model on all ranks
+        del mats
+        torch.cuda.empty_cache()
+        try:
+            dec_tp = decode_bench(640, 512, 128, measured_peak()[0])[0]
+        except Exception as exc:   # the lm_head line stands on its own
+            dec_tp = {"error": repr(exc)[:300]}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -347,13 +363,14 @@ def run_ours(args):
     value = alg_total * steps_timed / (total_ms * 1e-3) / 1e9
     achieved = alg_launch / (kern_ms * 1e-3) / 1e9
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps_timed, "warmup": max(args.warmup, 3) + 3 * NMAT,
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps_timed, "warmup": args.warmup,
+        "warmup_extra": max(0, 3 - args.warmup) + 3 * NMAT,  # at least three plain steps, then three replays of the step graph
         "ms_per_step": total_ms / steps_timed, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 dot, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"Q6_K lm_head matvec {ROWS}x{K} (benchmark spec configs[1]): Backend::matvec = Q8 quantize + matvec_q6k_q8 in one launch"
-                               + (f", rows sharded over {world} GPUs + all-gather of the logits" if world > 1 else ""),
-                   "rows": ROWS, "k": K, "rows_per_gpu": rows, "all_gather": gather_mode, "gather_identical_on_all_ranks": gather_ok,
-                   "l2": f"inputs larger than L2: {NMAT} rotating {rows * NSB * 210 / 1e6:.0f} MB weight matrices"},
+        "config": bench_config(),
+        "impl_detail": "Backend::matvec = Q8 quantize + matvec_q6k_q8 in one launch" + (f", rows sharded over {world} GPUs + all-gather of the logits" if world > 1 else ""),
+        "sharding": {"rows_per_gpu": rows, "all_gather": gather_mode, "gather_identical_on_all_ranks": gather_ok,
+                     "rotation": f"{NMAT} rotating {rows * NSB * 210 / 1e6:.0f} MB weight matrices per GPU"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH_FULL * rows // 128256, "kernel": "matvec_kq_q8_tma_kernel<Q6_K>",
                      "algorithmic_bytes_per_launch": alg_launch, "kernel_us": kern_ms * 1e3,
@@ -386,7 +403,9 @@ def run_ours(args):
                          "decode_llama32_3b": decode_bench(640, 512, 128, peak)[0]}
         from kernelcore_b200 import tiny_model as tm
         shape = tm.llama32_3b(16)
-        line["extra"]["decode_llama32_3b"]["cpu_baseline"] = cpu_decode_baseline(shape, tm.build(shape, seed=0))
+        attach_decode_cpu(line["extra"]["decode_llama32_3b"], shape, tm.build(shape, seed=0))
+    if dec_tp is not None:
+        line["extra"] = {"decode_llama32_3b": dec_tp}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -511,7 +530,9 @@ def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b", lean=False)
         import torch.distributed._symmetric_memory as symm_mem
         torch.cuda.set_device(local)
         dev = torch.device("cuda", local)
-        dist.init_process_group("nccl", device_id=dev)
+        own_group = not dist.is_initialized()
+        if own_group:
+            dist.init_process_group("nccl", device_id=dev)
         area = symm_mem.empty(decoder.FastDecoder.tp_shared_bytes(shape), dtype=torch.uint8, device=dev)
         area.zero_()
         handle = symm_mem.rendezvous(area, dist.group.WORLD.group_name)
@@ -570,10 +591,17 @@ def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b", lean=False)
            "picks_digest": int(np.asarray(hist, np.int64).sum() % 1000003),
            "sharding": "none" if world == 1 else f"tp{world}: heads / FFN rows / vocabulary rows; K-split wo, wd; in-kernel sum over peer loads",
            "exchange_timeouts": decoder.FastDecoder.tp_timeouts()}
+    if world == 1 and not lean and not shape.qk_norm:
+        # two tokens from position 0 through the graph, logits of the second kept for the check against the reference's
+        # decode loop on the host (cpu_decode_baseline runs the same two tokens)
+        d.set_prompt(prompt[:2])
+        d.run(2)
+        out["_logits_pos1"] = d.read(0, want_logits=True)[0].copy()
     d.close()
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+        if own_group:
+            dist.destroy_process_group()
     return out, rank
 
 
@@ -611,7 +639,20 @@ def batch_decode_bench(model_name, n_seq, n_prompt, n_gen):
     return out
 
 
-def cpu_decode_baseline(shape, model, n_tokens=2):
+def attach_decode_cpu(out, shape, model):
+    """Adds the host baselines of the decode entry and the relative difference of the GPU logits from the reference's."""
+    gpu = out.pop("_logits_pos1", None)
+    toks = [int(t) for t in np.random.default_rng(1).integers(0, shape.vocab, out["prompt_tokens"])[:2]]
+    out["cpu_baseline"] = cpu_decode_baseline(shape, model, toks)
+    if gpu is not None and out["cpu_baseline"] is not None:
+        ref = out["cpu_baseline"].pop("_logits")
+        out["check_vs_cpu_rel"] = float(np.abs(gpu - ref).max() / np.abs(ref).max())
+    elif out["cpu_baseline"] is not None:
+        out["cpu_baseline"].pop("_logits", None)
+    out["cpu_baseline_all_cores"] = cpu_decode_matvecs_all_cores(shape, model)
+
+
+def cpu_decode_baseline(shape, model, toks):
     """The reference's own decode loop (llm::decodeToken on its single-thread C++ backend, compiled in place from the
     reference sources) on the same model, timed on one host core for a bounded sample of tokens."""
     import ctypes as C
@@ -624,7 +665,7 @@ def cpu_decode_baseline(shape, model, n_tokens=2):
     h = oracle.ref.lib.kcref_model_open(C.byref(bm.c))
     t_open = time.perf_counter() - t0
     logits = np.zeros(shape.vocab, np.float32)
-    toks = [int(t) for t in np.random.default_rng(1).integers(0, shape.vocab, n_tokens)]
+    n_tokens = len(toks)
     t0 = time.perf_counter()
     for pos, tok in enumerate(toks):
         if oracle.ref.lib.kcref_model_decode(h, bm.embed(tok), pos, logits) != 0:
@@ -632,9 +673,55 @@ def cpu_decode_baseline(shape, model, n_tokens=2):
             return None
     dt = time.perf_counter() - t0
     oracle.ref.lib.kcref_model_close(h)
-    return {"value": n_tokens / dt, "unit": "tokens/s", "cores": 1, "kind": "reference",
+    return {"value": n_tokens / dt, "unit": "tokens/s", "cores": 1, "kind": "reference", "_logits": logits,
             "sample": f"{n_tokens} tokens at positions 0..{n_tokens - 1}: llm::decodeToken on the reference's C++ backend "
                       f"(weights repacked to its stream in {t_open:.1f} s, not timed)"}
+
+
+def cpu_decode_matvecs_all_cores(shape, model, reps=3):
+    """Every matrix-vector product of one decode token (7 per layer and the lm_head) with its Q8 quantize, through the
+    reference's generated AVX2 kernels on all host threads, on the model's own weights.  The other operators of the token
+    (norms, RoPE, attention, SwiGLU: a few percent of the scalar decode time) are not run, so tokens/s from this time
+    is an upper bound on what the reference's CPU path reaches on these cores."""
+    import ctypes as C
+
+    import oracle
+    from kernelcore_b200 import tiny_model as tm
+    simd_path = os.path.join(ROOT, "oracle", "_ref", "libkcref_simd.so")
+    if oracle.ref is None or not os.path.exists(simd_path):
+        return None
+    L = C.CDLL(simd_path)
+    i32p, f32p = np.ctypeslib.ndpointer(np.int32), np.ctypeslib.ndpointer(np.float32)
+    L.kcref_simd_matvec.argtypes = [C.c_int, i32p, i32p, f32p, f32p, C.c_int, C.c_int, C.c_int]
+    L.kcref_simd_quantize_q8x4.argtypes = [f32p, i32p, f32p, C.c_int]
+    L.kcref_simd_threads.argtypes = [C.c_int]
+    cores = L.kcref_simd_threads(0)
+
+    def stream(blocks, rows, k, q6):
+        qw = np.zeros(oracle.ref.lib.kcref_stream_ints(rows, k, int(q6)), np.int32)
+        oracle.ref.lib.kcref_repack(np.ascontiguousarray(blocks).ravel(), rows, k, int(q6), qw)
+        return qw, rows, k, int(q6), np.zeros(rows, np.float32)
+
+    shapes = tm.mat_shapes(shape)
+    mats = [stream(Lw[n], *shapes[n]) for Lw in model["layers"] for n in tm.MATS]
+    mats.append(stream(model["lm_head"], shape.vocab, shape.hidden, True))
+    xs = {k: np.random.default_rng(k).standard_normal(k).astype(np.float32) for k in {m[2] for m in mats}}
+    xq = {k: np.zeros(k // 4, np.int32) for k in xs}
+    xd = {k: np.zeros(k // 16, np.float32) for k in xs}
+
+    def token():
+        for qw, rows, k, q6, y in mats:
+            L.kcref_simd_quantize_q8x4(xs[k], xq[k], xd[k], k // 32)
+            L.kcref_simd_matvec(q6, qw, xq[k], xd[k], y, rows, k, 16)
+    token()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        token()
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": 1.0 / dt, "unit": "tokens/s", "cores": cores, "kind": "reference",
+            "sample": f"{reps} tokens: the {len(mats)} matvecs of a token (quantize_q8x4 + matvec_q4k_q8 / matvec_q6k_q8, the reference's "
+                      "generated AVX2 kernels, all host threads) on the model's weights; norms, RoPE, attention and SwiGLU not run, "
+                      "so this is an upper bound on the reference's CPU decode rate"}
 
 
 def run_decode(args):
@@ -651,7 +738,8 @@ def run_decode(args):
         from kernelcore_b200 import tiny_model as tm
         shape = (tm.qwen3_8b if args.model == "qwen3_8b" else tm.llama32_3b)(16)
         if not shape.qk_norm:   # the reference's decode loop has no per-head q/k norm (its ggml path does that in llama.cpp)
-            out["cpu_baseline"] = cpu_decode_baseline(shape, tm.build(shape, seed=0))
+            attach_decode_cpu(out, shape, tm.build(shape, seed=0))
+    out.pop("_logits_pos1", None)
     if rank == 0:
         cfg = "configs[4]" if args.model == "qwen3_8b" else "configs[3]"
         print(json.dumps({"metric": f"{args.model}_decode_tok_s", "value": out["decode_tok_s"], "unit": "tokens/s", "n_gpus": out["n_gpus"],

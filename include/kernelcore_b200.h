@@ -349,6 +349,15 @@ int kcb_decoder_sync(void* decoder);
 int kcb_decoder_read(void* decoder, float* logits_host, int* history_host, int n_history, int* pos_host);
 int kcb_decoder_info(void* decoder, int* launches_per_token, long long* weight_bytes);
 void* kcb_decoder_stream(void* decoder);   /* the cudaStream_t the decoder runs on */
+/* Test instrumentation (no counterpart in the reference; single-GPU decoders): after kcb_decoder_enable_trace every step
+ * also keeps the int8 words of each activation vector it quantizes and the residual stream (hidden floats, as bit
+ * patterns) after each of a layer's two additions, in the order the step runs -- layer 0's q|k|v input words, then per
+ * layer the wo input words, the residual, the gate|up and down input words, the residual, the next q|k|v (after the last
+ * layer: lm_head) input words; *words_per_step int32 words -- and kcb_decoder_read_trace copies the last step's to the
+ * host (it waits for the stream).  The parity tests run the CPU restatement stage by stage on these inputs and count the
+ * int8 values that rounded the other way (a value on a rounding boundary may, when a sum was taken in another order). */
+int kcb_decoder_enable_trace(void* decoder, size_t* words_per_step);
+int kcb_decoder_read_trace(void* decoder, int* words_host, size_t n_words);
 int kcb_decoder_destroy(void* decoder);
 const char* kcb_decoder_last_error(void);
 

@@ -335,6 +335,8 @@ struct DmvPro {
     // PRO 2: SwiGLU of g, u
     const float* g = nullptr;
     const float* u = nullptr;
+    // PRO != 0: where one CTA leaves the int8 words the prologue produced (test instrumentation; null = nowhere)
+    int* trace = nullptr;
     // PRO 3: merge of attention partials
     const float* part = nullptr;
     int heads = 0, hd = 0, nsplit = 0;
@@ -397,6 +399,8 @@ __global__ void __launch_bounds__(kThreads, 1) dmv_kernel(const DmvMat m4, const
         pro_combine(pro.part, sxq, sxd, pro.heads, pro.hd, pro.nsplit);
     }
     __syncthreads();
+    if (PRO != 0 && pro.trace && blockIdx.x == 0)
+        for (int i = threadIdx.x; i < nsb * 64; i += kThreads) pro.trace[i] = sxq[i];
     // this kernel's inputs are consumed: the next kernel may come up and request its weights
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -530,18 +534,18 @@ int decode_matvec_q8(const void* w4, float* y4, int rows4, const void* w6, float
     return dmv_dispatch<0>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
 }
 int decode_matvec_norm(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* x_in, const float* t, float* x_out,
-                       const float* wn, float eps, bool pdl, cudaStream_t s) {
+                       const float* wn, float eps, bool pdl, cudaStream_t s, int* trace) {
     if (!decode_matvec_shape_ok(rows4, rows6, k) || k % 128 || k > 8192 || !x_in || !x_out || !wn) return KCB_INVALID_VALUE;
     if (misaligned(x_in, 16) || misaligned(t, 16) || misaligned(x_out, 16) || misaligned(wn, 16)) return KCB_INVALID_POINTER;
     DmvPro p;
-    p.x_in = x_in, p.t = t, p.x_out = x_out, p.wn = wn, p.eps = eps;
+    p.x_in = x_in, p.t = t, p.x_out = x_out, p.wn = wn, p.eps = eps, p.trace = trace;
     return dmv_dispatch<1>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
 }
 int decode_matvec_swiglu(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* g, const float* u, bool pdl,
-                         cudaStream_t s) {
+                         cudaStream_t s, int* trace) {
     if (!decode_matvec_shape_ok(rows4, rows6, k) || !g || !u) return KCB_INVALID_VALUE;
     DmvPro p;
-    p.g = g, p.u = u;
+    p.g = g, p.u = u, p.trace = trace;
     return dmv_dispatch<2>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
 }
 int decode_matvec_combine(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* part, int heads, int hd,

@@ -762,6 +762,12 @@ public:
         if (const int e = record(false); e) return e;
         CU(cudaStreamSynchronize(stream_));
         CU(cudaMemsetAsync(state, 0, 64, stream_));
+        return capture();
+    }
+    // Captures one decode step into the graph that run() replays.
+    int capture() {
+        if (exec_) cudaGraphExecDestroy(exec_), exec_ = nullptr;
+        if (graph_) cudaGraphDestroy(graph_), graph_ = nullptr;
         CU(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeRelaxed));
         const int e = record(true);
         cudaGraph_t g = nullptr;
@@ -783,6 +789,30 @@ public:
         return KCB_SUCCESS;
     }
 
+    // Test instrumentation: from now on every step also leaves, in a device buffer, the int8 words of each activation
+    // vector it quantizes and the residual stream (hidden floats) after each of a layer's two additions, in the order
+    // the step runs: layer 0's q|k|v input words, then per layer the wo input words, the residual, the gate|up and down
+    // input words, the residual, the next q|k|v (after the last layer: lm_head) input words.  A test can then check
+    // every stage against the CPU restatement on the same inputs and count the int8 values that rounded the other way.
+    // Re-captures the step graph.
+    int enable_trace() {
+        if (tp.world != 1) return KCB_UNSUPPORTED_OPERATION;
+        if (trace_) return KCB_SUCCESS;
+        trace_words_ = 0;
+        for (const DLayer& L : layers) trace_words_ += (2 * hidden + L.wo.k + L.wd.k) / 4 + 2 * hidden;
+        trace_words_ += hidden / 4;
+        if (const int e = dev(reinterpret_cast<void**>(&trace_), trace_words_ * 4); e) return e;
+        CU(cudaMemsetAsync(trace_, 0, trace_words_ * 4, stream_));
+        CU(cudaStreamSynchronize(stream_));
+        return capture();
+    }
+    int read_trace(int* host, size_t n_words) {
+        if (!trace_ || !host || n_words > trace_words_) return KCB_INVALID_VALUE;
+        CU(cudaStreamSynchronize(stream_));
+        CU(cudaMemcpy(host, trace_, n_words * 4, cudaMemcpyDeviceToHost));
+        return KCB_SUCCESS;
+    }
+    size_t trace_words() const { return trace_words_; }
     int set_prompt(const int* tokens, int n, int start_pos) {
         if (n < 0 || start_pos < 0 || start_pos + n > max_ctx || (n && !tokens)) return KCB_INVALID_VALUE;
         std::vector<int> f(static_cast<size_t>(max_ctx), 0);
@@ -1203,6 +1233,22 @@ private:
     //   [add + norm + quantize | gate|up]  [SwiGLU + quantize | down]
     // chained by programmatic dependent launches, so each kernel's weights are requested while its predecessor still runs.
     // Single GPU; matrices whose shapes the fused kernels do not take keep the step on the unfused path (record()).
+    // where the next traced vector of k int8 values goes (nullptr when tracing is off)
+    int* trace_slot(int k) {
+        if (!trace_) return nullptr;
+        int* p = trace_ + trace_off_;
+        trace_off_ += static_cast<size_t>(k / 4);
+        return p;
+    }
+    int trace_copy(const int* words, int k) {
+        if (int* p = trace_slot(k)) CU(cudaMemcpyAsync(p, words, static_cast<size_t>(k / 4) * 4, cudaMemcpyDeviceToDevice, stream_));
+        return KCB_SUCCESS;
+    }
+    // the residual stream (hidden floats) into the trace
+    int trace_residual(const float* xs) {
+        if (int* p = trace_slot(4 * hidden)) CU(cudaMemcpyAsync(p, xs, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
+        return KCB_SUCCESS;
+    }
     bool fused_ok() const {
         if (tp.world != 1 || hidden % 128 || hidden > 4096) return false;
         if (const char* e = getenv("KCB_DECODE_FUSED"); e && atoi(e) == 0) return false;
@@ -1268,6 +1314,7 @@ private:
         const int qd = heads * hd;
         int *pos_p = state, *tok_p = state + 1, *nforced_p = state + 2, *used_p = state + 3;
         const bool pdl = !(getenv("KCB_DECODE_PDL") && atoi(getenv("KCB_DECODE_PDL")) == 0);
+        trace_off_ = 0;
         const size_t nblk = static_cast<size_t>(embed_w.rows) * (hidden / 256);
         embed_kernel<<<(hidden / 256 * 8 + 127) / 128, 128, 0, stream_>>>(embed_w.data, nblk, hidden / 256, embed_w.q6, vocab_total, tok_p, forced,
                                                                           nforced_p, pos_p, used_p, x);
@@ -1277,8 +1324,10 @@ private:
         for (size_t l = 0; l < layers.size(); ++l) {
             const DLayer& L = layers[l];
             const Pair a = pair_of(L.qkv, qkv);
-            if (const int e = decode_matvec_norm(a.w4, a.y4, a.rows4, a.w6, a.y6, a.rows6, hidden, cur, add, other, L.attn_norm, eps, pdl, stream_); e) return e;
+            int* xs = add ? trace_slot(4 * hidden) : nullptr;
+            if (const int e = decode_matvec_norm(a.w4, a.y4, a.rows4, a.w6, a.y6, a.rows6, hidden, cur, add, other, L.attn_norm, eps, pdl, stream_, trace_slot(hidden)); e) return e;
             std::swap(cur, other);
+            if (xs) CU(cudaMemcpyAsync(xs, cur, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
             float* vrows = qkv + qd + kv_heads * hd;
             const float *ff = rope_ff, *qn = L.q_norm, *kn = L.k_norm;
             if (const int e = launch_pdl(rope_kv_f16_kernel, dim3((heads + 2 * kv_heads + 3) / 4), dim3(128), 0, pdl, qkv, vrows, 0, 0, const_cast<const int*>(pos_p),
@@ -1292,18 +1341,23 @@ private:
                                          xd_of(xq_wo, L.wo.k), heads, hd, nsplit);
                 e)
                 return e;
+            if (const int e = trace_copy(xq_wo, L.wo.k); e) return e;
             const Pair o = pair_of(L.wo, t);
             if (const int e = decode_matvec_q8(o.w4, o.y4, o.rows4, o.w6, o.y6, o.rows6, L.wo.k, xq_wo, xd_of(xq_wo, L.wo.k), pdl, stream_); e) return e;
             const Pair gup = pair_of(L.gu, gu);
-            if (const int e = decode_matvec_norm(gup.w4, gup.y4, gup.rows4, gup.w6, gup.y6, gup.rows6, hidden, cur, t, other, L.ffn_norm, eps, pdl, stream_); e)
+            xs = trace_slot(4 * hidden);
+            if (const int e = decode_matvec_norm(gup.w4, gup.y4, gup.rows4, gup.w6, gup.y6, gup.rows6, hidden, cur, t, other, L.ffn_norm, eps, pdl, stream_, trace_slot(hidden)); e)
                 return e;
             std::swap(cur, other);
+            if (xs) CU(cudaMemcpyAsync(xs, cur, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
             const Pair dn = pair_of(L.wd, t);
-            if (const int e = decode_matvec_swiglu(dn.w4, dn.y4, dn.rows4, dn.w6, dn.y6, dn.rows6, L.wd.k, gu, gu + inter, pdl, stream_); e) return e;
+            if (const int e = decode_matvec_swiglu(dn.w4, dn.y4, dn.rows4, dn.w6, dn.y6, dn.rows6, L.wd.k, gu, gu + inter, pdl, stream_, trace_slot(L.wd.k)); e) return e;
             add = t;
         }
         const Pair lm = pair_of(lm_head, logits);
-        if (const int e = decode_matvec_norm(lm.w4, lm.y4, lm.rows4, lm.w6, lm.y6, lm.rows6, hidden, cur, add, other, out_norm, eps, pdl, stream_); e) return e;
+        int* xs = add ? trace_slot(4 * hidden) : nullptr;
+        if (const int e = decode_matvec_norm(lm.w4, lm.y4, lm.rows4, lm.w6, lm.y6, lm.rows6, hidden, cur, add, other, out_norm, eps, pdl, stream_, trace_slot(hidden)); e) return e;
+        if (xs) CU(cudaMemcpyAsync(xs, other, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
         if (const int e = argmax_partial(logits, vocab, cand_v, cand_i, kCand, stream_); e) return e;
         argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, tok_p, history, pos_p, max_ctx);
         return launch_status();
@@ -1315,11 +1369,13 @@ private:
         const int qd = heads * hd;
         int *pos_p = state, *tok_p = state + 1, *nforced_p = state + 2, *used_p = state + 3;
         xchg_ = 0;
+        trace_off_ = 0;
         const size_t nblk = static_cast<size_t>(embed_w.rows) * (hidden / 256);
         embed_kernel<<<(hidden / 256 * 8 + 127) / 128, 128, 0, stream_>>>(embed_w.data, nblk, hidden / 256, embed_w.q6, vocab_total, tok_p, forced,
                                                                           nforced_p, pos_p, used_p, x);
         if (const int e = launch_status(); e) return e;
         if (const int e = add_norm_q8_fast(x, nullptr, layers[0].attn_norm, xq, xd_of(xq, hidden), hidden, eps, stream_); e) return e;
+        if (const int e = trace_copy(xq, hidden); e) return e;
         for (size_t l = 0; l < layers.size(); ++l) {
             const DLayer& L = layers[l];
             float* y = qkv;
@@ -1341,9 +1397,12 @@ private:
             attn_combine_q8_kernel<<<(qd / 32 + 3) / 4, 128, 0, stream_>>>(part, attn, xq_wo + wo_win.first_block * 8,
                                                                             xd_of(xq_wo, L.wo.k) + wo_win.first_block * 2, heads, hd, nsplit);
             if (const int e = launch_status(); e) return e;
+            if (const int e = trace_copy(xq_wo, L.wo.k); e) return e;
             float* po = partial_out();
             if (const int e = mv(L.wo, xq_wo, po); e) return e;
             if (const int e = add_norm(po, L.ffn_norm, exchange); e) return e;
+            if (const int e = trace_residual(x); e) return e;
+            if (const int e = trace_copy(xq, hidden); e) return e;
             y = gu;
             for (const DMat& m : L.gu) {
                 if (const int e = mv(m, xq, y); e) return e;
@@ -1353,10 +1412,13 @@ private:
                                           inter, 1, stream_);
                 e)
                 return e;
+            if (const int e = trace_copy(xq_wd, L.wd.k); e) return e;
             po = partial_out();
             if (const int e = mv(L.wd, xq_wd, po); e) return e;
             const float* next = l + 1 < layers.size() ? layers[l + 1].attn_norm : out_norm;
             if (const int e = add_norm(po, next, exchange); e) return e;
+            if (const int e = trace_residual(x); e) return e;
+            if (const int e = trace_copy(xq, hidden); e) return e;
         }
         float* my_logits = logits + static_cast<size_t>(tp.rank) * vocab;
         if (const int e = mv(lm_head, xq, my_logits); e) return e;
@@ -1397,6 +1459,8 @@ private:
     int* cand_i = nullptr;
     int *xq = nullptr, *xq_wo = nullptr, *xq_wd = nullptr, *state = nullptr, *forced = nullptr, *history = nullptr;
     cudaStream_t stream_ = nullptr;
+    int* trace_ = nullptr;
+    size_t trace_words_ = 0, trace_off_ = 0;
     cudaGraph_t graph_ = nullptr;
     cudaGraphExec_t exec_ = nullptr;
     std::vector<void*> owned_;
@@ -1476,6 +1540,17 @@ int kcb_decoder_info(void* h, int* launches_per_token, long long* weight_bytes) 
     if (launches_per_token) *launches_per_token = static_cast<Decoder*>(h)->launches_per_token;
     if (weight_bytes) *weight_bytes = static_cast<Decoder*>(h)->weight_bytes;
     return kcb::KCB_SUCCESS;
+}
+int kcb_decoder_enable_trace(void* h, size_t* words_per_step) {
+    if (!h) return kcb::KCB_INVALID_VALUE;
+    auto* d = static_cast<Decoder*>(h);
+    const int e = d->enable_trace();
+    if (e != kcb::KCB_SUCCESS) kcb::tl_err = d->err_;
+    else if (words_per_step) *words_per_step = d->trace_words();
+    return e;
+}
+int kcb_decoder_read_trace(void* h, int* words_host, size_t n_words) {
+    return h ? static_cast<Decoder*>(h)->read_trace(words_host, n_words) : kcb::KCB_INVALID_VALUE;
 }
 void* kcb_decoder_stream(void* h) { return h ? static_cast<Decoder*>(h)->stream() : nullptr; }
 int kcb_decoder_destroy(void* h) {

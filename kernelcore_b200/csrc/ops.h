@@ -49,14 +49,15 @@ int matmul_tc_pipe_k_slices(int rows, int k, int ncols);
 size_t matmul_tc_workspace_bytes(int rows, int k, int ncols);
 unsigned tc_pipe_timeouts();
 
-// decode_matvec.cu: the decode step's matvecs with their producers as prologues (see the file header)
+// decode_matvec.cu: the decode step's matvecs with their producers as prologues (see the file header).
+// trace != nullptr: the k / 4 int8 words the prologue produced are also written there (by one CTA; test instrumentation).
 bool decode_matvec_shape_ok(int rows4, int rows6, int k);
 int decode_matvec_q8(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const int* xq, const float* xd, bool pdl,
                      cudaStream_t s);
 int decode_matvec_norm(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* x_in, const float* t, float* x_out,
-                       const float* wn, float eps, bool pdl, cudaStream_t s);
+                       const float* wn, float eps, bool pdl, cudaStream_t s, int* trace = nullptr);
 int decode_matvec_swiglu(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* g, const float* u, bool pdl,
-                         cudaStream_t s);
+                         cudaStream_t s, int* trace = nullptr);
 int decode_matvec_combine(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* part, int heads, int hd,
                           int nsplit, bool pdl, cudaStream_t s);
 unsigned decode_matvec_timeouts();

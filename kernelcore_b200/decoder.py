@@ -194,6 +194,20 @@ class FastDecoder:
                                            hist.ctypes.data_as(C.c_void_p), int(n_history), C.byref(pos)), "kcb_decoder_read")
         return logits, hist[:n_history], pos.value
 
+    def enable_trace(self) -> int:
+        """Test instrumentation: every later step keeps the int8 words of each activation vector it quantizes and the
+        residual stream after each addition (layout: include/kernelcore_b200.h, kcb_decoder_enable_trace).  Returns
+        the int32 words per step."""
+        n = C.c_size_t()
+        lib.check(lib.raw.kcb_decoder_enable_trace(self.handle, C.byref(n)), "kcb_decoder_enable_trace")
+        self._trace_words = n.value
+        return n.value
+
+    def read_trace(self) -> np.ndarray:
+        out = np.zeros(self._trace_words, np.int32)
+        lib.check(lib.raw.kcb_decoder_read_trace(self.handle, out.ctypes.data_as(C.c_void_p), C.c_size_t(out.size)), "kcb_decoder_read_trace")
+        return out
+
     @property
     def cuda_stream(self) -> int:
         lib.raw.kcb_decoder_stream.restype = C.c_void_p

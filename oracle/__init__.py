@@ -131,6 +131,13 @@ def _load_port():
     lib.lib.kqo_decode_token_ex.argtypes = [C.POINTER(Model), _f32p, i, _f32p, _f32p, _i32p, i]
     lib.lib.kqo_decode_scratch_floats.restype = C.c_long
     lib.lib.kqo_decode_scratch_floats.argtypes = [C.POINTER(Model)]
+    lib.lib.kqo_decode_set_trace.restype = None
+    lib.lib.kqo_decode_set_trace.argtypes = [C.c_void_p, C.c_long]
+    lib.lib.kqo_decode_trace_words.restype = C.c_long
+    lib.lib.kqo_decode_set_forced.restype = None
+    lib.lib.kqo_decode_set_forced.argtypes = [C.c_void_p, C.c_long]
+    lib.lib.kqo_decode_forced_stats.restype = None
+    lib.lib.kqo_decode_forced_stats.argtypes = [C.POINTER(C.c_long), C.POINTER(C.c_long), C.POINTER(C.c_int), C.POINTER(C.c_float)]
     lib.lib.kqo_decode_scratch_ints.restype = C.c_long
     lib.lib.kqo_decode_scratch_ints.argtypes = [C.POINTER(Model)]
     return lib
@@ -262,12 +269,51 @@ class BoundModel:
         port.dequant_row_q6k(np.ascontiguousarray(self.model["lm_head"][token]), self.shape.hidden, out)
         return out
 
-    def decode_port(self, x_in, pos, kv_f16=False):
+    def trace_words(self) -> int:
+        """int32 words one decode step traces: layer 0's q|k|v input words, then per layer the wo input words,
+        the residual stream (hidden floats), the gate|up and down input words, the residual stream again and the
+        next q|k|v (after the last layer: lm_head) input words; a vector of k int8 values is k / 4 words."""
+        s = self.shape
+        return s.layers * ((2 * s.hidden + s.qd + s.inter) // 4 + 2 * s.hidden) + s.hidden // 4
+
+    def trace_layout(self):
+        """[(kind, first word, words)] of one step's trace, kind "q8" or "x"."""
+        s, out, at = self.shape, [], 0
+        def add(kind, n):
+            nonlocal at
+            out.append((kind, at, n))
+            at += n
+        add("q8", s.hidden // 4)
+        for _ in range(s.layers):
+            add("q8", s.qd // 4), add("x", s.hidden), add("q8", s.hidden // 4), add("q8", s.inter // 4), add("x", s.hidden), add("q8", s.hidden // 4)
+        return out
+
+    def decode_port(self, x_in, pos, kv_f16=False, trace=None, forced=None):
         """One decode step on the CPU oracle.  kv_f16: K/V rounded to fp16 on entry to the cache; the
-        model shape's neox / qk_norm select the Qwen3-style variants."""
+        model shape's neox / qk_norm select the Qwen3-style variants.  trace: an int32 array of
+        trace_words() that receives the int8 words of every activation vector the step quantizes.
+        forced: the words another implementation traced for this step; each vector the step quantizes is
+        compared with them and then replaced by them, and so is the residual stream after each addition
+        (self.forced_stats = differing int8 values, vectors holding one, largest int8 step, largest residual
+        difference relative to its largest magnitude), so every stage runs on the inputs the other
+        implementation had."""
         logits = np.zeros(self.shape.vocab, np.float32)
+        if forced is not None:
+            assert forced.dtype == np.int32 and forced.size == self.trace_words() and forced.flags.c_contiguous
+            port.lib.kqo_decode_set_forced(forced.ctypes.data, forced.size)
+        if trace is not None:
+            assert trace.dtype == np.int32 and trace.size >= self.trace_words() and trace.flags.c_contiguous
+            port.lib.kqo_decode_set_trace(trace.ctypes.data, trace.size)
         sf = np.zeros(port.lib.kqo_decode_scratch_floats(C.byref(self.c)), np.float32)
         sq = np.zeros(port.lib.kqo_decode_scratch_ints(C.byref(self.c)), np.int32)
         flags = (1 if kv_f16 else 0) | (2 if self.shape.neox else 0) | (4 if self.shape.qk_norm else 0)
         port.lib.kqo_decode_token_ex(C.byref(self.c), np.ascontiguousarray(x_in, np.float32), pos, logits, sf, sq, flags)
+        if trace is not None:
+            assert port.lib.kqo_decode_trace_words() == self.trace_words()
+            port.lib.kqo_decode_set_trace(None, 0)
+        if forced is not None:
+            a, b, c, x = C.c_long(), C.c_long(), C.c_int(), C.c_float()
+            port.lib.kqo_decode_forced_stats(C.byref(a), C.byref(b), C.byref(c), C.byref(x))
+            self.forced_stats = (a.value, b.value, c.value, x.value)
+            port.lib.kqo_decode_set_forced(None, 0)
         return logits

@@ -786,6 +786,58 @@ long kqo_decode_scratch_ints(const kqo_model* m) {
     return 11L * (imax(imax(m->hidden, m->inter), m->heads * m->head_dim) / 32);
 }
 
+/* Test instrumentation for the decode loop below (no counterpart in the reference).  Every time the loop quantizes an
+ * activation vector -- per layer the inputs of q|k|v, wo, gate|up and down, then the lm_head's input -- its int8 words
+ * (k / 4 of them) are (1) appended to the trace buffer, when one is set, and (2) when forced words are set, compared
+ * with the forced words at the same offset (count of differing int8 values, of vectors holding one, largest step) and
+ * then REPLACED by them.  The residual stream is traced the same way after each of the two additions of a layer (hidden
+ * floats, as their bit patterns; compared by the largest difference relative to the largest magnitude).  With both
+ * forced, every stage is checked on the inputs the other implementation really had, and a value that rounded the other
+ * way cannot cascade into the stages after it.  Order of a step's trace: layer 0's q|k|v words, then per layer: wo
+ * words, residual, gate|up words, down words, residual, the next layer's q|k|v words (after the last: the lm_head's). */
+static int32_t* g_trace;
+static const int32_t* g_forced;
+static long g_trace_cap, g_trace_len, g_forced_len, g_diff_values, g_diff_vectors;
+static int g_diff_max;
+static float g_diff_x;
+void kqo_decode_set_trace(int32_t* buf, long cap_words) { g_trace = buf, g_trace_cap = cap_words, g_trace_len = 0; }
+long kqo_decode_trace_words(void) { return g_trace_len; }
+void kqo_decode_set_forced(const int32_t* words, long n_words) { g_forced = words, g_forced_len = n_words; }
+void kqo_decode_forced_stats(long* values, long* vectors, int* max_step, float* residual_rel) {
+    *values = g_diff_values, *vectors = g_diff_vectors, *max_step = g_diff_max, *residual_rel = g_diff_x;
+}
+static void trace_q8(int32_t* xq, int k) {
+    if (g_trace && g_trace_len + k / 4 <= g_trace_cap) memcpy(g_trace + g_trace_len, xq, (size_t)(k / 4) * sizeof(int32_t));
+    if (g_forced && g_trace_len + k / 4 <= g_forced_len) {
+        const int8_t* own = (const int8_t*)xq;
+        const int8_t* other = (const int8_t*)(g_forced + g_trace_len);
+        long n = 0;
+        for (int i = 0; i < k; ++i) {
+            const int d = abs((int)own[i] - (int)other[i]);
+            n += d != 0;
+            if (d > g_diff_max) g_diff_max = d;
+        }
+        g_diff_values += n;
+        g_diff_vectors += n != 0;
+        memcpy(xq, other, (size_t)k);
+    }
+    g_trace_len += k / 4;
+}
+static void trace_f32(float* x, int n) {
+    if (g_trace && g_trace_len + n <= g_trace_cap) memcpy(g_trace + g_trace_len, x, (size_t)n * sizeof(float));
+    if (g_forced && g_trace_len + n <= g_forced_len) {
+        const float* other = (const float*)(g_forced + g_trace_len);
+        float big = 0.0f, diff = 0.0f;
+        for (int i = 0; i < n; ++i) {
+            big = fmaxf(big, fabsf(x[i]));
+            diff = fmaxf(diff, fabsf(x[i] - other[i]));
+        }
+        if (big > 0.0f && diff / big > g_diff_x) g_diff_x = diff / big;
+        memcpy(x, other, (size_t)n * sizeof(float));
+    }
+    g_trace_len += n;
+}
+
 static void mv_q(const kqo_mat* w, const int32_t* xq, float* y) { /* CppBackend::matvecQuantized, llm_model.cpp:531-537 */
     const float* xd = (const float*)(xq + (w->k / 32) * 8);
     if (w->fmt == 6) kqo_matvec_q6k_q8(w->blocks, xq, xd, y, w->rows, w->k);
@@ -793,6 +845,7 @@ static void mv_q(const kqo_mat* w, const int32_t* xq, float* y) { /* CppBackend:
 }
 static void mv_f(const kqo_mat* w, const float* x, int32_t* xq, float* y) { /* CppBackend::matvec, :510-516 */
     kqo_quantize_q8x4(x, xq, (float*)(xq + (w->k / 32) * 8), w->k / 32);
+    trace_q8(xq, w->k);
     mv_q(w, xq, y);
 }
 
@@ -819,6 +872,7 @@ void kqo_decode_token_ex(const kqo_model* m, const float* x_in, int pos, float* 
     const float scale = 1.0f / sqrtf((float)m->head_dim);
     const int pairs = m->head_dim / 2;
 
+    g_trace_len = 0, g_diff_values = 0, g_diff_vectors = 0, g_diff_max = 0, g_diff_x = 0.0f;
     memcpy(x, x_in, (size_t)hid * sizeof(float));
     kqo_rms_norm(x, m->layers[0].attn_norm, xn, hid, 1, m->eps);
     for (int l = 0; l < m->n_layers; ++l) {
@@ -853,14 +907,27 @@ void kqo_decode_token_ex(const kqo_model* m, const float* x_in, int pos, float* 
         kqo_attn_values(scores, L->v_cache, attn, &ad);
         mv_f(&L->wo, attn, xq, t);
         kqo_add_sumsq(x, t, xq, hid / 32);
+        if (g_forced) { /* the sums of squares belong to the replaced values */
+            trace_f32(x, hid);
+            memset(t, 0, (size_t)hid * sizeof(float));
+            kqo_add_sumsq(x, t, xq, hid / 32);
+        } else trace_f32(x, hid);
         kqo_norm_q8x4(x, L->ffn_norm, xq, hid / 32, m->eps);
+        trace_q8(xq, hid);
         mv_q(&L->wg, xq, g);
         mv_q(&L->wu, xq, u);
         kqo_silu_mul_q8x4(g, u, xq, (float*)(xq + (m->inter / 32) * 8), m->inter / 32);
+        trace_q8(xq, m->inter);
         mv_q(&L->wd, xq, t);
         const float* next = l + 1 < m->n_layers ? m->layers[l + 1].attn_norm : m->out_norm;
         kqo_add_sumsq(x, t, xq, hid / 32);
+        if (g_forced) {
+            trace_f32(x, hid);
+            memset(t, 0, (size_t)hid * sizeof(float));
+            kqo_add_sumsq(x, t, xq, hid / 32);
+        } else trace_f32(x, hid);
         kqo_norm_q8x4(x, next, xq, hid / 32, m->eps);
+        trace_q8(xq, hid);
     }
     mv_q(&m->lm_head, xq, logits);
 }

@@ -138,6 +138,19 @@ void kqo_decode_token(const kqo_model* m, const float* x_in, int pos, float* log
 /* flags: 1 = fp16-rounded KV cache, 2 = NEOX RoPE, 4 = per-head q/k RMSNorm; 0 = kqo_decode_token. */
 void kqo_decode_token_ex(const kqo_model* m, const float* x_in, int pos, float* logits, float* scratch_f,
                          int32_t* scratch_q, int flags);
+/* Test instrumentation: from now on every decode step writes to buf the int8 words of each activation vector it
+ * quantizes and the residual stream (hidden floats, as bit patterns) after each of a layer's two additions, in the order
+ * the step runs: layer 0's q|k|v words, then per layer wo words, residual, gate|up words, down words, residual, the next
+ * q|k|v words (after the last layer: the lm_head's).  NULL switches it off.
+ * kqo_decode_trace_words() = words the last step produced (more than cap_words: the tail was dropped). */
+void kqo_decode_set_trace(int32_t* buf, long cap_words);
+long kqo_decode_trace_words(void);
+/* Test instrumentation: the trace another implementation made of the same step.  Each vector the loop quantizes, and
+ * the residual stream after each addition, is compared with it (kqo_decode_forced_stats: differing int8 values, vectors
+ * holding one, largest int8 step, largest residual difference relative to the residual's largest magnitude; reset by
+ * every step) and then replaced by it, so each stage is checked on the inputs the other implementation had. */
+void kqo_decode_set_forced(const int32_t* words, long n_words);
+void kqo_decode_forced_stats(long* values, long* vectors, int* max_step, float* residual_rel);
 long kqo_decode_scratch_floats(const kqo_model* m);
 long kqo_decode_scratch_ints(const kqo_model* m);
 

@@ -5,6 +5,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
+import oracle
 from helpers import OracleModel, oracle_prefill, rel_diff
 from kernelcore_b200 import decoder, lib, tiny_model as tm
 
@@ -87,6 +88,109 @@ def test_graph_decoder_against_oracle(shape_fn):
         assert int(logits_free.argmax()) == int(hist[11])
         with pytest.raises(lib.KcbError):
             d.set_prompt(list(range(49)))          # longer than the KV cache
+
+
+def _int8_diffs(a, b):
+    d = a.view(np.int8).astype(np.int32) - b.view(np.int8).astype(np.int32)
+    return int((d != 0).sum())
+
+
+@pytest.mark.parametrize("fused", [1, 0])
+@pytest.mark.parametrize("shape_fn", [tm.tiny, tm.tiny_qwen])
+def test_graph_decoder_stage_by_stage_with_flip_count(shape_fn, fused, monkeypatch):
+    """Why the test above needs 3e-2, measured instead of argued.  The decoder traces the int8 words of every activation
+    vector it quantizes (five per layer and the lm_head's input) and the residual stream after each addition.
+
+    Stage by stage: the oracle is run with every one of those vectors compared with the decoder's and then replaced by
+    it, so each of its stages works on exactly the inputs the decoder's stage had.  On 40 positions: no int8 value is
+    ever off by more than one step, at most 2 values of a step's 2816 differ (a value on a rounding boundary after a
+    sum taken in another order), 12 over all positions; the residual stream agrees to 1e-4 of its largest magnitude
+    (2e-3 on a step where one of those values fed a matvec), and the logits to 1e-5.
+
+    Free-running (oracle on its own words): up to and including the last position before the first differing int8
+    value, the logits agree to 1e-5 -- a hundred times tighter than the reference's 1e-4 bar
+    (tests/test_llm_kernels.cpp:925-928); after it the difference is the model's response to one int8 step (these
+    random-weight models amplify it: one step in one vector changes tens of values in the next), not an arithmetic
+    difference, and stays inside 3e-2.  Both forms of the step (producers fused into the matvecs, and one kernel each)
+    are held to the same numbers."""
+    monkeypatch.setenv("KCB_DECODE_FUSED", str(fused))
+    shape = shape_fn(max_ctx=48)
+    model = tm.build(shape, seed=5)
+    staged, free = OracleModel(shape, model), OracleModel(shape, model)
+    forced = [int(t) for t in np.random.default_rng(5).integers(0, shape.vocab, 40)]
+    total = clean = 0
+    diverged = False
+    with decoder.FastDecoder(shape, model) as d:
+        # embed + 7 launches per layer + lm_head + 2 for the pick when the producers are prologues of the matvecs
+        assert (d.launches_per_token == 4 + 7 * shape.layers) == bool(fused)
+        words = d.enable_trace()
+        assert words == staged.trace_words()
+        d.set_prompt(forced)
+        own = np.zeros(words, np.int32)
+        for pos, tok in enumerate(forced):
+            d.run(1)
+            logits, _, _ = d.read()
+            trace = d.read_trace()
+            want = staged.decode_port(staged.embed(tok), pos, kv_f16=True, forced=trace)
+            values, vectors, step, residual = staged.forced_stats
+            assert step <= 1 and values <= 2, (pos, staged.forced_stats)
+            assert residual < (2e-3 if values else 1e-4), (pos, staged.forced_stats)
+            assert rel_diff(logits, want) < 1e-5, pos
+            total += values
+            lone = free.decode_port(free.embed(tok), pos, kv_f16=True, trace=own)
+            q8 = [(a, n) for kind, a, n in free.trace_layout() if kind == "q8"]
+            diverged = diverged or any(_int8_diffs(trace[a:a + n], own[a:a + n]) for a, n in q8)
+            if not diverged:
+                clean += 1
+                assert rel_diff(logits, lone) < 1e-5, pos
+            assert rel_diff(logits, lone) < 3e-2, pos
+    assert total <= 12 and clean >= 6, (total, clean)
+
+
+def test_full_size_logits_against_the_reference_decode_loop():
+    """The Llama-3.2-3B-shape model (28 layers, real shapes, the benchmark's weights) at positions 0..2.
+
+    Stage by stage against the oracle on the decoder's own inputs (see the test above): no int8 value off by more than
+    one step, at most 0.1 % of a step's 489,472 values differing (measured: 3, 3, 108 -- the larger count is an fp16
+    rounding of a cached K or V element going the other way, which moves a whole attention output by ~1e-5), the
+    residual stream within 2e-3 of its largest magnitude, the logits within 1e-5.
+
+    Against llm::decodeToken of the reference itself (compiled from its sources; fp32 KV cache): 5e-2 of max|logit|
+    at every position, measured 3.5e-2, 3.0e-2, 2.7e-2.  That is not the reference's 1e-4 bar and cannot be on this
+    model: the oracle with nothing changed but K and V rounded to fp16 as they enter the cache -- the ggml path's
+    cache format -- is itself 3.0e-2, 2.6e-2, 2.5e-2 away from the reference here.  28 layers of 8-bit
+    re-quantization with random weights turn any perturbation, however small, into independent rounding noise of that
+    size; the stage-by-stage numbers above are what shows the arithmetic is the reference's."""
+    shape = tm.llama32_3b(16)
+    model = tm.build(shape, seed=0)
+    toks = [int(t) for t in np.random.default_rng(1).integers(0, shape.vocab, 512)[:3]]
+    staged = OracleModel(shape, model)
+    ref_logits = None
+    if oracle.ref is not None:
+        bound = OracleModel(shape, model)
+        h = oracle.ref.lib.kcref_model_open(C.byref(bound.c))
+        assert h
+        ref_logits = []
+        for pos, tok in enumerate(toks):
+            out = np.zeros(shape.vocab, np.float32)
+            assert oracle.ref.lib.kcref_model_decode(h, bound.embed(tok), pos, out) == 0
+            ref_logits.append(out)
+        oracle.ref.lib.kcref_model_close(h)
+    with decoder.FastDecoder(shape, model) as d:
+        assert d.launches_per_token == 4 + 7 * shape.layers     # the fused step is the one measured
+        words = d.enable_trace()
+        assert words == staged.trace_words()
+        d.set_prompt(toks)
+        for pos, tok in enumerate(toks):
+            d.run(1)
+            logits, _, _ = d.read()
+            want = staged.decode_port(staged.embed(tok), pos, kv_f16=True, forced=d.read_trace())
+            values, vectors, step, residual = staged.forced_stats
+            assert step <= 1 and values <= 489 and residual < 2e-3, (pos, staged.forced_stats)
+            assert rel_diff(logits, want) < 1e-5, pos
+            if ref_logits is not None:
+                assert rel_diff(logits, ref_logits[pos]) < 5e-2, pos
+    assert lib.raw.kcb_tma_timeouts() == 0
 
 
 def _tc_shape(max_ctx):

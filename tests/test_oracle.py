@@ -205,3 +205,32 @@ def test_batched_pipeline_restatement_agrees_with_the_decode_loop():
         assert rel_diff(oracle_prefill(shape, model, prompt, q8k=False), want) < 1e-5
         # per-256 activations: a different quantization of the same model, within the reference's Q8-vs-float bound
         assert rel_diff(oracle_prefill(shape, model, prompt), want) < 5e-2
+
+
+def test_decode_trace_and_stage_by_stage_mode():
+    """The instrumentation the decoder's stage-by-stage test rests on.  A step's trace holds every vector the loop
+    quantized and the residual after each addition; replaying the step with its own trace forced changes nothing
+    and counts no difference; one int8 step planted in the wo input is counted as exactly that, shows in the next
+    residual, and does not reach the logits, because every later vector is replaced as well -- while the same step
+    planted without the later replacements (a free-running loop) would."""
+    from helpers import OracleModel
+    from kernelcore_b200 import tiny_model as tm
+    shape = tm.tiny(max_ctx=8)
+    model = tm.build(shape, seed=2)
+    a, b = OracleModel(shape, model), OracleModel(shape, model)
+    layout = a.trace_layout()
+    assert sum(n for _, _, n in layout) == a.trace_words() and [k for k, _, _ in layout[:4]] == ["q8", "q8", "x", "q8"]
+    trace = np.zeros(a.trace_words(), np.int32)
+    for pos, tok in enumerate((3, 200, 17)):
+        want = a.decode_port(a.embed(tok), pos, kv_f16=True, trace=trace)
+        assert np.any(trace[layout[0][1]:layout[0][1] + layout[0][2]] != 0)
+        got = b.decode_port(b.embed(tok), pos, kv_f16=True, forced=trace)
+        assert (got == want).all() and b.forced_stats == (0, 0, 0, 0.0)
+    planted = trace.copy()
+    byte = planted.view(np.int8)
+    at = 4 * layout[1][1] + 37                      # a value of the wo input of layer 0
+    byte[at] += 1 if byte[at] < 127 else -1
+    got = b.decode_port(b.embed(17), 2, kv_f16=True, forced=planted)
+    values, vectors, step, residual = b.forced_stats
+    assert (values, vectors, step) == (1, 1, 1) and 1e-5 < residual < 1e-2
+    assert (got == want).all()

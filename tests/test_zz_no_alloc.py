@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from helpers import rel_diff
 from kernelcore_b200 import kquant, lib, synth
 
@@ -27,6 +28,15 @@ def test_static_scratch_matvec_matches_two_call_path_twice():
         torch.cuda.synchronize()
         assert rel_diff(got.cpu().numpy(), want.cpu().numpy()) < 1e-5
         assert torch.equal(got, want)  # same kernels on the same words: in fact identical
+        # and against the CPU oracle's Q8 arithmetic on the same blocks and activations (the bar of the other matvec tests)
+        ref = oracle.matvec_q8(oracle.port, synth.q4k_blocks(rows, k, 40 + call), x.cpu().numpy(), rows, k, 0)
+        assert rel_diff(got.cpu().numpy(), ref) < 1e-5
+        if call == 0:
+            # the first call on a device also loads the module and looks up the array's address; from the second call on
+            # the entry point must leave the device's free memory untouched
+            free_before = torch.cuda.mem_get_info()[0]
+        else:
+            assert torch.cuda.mem_get_info()[0] == free_before
     # sizes beyond the built-in scratch are refused up front, nothing is launched
     y = torch.zeros(8, device="cuda")
     big = torch.zeros(max_k + 256, device="cuda")
