@@ -117,7 +117,7 @@ int kcb_matvec_q4k_q8(const void* w_dev, const int32_t* xq_dev, const float* xd_
 int kcb_matvec_q6k_q8(const void* planes_dev, const int32_t* xq_dev, const float* xd_dev, float* y_dev, int rows,
                       int k, void* stream);
 /* Both of the above on the same activations in one launch: y4 = W4 x (Q4_K), y6 = W6 x (Q6_K planes) -- the q|k and
- * v projections of a Q4_K_M layer (llm_model.cpp's three Backend::matvec calls on the attention input), each output
+ * v projections of a Q4_K_M layer (the three Backend::matvec calls of llm::decodeToken on the attention input), each output
  * bit-identical to its own launch.  k <= 4096 and at most 6144 rows each; beyond that KCB_UNSUPPORTED_OPERATION (7),
  * and the caller launches them separately (larger matrices stream better through the bulk-copy kernel). */
 int kcb_matvec_q4k_q6k_pair_q8(const void* w4_dev, float* y4_dev, int rows4, const void* planes6_dev, float* y6_dev, int rows6,
@@ -278,9 +278,16 @@ typedef struct {
  * read them).  graphs != 0: each token's launches are recorded and run as one CUDA graph. */
 int kcb_model_create(const kcb_model_desc* desc, int graphs, void** model);
 /* llm::decodeToken: one decode step for `token` at position pos (0-based, == tokens decoded so far).
- * logits_host (vocab floats) may be NULL; argmax may be NULL. */
+ * logits_host (vocab floats) may be NULL; argmax may be NULL.  token < 0 only for synthetic models (below). */
 int kcb_model_decode(void* model, int token, int pos, float* logits_host, int* argmax);
 int kcb_model_destroy(void* model);
+/* llm::buildModels + llm::allocActs (llm/llm_model.cpp:217-283 of the reference): a random-weight model of the shape in
+ * desc (its pointer members are not read) in a synthetic format -- weights 0 = Q8, 1 = Q4, 2 = Q4X8, 3 = Q4X8Q8 --
+ * whose values are, for equal seeds, the reference's bit for bit; the KV caches start filled, so a step at any position
+ * is defined.  Such a model has no embedding table: kcb_model_decode takes token < 0 and starts from the vector drawn
+ * from start_seed. */
+int kcb_model_create_synthetic(const kcb_model_desc* desc, int weights, unsigned long long model_seed,
+                               unsigned long long start_seed, int graphs, void** model);
 /* Text of the last exception a kcb_model_* call on this thread turned into a status code (the reference's
  * decode loop reports failures as C++ exceptions, llm/llm_model.cpp:91-97). */
 const char* kcb_model_last_error(void);

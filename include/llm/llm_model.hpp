@@ -5,7 +5,7 @@
 // Type, member and function names are those of the reference's llm/llm_model.hpp:23-209, so programs written
 // against that header compile against this one.  What differs:
 //   - Weights::Q4K / Q6K / Gguf matrices hold this build's device layouts (see llm_reference.hpp);
-//   - makeKcBackend() gives a backend whose every operation is a CUDA kernel launched through kcLaunchKernel;
+//   - makeKcBackend() gives a backend whose every operation is a CUDA kernel on the kc runtime's default stream;
 //   - makeCppBackend() does not exist: nothing here computes on the CPU;
 //   - Config::neox and Config::qk_norm, Layer::q_norm / k_norm and Backend::rmsNormRows() are additions for
 //     Qwen3-style models (RoPE pairs half a head apart, RMSNorm of every q and k head before the rotation).
@@ -79,28 +79,45 @@ public:
     virtual void download(void* dst, const void* src, size_t bytes) = 0;  // and back
 };
 
+namespace detail {
+// The blocks an allocator has handed out, each with the function that gives it back; released newest first.
+class BlockLedger {
+public:
+    using Release = void (*)(void*);
+    explicit BlockLedger(Release release) : release_(release) {}
+    BlockLedger(const BlockLedger&) = delete;
+    BlockLedger& operator=(const BlockLedger&) = delete;
+    ~BlockLedger();
+    void* keep(void* block);
+
+private:
+    Release release_;
+    std::vector<void*> held_;
+};
+}  // namespace detail
+
 // Ordinary host memory: staging buffers and tests.
 class HostAllocator final : public Allocator {
 public:
-    ~HostAllocator() override;
+    HostAllocator();
     void* alloc(size_t bytes) override;
     void upload(void* dst, const void* src, size_t bytes) override;
     void download(void* dst, const void* src, size_t bytes) override;
 
 private:
-    std::vector<void*> blocks_;
+    detail::BlockLedger ledger_;
 };
 
 // Memory of the current GPU, through kcMalloc and kcMemcpy.
 class KcAllocator final : public Allocator {
 public:
-    ~KcAllocator() override;
+    KcAllocator();
     void* alloc(size_t bytes) override;
     void upload(void* dst, const void* src, size_t bytes) override;
     void download(void* dst, const void* src, size_t bytes) override;
 
 private:
-    std::vector<void*> blocks_;
+    detail::BlockLedger ledger_;
 };
 
 // ---- weights, caches, activations -----------------------------------------------------------------------------
@@ -154,6 +171,12 @@ struct Acts {
 };
 
 Acts allocActs(const Config& cfg, Allocator& alloc, uint64_t seed);
+
+// A model of random weights in one of the synthetic formats (Q8, Q4, Q4X8, Q4X8Q8), the same in every allocator of
+// `allocs` and, for a given seed, the same values the reference's buildModels draws (llm/llm_model.cpp:217-254): fused
+// q|k|v and gate|up matrices, norm weights near one, KV caches pre-filled with uniform values so that a step at any
+// position attends over defined data.  One Model per allocator is appended to `out` (which is cleared first).
+void buildModels(const Config& cfg, uint64_t seed, const std::vector<Allocator*>& allocs, std::vector<Model>& out);
 
 // A K-quant model described by pointers to canonical GGUF block bytes on the host.  uploadModel() converts each
 // matrix to its device layout and uploads it through `alloc`, allocates the KV caches and makes Model::embed look
@@ -234,8 +257,9 @@ public:
 // norm and the LM head leave the logits in Acts::logits.
 void decodeToken(Backend& b, const Model& m, const Acts& a, int pos, Profiler* prof = nullptr, int token = -1);
 
-// The backend that launches through kcLaunchKernel on the current device.  With `graphs` each token is recorded
-// into one CUDA graph.  `workers` and `two_rows` schedule CPU threads in the reference and mean nothing here.
+// The CUDA backend of the current device: every operation is enqueued on the kc runtime's default stream, the
+// residual add, RMSNorm and quantization of addRmsNormQuant as one launch.  With `graphs` each token is recorded into
+// one CUDA graph.  `workers` and `two_rows` schedule CPU threads in the reference and mean nothing here.
 std::unique_ptr<Backend> makeKcBackend(const Model& m, unsigned workers, bool graphs = true, bool two_rows = false);
 
 }  // namespace llm

@@ -6,6 +6,7 @@
 #include <llm_model.hpp>
 
 #include <memory>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -58,9 +59,37 @@ int kcb_model_create(const kcb_model_desc* d, int graphs, void** out) {
     return kcb::KCB_SUCCESS;
 }
 
+int kcb_model_create_synthetic(const kcb_model_desc* d, int weights, unsigned long long model_seed, unsigned long long start_seed, int graphs,
+                               void** out) {
+    if (!d || !out || weights < 0 || weights > 3) return kcb::KCB_INVALID_VALUE;
+    *out = nullptr;
+    try {
+        llm::Config c;
+        c.name = "kcb synthetic model";
+        c.hidden = d->hidden, c.inter = d->inter, c.layers = d->n_layers, c.heads = d->heads, c.kv_heads = d->kv_heads;
+        c.head_dim = d->head_dim, c.vocab = d->vocab, c.max_ctx = d->max_ctx, c.eps = d->eps, c.rope_base = d->rope_base;
+        c.weights = static_cast<llm::Weights>(weights);
+        auto om = std::make_unique<OpenModel>();
+        std::vector<llm::Model> built;
+        llm::buildModels(c, model_seed, {&om->alloc}, built);
+        om->model = std::move(built.front());
+        om->acts = llm::allocActs(c, om->alloc, start_seed);
+        om->backend = llm::makeKcBackend(om->model, 0, graphs != 0);
+        om->logits.resize(size_t(c.vocab));
+        *out = om.release();
+    } catch (const std::invalid_argument& e) {
+        tl_what = e.what();
+        return kcb::KCB_INVALID_VALUE;
+    } catch (const std::exception& e) {
+        tl_what = e.what();
+        return kcb::KCB_INTERNAL_ERROR;
+    }
+    return kcb::KCB_SUCCESS;
+}
+
 int kcb_model_decode(void* h, int token, int pos, float* logits_host, int* argmax) {
     auto* om = static_cast<OpenModel*>(h);
-    if (!om || token < 0) return kcb::KCB_INVALID_VALUE;
+    if (!om || (token < 0 && om->model.embed)) return kcb::KCB_INVALID_VALUE;
     try {
         llm::decodeToken(*om->backend, om->model, om->acts, pos, nullptr, token);
         om->backend->finish();

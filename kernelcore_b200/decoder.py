@@ -54,6 +54,25 @@ class Model:
             L.kcb_model_last_error.restype = C.c_char_p
             raise RuntimeError(f"kcb_model_create: status {st}: {L.kcb_model_last_error().decode()}")
 
+    @classmethod
+    def synthetic(cls, shape: tm.Shape, weights: int, model_seed: int, start_seed: int, graphs: int = 1) -> "Model":
+        """llm::buildModels + llm::allocActs: a random-weight model in a synthetic format (weights 0 = Q8, 1 = Q4,
+        2 = Q4X8, 3 = Q4X8Q8) with the reference's values for these seeds.  decode() takes token -1."""
+        L = lib.raw
+        lib.check(L.kcb_init(), "kcb_init")
+        self = cls.__new__(cls)
+        self.shape, self._keep = shape, []
+        d = _Desc()
+        for f in ("hidden", "inter", "heads", "kv_heads", "head_dim", "vocab", "max_ctx"):
+            setattr(d, f, getattr(shape, f))
+        d.n_layers, d.eps, d.rope_base = shape.layers, shape.eps, shape.rope_base
+        self.handle = C.c_void_p()
+        st = L.kcb_model_create_synthetic(C.byref(d), int(weights), C.c_ulonglong(model_seed), C.c_ulonglong(start_seed), graphs, C.byref(self.handle))
+        if st != 0:
+            L.kcb_model_last_error.restype = C.c_char_p
+            raise RuntimeError(f"kcb_model_create_synthetic: status {st}: {L.kcb_model_last_error().decode()}")
+        return self
+
     def _ptr(self, a):
         a = np.ascontiguousarray(a)
         self._keep.append(a)

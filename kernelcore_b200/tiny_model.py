@@ -46,6 +46,11 @@ def tiny_qwen(max_ctx: int = 40) -> Shape:
     return Shape("tiny-qwen", 256, 512, 2, 4, 1, 128, 256, max_ctx, eps=1e-6, rope_base=1e6, neox=True, qk_norm=True)
 
 
+def reference_tiny() -> Shape:
+    """The reference's tinyConfig (llm/llm_model.cpp:51-57) exactly: the shape of its synthetic-format models."""
+    return Shape("tiny", 256, 640, 2, 4, 2, 64, 1000, 40)
+
+
 def llama32_3b(max_ctx: int) -> Shape:
     return Shape("llama-3.2-3b-arch", 3072, 8192, 28, 24, 8, 128, 128256, max_ctx)
 

@@ -156,6 +156,8 @@ def _load_ref():
     L.kcref_matvec_stream_q8.argtypes = [_i32p, _i32p, _f32p, _f32p, i, i, i]
     L.kcref_matvec_stream_q8k.restype = None
     L.kcref_matvec_stream_q8k.argtypes = [_i32p, _i32p, _f32p, i, i, i]
+    L.kcref_synthetic_tiny_logits.restype = i
+    L.kcref_synthetic_tiny_logits.argtypes = [i, C.c_ulonglong, C.c_ulonglong, i, _f32p, C.POINTER(C.c_double)]
     L.kcref_model_open.restype, L.kcref_model_open.argtypes = C.c_void_p, [C.POINTER(Model)]
     L.kcref_model_decode.restype, L.kcref_model_decode.argtypes = i, [C.c_void_p, _f32p, i, _f32p]
     L.kcref_model_close.restype, L.kcref_model_close.argtypes = None, [C.c_void_p]

@@ -248,4 +248,33 @@ int kcref_model_decode(void* h, const float* x_in, int pos, float* logits) {
 }
 void kcref_model_close(void* h) { delete static_cast<OpenModel*>(h); }
 
+// The reference's synthetic tiny model (llm::tinyConfig + llm::buildModels, weights 0 = Q8, 1 = Q4, 2 = Q4X8,
+// 3 = Q4X8Q8) on its single-thread C++ backend: one decodeToken from the start vector of allocActs at `pos`, as its
+// own test tiny_decode_token_kc_vs_cpp does (tests/test_llm_kernels.cpp:891-930).  Returns the vocabulary size, or
+// -1 on an exception.  A checksum over the first matrix's bytes and scales is written to *weight_sum when not null.
+int kcref_synthetic_tiny_logits(int weights, unsigned long long model_seed, unsigned long long start_seed, int pos, float* logits,
+                                double* weight_sum) {
+    try {
+        const llm::Config cfg = llm::tinyConfig(static_cast<llm::Weights>(weights));
+        llm::HostAllocator alloc;
+        std::vector<llm::Model> models;
+        llm::buildModels(cfg, model_seed, {&alloc}, models);
+        const llm::Acts acts = llm::allocActs(cfg, alloc, start_seed);
+        auto backend = llm::makeCppBackend(models[0]);
+        llm::decodeToken(*backend, models[0], acts, pos);
+        if (logits) std::memcpy(logits, acts.logits, size_t(cfg.vocab) * sizeof(float));
+        if (weight_sum) {
+            const llm::Mat& w = models[0].layers[0].wqkv;
+            double sum = 0.0;
+            const size_t bytes = size_t(w.rows) * size_t(w.k) / (weights == 0 ? 1 : 2) + (weights == 3 ? size_t(w.rows) * size_t(w.k) / 8 : 0);
+            const uint8_t* q = static_cast<const uint8_t*>(w.q);
+            for (size_t i = 0; i < bytes; ++i) sum += double(q[i]) * double(i % 251 + 1);
+            *weight_sum = sum;
+        }
+        return cfg.vocab;
+    } catch (...) {
+        return -1;
+    }
+}
+
 } // extern "C"

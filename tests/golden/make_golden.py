@@ -198,7 +198,20 @@ def decode():
          digest=np.frombuffer(bytes.fromhex(tm.digest(model)), np.uint8))
 
 
+def synthetic():
+    """The reference's buildModels(tinyConfig(w), 42) + allocActs(seed 7) + decodeToken on its C++ backend at position
+    17 (its own test's choice, tests/test_llm_kernels.cpp:891-930) and at position 0, for the four synthetic formats."""
+    out = {}
+    for w, name in enumerate(("q8", "q4", "q4x8", "q4x8q8")):
+        for pos in (17, 0):
+            logits = np.zeros(1000, np.float32)
+            assert ref.lib.kcref_synthetic_tiny_logits(w, 42, 7, pos, logits, None) == 1000
+            out[f"{name}_pos{pos}"] = logits
+    save("synthetic_tiny", **out)
+
+
 if __name__ == "__main__":
+    synthetic()
     kquant()
     halfs()
     glue()

@@ -25,6 +25,24 @@ def test_tiny_model_against_reference_logits(golden, graphs):
             assert arg == int(g["logits"][pos].argmax())
 
 
+@pytest.mark.parametrize("graphs", [0, 1])
+def test_synthetic_format_models_against_reference_logits(golden, graphs):
+    """llm::buildModels + makeKcBackend + decodeToken on the reference's tiny shape in its four synthetic formats: the
+    shapes, seeds and position of its own test tiny_decode_token_kc_vs_cpp (tests/test_llm_kernels.cpp:891-930), against
+    logits its C++ backend produced for models it built itself -- so the weights drawn here must be its weights bit for
+    bit, and the bar is its bar: relDiff < 1e-4 and the same argmax."""
+    g = golden("synthetic_tiny")
+    for weights, name in enumerate(("q8", "q4", "q4x8", "q4x8q8")):
+        with decoder.Model.synthetic(tm.reference_tiny(), weights, model_seed=42, start_seed=7, graphs=graphs) as m:
+            for pos in (17, 0):       # each golden vector is a first step on a fresh model: 17 then 0 touch different cache rows
+                logits, arg = m.decode(-1, pos)
+                want = g[f"{name}_pos{pos}"]
+                assert rel_diff(logits, want) < 1e-4, (name, pos)
+                assert arg == int(want.argmax())
+    with pytest.raises(RuntimeError):
+        decoder.Model.synthetic(tm.Shape("odd", 250, 640, 2, 4, 2, 64, 1000, 40), 0, 1, 1)   # hidden not a multiple of 32
+
+
 def test_greedy_generation_matches_oracle():
     """Free-running greedy decode: same tokens as the CPU oracle for 12 steps, and bad positions refused."""
     shape = tm.tiny(max_ctx=24)
