@@ -73,6 +73,10 @@ int kcb_graph_launch(void* graph, void* stream);      /* kcGraphLaunch, api.hpp:
 int kcb_graph_destroy(void* graph);                   /* kcGraphDestroy, api.hpp:70 */
 int kcb_stream_concurrent(void* stream, int begin);   /* kcStreamConcurrentBegin/End, api.hpp:68-69 */
 int kcb_get_last_fault(void* fault_info);             /* kcGetLastFault, api.hpp:79 (kc::FaultInfo*) */
+/* Test hook: the next runtime call on the current device that waits for or enqueues device work, and itself
+ * succeeds, reports this CUDA error code instead (once).  Lets a test drive KernelFault -> ContextPoisoned ->
+ * kcDeviceReset (src/runtime.cpp:238-252, 602-615 of the reference) without making a kernel fail. */
+int kcb_test_inject_device_error(int cuda_error);
 const char* kcb_last_error_detail(void);              /* kcGetLastErrorDetail, api.hpp:85 */
 /* The cudaStream_t behind a stream handle, for callers that mix kcb_* op entry points with runtime streams. */
 void* kcb_stream_native(void* stream);
@@ -172,6 +176,14 @@ int kcb_matvec_q6k_q8_gather(const void* planes_dev, const int32_t* xq_dev, cons
  * kcb_peer_timeouts() and the kernel returns.  Use a fresh, increasing epoch per step. */
 int kcb_peer_barrier(unsigned* const* flags, int rank, int world, unsigned epoch, void* stream);
 unsigned kcb_peer_timeouts(void);
+/* Failure handling of the cross-GPU waits (kcb_peer_barrier and the barrier inside kcb_matvec_q6k_f32x_sharded).  A
+ * wait polls at most `polls` times (0 restores the default, about a second) and then gives up: the expiry is counted,
+ * the kernel returns, and the group is marked broken so that later barriers announce themselves, poll once and return
+ * -- a rank whose peer is gone does not wait out every step.  The context stays usable.  kcb_peer_reset clears the
+ * count and the mark once the host has dealt with the failure.  Both calls are synchronous.  (The reference detects a
+ * lost worker on the host, src/runtime.cpp:238-252; this is the device-side half a multi-GPU step needs.) */
+int kcb_peer_set_poll_limit(unsigned polls);
+int kcb_peer_reset(void);
 /* The whole sharded step in ONE kernel launch: x (fp32, k floats) is quantized to Q8 blocks of 32 inside the
  * kernel (quantize_q8x4's arithmetic), the row shard is multiplied, results go to y_local and to the npeers other
  * ranks' outputs, and -- world > 1 -- the last CTA to finish runs the step barrier on `flags` (as
@@ -335,6 +347,10 @@ int kcb_decoder_create(const kcb_model_desc* desc, void** decoder);
 size_t kcb_decoder_tp_shared_bytes(const kcb_model_desc* desc);
 int kcb_decoder_create_tp(const kcb_model_desc* desc, int rank, int world, void* const* shared, void** decoder);
 unsigned kcb_decoder_tp_timeouts(void);
+/* The same for the tensor-parallel decoder's exchanges: polls per wait (0 = default), and clearing the expiry count and
+ * the "group dead" mark after which every exchange polls once and returns. */
+int kcb_decoder_tp_set_poll_limit(unsigned polls);
+int kcb_decoder_tp_reset(void);
 int kcb_decoder_set_prompt(void* decoder, const int* tokens, int n, int start_pos);
 /* Batched prompt pass (single GPU): all n tokens through every layer together -- the reference's batched path in its
  * ggml backend (integrations/llama.cpp/ggml/src/ggml-kernelcore/ggml-kernelcore.cpp:548-589 mul_mat with per-256

@@ -194,5 +194,7 @@ int kcb_matvec_q6k_f32x_sharded(const void* w, const float* x, float* y_local, f
 }
 
 unsigned kcb_peer_timeouts(void) { return peer_timeouts() + tma_timeouts(); }
+int kcb_peer_set_poll_limit(unsigned polls) { return peer_set_poll_limit(polls); }
+int kcb_peer_reset(void) { return peer_reset(); }
 
 }  // extern "C"

@@ -479,6 +479,7 @@ struct TpCtx {
 };
 __device__ unsigned g_tp_timeouts = 0;
 __device__ unsigned g_tp_dead = 0;
+__device__ unsigned g_tp_poll_limit = 1u << 22;  // polls of one wait before it gives up (about a second)
 
 __device__ __forceinline__ float ld_peer_f32(const float* p) {
     float v;
@@ -506,7 +507,7 @@ __device__ void tp_arrive_and_wait(const TpCtx& c) {
     if (threadIdx.x < static_cast<unsigned>(c.world)) {
         const int r = threadIdx.x;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(c.flags[r] + c.rank), "r"(e) : "memory");
-        const unsigned limit = *reinterpret_cast<volatile unsigned*>(&g_tp_dead) ? 1u : (1u << 22);
+        const unsigned limit = *reinterpret_cast<volatile unsigned*>(&g_tp_dead) ? 1u : *reinterpret_cast<volatile unsigned*>(&g_tp_poll_limit);
         bool arrived = false;
         for (unsigned i = 0; i < limit; ++i) {
             unsigned v;
@@ -1506,6 +1507,15 @@ unsigned kcb_decoder_tp_timeouts(void) {
     unsigned v = 0;
     cudaMemcpyFromSymbol(&v, kcb::g_tp_timeouts, sizeof v);
     return v;
+}
+int kcb_decoder_tp_set_poll_limit(unsigned polls) {
+    if (polls == 0) polls = 1u << 22;
+    return cudaMemcpyToSymbol(kcb::g_tp_poll_limit, &polls, sizeof polls) == cudaSuccess ? kcb::KCB_SUCCESS : kcb::KCB_INTERNAL_ERROR;
+}
+int kcb_decoder_tp_reset(void) {
+    const unsigned zero = 0;
+    const bool ok = cudaMemcpyToSymbol(kcb::g_tp_timeouts, &zero, sizeof zero) == cudaSuccess && cudaMemcpyToSymbol(kcb::g_tp_dead, &zero, sizeof zero) == cudaSuccess;
+    return ok ? kcb::KCB_SUCCESS : kcb::KCB_INTERNAL_ERROR;
 }
 int kcb_decoder_set_prompt(void* h, const int* tokens, int n, int start_pos) {
     return h ? static_cast<Decoder*>(h)->set_prompt(tokens, n, start_pos) : kcb::KCB_INVALID_VALUE;

@@ -660,6 +660,13 @@ __global__ void __launch_bounds__(kThreads) matvec_q4k_q6k_pair_kernel(const uin
 // Stage reuse is ordered by one __syncthreads per tile: after it, thread 0 refills the stage just
 // consumed.  Every mbarrier wait is bounded; on expiry the CTA records it in g_tma_timeouts and leaves.
 __device__ unsigned g_tma_timeouts = 0;
+// Cross-GPU waits (the step barrier below and the one fused into the sharded matvec) give up after g_peer_poll_limit
+// polls (about a second by default), count the expiry and mark the group broken: later barriers still announce
+// themselves but poll once, so a rank whose peer is gone returns at once instead of waiting out every step.
+// peer_reset() clears both after the host has dealt with the failure.
+__device__ unsigned g_peer_timeouts = 0;
+__device__ unsigned g_peer_broken = 0;
+__device__ unsigned g_peer_poll_limit = 1u << 22;
 
 // Other ranks' gather buffers (already offset to this rank's first row), for the fused all-gather epilogue.
 struct PeerOut {
@@ -912,13 +919,17 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
             const int r = threadIdx.x;
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[r] + peers.rank), "r"(epoch) : "memory");
             bool arrived = false;
-            for (int it = 0; it < (1 << 22) && !arrived; ++it) {
+            const unsigned limit = *reinterpret_cast<volatile unsigned*>(&g_peer_broken) ? 1u : *reinterpret_cast<volatile unsigned*>(&g_peer_poll_limit);
+            for (unsigned it = 0; it < limit && !arrived; ++it) {
                 unsigned v;
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(peers.flags[peers.rank] + r) : "memory");
                 arrived = static_cast<int>(v - epoch) >= 0;
                 if (!arrived) __nanosleep(64);
             }
-            if (!arrived) atomicAdd(&g_tma_timeouts, 1u);
+            if (!arrived) {
+                atomicAdd(&g_peer_timeouts, 1u);
+                atomicExch(&g_peer_broken, 1u);
+            }
         }
     }
 }
@@ -1004,7 +1015,6 @@ bool shape_ok(int rows, int k) { return rows >= 0 && k > 0 && k % 256 == 0 && k 
 // same offset -- the transfer rides on the matvec's own stores instead of a separate collective.
 // peer_barrier then makes the step visible: each rank releases `epoch` into its slot of every peer's flag
 // array and waits (bounded) until all its own slots reach `epoch`.
-__device__ unsigned g_peer_timeouts = 0;
 
 struct PeerFlags {
     unsigned* f[8] = {};
@@ -1022,19 +1032,30 @@ __global__ void peer_barrier_kernel(PeerFlags flags, int rank, int world, unsign
     __threadfence_system();  // order this GPU's earlier peer stores before the flag
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.f[r] + rank), "r"(epoch) : "memory");
     const unsigned* mine = flags.f[rank] + r;
-    for (int i = 0; i < (1 << 22); ++i) {
+    const unsigned limit = *reinterpret_cast<volatile unsigned*>(&g_peer_broken) ? 1u : *reinterpret_cast<volatile unsigned*>(&g_peer_poll_limit);
+    for (unsigned i = 0; i < limit; ++i) {
         unsigned v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
         if (static_cast<int>(v - epoch) >= 0) return;
         __nanosleep(64);
     }
     atomicAdd(&g_peer_timeouts, 1u);  // a peer never arrived: report and leave, nothing spins forever
+    atomicExch(&g_peer_broken, 1u);
 }
 
 unsigned peer_timeouts() {
     unsigned v = 0;
     cudaMemcpyFromSymbol(&v, g_peer_timeouts, sizeof v);
     return v;
+}
+int peer_set_poll_limit(unsigned polls) {
+    if (polls == 0) polls = 1u << 22;
+    return cudaMemcpyToSymbol(g_peer_poll_limit, &polls, sizeof polls) == cudaSuccess ? KCB_SUCCESS : KCB_INTERNAL_ERROR;
+}
+int peer_reset() {
+    const unsigned zero = 0;
+    const bool ok = cudaMemcpyToSymbol(g_peer_timeouts, &zero, sizeof zero) == cudaSuccess && cudaMemcpyToSymbol(g_peer_broken, &zero, sizeof zero) == cudaSuccess;
+    return ok ? KCB_SUCCESS : KCB_INTERNAL_ERROR;
 }
 
 int peer_barrier(unsigned* const* flags, int rank, int world, unsigned epoch, unsigned* epoch_counter, cudaStream_t s) {

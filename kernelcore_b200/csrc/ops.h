@@ -21,6 +21,8 @@ unsigned tma_timeouts();
 int matvec_q6k_f32x_sharded(const void* w, const float* x, float* y_local, float* const* y_peers, int npeers, unsigned* const* flags,
                             unsigned* epoch_counter, unsigned* done_counter, int rank, int world, int rows, int k, cudaStream_t s);
 unsigned peer_timeouts();
+int peer_set_poll_limit(unsigned polls);  // 0 = the default; synchronous
+int peer_reset();                         // clears the expiry count and the "group broken" mark; synchronous
 int peer_barrier(unsigned* const* flags, int rank, int world, unsigned epoch, unsigned* epoch_counter, cudaStream_t s);
 int matvec_q6k_q8_gather(const void* w, const int* xq, const float* xd, float* y_local, float* const* y_peers, int npeers, int rows,
                          int k, cudaStream_t s);  // bounded mbarrier waits that expired since load (synchronous read)

@@ -31,6 +31,7 @@
 #include <mutex>
 #include <set>
 #include <string>
+#include <utility>
 #include <vector>
 
 using namespace kcb;
@@ -65,6 +66,7 @@ struct Device {
     std::set<kcGraph_st*> graphs;
     int capturing = 0;  // streams of this device in capture
     bool poisoned = false;
+    cudaError_t injected = cudaSuccess;  // test hook: reported by the next successful wait or launch
     kc::FaultInfo fault{};
     char props_name[128] = {};
 };
@@ -118,6 +120,14 @@ int fault(Device& d, const char* what, cudaError_t e) {
     std::snprintf(d.fault.kernel, sizeof d.fault.kernel, "%s", what);
     cudaGetLastError();
     return fail(KCB_KERNEL_FAULT, cuda_text(what, e));
+}
+
+// The result of a call that waited for, or enqueued, device work.  A test can plant one error code per device
+// (kcb_test_inject_device_error): the next such call that itself succeeded reports the planted code instead, which
+// drives the fault -> poisoned -> reset cycle without any failing kernel.
+int after_device_work(Device& d, const char* what, cudaError_t e) {
+    if (e == cudaSuccess && d.injected != cudaSuccess) std::swap(e, d.injected);
+    return e == cudaSuccess ? KCB_SUCCESS : fault(d, what, e);
 }
 
 int usable(Device*& d) {
@@ -188,6 +198,7 @@ void release_everything(Device& d) {
     d.capturing = 0;
     d.dflt.capturing = false;
     d.poisoned = false;
+    d.injected = cudaSuccess;
     d.fault = kc::FaultInfo{};
 }
 
@@ -280,7 +291,7 @@ int kcb_device_synchronize(void) {
     if (const int e = usable(d); e != KCB_SUCCESS) return e;
     if (d->capturing) return fail(KCB_UNSUPPORTED_OPERATION, "device synchronisation while a stream is capturing");
     const cudaError_t e = cudaDeviceSynchronize();
-    return e == cudaSuccess ? KCB_SUCCESS : fault(*d, "cudaDeviceSynchronize", e);
+    return after_device_work(*d, "cudaDeviceSynchronize", e);
 }
 
 int kcb_malloc(void** ptr, size_t bytes) {
@@ -341,7 +352,7 @@ int kcb_memcpy(void* dst, const void* src, size_t bytes, int kind) {
     static const cudaMemcpyKind kinds[3] = {cudaMemcpyHostToDevice, cudaMemcpyDeviceToHost, cudaMemcpyDeviceToDevice};
     cudaError_t e = cudaDeviceSynchronize();  // ordered after everything queued on the device
     if (e == cudaSuccess) e = cudaMemcpy(dst, src, bytes, kinds[kind]);
-    return e == cudaSuccess ? KCB_SUCCESS : fault(*d, "cudaMemcpy", e);
+    return after_device_work(*d, "cudaMemcpy", e);
 }
 
 int kcb_memset(void* dst, int value, size_t bytes) {
@@ -355,7 +366,7 @@ int kcb_memset(void* dst, int value, size_t bytes) {
     cudaError_t e = cudaDeviceSynchronize();
     if (e == cudaSuccess) e = cudaMemset(dst, value, bytes);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
-    return e == cudaSuccess ? KCB_SUCCESS : fault(*d, "cudaMemset", e);
+    return after_device_work(*d, "cudaMemset", e);
 }
 
 int kcb_check_range(const void* ptr, size_t bytes) {
@@ -388,7 +399,7 @@ int kcb_launch_kernel(const char* name, const void* typed_args, void* stream_han
     if (status != KCB_SUCCESS) return status;
     if (st->capturing || !st->is_default) return KCB_SUCCESS;
     const cudaError_t e = cudaStreamSynchronize(st->s);  // null stream: synchronous, returns the kernel's result
-    return e == cudaSuccess ? KCB_SUCCESS : fault(*d, name, e);
+    return after_device_work(*d, name, e);
 }
 
 int kcb_register_kernel(const void* entry) {
@@ -448,7 +459,7 @@ int kcb_stream_synchronize(void* h) {
     if (const int e = resolve(*d, static_cast<kcStream_t>(h), s); e != KCB_SUCCESS) return e;
     if (s->capturing) return fail(KCB_UNSUPPORTED_OPERATION, "synchronising a capturing stream");
     const cudaError_t e = cudaStreamSynchronize(s->s);
-    return e == cudaSuccess ? KCB_SUCCESS : fault(*d, "cudaStreamSynchronize", e);
+    return after_device_work(*d, "cudaStreamSynchronize", e);
 }
 
 int kcb_stream_query(void* h) {
@@ -527,7 +538,7 @@ int kcb_event_synchronize(void* h) {
     auto* ev = static_cast<kcEvent_st*>(h);
     if (!ev || !d->events.count(ev)) return fail(KCB_INVALID_RESOURCE_HANDLE, "unknown event handle");
     const cudaError_t e = cudaEventSynchronize(ev->e);
-    return e == cudaSuccess ? KCB_SUCCESS : fault(*d, "cudaEventSynchronize", e);
+    return after_device_work(*d, "cudaEventSynchronize", e);
 }
 int kcb_event_query(void* h) {
     KCB_LOCK;
@@ -623,7 +634,7 @@ int kcb_graph_launch(void* gh, void* stream) {
     if (e != cudaSuccess) return fail(KCB_LAUNCH_FAILURE, cuda_text("cudaGraphLaunch", e));
     if (!s->is_default) return KCB_SUCCESS;
     e = cudaStreamSynchronize(s->s);
-    return e == cudaSuccess ? KCB_SUCCESS : fault(*d, "graph", e);
+    return after_device_work(*d, "graph", e);
 }
 int kcb_graph_destroy(void* gh) {
     KCB_LOCK;
@@ -646,6 +657,15 @@ int kcb_stream_concurrent(void* h, int begin) {
     if (const int e = resolve(*d, static_cast<kcStream_t>(h), s); e != KCB_SUCCESS) return e;
     if (!s->capturing) return fail(KCB_INVALID_VALUE, "concurrent sections only exist inside a capture");
     return KCB_SUCCESS;  // launches stay ordered; a valid (conservative) schedule of independent launches
+}
+
+int kcb_test_inject_device_error(int cuda_error) {
+    KCB_LOCK;
+    Device* d;
+    if (const int e = device_ready(d); e != KCB_SUCCESS) return e;
+    if (cuda_error < 0) return fail(KCB_INVALID_VALUE, "not a CUDA error code");
+    d->injected = static_cast<cudaError_t>(cuda_error);
+    return KCB_SUCCESS;
 }
 
 int kcb_get_last_fault(void* info) {
