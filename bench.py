@@ -578,8 +578,24 @@ def decode_bench(max_ctx, n_prompt, n_gen, peak, model="llama32_3b", lean=False)
         prompt_mode = "batched: Q8_K activation slots, tcgen05 K-quant matmuls, 512-token chunks"
         ms_g = timed(n_gen)
     else:
-        d.set_prompt(prompt)
-        ms_p, ms_g = timed(n_prompt), timed(n_gen)
+        from kernelcore_b200 import lib as _lib
+        try:   # batched prompt pass under tensor parallelism (every rank's K shares whole super-blocks), else token by token
+            d.prefill(prompt)
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            d.prefill(prompt)
+            e1.record(stream)
+            d.sync()
+            t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_p = float(t.item())
+            prompt_mode = "batched under tensor parallelism: row-sharded tcgen05 matmuls, K-split partial rows summed over peer loads"
+        except _lib.KcbError:
+            d.set_prompt(prompt)
+            ms_p = timed(n_prompt)
+        ms_g = timed(n_gen)
     _, hist, _ = d.read(n_prompt + n_gen, want_logits=False)
     total_weight_bytes = tm.weight_bytes_per_token(shape)
     out = {"model": shape.name, "n_gpus": world, "prompt_tokens": n_prompt, "generated_tokens": n_gen, "prompt_tok_s": n_prompt / ms_p * 1e3,

@@ -474,6 +474,7 @@ struct TpCtx {
     unsigned* flags[8] = {};  // rank r: flags[src] = last exchange number src announced to r
     float* cand_v[8] = {};    // rank r's argmax candidates
     int* cand_i[8] = {};
+    float* rows[8] = {};      // rank r: [2][kTpRowsChunk][hidden] floats, the K-split partial products of a prompt chunk
     unsigned* epoch = nullptr;  // this rank's exchange counter (local memory)
     int rank = 0, world = 1;
 };
@@ -602,12 +603,31 @@ __global__ void tp_argmax_advance_kernel(TpCtx c, int ncand, int rows_per_rank, 
     }
 }
 
+// The batched prompt pass under tensor parallelism: the barrier of an exchange as a launch of its own, then the sum of
+// every rank's partial rows (rank order, so all ranks compute the same bits) as a grid over the whole chunk.
+__global__ void tp_barrier_kernel(TpCtx c) { tp_arrive_and_wait(c); }
+__global__ void tp_sum_rows_kernel(TpCtx c, size_t offset, float* out, size_t count4) {
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count4; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float4 p[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < c.world) p[r] = ld_peer_f32x4(c.rows[r] + offset + 4 * i);
+        float4 t = p[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r)
+            if (r < c.world) t.x = __fadd_rn(t.x, p[r].x), t.y = __fadd_rn(t.y, p[r].y), t.z = __fadd_rn(t.z, p[r].z), t.w = __fadd_rn(t.w, p[r].w);
+        *reinterpret_cast<float4*>(out + 4 * i) = t;
+    }
+}
+
 constexpr int kCand = 296;
 constexpr size_t kTpFlagBytes = 256;
-inline size_t tp_shared_bytes(int hidden) {
+constexpr int kTpRowsChunk = 512;  // tokens per chunk of the batched prompt pass
+inline size_t tp_vector_bytes(int hidden) {  // flags, the decode step's two partial vectors, the pick's candidates
     const size_t b = kTpFlagBytes + static_cast<size_t>(2) * hidden * 4 + static_cast<size_t>(kCand) * 8;
     return (b + 255) / 256 * 256;
 }
+inline size_t tp_shared_bytes(int hidden) { return tp_vector_bytes(hidden) + static_cast<size_t>(2) * kTpRowsChunk * hidden * 4; }
 
 struct DMat {
     uint8_t* data = nullptr;
@@ -742,6 +762,7 @@ public:
                 tp.partial[r] = reinterpret_cast<float*>(b + kTpFlagBytes);
                 tp.cand_v[r] = tp.partial[r] + 2 * hidden;
                 tp.cand_i[r] = reinterpret_cast<int*>(tp.cand_v[r] + kCand);
+                tp.rows[r] = reinterpret_cast<float*>(b + tp_vector_bytes(hidden));
             }
             if (const int e = dev(reinterpret_cast<void**>(&tp.epoch), 64); e) return e;
             CU(cudaMemsetAsync(tp.epoch, 0, 64, stream_));
@@ -835,8 +856,9 @@ public:
     // [start_pos, start_pos + n) filled, logits and greedy pick of the last token, position start_pos + n.
     // seq >= 0: the prompt of sequence `seq` of a batch (batch_begin): its own cache, first pick into the batch's token list.
     int prefill(const int* tokens, int n, int start_pos, int seq = -1) {
-        if (tp.world != 1) {
-            err_ = "batched prompt pass is single-GPU; feed the prompt through kcb_decoder_set_prompt + kcb_decoder_run";
+        if (tp.world != 1 && (wo_win.first_block != 0 || wd_win.first_block != 0 || layers.front().wo.k != heads * hd || layers.front().wd.k != inter)) {
+            err_ = "batched prompt pass under tensor parallelism needs every rank's share of the attention output and of the FFN to be whole "
+                   "256-channel super-blocks; feed the prompt through kcb_decoder_set_prompt + kcb_decoder_run";
             return KCB_UNSUPPORTED_OPERATION;
         }
         if (n < 1 || start_pos < 0 || start_pos + n > max_ctx || !tokens || seq >= batch_) return KCB_INVALID_VALUE;
@@ -878,7 +900,8 @@ public:
                 if (const int e = hd == 128 ? attention<128>(L, pQK, qk_stride, m, p0, pA, kc, vc) : attention<64>(L, pQK, qk_stride, m, p0, pA, kc, vc); e)
                     return e;
                 if (const int e = quantize_cols_k(pA, pSlots, qd, m, stream_); e) return e;
-                if (const int e = matmul_kq_q8(L.wo.data, pSlots, pT, L.wo.rows, L.wo.k, m, L.wo.q6, 1, stream_, pWs, kWsBytes); e) return e;
+                if (const int e = matmul_kq_q8(L.wo.data, pSlots, rows_out(), L.wo.rows, L.wo.k, m, L.wo.q6, 1, stream_, pWs, kWsBytes); e) return e;
+                if (const int e = sum_rows(m); e) return e;
                 if (const int e = add_norm_q8(pX, pT, pX, L.ffn_norm, nullptr, pSlots, pSq, hidden, m, eps, 3, 1, stream_); e) return e;
                 // gate and up separately so that each is a contiguous [m][inter] matrix for SwiGLU
                 float* go = pG;
@@ -894,7 +917,8 @@ public:
                 }
                 if (const int e = silu_mul(pG, pU, pG, static_cast<size_t>(m) * inter, stream_); e) return e;
                 if (const int e = quantize_cols_k(pG, pSlots, inter, m, stream_); e) return e;
-                if (const int e = matmul_kq_q8(L.wd.data, pSlots, pT, L.wd.rows, L.wd.k, m, L.wd.q6, 1, stream_, pWs, kWsBytes); e) return e;
+                if (const int e = matmul_kq_q8(L.wd.data, pSlots, rows_out(), L.wd.rows, L.wd.k, m, L.wd.q6, 1, stream_, pWs, kWsBytes); e) return e;
+                if (const int e = sum_rows(m); e) return e;
             }
             if (c0 + m < n) continue;
             // last token: residual add, final norm, logits, greedy pick, position
@@ -902,18 +926,34 @@ public:
             int* pos_word = seq >= 0 ? seq_pos + seq : state;  // position word the pick advances
             int* tok_word = seq >= 0 ? tokB + seq : state + 1;
             int* hist = seq >= 0 ? historyB + static_cast<size_t>(seq) * max_ctx : history;
-            float* lg = seq >= 0 ? logitsB + static_cast<size_t>(seq) * vocab : logits;
+            float* lg = seq >= 0 ? logitsB + static_cast<size_t>(seq) * vocab : logits + static_cast<size_t>(tp.rank) * vocab;
             if (seq >= 0) CU(cudaMemcpyAsync(pos_word, st, 4, cudaMemcpyHostToDevice, stream_));
             else CU(cudaMemcpyAsync(state, st, sizeof st, cudaMemcpyHostToDevice, stream_));
             float* xl = pX + static_cast<size_t>(m - 1) * hidden;
             if (const int e = add_norm_q8_fast(xl, pT + static_cast<size_t>(m - 1) * hidden, out_norm, xq, xd_of(xq, hidden), hidden, eps, stream_); e) return e;
             if (const int e = mv(lm_head, xq, lg); e) return e;
             if (const int e = argmax_partial(lg, vocab, cand_v, cand_i, kCand, stream_); e) return e;
-            argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, tok_word, hist, pos_word, max_ctx);
+            if (tp.world == 1) argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, tok_word, hist, pos_word, max_ctx);
+            else tp_argmax_advance_kernel<<<1, 256, 0, stream_>>>(tp, kCand, vocab, tok_word, hist, pos_word, max_ctx);
             if (const int e = launch_status(); e) return e;
         }
         CU(cudaStreamSynchronize(stream_));
         return KCB_SUCCESS;
+    }
+    // Where a K-split matmul of the prompt pass writes its [m][hidden] product: the chunk scratch on one GPU, this rank's
+    // half of its exchange area (by exchange parity) under tensor parallelism.
+    float* rows_out() { return tp.world == 1 ? pT : tp.rows[tp.rank] + rows_parity_ * static_cast<size_t>(kPrefillChunk) * hidden; }
+    // Under tensor parallelism: all ranks meet, then pT = the sum of every rank's partial rows.  The parity alternates so
+    // that a rank one exchange ahead writes the half its peers are not reading.
+    int sum_rows(int m) {
+        if (tp.world == 1) return KCB_SUCCESS;
+        tp_barrier_kernel<<<1, 32, 0, stream_>>>(tp);
+        if (const int e = launch_status(); e) return e;
+        const size_t count4 = static_cast<size_t>(m) * hidden / 4;
+        const int grid = static_cast<int>(std::min<size_t>((count4 + 255) / 256, static_cast<size_t>(4) * kSmCount));
+        tp_sum_rows_kernel<<<grid, 256, 0, stream_>>>(tp, rows_parity_ * static_cast<size_t>(kPrefillChunk) * hidden, pT, count4);
+        rows_parity_ ^= 1;
+        return launch_status();
     }
     // ---- a batch of independent sequences decoded in lockstep (every sequence at the same position) ----------------
     // One step feeds one token per sequence through every layer together: the weights are read once per step for the whole
@@ -1042,7 +1082,7 @@ public:
     long long weight_bytes = 0;
 
 private:
-    static constexpr int kPrefillChunk = 512;
+    static constexpr int kPrefillChunk = kTpRowsChunk;
     // Scratch of the batched prompt pass for chunks of up to m tokens, allocated on first use.
     int prefill_buffers(int m) {
         if (m <= prefill_cap_) return KCB_SUCCESS;
@@ -1460,6 +1500,7 @@ private:
     int* cand_i = nullptr;
     int *xq = nullptr, *xq_wo = nullptr, *xq_wd = nullptr, *state = nullptr, *forced = nullptr, *history = nullptr;
     cudaStream_t stream_ = nullptr;
+    size_t rows_parity_ = 0;  // which half of the exchange area's row buffers the next K-split matmul of a prompt chunk writes
     int* trace_ = nullptr;
     size_t trace_words_ = 0, trace_off_ = 0;
     cudaGraph_t graph_ = nullptr;

@@ -24,8 +24,10 @@ def _shape(which=0):
     from kernelcore_b200 import tiny_model as tm
     if which == 0:   # FFN share 384 = 1.5 super-blocks (a straddled K window), 8 query / 2 kv heads of 64
         return tm.Shape("tp-tiny", 512, 768, 2, 8, 2, 64, 512, 48)
-    # attention-output share 384 channels as well (12 heads of 64 over 2 ranks): both K windows straddle a super-block
-    return tm.Shape("tp-straddle", 768, 768, 2, 12, 4, 64, 512, 48)
+    if which == 1:   # attention-output share 384 channels as well (12 heads of 64 over 2 ranks): both K windows straddle a super-block
+        return tm.Shape("tp-straddle", 768, 768, 2, 12, 4, 64, 512, 48)
+    # every share a whole number of super-blocks (256 attention channels, 512 FFN rows per rank): the batched prompt pass runs too
+    return tm.Shape("tp-aligned", 512, 1024, 2, 8, 2, 64, 512, 48)
 
 
 def _free_port():
@@ -39,7 +41,7 @@ def _worker(rank, world, port, which, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import torch.distributed as dist
     import torch.distributed._symmetric_memory as symm_mem
-    from kernelcore_b200 import decoder, tiny_model as tm
+    from kernelcore_b200 import decoder, lib, tiny_model as tm
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -61,12 +63,25 @@ def _worker(rank, world, port, which, out):
             r0, r1 = dec.local_rows()
             per_step.append(logits[r0:r1].copy())
         _, hist, pos = dec.read(STEPS)
-        out[rank] = (np.stack(per_step), hist.copy(), pos, decoder.FastDecoder.tp_timeouts())
+        # the batched prompt pass under tensor parallelism, then two more steps through the graph on top of its cache
+        dist.barrier()
+        batched = None
+        try:
+            dec.prefill(prompt)
+            logits, _, ppos = dec.read(0)
+            r0, r1 = dec.local_rows()
+            first = logits[r0:r1].copy()
+            dec.run(2)
+            _, hist2, ppos2 = dec.read(PROMPT + 2)
+            batched = (first, (ppos, ppos2), hist2.copy())
+        except lib.KcbError as e:      # shares that straddle a super-block: refused on every rank alike, before any launch
+            batched = str(e)
+        out[rank] = (np.stack(per_step), hist.copy(), pos, decoder.FastDecoder.tp_timeouts(), batched)
         dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("which", [0, 1])
+@pytest.mark.parametrize("which", [0, 1, 2])
 def test_two_rank_decoder_matches_single_gpu(which):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -96,3 +111,14 @@ def test_two_rank_decoder_matches_single_gpu(which):
             errs.append(rel_diff(tp_logits[s], logits))
     assert max(errs) < 3e-2, errs
     assert errs[0] < 1e-4, errs
+    # the batched prompt pass under tensor parallelism
+    if which != 2:
+        assert isinstance(res[0][4], str) and "super-blocks" in res[0][4] and isinstance(res[1][4], str)
+        return
+    (f0, pos0, h0), (f1, pos1, h1) = res[0][4], res[1][4]
+    assert pos0 == pos1 == (PROMPT, PROMPT + 2)
+    assert np.array_equal(h0, h1)                                 # the ranks went on with the same tokens
+    with decoder.FastDecoder(shape, model) as dec:
+        dec.prefill(prompt)
+        assert rel_diff(np.concatenate([f0, f1]), dec.read(0)[0]) < 3e-2
+    assert res[0][3] == 0 and res[1][3] == 0
