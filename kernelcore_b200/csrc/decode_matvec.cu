@@ -396,7 +396,7 @@ __global__ void __launch_bounds__(kThreads, 1) dmv_kernel(const DmvMat m4, const
     } else if (PRO == 1) {
         pro_add_norm<4>(pro.x_in, pro.t, pro.x_out, blockIdx.x == 0, pro.wn, sxq, sxd, nsb * 256, pro.eps, gsum);
     } else if (PRO == 2) {
-        pro_swiglu<16>(pro.g, pro.u, sxq, sxd, nsb * 256);
+        pro_swiglu<(KSPLIT > 2 ? 32 : 16)>(pro.g, pro.u, sxq, sxd, nsb * 256);  // n <= 8192, 16384 with four warps per row
     } else {
         pro_combine(pro.part, sxq, sxd, pro.heads, pro.hd, pro.nsplit);
     }
@@ -486,6 +486,30 @@ int row_times(int rows4, int rows6, int tr) {
     return std::max(r4, r6) * tr;
 }
 
+// k in (8192, 16384], a multiple of 1024: 8-row tiles, four warps per row (at most 16 super-blocks each).
+template <int PRO>
+int dmv_launch_quad(const DmvMat& m4, const DmvMat& m6, int nsb, const DmvPro& pro, bool pdl, cudaStream_t s) {
+    if (nsb > 64 || nsb % 4 || PRO == 1 || PRO == 3) return KCB_UNSUPPORTED_OPERATION;  // (no norm / merge prologue is that wide)
+    constexpr int TR = 8;
+    const bool has4 = m4.rows > 0;
+    const size_t fixed = kBarBytes + static_cast<size_t>((nsb * 320 + 127) / 128) * 128;
+    const int rows = has4 ? m4.rows : m6.rows;
+    const int tiles = (rows + TR - 1) / TR, c = std::min(tiles, kSmCount);
+    const size_t stage_bytes = static_cast<size_t>(TR) * nsb * (has4 ? kQ4KBlock : kQ6KBlock);
+    const int st = stages_for((tiles + c - 1) / c, stage_bytes, fixed);
+    if (st < 1) return KCB_UNSUPPORTED_OPERATION;
+    const size_t smem = fixed + static_cast<size_t>(st) * stage_bytes;
+    static PerDeviceFlag raised[4];
+    const bool three = nsb <= 48;  // super-blocks per warp <= 12: three rounds of four
+    if constexpr (PRO == 0 || PRO == 2) {
+        if (has4) return three ? launch_dmv(dmv_kernel<3, TR, 4, PRO, true, false>, c, smem, pdl, s, m4, m6, c, nsb, pro, st, 1, raised[0])
+                               : launch_dmv(dmv_kernel<4, TR, 4, PRO, true, false>, c, smem, pdl, s, m4, m6, c, nsb, pro, st, 1, raised[1]);
+        return three ? launch_dmv(dmv_kernel<3, TR, 4, PRO, false, true>, c, smem, pdl, s, m4, m6, 0, nsb, pro, 1, st, raised[2])
+                     : launch_dmv(dmv_kernel<4, TR, 4, PRO, false, true>, c, smem, pdl, s, m4, m6, 0, nsb, pro, 1, st, raised[3]);
+    }
+    return KCB_UNSUPPORTED_OPERATION;
+}
+
 template <int PRO>
 int dmv_dispatch(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const DmvPro& pro, bool pdl, cudaStream_t s) {
     const int nsb = k / 256;
@@ -493,9 +517,11 @@ int dmv_dispatch(const void* w4, float* y4, int rows4, const void* w6, float* y6
     if (nsb <= 16)  // 8-row tiles where they balance the SMs better (few tiles per CTA), else two rows per warp
         return row_times(rows4, rows6, 16) < row_times(rows4, rows6, 32) ? dmv_launch_narrow<PRO, 16>(m4, m6, nsb, pro, pdl, s)
                                                                           : dmv_launch_narrow<PRO, 32>(m4, m6, nsb, pro, pdl, s);
-    // k up to 8192: 4-row tiles, two warps per row (16 super-blocks each at most)
+    // k up to 8192: 8-row tiles, two warps per row (16 super-blocks each at most); up to 16384: four warps per row
     const bool has4 = rows4 > 0;
-    if (nsb > 32 || nsb % 2 || (rows4 > 0 && rows6 > 0)) return KCB_UNSUPPORTED_OPERATION;
+    if (rows4 > 0 && rows6 > 0) return KCB_UNSUPPORTED_OPERATION;
+    if (nsb > 32) return dmv_launch_quad<PRO>(m4, m6, nsb, pro, pdl, s);
+    if (nsb % 2) return KCB_UNSUPPORTED_OPERATION;
     constexpr int TR = 8;
     const size_t fixed = kBarBytes + static_cast<size_t>((nsb * 320 + 127) / 128) * 128;
     const int rows = has4 ? rows4 : rows6;
@@ -522,7 +548,8 @@ bool decode_matvec_shape_ok(int rows4, int rows6, int k) {
     // (rows % 8 and an even number of super-blocks keep every Q6_K plane of a 4- or 8-row tile 16-byte aligned)
     const int nsb = k / 256;
     if (nsb <= 16) return true;
-    return nsb <= 32 && nsb % 2 == 0 && !(rows4 && rows6);
+    if (rows4 && rows6) return false;
+    return nsb <= 32 ? nsb % 2 == 0 : (nsb <= 64 && nsb % 4 == 0);  // (k > 8192: given Q8 blocks or the SwiGLU prologue only)
 }
 
 // y4 = W4 a, y6 = W6 a (either may be absent: rows 0) with the activation vector a produced by the prologue:

@@ -1351,6 +1351,34 @@ private:
         }
 #undef KCB_ATTN
     }
+    // A matrix above fuse_limit_ bytes (32 MB; KCB_DECODE_FUSE_MB) streams for longer than its producer takes as a launch
+    // of its own, while a prologue repeated by every CTA grows with the vector: measured on Qwen3-8B shapes, the 41 MB
+    // down projection with its 12288-wide SwiGLU folded in and the 57 MB gate|up with its norm folded in gave 380 tokens/s,
+    // with both producers as launches 429 (no fusion at all: 402); on Llama-3.2-3B shapes only the lm_head is above the
+    // limit (723 against 720).
+    bool streams_long(const DMat& m) const { return kcb_kquant_bytes(m.rows, m.k, m.q6) > fuse_limit_; }
+    // cur (+= add) -> RMSNorm * w -> Q8 -> y = [W...] a, for one matrix or a Q4_K / Q6_K pair on the same input.
+    // Fused: one launch, the new residual stream lands in `other` and the two pointers swap.  Streaming: in place.
+    int norm_then_matvecs(const std::vector<DMat>& mats, float* y, float*& cur, float*& other, const float* add, const float* w, bool pdl) {
+        size_t bytes = 0;
+        for (const DMat& m : mats) bytes += kcb_kquant_bytes(m.rows, m.k, m.q6);
+        int* xs = add ? trace_slot(4 * hidden) : nullptr;
+        if (bytes > fuse_limit_) {
+            if (const int e = add_norm_q8_fast(cur, add, w, xq, xd_of(xq, hidden), hidden, eps, stream_); e) return e;
+            if (xs) CU(cudaMemcpyAsync(xs, cur, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
+            if (const int e = trace_copy(xq, hidden); e) return e;
+            for (const DMat& m : mats) {
+                if (const int e = mv(m, xq, y); e) return e;
+                y += m.rows;
+            }
+            return KCB_SUCCESS;
+        }
+        const Pair p = pair_of(mats, y);
+        if (const int e = decode_matvec_norm(p.w4, p.y4, p.rows4, p.w6, p.y6, p.rows6, hidden, cur, add, other, w, eps, pdl, stream_, trace_slot(hidden)); e) return e;
+        std::swap(cur, other);
+        if (xs) CU(cudaMemcpyAsync(xs, cur, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
+        return KCB_SUCCESS;
+    }
     int record_fused() {
         const int qd = heads * hd;
         int *pos_p = state, *tok_p = state + 1, *nforced_p = state + 2, *used_p = state + 3;
@@ -1364,11 +1392,7 @@ private:
         const float* add = nullptr;   // what the next norm prologue adds to the residual stream first
         for (size_t l = 0; l < layers.size(); ++l) {
             const DLayer& L = layers[l];
-            const Pair a = pair_of(L.qkv, qkv);
-            int* xs = add ? trace_slot(4 * hidden) : nullptr;
-            if (const int e = decode_matvec_norm(a.w4, a.y4, a.rows4, a.w6, a.y6, a.rows6, hidden, cur, add, other, L.attn_norm, eps, pdl, stream_, trace_slot(hidden)); e) return e;
-            std::swap(cur, other);
-            if (xs) CU(cudaMemcpyAsync(xs, cur, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
+            if (const int e = norm_then_matvecs(L.qkv, qkv, cur, other, add, L.attn_norm, pdl); e) return e;
             float* vrows = qkv + qd + kv_heads * hd;
             const float *ff = rope_ff, *qn = L.q_norm, *kn = L.k_norm;
             if (const int e = launch_pdl(rope_kv_f16_kernel, dim3((heads + 2 * kv_heads + 3) / 4), dim3(128), 0, pdl, qkv, vrows, 0, 0, const_cast<const int*>(pos_p),
@@ -1385,20 +1409,19 @@ private:
             if (const int e = trace_copy(xq_wo, L.wo.k); e) return e;
             const Pair o = pair_of(L.wo, t);
             if (const int e = decode_matvec_q8(o.w4, o.y4, o.rows4, o.w6, o.y6, o.rows6, L.wo.k, xq_wo, xd_of(xq_wo, L.wo.k), pdl, stream_); e) return e;
-            const Pair gup = pair_of(L.gu, gu);
-            xs = trace_slot(4 * hidden);
-            if (const int e = decode_matvec_norm(gup.w4, gup.y4, gup.rows4, gup.w6, gup.y6, gup.rows6, hidden, cur, t, other, L.ffn_norm, eps, pdl, stream_, trace_slot(hidden)); e)
-                return e;
-            std::swap(cur, other);
-            if (xs) CU(cudaMemcpyAsync(xs, cur, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
-            const Pair dn = pair_of(L.wd, t);
-            if (const int e = decode_matvec_swiglu(dn.w4, dn.y4, dn.rows4, dn.w6, dn.y6, dn.rows6, L.wd.k, gu, gu + inter, pdl, stream_, trace_slot(L.wd.k)); e) return e;
+            if (const int e = norm_then_matvecs(L.gu, gu, cur, other, t, L.ffn_norm, pdl); e) return e;
+            if (streams_long(L.wd)) {  // SwiGLU + quantize as its own launch, then the streaming matvec
+                if (const int e = silu_mul_q8(gu, gu + inter, nullptr, nullptr, xq_wd, xd_of(xq_wd, L.wd.k), inter, 1, stream_); e) return e;
+                if (const int e = trace_copy(xq_wd, L.wd.k); e) return e;
+                if (const int e = mv(L.wd, xq_wd, t); e) return e;
+            } else {
+                const Pair dn = pair_of(L.wd, t);
+                if (const int e = decode_matvec_swiglu(dn.w4, dn.y4, dn.rows4, dn.w6, dn.y6, dn.rows6, L.wd.k, gu, gu + inter, pdl, stream_, trace_slot(L.wd.k)); e)
+                    return e;
+            }
             add = t;
         }
-        const Pair lm = pair_of(lm_head, logits);
-        int* xs = add ? trace_slot(4 * hidden) : nullptr;
-        if (const int e = decode_matvec_norm(lm.w4, lm.y4, lm.rows4, lm.w6, lm.y6, lm.rows6, hidden, cur, add, other, out_norm, eps, pdl, stream_, trace_slot(hidden)); e) return e;
-        if (xs) CU(cudaMemcpyAsync(xs, other, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
+        if (const int e = norm_then_matvecs(std::vector<DMat>{lm_head}, logits, cur, other, add, out_norm, pdl); e) return e;
         if (const int e = argmax_partial(logits, vocab, cand_v, cand_i, kCand, stream_); e) return e;
         argmax_advance_kernel<<<1, 256, 0, stream_>>>(cand_v, cand_i, kCand, tok_p, history, pos_p, max_ctx);
         return launch_status();
@@ -1500,6 +1523,7 @@ private:
     int* cand_i = nullptr;
     int *xq = nullptr, *xq_wo = nullptr, *xq_wd = nullptr, *state = nullptr, *forced = nullptr, *history = nullptr;
     cudaStream_t stream_ = nullptr;
+    size_t fuse_limit_ = (getenv("KCB_DECODE_FUSE_MB") ? static_cast<size_t>(atoi(getenv("KCB_DECODE_FUSE_MB"))) : 32) << 20;
     size_t rows_parity_ = 0;  // which half of the exchange area's row buffers the next K-split matmul of a prompt chunk writes
     int* trace_ = nullptr;
     size_t trace_words_ = 0, trace_off_ = 0;

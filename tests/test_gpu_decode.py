@@ -113,8 +113,14 @@ def _int8_diffs(a, b):
     return int((d != 0).sum())
 
 
+def _wide_ffn(max_ctx):
+    # FFN of 9216 = 36 super-blocks: the down projection takes the four-warps-per-row form of the decode matvec
+    # (k above 8192, Qwen3-8B's 12288 in small), SwiGLU prologue included
+    return tm.Shape("wide-ffn", 256, 9216, 2, 4, 2, 64, 256, max_ctx)
+
+
 @pytest.mark.parametrize("fused", [1, 0])
-@pytest.mark.parametrize("shape_fn", [tm.tiny, tm.tiny_qwen])
+@pytest.mark.parametrize("shape_fn", [tm.tiny, tm.tiny_qwen, _wide_ffn])
 def test_graph_decoder_stage_by_stage_with_flip_count(shape_fn, fused, monkeypatch):
     """Why the test above needs 3e-2, measured instead of argued.  The decoder traces the int8 words of every activation
     vector it quantizes (five per layer and the lm_head's input) and the residual stream after each addition.
@@ -122,7 +128,8 @@ def test_graph_decoder_stage_by_stage_with_flip_count(shape_fn, fused, monkeypat
     Stage by stage: the oracle is run with every one of those vectors compared with the decoder's and then replaced by
     it, so each of its stages works on exactly the inputs the decoder's stage had.  On 40 positions: no int8 value is
     ever off by more than one step, at most 2 values of a step's 2816 differ (a value on a rounding boundary after a
-    sum taken in another order), 12 over all positions; the residual stream agrees to 1e-4 of its largest magnitude
+    sum taken in another order; 1 in 2000 on the model with the 9216-wide FFN), 12 over all positions; the residual
+    stream agrees to 1e-4 of its largest magnitude
     (2e-3 on a step where one of those values fed a matvec), and the logits to 1e-5.
 
     Free-running (oracle on its own words): up to and including the last position before the first differing int8
@@ -143,6 +150,7 @@ def test_graph_decoder_stage_by_stage_with_flip_count(shape_fn, fused, monkeypat
         assert (d.launches_per_token == 4 + 7 * shape.layers) == bool(fused)
         words = d.enable_trace()
         assert words == staged.trace_words()
+        per_step = 4 * sum(n for kind, _, n in staged.trace_layout() if kind == "q8")     # int8 values a step quantizes
         d.set_prompt(forced)
         own = np.zeros(words, np.int32)
         for pos, tok in enumerate(forced):
@@ -151,7 +159,7 @@ def test_graph_decoder_stage_by_stage_with_flip_count(shape_fn, fused, monkeypat
             trace = d.read_trace()
             want = staged.decode_port(staged.embed(tok), pos, kv_f16=True, forced=trace)
             values, vectors, step, residual = staged.forced_stats
-            assert step <= 1 and values <= 2, (pos, staged.forced_stats)
+            assert step <= 1 and values <= max(2, per_step // 2000), (pos, staged.forced_stats)
             assert residual < (2e-3 if values else 1e-4), (pos, staged.forced_stats)
             assert rel_diff(logits, want) < 1e-5, pos
             total += values
@@ -162,7 +170,7 @@ def test_graph_decoder_stage_by_stage_with_flip_count(shape_fn, fused, monkeypat
                 clean += 1
                 assert rel_diff(logits, lone) < 1e-5, pos
             assert rel_diff(logits, lone) < 3e-2, pos
-    assert total <= 12 and clean >= 6, (total, clean)
+    assert total <= max(12, 40 * per_step // 4000) and clean >= (6 if per_step < 4000 else 1), (total, clean)
 
 
 def test_full_size_logits_against_the_reference_decode_loop():
