@@ -444,6 +444,39 @@ def q4k_config0(torch, kquant, synth, peak):
             "protocol": f"{n} launches in one CUDA graph over {nmat} rotating matrices, median of 5 replays"}
 
 
+def q4k_stream_bench(rows, k=3072, nmat=3, n=30):
+    """The bulk-copy streaming matvec on a Q4_K matrix too large for L2 (rows x 3072; 262144 rows = 453 MB): nmat rotating
+    copies, n launches in one CUDA graph, median of 5 replays."""
+    import torch
+
+    from kernelcore_b200 import kquant, synth
+    base = synth.q4k_blocks(rows, k, 0)
+    mats = [kquant.KMatrix(np.roll(base, i, axis=0), rows, k, False) for i in range(nmat)]
+    x = torch.from_numpy(synth.activations(k, 1)).cuda()
+    xq, xd = kquant.quantize_q8x4(x, kquant.Q8Scratch(k))
+    y = torch.empty(rows, device="cuda")
+    st, g = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(st):
+        for i in range(3):
+            kquant.matvec_q8(mats[i % nmat], xq, xd, y)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(n):
+                kquant.matvec_q8(mats[i % nmat], xq, xd, y)
+    times = []
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / n * 1e3)
+    us = statistics.median(times[1:])
+    alg = rows * (k // 256) * 144 + k * 4 + rows * 4
+    peak = measured_peak()[0]
+    return {"rows": rows, "k": k, "us_per_matvec": us, "gbs": alg / us / 1e3, "frac_of_measured_hbm": alg / us / 1e3 / peak, "algorithmic_bytes": alg}
+
+
 def matmul_bench(ms_list=(32, 128, 512, 2048), reps=5, q6=False):
     """Benchmark spec configs[2]: Y[M x 8192] = X[M x 3072] . W^T, W Q4_K; X quantized on the fly to per-256 int8 slots
     (quantize_cols_k) and contracted on the tensor cores (tcgen05 int8).  One step = quantize + matmul.
@@ -773,7 +806,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="lm_head", choices=["lm_head", "decode", "matmul"],
+    ap.add_argument("--workload", default="lm_head", choices=["lm_head", "decode", "matmul", "q4k_matvec"],
                     help="lm_head: the benchmark line; decode: Llama-3.2-3B-shape decode only (profiling, quick checks)")
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--gen", type=int, default=128)
@@ -788,6 +821,9 @@ def main():
     ROWS = args.rows
     if args.workload == "decode":
         run_decode(args)
+    elif args.workload == "q4k_matvec":
+        print(json.dumps({"metric": "q4k_matvec_hbm_gbs", "unit": "GB/s", "n_gpus": 1, "data": "synthetic",
+                          "detail": q4k_stream_bench(args.rows if args.rows != 128256 else 262144)}))
     elif args.workload == "matmul":
         print(json.dumps({"metric": ("q6k" if args.q6 else "q4k") + "_matmul_tflops", "unit": "TFLOP/s", "n_gpus": 1, "data": "synthetic",
                           "detail": matmul_bench((args.prompt,), reps=2, q6=args.q6)}))
