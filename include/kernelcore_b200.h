@@ -200,8 +200,9 @@ int kcb_matvec_q6k_f32x_sharded(const void* planes_dev, const float* x_dev, floa
  * the call allocates nothing and needs no caller scratch -- for hosts that may not allocate device memory
  * at call time (plugins under an application that owns all buffers, allocation-free serving loops).
  * k % 256 == 0 and k <= kcb_static_scratch_max_k() (16384), else InvalidValue.  The first call on a device
- * looks up the array's address: make it before any stream capture.  All calls share the one array per GPU:
- * calls whose GPU work may overlap race; keep them on one stream. */
+ * looks up the array's address and loads the kernels (the CUDA runtime may allocate for that): make one warm-up
+ * call before any stream capture and before memory is counted; later calls only launch.  All calls share the
+ * one array per GPU: calls whose GPU work may overlap race; keep them on one stream. */
 int kcb_matvec_q4k_f32x_static(const void* w_dev, const float* x_dev, float* y_dev, int rows, int k, void* stream);
 int kcb_static_scratch_max_k(void);
 

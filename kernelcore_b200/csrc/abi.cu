@@ -161,7 +161,7 @@ int kcb_matmul_kq_q8_ws(const void* w, const int32_t* xq, float* y, int rows, in
     return matmul_kq_q8(w, xq, y, rows, k, ncols, q6, q8k, st(s), workspace, workspace_bytes);
 }
 size_t kcb_matmul_tc_workspace_bytes(int rows, int k, int ncols) { return matmul_tc_workspace_bytes(rows, k, ncols); }
-unsigned kcb_tc_timeouts(void) { return tc_timeouts() + tc_pipe_timeouts(); }
+unsigned kcb_tc_timeouts(void) { return tc_pipe_timeouts(); }
 int kcb_matmul_tc_k_slices(int rows, int k, int ncols) { return matmul_tc_pipe_k_slices(rows, k, ncols); }
 int kcb_kernel_count(void) { return kernel_count(); }
 const char* kcb_kernel_name(int i) { return kernel_name(i); }

@@ -128,7 +128,7 @@ File::File(const std::string& path) {
         if (std::memcmp(c.p, "GGUF", 4) != 0) throw std::runtime_error("not a GGUF file: " + path);
         c.p += 4;
         const uint32_t version = c.take<uint32_t>();
-        if (version < 2 || version > 3) throw std::runtime_error("GGUF version not supported: " + std::to_string(version));
+        if (version < 2) throw std::runtime_error("GGUF version not supported: " + std::to_string(version));  // (as llm/gguf.cpp:95)
         const uint64_t n_tensors = c.take<uint64_t>(), n_meta = c.take<uint64_t>();
         for (uint64_t i = 0; i < n_meta; ++i) {
             std::string key = c.str();
@@ -141,22 +141,43 @@ File::File(const std::string& path) {
             t.name = c.str();
             const uint32_t nd = c.take<uint32_t>();
             if (nd == 0 || nd > 4) throw std::runtime_error("tensor rank not supported: " + t.name);
-            for (uint32_t d = 0; d < nd; ++d) t.ne.push_back(static_cast<int64_t>(c.take<uint64_t>()));
+            for (uint32_t d = 0; d < nd; ++d) {
+                const uint64_t n = c.take<uint64_t>();
+                if (n == 0 || n > (uint64_t(1) << 40)) throw std::runtime_error("tensor extent out of range: " + t.name);
+                t.ne.push_back(static_cast<int64_t>(n));
+            }
             t.type = c.take<uint32_t>();
             t.offset = c.take<uint64_t>();
+            // A type this reader has no block size for (BF16, Q5_0, Q3_K, ...) stays in the list with bytes = 0 and no
+            // data pointer, as the reference lists it (llm/gguf.cpp:126-130): the file opens, the tensor cannot be read.
             size_t bb = 0, bv = 0;
-            if (!blockInfo(t.type, &bb, &bv) || t.ne[0] % static_cast<int64_t>(bv)) throw std::runtime_error("tensor type not supported: " + t.name);
-            size_t rows = 1;
-            for (uint32_t d = 1; d < nd; ++d) rows *= static_cast<size_t>(t.ne[d]);
-            t.bytes = rows * (static_cast<size_t>(t.ne[0]) / bv) * bb;
+            t.bytes = 0;
+            if (blockInfo(t.type, &bb, &bv)) {
+                if (t.ne[0] % static_cast<int64_t>(bv)) throw std::runtime_error("row length is not a whole number of blocks: " + t.name);
+                unsigned __int128 bytes = static_cast<unsigned __int128>(t.ne[0] / static_cast<int64_t>(bv)) * bb;
+                for (uint32_t d = 1; d < nd; ++d) {
+                    bytes *= static_cast<uint64_t>(t.ne[d]);
+                    if (bytes > size_) throw std::runtime_error("tensor is larger than the file: " + t.name);
+                }
+                if (bytes > size_) throw std::runtime_error("tensor is larger than the file: " + t.name);
+                t.bytes = static_cast<size_t>(bytes);
+            }
             order.push_back(std::move(t));
         }
         const auto al = meta_.find("general.alignment");
-        const size_t align = al != meta_.end() && al->second.num >= 1 ? static_cast<size_t>(al->second.num) : 32;
-        const size_t data0 = (static_cast<size_t>(c.p - base_) + align - 1) / align * align;
+        const double want = al != meta_.end() ? al->second.num : 32.0;
+        if (!(want >= 1.0 && want <= 65536.0)) throw std::runtime_error("general.alignment out of range");
+        const size_t align = static_cast<size_t>(want);
+        if (align & (align - 1)) throw std::runtime_error("general.alignment is not a power of two");
+        const size_t header = static_cast<size_t>(c.p - base_);
+        const size_t data0 = (header + align - 1) / align * align;
+        if (data0 > size_ && !order.empty()) throw std::runtime_error("the file ends inside its header");
         for (Tensor& t : order) {
-            if (data0 + t.offset + t.bytes > size_) throw std::runtime_error("tensor data runs past the end of the file: " + t.name);
-            t.data = base_ + data0 + t.offset;
+            if (t.bytes != 0) {  // (written so that no sum of file-controlled numbers can wrap)
+                const size_t room = data0 <= size_ ? size_ - data0 : 0;
+                if (t.offset > room || t.bytes > room - t.offset) throw std::runtime_error("tensor data runs past the end of the file: " + t.name);
+                t.data = base_ + data0 + t.offset;
+            }
             tensors_[t.name] = t;
         }
     } catch (...) {

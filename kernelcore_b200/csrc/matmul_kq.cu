@@ -177,17 +177,14 @@ int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int nc
     if (rows <= 0 || k <= 0 || k % 256 || k > 32768 || ncols <= 0 || !w || !xq || !y) return KCB_INVALID_VALUE;
     if (misaligned(w, 16) || misaligned(xq, 16) || misaligned(y, 4)) return KCB_INVALID_POINTER;
     // Per-256 activation slots and whole 128-row tiles go to the tensor cores (bit-identical results);
-    // KCB_MATMUL_TC=0 keeps everything on the CUDA-core kernel below, KCB_MATMUL_TC=1 selects the earlier
-    // one-CTA-per-tile tensor-core kernels instead of the pipelined ones (kept for comparison measurements).
-    static const int tc = [] {
+    // KCB_MATMUL_TC=0 keeps everything on the CUDA-core kernel below (comparison measurements).
+    static const bool tc = [] {
         const char* e = getenv("KCB_MATMUL_TC");
-        return e ? atoi(e) : 2;
+        return !e || atoi(e) != 0;
     }();
     // (the activation slots of 85 * nsb ints are read in 16-byte pieces: nsb % 4 == 0)
-    if (tc && q8k && rows % 128 == 0 && ncols >= 16 && (k / 256) % 4 == 0) {
-        if (tc == 1) return q6 ? matmul_q6k_q8k_tc(w, xq, y, rows, k, ncols, s) : matmul_q4k_q8k_tc(w, xq, y, rows, k, ncols, s);
+    if (tc && q8k && rows % 128 == 0 && ncols >= 16 && (k / 256) % 4 == 0)
         return matmul_kq_q8k_tc_pipe(w, xq, y, rows, k, ncols, q6, workspace, workspace_bytes, s);
-    }
     const int nsb = k / 256, nb = nsb * 8;
     const int slot_ints = q8k ? nsb * 85 : nb * 11;
     const size_t col_bytes = static_cast<size_t>(nsb * 64 + nb * 2 + (q6 ? nb * 2 : 0)) * 4;

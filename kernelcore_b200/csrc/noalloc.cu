@@ -12,7 +12,9 @@
 // Limits and rules:
 //   * k <= kStaticMaxK (16384 columns; 22 KB of scratch per GPU); larger k is refused with InvalidValue;
 //   * the first call on a device resolves the array's device address (cudaGetSymbolAddress, once per
-//     device, with that device current).  Make that first call outside any stream capture;
+//     device, with that device current), loads the kernels' module and may set a kernel attribute.  That
+//     warm-up call is the one to make outside any stream capture and before memory is counted; from the
+//     second call on, the call makes no CUDA call other than its two launches;
 //   * every call uses the same array, so two calls whose GPU work can overlap (different streams, or
 //     different host threads) race on it -- serialise them on one stream.  The quantizer rewrites every
 //     word the matvec reads, so nothing has to be cleared between calls.
@@ -23,6 +25,8 @@
 #include "common.cuh"
 #include "ops.h"
 
+#include <atomic>
+
 namespace {
 
 constexpr int kStaticMaxK = 16384;
@@ -32,21 +36,24 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) int g_static_q8_scratch[kStaticInts];
 
 // Host code must not pass g_static_q8_scratch itself to a kernel: on the host that name is only a handle.
-// The device address is looked up once per device and cached here.
-int* g_scratch_addr[kMaxDevices] = {};
+// The device address is looked up once per device and cached here (two host threads making their first call on
+// one device may both look it up; they store the same value).
+std::atomic<int*> g_scratch_addr[kMaxDevices] = {};
 
 int scratch_for_current_device(int** out) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return kcb::KCB_INVALID_DEVICE;
-    if (!g_scratch_addr[dev]) {
+    int* addr = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!addr) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_static_q8_scratch) != cudaSuccess || !p) {
             cudaGetLastError();
             return kcb::KCB_INTERNAL_ERROR;
         }
-        g_scratch_addr[dev] = static_cast<int*>(p);
+        addr = static_cast<int*>(p);
+        g_scratch_addr[dev].store(addr, std::memory_order_release);
     }
-    *out = g_scratch_addr[dev];
+    *out = addr;
     return kcb::KCB_SUCCESS;
 }
 

@@ -1,5 +1,8 @@
-// Internal C++ launchers behind the C ABI.  Every function enqueues work on `s` and returns a
-// status code (common.cuh); none synchronises or allocates.
+// Internal C++ launchers behind the C ABI.  Every function that takes a stream enqueues work on it and returns a
+// status code (common.cuh) without synchronising or allocating; the first launch of a kernel that needs more than 48 KB
+// of shared memory makes one cudaFuncSetAttribute call per device, and every launch of a tensor-core matmul
+// encodes its two tensor maps on the host.  The few functions without a stream (the *_timeouts readers, the poll-limit
+// and reset calls) are synchronous copies from or to a device variable.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -37,12 +40,6 @@ int quantize_cols_k(const float* x, int* q, int k, int ncols, cudaStream_t s);
 // matmul_kq.cu
 int matmul_kq_q8(const void* w, const int* xq, float* y, int rows, int k, int ncols, int q6, int q8k, cudaStream_t s, void* workspace = nullptr,
                  size_t workspace_bytes = 0);
-
-// matmul_tc.cu
-int matmul_q4k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s);
-int matmul_q6k_q8k_tc(const void* w, const int* xq, float* y, int rows, int k, int ncols, cudaStream_t s);
-unsigned tc_timeouts();
-int matmul_tc_k_slices(int rows, int k, int ncols);
 
 // matmul_tc_pipe.cu: the warp-specialised tensor-core kernels.  `workspace` (device, may be null) allows K slices.
 int matmul_kq_q8k_tc_pipe(const void* w, const int* xq, float* y, int rows, int k, int ncols, int q6, void* workspace, size_t workspace_bytes,

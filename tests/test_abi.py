@@ -99,3 +99,39 @@ def test_tensor_core_k_slices_follow_the_wave_model():
     assert ks(3072, 8192, 32) == 6                                     # 24 tiles x 32 super-blocks
     assert ks(100, 1024, 16) == 0 and ks(128, 768, 16) == 0            # not tensor-core shapes
     assert ws(8192, 3072, 512) == 0 and ws(3072, 8192, 512) == 3 * 512 * 3072 * 4 and ws(100, 1024, 16) == 0
+
+
+def test_misaligned_pointers_are_refused_before_any_launch():
+    """The kernels read weights, quantized activations and fp32 vectors 16 bytes at a time, and bulk copies need 16-byte
+    aligned addresses; the reference's range check accepts any interior pointer.  So the launchers check alignment on
+    the host and answer InvalidPointer (5) instead of letting a kernel fault.  Nothing here launches: every call is
+    refused first (which is why it runs without a GPU), and the pointers are never dereferenced."""
+    import ctypes as C
+    from kernelcore_b200 import lib
+    L = lib.raw
+    good, odd4, odd1 = C.c_void_p(0x7000_0000_1000), C.c_void_p(0x7000_0000_1004), C.c_void_p(0x7000_0000_1001)
+    INVALID_POINTER, INVALID_VALUE = 5, 2
+    f = C.c_float
+    cases = [
+        (L.kcb_matvec_q4k_q8, (odd4, good, good, good, 64, 1024, None)),          # weights need 16
+        (L.kcb_matvec_q4k_q8, (good, odd4, good, good, 64, 1024, None)),          # Q8 words need 16
+        (L.kcb_matvec_q4k_q8, (good, good, odd4, good, 64, 1024, None)),          # Q8 scales need 16
+        (L.kcb_matvec_q4k_q8, (good, good, good, odd1, 64, 1024, None)),          # outputs need 4
+        (L.kcb_matvec_q6k_q8, (odd4, good, good, good, 64, 1024, None)),
+        (L.kcb_quantize_q8x4, (odd1, good, good, 32, None)),                      # scalar loads and stores: 4
+        (L.kcb_quantize_q8x4, (good, odd1, good, 32, None)),
+        (L.kcb_quantize_cols_k, (odd1, good, 1024, 4, None)),
+        (L.kcb_matmul_kq_q8, (odd4, good, good, 128, 1024, 16, 0, 1, None)),
+        (L.kcb_matmul_kq_q8, (good, odd4, good, 128, 1024, 16, 0, 1, None)),
+        (L.kcb_matmul_kq_q8, (good, good, odd1, 128, 1024, 16, 0, 1, None)),
+        (L.kcb_rms_norm, (odd1, good, good, 256, 1, f(1e-5), None)),
+        (L.kcb_add_rms_norm, (good, odd1, good, good, 256, f(1e-5), None)),
+        (L.kcb_rope, (odd1, None, 32, 0, 64, f(19.0), None)),
+        (L.kcb_matvec_q4k_f32x_static, (good, good, good, 64, 1024 + 1, None)),  # (k not a multiple of 256: InvalidValue)
+    ]
+    for fn, args in cases[:-1]:
+        assert fn(*args) == INVALID_POINTER, (fn.__name__, args)
+    assert cases[-1][0](*cases[-1][1]) == INVALID_VALUE
+    # null pointers and bad shapes stay InvalidValue, also checked before anything is launched
+    assert L.kcb_matvec_q4k_q8(None, good, good, good, 64, 1024, None) == INVALID_VALUE
+    assert L.kcb_matvec_q4k_q8(good, good, good, good, 64, 1000, None) == INVALID_VALUE

@@ -60,6 +60,43 @@ def test_bad_files_are_refused(tmp_path):
     lib.raw.kcb_gguf_close(h)
 
 
+def _patched(raw: bytes, tensor: bytes, field: str, value: int) -> bytes:
+    """raw with one field of `tensor`'s directory entry replaced: name, u32 rank, u64 extents, u32 type, u64 offset."""
+    at = raw.index(len(tensor).to_bytes(8, "little") + tensor) + 8 + len(tensor)
+    rank = int.from_bytes(raw[at:at + 4], "little")
+    where = {"ne0": (at + 4, 8), "ne1": (at + 12, 8), "type": (at + 4 + 8 * rank, 4), "offset": (at + 8 + 8 * rank, 8)}[field]
+    return raw[:where[0]] + value.to_bytes(where[1], "little") + raw[where[0] + where[1]:]
+
+
+def test_crafted_directories_cannot_point_outside_the_file(tmp_path):
+    """Offsets and extents are 64-bit numbers under the file's control: none of them may wrap a sum or a product into
+    something that passes the bounds check (the reader computes sizes in 128 bits and compares by subtraction).  A tensor
+    of a type the reader has no block size for stays listed and unreadable, as in the reference (llm/gguf.cpp:126-130),
+    and a newer format version is not refused (llm/gguf.cpp:95 refuses only versions below 2)."""
+    shape = tm.tiny(max_ctx=8)
+    good = tmp_path / "good.gguf"
+    write(good, shape, tm.build(shape, seed=4))
+    raw = good.read_bytes()
+    q = b"blk.0.attn_q.weight"
+    cases = {
+        "offset_wraps": (_patched(raw, q, "offset", 2**64 - 64), b"past the end"),
+        "offset_far": (_patched(raw, q, "offset", 2**62), b"past the end"),
+        "rows_huge": (_patched(raw, q, "ne1", 2**62), b"extent out of range"),
+        "rows_wrap": (_patched(raw, q, "ne1", 2**39), b"larger than the file"),
+        "cols_zero": (_patched(raw, q, "ne0", 0), b"extent out of range"),
+        "cols_ragged": (_patched(raw, q, "ne0", shape.hidden + 32), b"whole number of blocks"),
+        "type_unknown": (_patched(raw, q, "type", 30), b"matrix type not supported"),       # listed, then refused by the loader
+    }
+    for name, (data, needle) in cases.items():
+        (tmp_path / f"{name}.gguf").write_bytes(data)
+        st, h, _ = open_gguf(tmp_path / f"{name}.gguf", 8)
+        assert st == 15 and needle in lib.raw.kcb_gguf_last_error(), (name, lib.raw.kcb_gguf_last_error())
+    (tmp_path / "v4.gguf").write_bytes(raw[:4] + (4).to_bytes(4, "little") + raw[8:])
+    st, h, _ = open_gguf(tmp_path / "v4.gguf", 8)
+    assert st == 0, lib.raw.kcb_gguf_last_error()
+    lib.raw.kcb_gguf_close(h)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("shape_fn,arch", [(tm.tiny, "llama"), (tm.tiny_qwen, "qwen3")])
 def test_decoder_from_file_equals_decoder_from_arrays(tmp_path, shape_fn, arch):
