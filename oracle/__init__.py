@@ -156,6 +156,14 @@ def _load_ref():
     L.kcref_matvec_stream_q8.argtypes = [_i32p, _i32p, _f32p, _f32p, i, i, i]
     L.kcref_matvec_stream_q8k.restype = None
     L.kcref_matvec_stream_q8k.argtypes = [_i32p, _i32p, _f32p, i, i, i]
+    L.kcref_gguf_open.restype, L.kcref_gguf_open.argtypes = C.c_void_p, [C.c_char_p, i]
+    L.kcref_gguf_last_error.restype = C.c_char_p
+    L.kcref_gguf_config.restype, L.kcref_gguf_config.argtypes = None, [C.c_void_p, C.POINTER(C.c_int * 8), C.POINTER(C.c_float), C.POINTER(C.c_float)]
+    L.kcref_gguf_tensor.restype = i
+    L.kcref_gguf_tensor.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint), C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong),
+                                    C.POINTER(C.c_longlong * 4), C.POINTER(C.c_ulonglong)]
+    L.kcref_gguf_decode.restype, L.kcref_gguf_decode.argtypes = i, [C.c_void_p, i, i, _f32p]
+    L.kcref_gguf_close.restype, L.kcref_gguf_close.argtypes = None, [C.c_void_p]
     L.kcref_synthetic_tiny_logits.restype = i
     L.kcref_synthetic_tiny_logits.argtypes = [i, C.c_ulonglong, C.c_ulonglong, i, _f32p, C.POINTER(C.c_double)]
     L.kcref_model_open.restype, L.kcref_model_open.argtypes = C.c_void_p, [C.POINTER(Model)]

@@ -13,6 +13,7 @@
 #include "kq_oracle.h"  // struct layouts only (kqo_attn_dims, kqo_fa_dims, kqo_model)
 
 #include "llm_model.hpp"
+#include "gguf_model.hpp"
 #include "llm_reference.hpp"
 
 #include <cmath>
@@ -247,6 +248,65 @@ int kcref_model_decode(void* h, const float* x_in, int pos, float* logits) {
     return 0;
 }
 void kcref_model_close(void* h) { delete static_cast<OpenModel*>(h); }
+
+// ---- the reference's own GGUF reader and loader (llm/gguf.cpp, llm/gguf_model.cpp) -------------------------------
+// kcref_gguf_open reads a file with the reference's reader and loads it with llm::loadGguf onto its single-thread C++
+// backend: the counterpart of kcb_gguf_open + kcb_model_create, for files this project's tests write.  A reader and a
+// writer by the same author could share a misreading of the format; the reference's reader does not.
+struct OpenGguf {
+    std::unique_ptr<llm::gguf::File> file;
+    llm::HostAllocator alloc;
+    llm::Model model;
+    llm::Acts acts;
+    std::unique_ptr<llm::Backend> backend;
+    std::string error;
+};
+static thread_local std::string g_gguf_error;
+const char* kcref_gguf_last_error() { return g_gguf_error.c_str(); }
+void* kcref_gguf_open(const char* path, int max_ctx) {
+    auto g = std::make_unique<OpenGguf>();
+    try {
+        g->file = std::make_unique<llm::gguf::File>(path);
+        g->model = llm::loadGguf(*g->file, max_ctx, g->alloc);
+        g->acts = llm::allocActs(g->model.cfg, g->alloc, 1);
+        g->backend = llm::makeCppBackend(g->model);
+    } catch (const std::exception& e) {
+        g_gguf_error = e.what();
+        return nullptr;
+    }
+    return g.release();
+}
+// dims: hidden, inter, layers, heads, kv_heads, head_dim, vocab, max_ctx; eps and rope_base as floats.
+void kcref_gguf_config(void* h, int* dims, float* eps, float* rope_base) {
+    const llm::Config& c = static_cast<OpenGguf*>(h)->model.cfg;
+    const int v[8] = {c.hidden, c.inter, c.layers, c.heads, c.kv_heads, c.head_dim, c.vocab, c.max_ctx};
+    std::memcpy(dims, v, sizeof v);
+    *eps = c.eps, *rope_base = c.rope_base;
+}
+// One directory entry as the reference's reader sees it; returns 0 when the tensor is absent.
+int kcref_gguf_tensor(void* h, const char* name, unsigned* type, unsigned long long* offset, unsigned long long* bytes, long long* ne4,
+                      unsigned long long* byte_sum) {
+    const llm::gguf::Tensor* t = static_cast<OpenGguf*>(h)->file->find(name);
+    if (!t) return 0;
+    *type = t->type, *offset = t->offset, *bytes = t->bytes;
+    for (int d = 0; d < 4; ++d) ne4[d] = d < int(t->ne.size()) ? t->ne[size_t(d)] : 1;
+    unsigned long long sum = 0;
+    for (size_t i = 0; i < t->bytes; ++i) sum += static_cast<unsigned long long>(t->data[i]) * (i % 251 + 1);
+    *byte_sum = sum;
+    return 1;
+}
+int kcref_gguf_decode(void* h, int token, int pos, float* logits) {
+    auto* g = static_cast<OpenGguf*>(h);
+    try {
+        llm::decodeToken(*g->backend, g->model, g->acts, pos, nullptr, token);
+        std::memcpy(logits, g->acts.logits, size_t(g->model.cfg.vocab) * sizeof(float));
+    } catch (const std::exception& e) {
+        g_gguf_error = e.what();
+        return 1;
+    }
+    return 0;
+}
+void kcref_gguf_close(void* h) { delete static_cast<OpenGguf*>(h); }
 
 // The reference's synthetic tiny model (llm::tinyConfig + llm::buildModels, weights 0 = Q8, 1 = Q4, 2 = Q4X8,
 // 3 = Q4X8Q8) on its single-thread C++ backend: one decodeToken from the start vector of allocActs at `pos`, as its
