@@ -660,8 +660,22 @@ def batch_decode_bench(model_name, n_seq, n_prompt, n_gen):
     import torch
 
     from kernelcore_b200 import decoder, tiny_model as tm
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     shape = (tm.qwen3_8b if model_name == "qwen3_8b" else tm.llama32_3b)(n_prompt + n_gen + 8)
-    d = decoder.FastDecoder(shape, tm.build(shape, seed=0))
+    tp = None
+    if world > 1:   # tensor parallel: one rank per GPU, exchange areas in symmetric memory (as decode_bench)
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        dist.init_process_group("nccl", device_id=dev)
+        area = symm_mem.empty(decoder.FastDecoder.tp_shared_bytes(shape), dtype=torch.uint8, device=dev)
+        area.zero_()
+        handle = symm_mem.rendezvous(area, dist.group.WORLD.group_name)
+        torch.cuda.synchronize()
+        dist.barrier()
+        tp = (rank, world, list(handle.buffer_ptrs))
+    d = decoder.FastDecoder(shape, tm.build(shape, seed=0), tp=tp)
     stream = torch.cuda.ExternalStream(d.cuda_stream)
     rng = np.random.default_rng(1)
     d.batch_begin(n_seq)
@@ -671,21 +685,31 @@ def batch_decode_bench(model_name, n_seq, n_prompt, n_gen):
     d.sync()
     t_prompt = time.perf_counter() - t0
     d.batch_run(2)   # warm-up steps (counted in the position, not in the time)
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     d.batch_run(n_gen - 2)
     e1.record(stream)
     d.sync()
     ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
     steps = n_gen - 2
     _, hist, pos = d.batch_read(0, n_prompt + n_gen)
-    out = {"model": shape.name, "sequences": n_seq, "prompt_tokens_each": n_prompt, "timed_steps": steps, "ms_per_step": ms / steps,
+    out = {"model": shape.name, "n_gpus": world, "exchange_timeouts": decoder.FastDecoder.tp_timeouts(), "sequences": n_seq, "prompt_tokens_each": n_prompt, "timed_steps": steps, "ms_per_step": ms / steps,
            "aggregate_tok_s": n_seq * steps / ms * 1e3, "per_sequence_tok_s": steps / ms * 1e3,
            "prompt_tok_s_batched_pass": n_seq * n_prompt / t_prompt, "position": pos,
            "weight_bytes_per_step": d.weight_bytes, "frac_of_measured_hbm_weights_only": d.weight_bytes / (ms / steps * 1e-3) / (measured_peak()[0] * 1e9),
            "kv_cache": "fp16, one per sequence", "picks_digest": int(np.asarray(hist, np.int64).sum() % 1000003)}
     d.close()
-    return out
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out if rank == 0 else None
 
 
 def attach_decode_cpu(out, shape, model):
@@ -779,7 +803,9 @@ def cpu_decode_matvecs_all_cores(shape, model, reps=3):
 def run_decode(args):
     if args.batch > 1:
         out = batch_decode_bench(args.model, args.batch, args.prompt, args.gen)
-        print(json.dumps({"metric": f"{args.model}_batch{args.batch}_decode_tok_s", "value": out["aggregate_tok_s"], "unit": "tokens/s", "n_gpus": 1,
+        if out is None:
+            return
+        print(json.dumps({"metric": f"{args.model}_batch{args.batch}_decode_tok_s", "value": out["aggregate_tok_s"], "unit": "tokens/s", "n_gpus": out["n_gpus"],
                           "higher_is_better": True, "data": "synthetic", "dtype": "int8 dot, fp32 accumulate",
                           "config": {"workload": f"benchmark spec configs[4]-style batch of {args.batch} independent sequences, lockstep decode"},
                           "detail": out}))

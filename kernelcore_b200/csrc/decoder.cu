@@ -386,8 +386,9 @@ __global__ void attn_combine_rows_kernel(const float* __restrict__ part, float* 
 
 // Greedy pick of every sequence of a batch: one CTA per row of logits, first maximum; the pick becomes the sequence's
 // next token and goes into its history at the common position.
+// With out_v / out_i given, the row's (maximum, index) go there instead -- one rank's candidates under tensor parallelism.
 __global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restrict__ logits, int vocab, int* tok, int* history,
-                                                           const int* __restrict__ pos_p, int max_ctx) {
+                                                           const int* __restrict__ pos_p, int max_ctx, float* out_v = nullptr, int* out_i = nullptr) {
     __shared__ float bv[32];
     __shared__ int bi[32];
     const float* row = logits + static_cast<size_t>(blockIdx.x) * vocab;
@@ -412,7 +413,10 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restri
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
             if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
         }
-        if (lane == 0) {
+        if (lane == 0 && out_v) {
+            out_v[blockIdx.x] = best;
+            out_i[blockIdx.x] = idx;
+        } else if (lane == 0) {
             const int pos = *pos_p;
             tok[blockIdx.x] = idx;
             if (pos < max_ctx) history[static_cast<size_t>(blockIdx.x) * max_ctx + pos] = idx;
@@ -618,6 +622,23 @@ __global__ void tp_sum_rows_kernel(TpCtx c, size_t offset, float* out, size_t co
             if (r < c.world) t.x = __fadd_rn(t.x, p[r].x), t.y = __fadd_rn(t.y, p[r].y), t.z = __fadd_rn(t.z, p[r].z), t.w = __fadd_rn(t.w, p[r].w);
         *reinterpret_cast<float4*>(out + 4 * i) = t;
     }
+}
+
+// Greedy pick of every sequence of a batch under tensor parallelism: rank r left (maximum, local index) of its vocabulary
+// rows for sequence b at rows[r] + offset + b and + cap + b; the first maximum in global index order wins, on every rank alike.
+__global__ void tp_pick_rows_kernel(TpCtx c, size_t offset, int cap, int n_seq, int rows_per_rank, int* tok, int* history, const int* pos_p, int max_ctx) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_seq) return;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int r = 0; r < c.world; ++r) {
+        const float v = ld_peer_f32(c.rows[r] + offset + b);
+        const int i = ld_peer_s32(reinterpret_cast<const int*>(c.rows[r] + offset + cap) + b);
+        if (v > best) best = v, idx = i + r * rows_per_rank;
+    }
+    const int pos = *pos_p;
+    tok[b] = idx;
+    if (pos < max_ctx) history[static_cast<size_t>(b) * max_ctx + pos] = idx;
 }
 
 constexpr int kCand = 296;
@@ -960,8 +981,9 @@ public:
     // batch (per-256 activation slots + the tensor-core matmuls from 16 sequences up), each sequence attends to its own
     // fp16 cache.  The arithmetic per sequence is that of the batched prompt pass with one row.
     int batch_begin(int n_seq) {
-        if (tp.world != 1) {
-            err_ = "batched decoding is single-GPU";
+        if (tp.world != 1 && (wo_win.first_block != 0 || wd_win.first_block != 0 || layers.front().wo.k != heads * hd || layers.front().wd.k != inter)) {
+            err_ = "batched decoding under tensor parallelism needs every rank's share of the attention output and of the FFN to be whole "
+                   "256-channel super-blocks";
             return KCB_UNSUPPORTED_OPERATION;
         }
         if (n_seq < 1 || n_seq > kPrefillChunk || batch_ != 0) return KCB_INVALID_VALUE;
@@ -1027,7 +1049,8 @@ public:
             attn_combine_rows_kernel<<<dim3((qd + 127) / 128, B), 128, 0, stream_>>>(partB, pA, heads, hd, nsplit);
             if (const int e = launch_status(); e) return e;
             if (const int e = quantize_cols_k(pA, pSlots, qd, B, stream_); e) return e;
-            if (const int e = matmul_kq_q8(L.wo.data, pSlots, pT, L.wo.rows, L.wo.k, B, L.wo.q6, 1, stream_, pWs, kWsBytes); e) return e;
+            if (const int e = matmul_kq_q8(L.wo.data, pSlots, rows_out(), L.wo.rows, L.wo.k, B, L.wo.q6, 1, stream_, pWs, kWsBytes); e) return e;
+            if (const int e = sum_rows(B); e) return e;
             if (const int e = add_norm_q8(pX, pT, pX, L.ffn_norm, nullptr, pSlots, pSq, hidden, B, eps, 3, 1, stream_); e) return e;
             float* go = pG;
             for (const DMat& w : L.gu) {
@@ -1042,11 +1065,23 @@ public:
             }
             if (const int e = silu_mul(pG, pU, pG, static_cast<size_t>(B) * inter, stream_); e) return e;
             if (const int e = quantize_cols_k(pG, pSlots, inter, B, stream_); e) return e;
-            if (const int e = matmul_kq_q8(L.wd.data, pSlots, pT, L.wd.rows, L.wd.k, B, L.wd.q6, 1, stream_, pWs, kWsBytes); e) return e;
+            if (const int e = matmul_kq_q8(L.wd.data, pSlots, rows_out(), L.wd.rows, L.wd.k, B, L.wd.q6, 1, stream_, pWs, kWsBytes); e) return e;
+            if (const int e = sum_rows(B); e) return e;
         }
         if (const int e = add_norm_q8(pX, pT, pX, out_norm, nullptr, pSlots, pSq, hidden, B, eps, 3, 1, stream_); e) return e;
         if (const int e = matmul_kq_q8(lm_head.data, pSlots, logitsB, lm_head.rows, lm_head.k, B, lm_head.q6, 1, stream_, pWs, kWsBytes); e) return e;
-        argmax_rows_kernel<<<B, 1024, 0, stream_>>>(logitsB, vocab, tokB, historyB, bpos, max_ctx);
+        if (tp.world == 1) {
+            argmax_rows_kernel<<<B, 1024, 0, stream_>>>(logitsB, vocab, tokB, historyB, bpos, max_ctx);
+        } else {  // every rank's (maximum, index) per sequence through the exchange area, then the same pick on every rank
+            float* mine = rows_out();
+            argmax_rows_kernel<<<B, 1024, 0, stream_>>>(logitsB, vocab, nullptr, nullptr, bpos, max_ctx, mine, reinterpret_cast<int*>(mine + kPrefillChunk));
+            if (const int e = launch_status(); e) return e;
+            tp_barrier_kernel<<<1, 32, 0, stream_>>>(tp);
+            if (const int e = launch_status(); e) return e;
+            tp_pick_rows_kernel<<<(B + 127) / 128, 128, 0, stream_>>>(tp, rows_parity_ * static_cast<size_t>(kPrefillChunk) * hidden, kPrefillChunk, B, vocab, tokB,
+                                                                      historyB, bpos, max_ctx);
+            rows_parity_ ^= 1;
+        }
         advance_pos_kernel<<<1, 1, 0, stream_>>>(bpos);
         return launch_status();
     }

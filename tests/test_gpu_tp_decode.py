@@ -73,7 +73,15 @@ def _worker(rank, world, port, which, out):
             first = logits[r0:r1].copy()
             dec.run(2)
             _, hist2, ppos2 = dec.read(PROMPT + 2)
-            batched = (first, (ppos, ppos2), hist2.copy())
+            # a batch of three sequences in lockstep: prompts, then four steps
+            seqs = [[int(t) for t in np.random.default_rng(30 + i).integers(0, shape.vocab, 8)] for i in range(3)]
+            dec.batch_begin(3)
+            for i, sq in enumerate(seqs):
+                dec.batch_prefill(i, sq)
+            first_rows = [dec.batch_read(i)[0][:r1 - r0].copy() for i in range(3)]
+            dec.batch_run(4)
+            hists = [dec.batch_read(i, 12)[1].copy() for i in range(3)]
+            batched = (first, (ppos, ppos2), hist2.copy(), np.stack(first_rows), np.stack(hists))
         except lib.KcbError as e:      # shares that straddle a super-block: refused on every rank alike, before any launch
             batched = str(e)
         out[rank] = (np.stack(per_step), hist.copy(), pos, decoder.FastDecoder.tp_timeouts(), batched)
@@ -115,10 +123,19 @@ def test_two_rank_decoder_matches_single_gpu(which):
     if which != 2:
         assert isinstance(res[0][4], str) and "super-blocks" in res[0][4] and isinstance(res[1][4], str)
         return
-    (f0, pos0, h0), (f1, pos1, h1) = res[0][4], res[1][4]
+    (f0, pos0, h0, b0, bh0), (f1, pos1, h1, b1, bh1) = res[0][4], res[1][4]
     assert pos0 == pos1 == (PROMPT, PROMPT + 2)
     assert np.array_equal(h0, h1)                                 # the ranks went on with the same tokens
     with decoder.FastDecoder(shape, model) as dec:
         dec.prefill(prompt)
         assert rel_diff(np.concatenate([f0, f1]), dec.read(0)[0]) < 3e-2
     assert res[0][3] == 0 and res[1][3] == 0
+    # the batch of sequences: ranks picked the same tokens for every sequence; logits after the prompts match one GPU
+    assert np.array_equal(bh0, bh1) and (bh0[:, 8:12] >= 0).all() and (bh0[:, 8:12] < shape.vocab).all()
+    seqs = [[int(t) for t in np.random.default_rng(30 + i).integers(0, shape.vocab, 8)] for i in range(3)]
+    with decoder.FastDecoder(shape, model) as dec:
+        dec.batch_begin(3)
+        for i, sq in enumerate(seqs):
+            dec.batch_prefill(i, sq)
+        for i in range(3):
+            assert rel_diff(np.concatenate([b0[i], b1[i]]), dec.batch_read(i)[0]) < 3e-2, i
