@@ -353,14 +353,18 @@ unsigned kcb_decoder_tp_timeouts(void);
 int kcb_decoder_tp_set_poll_limit(unsigned polls);
 int kcb_decoder_tp_reset(void);
 int kcb_decoder_set_prompt(void* decoder, const int* tokens, int n, int start_pos);
-/* Batched prompt pass (single GPU): all n tokens through every layer together -- the reference's batched path in its
+/* Batched prompt pass: all n tokens through every layer together -- the reference's batched path in its
  * ggml backend (integrations/llama.cpp/ggml/src/ggml-kernelcore/ggml-kernelcore.cpp:548-589 mul_mat with per-256
  * activation slots, :502-522 fused norm, :663-697 attention over the fp16 cache) -- on the tensor-core matmuls.
  * Leaves the decoder where n single steps would: KV rows filled, logits and greedy pick of the last prompt token,
- * position start_pos + n; kcb_decoder_run then generates.  Returns after the pass has finished. */
+ * position start_pos + n; kcb_decoder_run then generates.  Returns after the pass has finished.  On a tensor-parallel
+ * decoder every rank makes the same call; it needs each rank's share of the attention output and of the FFN to be a
+ * whole number of 256-channel super-blocks and answers UnsupportedOperation otherwise (then feed the prompt through
+ * kcb_decoder_set_prompt + kcb_decoder_run). */
 int kcb_decoder_prefill(void* decoder, const int* tokens, int n, int start_pos);
 int kcb_decoder_run(void* decoder, int steps);
-/* A batch of independent sequences decoded in lockstep on one GPU (the benchmark spec's batch-32 case; the reference's batched
+/* A batch of independent sequences decoded in lockstep, on one GPU or tensor parallel under the same condition as the
+ * batched prompt pass (the benchmark spec's batch-32 case; the reference's batched
  * path is its ggml backend with several tokens per graph, ggml-kernelcore.cpp:548-603): begin allocates one fp16 KV
  * cache per sequence; batch_prefill runs sequence `seq`'s prompt (all prompts the same length) and makes its first
  * pick; batch_run advances every sequence by `steps` greedy tokens, reading the weights once per step for the whole

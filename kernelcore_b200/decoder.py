@@ -168,14 +168,14 @@ class FastDecoder:
         lib.check(lib.raw.kcb_decoder_set_prompt(self.handle, t.ctypes.data_as(C.c_void_p), int(t.size), int(start_pos)), "kcb_decoder_set_prompt")
 
     def prefill(self, tokens, start_pos=0):
-        """Batched prompt pass (single GPU): returns once the KV cache holds the prompt and the first pick is made."""
+        """Batched prompt pass (one GPU, or tensor parallel with whole-super-block shares): returns once the KV cache holds the prompt and the first pick is made."""
         t = np.ascontiguousarray(tokens, np.int32)
         st = lib.raw.kcb_decoder_prefill(self.handle, t.ctypes.data_as(C.c_void_p), int(t.size), int(start_pos))
         if st != 0:
             lib.raw.kcb_decoder_last_error.restype = C.c_char_p
             raise lib.KcbError("kcb_decoder_prefill", st, lib.raw.kcb_decoder_last_error().decode())
 
-    # ---- a batch of independent sequences in lockstep (single GPU) ----
+    # ---- a batch of independent sequences in lockstep ----
     def batch_begin(self, n_sequences: int):
         self._batch_call(lib.raw.kcb_decoder_batch_begin(self.handle, int(n_sequences)), "kcb_decoder_batch_begin")
 
