@@ -121,8 +121,8 @@ int kcb_matvec_q4k_q8(const void* w_dev, const int32_t* xq_dev, const float* xd_
 int kcb_matvec_q6k_q8(const void* planes_dev, const int32_t* xq_dev, const float* xd_dev, float* y_dev, int rows,
                       int k, void* stream);
 /* Both of the above on the same activations in one launch: y4 = W4 x (Q4_K), y6 = W6 x (Q6_K planes) -- the q|k and
- * v projections of a Q4_K_M layer (the three Backend::matvec calls of llm::decodeToken on the attention input), each output
- * bit-identical to its own launch.  k <= 4096 and at most 6144 rows each; beyond that KCB_UNSUPPORTED_OPERATION (7),
+ * v projections of a Q4_K_M layer (the three Backend::matvec calls of llm::decodeToken on the attention input), the Q6_K
+ * output bit-identical to its own launch, the Q4_K output to 1e-6 (same integer dot products, fp32 sums in another order).  k <= 4096 and at most 6144 rows each; beyond that KCB_UNSUPPORTED_OPERATION (7),
  * and the caller launches them separately (larger matrices stream better through the bulk-copy kernel). */
 int kcb_matvec_q4k_q6k_pair_q8(const void* w4_dev, float* y4_dev, int rows4, const void* planes6_dev, float* y6_dev, int rows6,
                                const int32_t* xq_dev, const float* xd_dev, int k, void* stream);

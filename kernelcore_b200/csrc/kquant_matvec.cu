@@ -678,6 +678,13 @@ struct PeerOut {
     unsigned* done_counter = nullptr;   // local device word, CTAs finished in this launch
     int rank = 0, world = 1;
 };
+constexpr unsigned kHi4 = 0xF0F0F0F0u;
+// dot product of four unsigned bytes with four signed bytes, accumulated (the plain intrinsic takes both as signed)
+__device__ __forceinline__ unsigned dp4a_u8s8(unsigned a, unsigned b, unsigned c) {
+    unsigned d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 constexpr int kProlBytes = 5120;  // shared-memory room for an in-kernel Q8 copy of x (k <= 4096)
 
 constexpr int kTmaMaxStages = 8;
@@ -755,21 +762,31 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
     }
 
     // ---- this lane's slice of the activations, in registers ----
+    // Q6_K: eight lanes per super-block (g = which of four super-blocks of a step, c8 = which 16 bytes of the low-nibble
+    // plane), each warp takes its RPW rows one after the other.
+    // Q4_K: FOUR lanes per super-block -- lane j4 owns the whole 32-byte chunk of sub-blocks 2 j4 and 2 j4 + 1 -- and the
+    // two half-warps take the warp's two rows at the same time.  The 16-byte header of a block (d, dmin, twelve bytes of
+    // 6-bit scales and mins) is then unpacked by four lanes per block instead of eight, per 64 weights instead of 32:
+    // the kernel is bound by its integer instruction stream, not by memory, and this is a third of it.
+    static_assert(kQ6 || RPW == 2, "the Q4_K lane mapping takes two rows per warp");
     uint4 xa[ITERS], xb[ITERS];
+    uint4 xa1[kQ6 ? 1 : ITERS], xb1[kQ6 ? 1 : ITERS];  // Q4_K: the second 16 values of each of the two blocks
     float4 dd[ITERS];
     int sa[ITERS], sb2[ITERS];
     bool ok[ITERS];
     // Q4_K lane roles
-    const int j = c8 >> 1, h = c8 & 1, sh = 16 * (j & 1);
+    const int hw = lane >> 4, g4 = (lane >> 2) & 3, j = lane & 3, sh = 16 * (j & 1);
     // Q6_K lane roles
+    const int h = c8 & 1;
     const int n = c8 >> 2, a = (c8 >> 1) & 1;
     const int shl = 4 - 2 * a, shr = 2 * a;
     const unsigned sel = static_cast<unsigned>(2 * a + h) * 0x1111u | 0x8880u;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
-        const int sb = 4 * it + g;
+        const int sb = 4 * it + (kQ6 ? g : g4);
         ok[it] = sb < nsb;
         xa[it] = xb[it] = make_uint4(0, 0, 0, 0);
+        if (!kQ6) xa1[it] = xb1[it] = make_uint4(0, 0, 0, 0);
         dd[it] = make_float4(0.f, 0.f, 0.f, 0.f);
         sa[it] = sb2[it] = 0;
         if (!ok[it]) continue;
@@ -792,10 +809,12 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
             sb2[it] = 32 * s1;
         } else {
             const int b = sb * 8 + 2 * j;
-            xa[it] = *reinterpret_cast<const uint4*>(xq + b * 8 + 4 * h);
-            xb[it] = *reinterpret_cast<const uint4*>(xq + b * 8 + 8 + 4 * h);
+            xa[it] = *reinterpret_cast<const uint4*>(xq + b * 8);
+            xa1[it] = *reinterpret_cast<const uint4*>(xq + b * 8 + 4);
+            xb[it] = *reinterpret_cast<const uint4*>(xq + b * 8 + 8);
+            xb1[it] = *reinterpret_cast<const uint4*>(xq + b * 8 + 12);
             const float4 t = *reinterpret_cast<const float4*>(xd + 2 * b);
-            dd[it] = make_float4(t.x, h == 0 ? __fmul_rn(t.x, t.y) : 0.f, t.z, h == 0 ? __fmul_rn(t.z, t.w) : 0.f);
+            dd[it] = make_float4(t.x, __fmul_rn(t.x, t.y), t.z, __fmul_rn(t.z, t.w));
         }
     }
 
@@ -819,19 +838,34 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
         const int th = prmt_sbyte(sc.y, sel) * (dh0 + dh1 - sb2[it]);
         return half_bits_to_float(dq) * (static_cast<float>(tl) * dd[it].x + static_cast<float>(th) * dd[it].z);
     };
+    // Q4_K: the lane's 64 weights of one block (sub-blocks 2 j and 2 j + 1: low and high nibbles of 32 bytes).  The high
+    // nibbles stay in place (bytes 16 q): their dot product is an exact multiple of 16 and shifts back once.
     auto q4_step = [&](const uint8_t* st, int rl, int it) -> float {
-        const uint8_t* pb = st + (static_cast<size_t>(rl) * nsb + g + 4 * it) * kQ4KBlock;
+        const uint8_t* pb = st + (static_cast<size_t>(rl) * nsb + g4 + 4 * it) * kQ4KBlock;
         const uint4 hd = *reinterpret_cast<const uint4*>(pb);
-        const uint4 q = *reinterpret_cast<const uint4*>(pb + 16 + 16 * c8);
-        int da0 = 0, da1 = 0, db0 = 0, db1 = 0;
-        da0 = __dp4a(static_cast<int>(q.x & kLo4), static_cast<int>(xa[it].x), da0);
-        da1 = __dp4a(static_cast<int>(q.y & kLo4), static_cast<int>(xa[it].y), da1);
-        da0 = __dp4a(static_cast<int>(q.z & kLo4), static_cast<int>(xa[it].z), da0);
-        da1 = __dp4a(static_cast<int>(q.w & kLo4), static_cast<int>(xa[it].w), da1);
-        db0 = __dp4a(static_cast<int>((q.x >> 4) & kLo4), static_cast<int>(xb[it].x), db0);
-        db1 = __dp4a(static_cast<int>((q.y >> 4) & kLo4), static_cast<int>(xb[it].y), db1);
-        db0 = __dp4a(static_cast<int>((q.z >> 4) & kLo4), static_cast<int>(xb[it].z), db0);
-        db1 = __dp4a(static_cast<int>((q.w >> 4) & kLo4), static_cast<int>(xb[it].w), db1);
+        const uint4 q0 = *reinterpret_cast<const uint4*>(pb + 16 + 32 * j);
+        const uint4 q1 = *reinterpret_cast<const uint4*>(pb + 32 + 32 * j);
+        int da0 = 0, da1 = 0, da2 = 0, da3 = 0;  // four short chains each
+        unsigned db0 = 0, db1 = 0, db2 = 0, db3 = 0;
+        da0 = __dp4a(static_cast<int>(q0.x & kLo4), static_cast<int>(xa[it].x), da0);
+        da1 = __dp4a(static_cast<int>(q0.y & kLo4), static_cast<int>(xa[it].y), da1);
+        da2 = __dp4a(static_cast<int>(q0.z & kLo4), static_cast<int>(xa[it].z), da2);
+        da3 = __dp4a(static_cast<int>(q0.w & kLo4), static_cast<int>(xa[it].w), da3);
+        db0 = dp4a_u8s8(q0.x & kHi4, xb[it].x, db0);
+        db1 = dp4a_u8s8(q0.y & kHi4, xb[it].y, db1);
+        db2 = dp4a_u8s8(q0.z & kHi4, xb[it].z, db2);
+        db3 = dp4a_u8s8(q0.w & kHi4, xb[it].w, db3);
+        da0 = __dp4a(static_cast<int>(q1.x & kLo4), static_cast<int>(xa1[it].x), da0);
+        da1 = __dp4a(static_cast<int>(q1.y & kLo4), static_cast<int>(xa1[it].y), da1);
+        da2 = __dp4a(static_cast<int>(q1.z & kLo4), static_cast<int>(xa1[it].z), da2);
+        da3 = __dp4a(static_cast<int>(q1.w & kLo4), static_cast<int>(xa1[it].w), da3);
+        db0 = dp4a_u8s8(q1.x & kHi4, xb1[it].x, db0);
+        db1 = dp4a_u8s8(q1.y & kHi4, xb1[it].y, db1);
+        db2 = dp4a_u8s8(q1.z & kHi4, xb1[it].z, db2);
+        db3 = dp4a_u8s8(q1.w & kHi4, xb1[it].w, db3);
+        da0 += da2, da1 += da3;
+        db0 += db2, db1 += db3;
+        const int db = static_cast<int>(db0 + db1) >> 4;
         unsigned scw, mw;
         if (j < 2) {
             scw = hd.y & 0x3F3F3F3Fu;
@@ -843,7 +877,7 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
         const int sca = (scw >> sh) & 255, scb = (scw >> (sh + 8)) & 255;
         const int ma = (mw >> sh) & 255, mb = (mw >> (sh + 8)) & 255;
         const float d = half_bits_to_float(hd.x & 0xFFFFu), dmin = half_bits_to_float(hd.x >> 16);
-        const float t1 = static_cast<float>(sca * (da0 + da1)) * dd[it].x + static_cast<float>(scb * (db0 + db1)) * dd[it].z;
+        const float t1 = static_cast<float>(sca * (da0 + da1)) * dd[it].x + static_cast<float>(scb * db) * dd[it].z;
         const float t2 = static_cast<float>(ma) * dd[it].y + static_cast<float>(mb) * dd[it].w;
         return d * t1 - dmin * t2;
     };
@@ -867,25 +901,41 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
         }
         const int row0 = (blockIdx.x + i * gridDim.x) * TR;
         const uint8_t* st = buf + static_cast<size_t>(s) * stage_bytes;
-        float acc[RPW];
+        if constexpr (kQ6) {
+            float acc[RPW];
 #pragma unroll
-        for (int r = 0; r < RPW; ++r) acc[r] = 0.0f;
+            for (int r = 0; r < RPW; ++r) acc[r] = 0.0f;
 #pragma unroll
-        for (int it = 0; it < ITERS; ++it) {
-            if (!ok[it]) continue;
+            for (int it = 0; it < ITERS; ++it) {
+                if (!ok[it]) continue;
+#pragma unroll
+                for (int r = 0; r < RPW; ++r) {
+                    const int rl = warp + r * NW;
+                    if (row0 + rl < rows) acc[r] += q6_step(st, rl, it);
+                }
+            }
 #pragma unroll
             for (int r = 0; r < RPW; ++r) {
-                const int rl = warp + r * NW;
-                if (row0 + rl < rows) acc[r] += kQ6 ? q6_step(st, rl, it) : q4_step(st, rl, it);
+                const float v = warp_sum(acc[r]);
+                const int row = row0 + warp + r * NW;
+                if (lane == 0 && row < rows) {
+                    y[row] = v;
+                    ytile[i & 1][warp + r * NW] = v;
+                }
             }
-        }
+        } else {  // half-warp hw on tile row warp + hw * NW
+            const int rl = warp + hw * NW;
+            float acc = 0.0f;
+            if (row0 + rl < rows) {
 #pragma unroll
-        for (int r = 0; r < RPW; ++r) {
-            const float v = warp_sum(acc[r]);
-            const int row = row0 + warp + r * NW;
-            if (lane == 0 && row < rows) {
-                y[row] = v;
-                ytile[i & 1][warp + r * NW] = v;
+                for (int it = 0; it < ITERS; ++it)
+                    if (ok[it]) acc += q4_step(st, rl, it);
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);  // within the half-warp
+            if ((lane & 15) == 0 && row0 + rl < rows) {
+                y[row0 + rl] = acc;
+                ytile[i & 1][rl] = acc;
             }
         }
         __syncthreads();  // every warp is done with stage s

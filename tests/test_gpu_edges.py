@@ -102,8 +102,11 @@ def test_attention_over_a_single_position():
 
 @pytest.mark.parametrize("rows4,rows6,k", [(4096, 1024, 3072), (8, 8, 256), (5120, 1024, 4096), (6144, 3000, 4096), (520, 4000, 1024)])
 def test_q4k_and_q6k_matvec_in_one_launch_equal_their_own_launches(rows4, rows6, k):
-    """The q|k (Q4_K) and v (Q6_K) projections of a Q4_K_M layer share their input; the pair launch gives each output
-    bit for bit what its own launch gives, whether the grid holds every CTA at once or is shared out by bytes."""
+    """The q|k (Q4_K) and v (Q6_K) projections of a Q4_K_M layer share their input; the pair launch gives what each
+    matrix's own launch gives, whether the grid holds every CTA at once or is shared out by bytes: the Q6_K output bit for
+    bit, the Q4_K output to 1e-6 of its largest value -- the integer dot products are the same, but the stand-alone Q4_K
+    kernels sum a sub-block's 32 products in the integer domain where the pair kernel's lanes hold 16 each and add the
+    two halves as floats."""
     w4 = kquant.KMatrix(synth.raw_blocks(rows4, k, 21, False), rows4, k, False)
     w6 = kquant.KMatrix(synth.raw_blocks(rows6, k, 22, True), rows6, k, True)
     nb = k // 32
@@ -114,7 +117,9 @@ def test_q4k_and_q6k_matvec_in_one_launch_equal_their_own_launches(rows4, rows6,
     lib.call("matvec_q6k_q8", w6.data, xq, xd, a6, rows6, k)
     b4, b6 = torch.zeros(rows4, device="cuda"), torch.zeros(rows6, device="cuda")
     lib.call("matvec_q4k_q6k_pair_q8", w4.data, b4, rows4, w6.data, b6, rows6, xq, xd, k)
-    assert bit_equal(a4.cpu().numpy(), b4.cpu().numpy()) and bit_equal(a6.cpu().numpy(), b6.cpu().numpy())
+    assert bit_equal(a6.cpu().numpy(), b6.cpu().numpy())
+    a4, b4 = a4.cpu().numpy(), b4.cpu().numpy()
+    assert np.abs(a4 - b4).max() <= 1e-6 * np.abs(a4).max()
 
 
 def test_pair_launch_declines_what_the_bulk_copy_kernel_takes():
