@@ -72,6 +72,19 @@ __device__ __forceinline__ unsigned f32_to_f16_bits(float x) {
     return sign | (static_cast<unsigned>(__half_as_ushort(__float2half_rn(a))) & 0x7fffu);
 }
 
+// Rotation of one RoPE pair (x0, x1) = elements of pair index p (of `pairs` per head) at position pos: the arithmetic of
+// kernels/llm/rope.cu:4-17 / rope_ff.cu of the reference, separately rounded.  ff: optional frequency factors.
+__device__ __forceinline__ void rope_pair(float x0, float x1, int p, int pairs, int pos, float log2_base, const float* ff, float& y0, float& y1) {
+    const float e = __fmul_rn(__fdiv_rn(-static_cast<float>(p), static_cast<float>(pairs)), log2_base);
+    float th = __fmul_rn(static_cast<float>(pos), exp2f(e));
+    if (ff) th = __fdiv_rn(th, ff[p]);
+    const float ang = __fmul_rn(__fmul_rn(th, 0.159154943f), 6.28318548f);
+    float s, c;
+    sincosf(ang, &s, &c);
+    y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+    y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+}
+
 // Quantizes the 32 values held one per lane into Q8 block `b` of (xq, xd) -- quantize_q8x4's block.
 __device__ __forceinline__ void quantize_block_warp(float v, int* xq, float* xd, int b, int lane) {
     const float amax = warp_max(fabsf(v));

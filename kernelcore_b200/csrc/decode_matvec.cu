@@ -49,6 +49,7 @@ struct DmvMat {
     const uint8_t* w = nullptr;  // Q4_K blocks or Q6_K planes of `rows` rows
     float* y = nullptr;
     int rows = 0;
+    int row_off = 0;             // with a rotation tail: where this matrix's rows stand in q heads | k heads | v heads
 };
 
 // ---- prologues: the activation vector as Q8 blocks of 32 in shared memory ------------------------------------------
@@ -164,7 +165,7 @@ __device__ __forceinline__ void pro_combine(const float* part, int* xq, float* x
 // ks = w / (kWarps / KSPLIT).  ITERS = ceil(nsb / KSPLIT / 4).
 template <bool kQ6, int ITERS, int TR, int KSPLIT, bool kLanes4>
 __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq, const float* sxd, uint64_t* full, uint8_t* buf, int stages, int cta,
-                                         int nctas, float (*ytile)[TR * KSPLIT]) {
+                                         int nctas, float (*ytile)[TR * KSPLIT], const DecodeRopeTail& tail) {
     constexpr int kBlk = kQ6 ? kQ6KBlock : kQ4KBlock;
     constexpr int NR = kWarps / KSPLIT;  // rows worked on at once (Q4_K: twice that, see below)
     constexpr int RPW = TR / NR;         // rows per warp and tile
@@ -188,6 +189,7 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
     const int ntiles = (rows + TR - 1) / TR;
     const int my_tiles = cta < ntiles ? (ntiles - 1 - cta) / nctas + 1 : 0;
     const size_t nblk = static_cast<size_t>(rows) * nsb;
+    const bool with_tail = KSPLIT == 1 && tail.hd != 0;  // results go through ytile and the rotation / cache tail
 
     auto issue = [&](int i) {  // thread 0 only; the kernel has already requested tiles 0 .. stages - 1
         const int s = i % stages;
@@ -381,7 +383,7 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
             for (int r = 0; r < RPW; ++r) {
                 const float v = warp_sum(acc[r]);
                 const int rl = wr + r * NR;
-                if (KSPLIT == 1) {
+                if (KSPLIT == 1 && !with_tail) {
                     if (lane == 0 && row0 + rl < rows) m.y[row0 + rl] = v;
                 } else if (lane == 0) {
                     ytile[i & 1][ks * TR + rl] = v;  // double-buffered: tile i + 2 writes it only after the barrier of tile i + 1
@@ -404,7 +406,7 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
             for (int r = 0; r < RPW; ++r) {
                 const float v = warp_sum(acc[r]);
                 const int rl = wr + r * NR;
-                if (KSPLIT == 1) {
+                if (KSPLIT == 1 && !with_tail) {
                     if (lane == 0 && row0 + rl < rows) m.y[row0 + rl] = v;
                 } else if (lane == 0) {
                     ytile[i & 1][ks * TR + rl] = v;
@@ -430,7 +432,7 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
                 for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);  // within the half-warp
                 const int rl = wr + (2 * p + hw) * NR;
                 if ((lane & 15) != 0) continue;
-                if (KSPLIT == 1) {
+                if (KSPLIT == 1 && !with_tail) {
                     if (row0 + rl < rows) m.y[row0 + rl] = v;
                 } else {
                     ytile[i & 1][ks * TR + rl] = v;
@@ -439,6 +441,31 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
         }
         __syncthreads();  // every warp is done with stage s (and the K shares of the tile's rows are in ytile)
         if (threadIdx.x == 0 && i + stages < my_tiles) issue(i + stages);
+        if (KSPLIT == 1 && with_tail && threadIdx.x < TR / 2) {
+            // the tile's rows sit in ytile: rotate the q and k pairs, append k and v to the cache (see DecodeRopeTail)
+            const int r = row0 + 2 * static_cast<int>(threadIdx.x);
+            if (r < rows) {
+                const float x0 = ytile[i & 1][2 * threadIdx.x], x1 = ytile[i & 1][2 * threadIdx.x + 1];
+                const int L = m.row_off + r, qd = tail.heads * tail.hd, kvd = tail.kv_heads * tail.hd;
+                const int pos = min(*tail.pos_p, tail.max_ctx - 1);
+                if (L >= qd + kvd) {  // v: cast and append
+                    unsigned short* dst = tail.vc + static_cast<size_t>(pos) * kvd + (L - qd - kvd);
+                    dst[0] = static_cast<unsigned short>(f32_to_f16_bits(x0));
+                    dst[1] = static_cast<unsigned short>(f32_to_f16_bits(x1));
+                } else {
+                    float y0, y1;
+                    rope_pair(x0, x1, (L % tail.hd) / 2, tail.hd / 2, pos, tail.log2_base, tail.ff, y0, y1);
+                    if (L < qd) {
+                        m.y[r] = y0;
+                        m.y[r + 1] = y1;
+                    } else {
+                        unsigned short* dst = tail.kc + static_cast<size_t>(pos) * kvd + (L - qd);
+                        dst[0] = static_cast<unsigned short>(f32_to_f16_bits(y0));
+                        dst[1] = static_cast<unsigned short>(f32_to_f16_bits(y1));
+                    }
+                }
+            }
+        }
         if (KSPLIT > 1 && threadIdx.x < TR && row0 + static_cast<int>(threadIdx.x) < rows) {
             float v = ytile[i & 1][threadIdx.x];
 #pragma unroll
@@ -466,6 +493,8 @@ struct DmvPro {
     // PRO 3: merge of attention partials
     const float* part = nullptr;
     int heads = 0, hd = 0, nsplit = 0;
+    // optional tail of a q|k|v product (hd == 0: none)
+    DecodeRopeTail tail;
 };
 
 // One launch: matrix m4 (Q4_K) on CTAs [0, c4) and, when c6 > 0, matrix m6 (Q6_K planes) on CTAs [c4, c4 + c6), both on
@@ -531,9 +560,9 @@ __global__ void __launch_bounds__(kThreads, 1) dmv_kernel(const DmvMat m4, const
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (is4) {
-        if constexpr (kHas4) dmv_body<false, ITERS, TR, KSPLIT, kLanes4>(m4, nsb, sxq, sxd, full, buf, stages, cta, nctas, ytile);
+        if constexpr (kHas4) dmv_body<false, ITERS, TR, KSPLIT, kLanes4>(m4, nsb, sxq, sxd, full, buf, stages, cta, nctas, ytile, pro.tail);
     } else {
-        if constexpr (kHas6) dmv_body<true, ITERS, TR, KSPLIT, false>(m6, nsb, sxq, sxd, full, buf, stages, cta, nctas, ytile);
+        if constexpr (kHas6) dmv_body<true, ITERS, TR, KSPLIT, false>(m6, nsb, sxq, sxd, full, buf, stages, cta, nctas, ytile, pro.tail);
     }
 }
 
@@ -643,6 +672,8 @@ template <int PRO>
 int dmv_dispatch(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const DmvPro& pro, bool pdl, cudaStream_t s) {
     const int nsb = k / 256;
     DmvMat m4{static_cast<const uint8_t*>(w4), y4, rows4}, m6{static_cast<const uint8_t*>(w6), y6, rows6};
+    m6.row_off = rows4;  // (read by the rotation tail only)
+    if (pro.tail.hd != 0 && nsb > 16) return KCB_INVALID_VALUE;
     if (nsb <= 16)  // 8-row tiles where they balance the SMs better (few tiles per CTA), else two rows per warp
         return row_times(rows4, rows6, 16) < row_times(rows4, rows6, 32) ? dmv_launch_narrow<PRO, 16>(m4, m6, nsb, pro, pdl, s)
                                                                           : dmv_launch_narrow<PRO, 32>(m4, m6, nsb, pro, pdl, s);
@@ -692,11 +723,17 @@ int decode_matvec_q8(const void* w4, float* y4, int rows4, const void* w6, float
     return dmv_dispatch<0>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
 }
 int decode_matvec_norm(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* x_in, const float* t, float* x_out,
-                       const float* wn, float eps, bool pdl, cudaStream_t s, int* trace) {
+                       const float* wn, float eps, bool pdl, cudaStream_t s, int* trace, const DecodeRopeTail* tail) {
     if (!decode_matvec_shape_ok(rows4, rows6, k) || k % 128 || k > 8192 || !x_in || !x_out || !wn) return KCB_INVALID_VALUE;
     if (misaligned(x_in, 16) || misaligned(t, 16) || misaligned(x_out, 16) || misaligned(wn, 16)) return KCB_INVALID_POINTER;
     DmvPro p;
     p.x_in = x_in, p.t = t, p.x_out = x_out, p.wn = wn, p.eps = eps, p.trace = trace;
+    if (tail) {  // q heads | k heads | v heads over the rows of the Q4_K matrix and then the Q6_K one, whole heads each
+        const int all = (tail->heads + 2 * tail->kv_heads) * tail->hd;
+        if (k > 4096 || tail->hd <= 0 || tail->hd % 2 || rows4 + rows6 != all || rows4 % tail->hd || !tail->pos_p || !tail->kc || !tail->vc)
+            return KCB_INVALID_VALUE;
+        p.tail = *tail;
+    }
     return dmv_dispatch<1>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
 }
 int decode_matvec_swiglu(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* g, const float* u, bool pdl,

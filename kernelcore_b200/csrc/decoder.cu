@@ -151,14 +151,8 @@ __global__ void rope_kv_f16_kernel(float* qk, float* v, int qk_stride, int v_str
             x0 = __fmul_rn(__fmul_rn(x0, r), wn[a]);
             x1 = __fmul_rn(__fmul_rn(x1, r), wn[b]);
         }
-        const float e = __fmul_rn(__fdiv_rn(-static_cast<float>(p), static_cast<float>(pairs)), log2_base);
-        float th = __fmul_rn(static_cast<float>(pos), exp2f(e));
-        if (ff) th = __fdiv_rn(th, ff[p]);
-        const float ang = __fmul_rn(__fmul_rn(th, 0.159154943f), 6.28318548f);
-        float s, c;
-        sincosf(ang, &s, &c);
-        const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-        const float y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+        float y0, y1;
+        rope_pair(x0, x1, p, pairs, pos, log2_base, ff, y0, y1);
         if (kdst) {
             kdst[a] = static_cast<unsigned short>(f32_to_f16_bits(y0));
             kdst[b] = static_cast<unsigned short>(f32_to_f16_bits(y1));
@@ -1394,7 +1388,10 @@ private:
     bool streams_long(const DMat& m) const { return kcb_kquant_bytes(m.rows, m.k, m.q6) > fuse_limit_; }
     // cur (+= add) -> RMSNorm * w -> Q8 -> y = [W...] a, for one matrix or a Q4_K / Q6_K pair on the same input.
     // Fused: one launch, the new residual stream lands in `other` and the two pointers swap.  Streaming: in place.
-    int norm_then_matvecs(const std::vector<DMat>& mats, float* y, float*& cur, float*& other, const float* add, const float* w, bool pdl) {
+    // tail (q|k|v only): rotation and cache append inside the fused launch; *tail_done tells whether that happened.
+    int norm_then_matvecs(const std::vector<DMat>& mats, float* y, float*& cur, float*& other, const float* add, const float* w, bool pdl,
+                          const DecodeRopeTail* tail = nullptr, bool* tail_done = nullptr) {
+        if (tail_done) *tail_done = false;
         size_t bytes = 0;
         for (const DMat& m : mats) bytes += kcb_kquant_bytes(m.rows, m.k, m.q6);
         int* xs = add ? trace_slot(4 * hidden) : nullptr;
@@ -1409,7 +1406,12 @@ private:
             return KCB_SUCCESS;
         }
         const Pair p = pair_of(mats, y);
-        if (const int e = decode_matvec_norm(p.w4, p.y4, p.rows4, p.w6, p.y6, p.rows6, hidden, cur, add, other, w, eps, pdl, stream_, trace_slot(hidden)); e) return e;
+        const bool use_tail = tail && p.rows4 % tail->hd == 0;  // (whole heads in the Q4_K matrix)
+        if (const int e = decode_matvec_norm(p.w4, p.y4, p.rows4, p.w6, p.y6, p.rows6, hidden, cur, add, other, w, eps, pdl, stream_, trace_slot(hidden),
+                                             use_tail ? tail : nullptr);
+            e)
+            return e;
+        if (tail_done) *tail_done = use_tail;
         std::swap(cur, other);
         if (xs) CU(cudaMemcpyAsync(xs, cur, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
         return KCB_SUCCESS;
@@ -1427,13 +1429,21 @@ private:
         const float* add = nullptr;   // what the next norm prologue adds to the residual stream first
         for (size_t l = 0; l < layers.size(); ++l) {
             const DLayer& L = layers[l];
-            if (const int e = norm_then_matvecs(L.qkv, qkv, cur, other, add, L.attn_norm, pdl); e) return e;
-            float* vrows = qkv + qd + kv_heads * hd;
-            const float *ff = rope_ff, *qn = L.q_norm, *kn = L.k_norm;
-            if (const int e = launch_pdl(rope_kv_f16_kernel, dim3((heads + 2 * kv_heads + 3) / 4), dim3(128), 0, pdl, qkv, vrows, 0, 0, const_cast<const int*>(pos_p),
-                                         0, L.kc, L.vc, ff, qn, kn, heads, kv_heads, hd, log2_base, neox, eps, max_ctx, 0);
-                e)
-                return e;
+            // adjacent-pair RoPE without per-head norms: rotation and cache append ride on the q|k|v launch's finished tiles
+            DecodeRopeTail tail;
+            tail.pos_p = pos_p, tail.kc = L.kc, tail.vc = L.vc, tail.ff = rope_ff, tail.heads = heads, tail.kv_heads = kv_heads, tail.hd = hd;
+            tail.max_ctx = max_ctx, tail.log2_base = log2_base;
+            const bool can_tail = rope_tail_ && !neox && !L.q_norm && !L.k_norm && hd % 2 == 0;
+            bool rotated = false;
+            if (const int e = norm_then_matvecs(L.qkv, qkv, cur, other, add, L.attn_norm, pdl, can_tail ? &tail : nullptr, &rotated); e) return e;
+            if (!rotated) {
+                float* vrows = qkv + qd + kv_heads * hd;
+                const float *ff = rope_ff, *qn = L.q_norm, *kn = L.k_norm;
+                if (const int e = launch_pdl(rope_kv_f16_kernel, dim3((heads + 2 * kv_heads + 3) / 4), dim3(128), 0, pdl, qkv, vrows, 0, 0,
+                                             const_cast<const int*>(pos_p), 0, L.kc, L.vc, ff, qn, kn, heads, kv_heads, hd, log2_base, neox, eps, max_ctx, 0);
+                    e)
+                    return e;
+            }
             if (const int e = hd == 128 ? attention_pdl<128>(L, pdl) : attention_pdl<64>(L, pdl); e) return e;
             // the merge of the partials stays a launch of its own: a block of 32 channels per warp over 24 CTAs is one
             // round trip to L2, where every CTA of the wo launch redoing all 96 blocks took six
@@ -1558,6 +1568,7 @@ private:
     int* cand_i = nullptr;
     int *xq = nullptr, *xq_wo = nullptr, *xq_wd = nullptr, *state = nullptr, *forced = nullptr, *history = nullptr;
     cudaStream_t stream_ = nullptr;
+    bool rope_tail_ = !(getenv("KCB_DECODE_ROPE_TAIL") && atoi(getenv("KCB_DECODE_ROPE_TAIL")) == 0);
     size_t fuse_limit_ = (getenv("KCB_DECODE_FUSE_MB") ? static_cast<size_t>(atoi(getenv("KCB_DECODE_FUSE_MB"))) : 32) << 20;
     size_t rows_parity_ = 0;  // which half of the exchange area's row buffers the next K-split matmul of a prompt chunk writes
     int* trace_ = nullptr;

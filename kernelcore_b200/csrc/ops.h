@@ -50,11 +50,23 @@ unsigned tc_pipe_timeouts();
 
 // decode_matvec.cu: the decode step's matvecs with their producers as prologues (see the file header).
 // trace != nullptr: the k / 4 int8 words the prologue produced are also written there (by one CTA; test instrumentation).
+// Optional tail of decode_matvec_norm for a layer's q|k|v product (k <= 4096, adjacent-pair RoPE, no per-head norm): every
+// finished tile rotates its q and k pairs at the device-side position (the arithmetic of rope_kv_f16_kernel), leaves q
+// rotated in y and appends k and v as fp16 to the cache rows of that position, so the step needs no rotation launch.
+// Output rows are taken in the order q heads | k heads | v heads (the Q4_K matrix first, then the Q6_K one).
+struct DecodeRopeTail {
+    const int* pos_p = nullptr;      // device-side position
+    unsigned short* kc = nullptr;    // fp16 caches [max_ctx][kv_heads * hd]
+    unsigned short* vc = nullptr;
+    const float* ff = nullptr;       // optional frequency factors [hd / 2]
+    int heads = 0, kv_heads = 0, hd = 0, max_ctx = 0;
+    float log2_base = 0.0f;
+};
 bool decode_matvec_shape_ok(int rows4, int rows6, int k);
 int decode_matvec_q8(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const int* xq, const float* xd, bool pdl,
                      cudaStream_t s);
 int decode_matvec_norm(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* x_in, const float* t, float* x_out,
-                       const float* wn, float eps, bool pdl, cudaStream_t s, int* trace = nullptr);
+                       const float* wn, float eps, bool pdl, cudaStream_t s, int* trace = nullptr, const DecodeRopeTail* tail = nullptr);
 int decode_matvec_swiglu(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* g, const float* u, bool pdl,
                          cudaStream_t s, int* trace = nullptr);
 int decode_matvec_combine(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* part, int heads, int hd,
