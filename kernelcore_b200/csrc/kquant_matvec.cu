@@ -690,12 +690,13 @@ constexpr int kProlBytes = 5120;  // shared-memory room for an in-kernel Q8 copy
 constexpr int kTmaMaxStages = 8;
 
 template <bool kQ6, int ITERS, int TR, int RPW>
-__global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(const uint8_t* __restrict__ w,
-                                                                             const int* __restrict__ xq,
-                                                                             const float* __restrict__ xd,
-                                                                             float* __restrict__ y, int rows, int nsb,
-                                                                             int stages, PeerOut peers,
-                                                                             const float* __restrict__ xf32) {
+// The launch carries a programmatic dependency on the kernel before it in the stream: the first weight tiles are
+// requested before griddepcontrol.wait (weights never depend on a preceding kernel), everything that reads the
+// activations or writes results comes after it.  The activation pointers are therefore plain (no const __restrict__, no
+// __ldg): the read-only data path is only defined for data that does not change while the kernel is resident, and under
+// a programmatic dependency the kernel is resident while its predecessor may still be writing them.
+__global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(const uint8_t* __restrict__ w, const int* xq, const float* xd, float* y,
+                                                                             int rows, int nsb, int stages, PeerOut peers, const float* xf32) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float ytile[2][TR];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -727,24 +728,25 @@ __global__ void __launch_bounds__(TR / RPW * 32, 1) matvec_kq_q8_tma_kernel(cons
         }
     };
 
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+        mbar_init_fence();
+        for (int i = 0; i < stages && i < my_tiles; ++i) issue(i);  // weights first: they depend on no preceding kernel
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next kernel may queue up behind this one
+    asm volatile("griddepcontrol.wait;" ::: "memory");               // the preceding kernel's results from here on
+    __syncthreads();                                                 // (the barriers are initialised for every thread)
     // fp32 activations (quantized below): groups of four blocks (128 values), group gi = warp + i * NW, one 16-byte
-    // load per lane, all issued before anything else so their latency overlaps the barrier set-up
+    // load per lane; their latency overlaps the weight tiles already in flight
     constexpr int kMaxPerWarp = (16 * 2 + NW - 1) / NW;  // nsb <= 16: at most 32 groups
     float4 xv[kMaxPerWarp];
     if (xf32) {
 #pragma unroll
         for (int i = 0; i < kMaxPerWarp; ++i) {
             const int gi = warp + i * NW;
-            xv[i] = gi < nsb * 2 ? __ldg(reinterpret_cast<const float4*>(xf32) + gi * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+            xv[i] = gi < nsb * 2 ? *(reinterpret_cast<const float4*>(xf32) + gi * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
-        mbar_init_fence();
-    }
-    __syncthreads();
-    if (threadIdx.x == 0)
-        for (int i = 0; i < stages && i < my_tiles; ++i) issue(i);
 
     // fp32 activations: every CTA quantizes x itself (quantize_q8x4's arithmetic, one warp per block of 32) while
     // its first weight tiles are in flight; saves a launch and the scratch round trip.
@@ -997,8 +999,14 @@ int launch_tma_cfg(const uint8_t* wb, const int* xq, const float* xd, float* y, 
     if (!raise_dynamic_smem(kern, 226 * 1024, raised)) return KCB_LAUNCH_FAILURE;
     const int ntiles = (rows + TR - 1) / TR;
     const int grid = ntiles < kSmCount ? ntiles : kSmCount;
-    kern<<<grid, TR / RPW * 32, smem, s>>>(wb, xq, xd, y, rows, nsb, stages, peers, xf32);
-    return launch_status();
+    static const bool pdl = !(getenv("KCB_MATVEC_PDL") && atoi(getenv("KCB_MATVEC_PDL")) == 0);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid), cfg.blockDim = dim3(TR / RPW * 32), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, wb, xq, xd, y, rows, nsb, stages, peers, xf32) == cudaSuccess ? KCB_SUCCESS : KCB_LAUNCH_FAILURE;
 }
 
 template <bool kQ6, int ITERS>
