@@ -11,13 +11,15 @@
 //     already arriving while the previous kernel drains;
 //   * each kernel releases its dependents as soon as its own prologue is done;
 //   * rows are dealt in tiles to one persistent CTA of 16 warps per SM with a ring of up to six tiles in 224 KB of shared
-//     memory; wide matrices (k = 8192) split a row's super-blocks over two warps so that a lane's activation slice
-//     still fits in registers.  (Two CTAs of 8 warps and 110 KB per SM, so that the next kernel's CTAs sit beside this
+//     memory; wide matrices split a row's super-blocks over two (k <= 8192) or four (k <= 16384) warps so that a lane's
+//     activation slice still fits in registers.  (Two CTAs of 8 warps and 110 KB per SM, so that the next kernel's CTAs sit beside this
 //     one's and its weights arrive while this one computes, measured slower: 7.4 against 5.7 us on an 8192 x 3072
 //     Q4_K matrix, 638 against 687 tokens/s on the Llama-3.2-3B-shape decode step in the same run.)
 // The per-row arithmetic is that of the bulk-copy matvec in kquant_matvec.cu (integer dot products, the reference's
-// fp32 scale products, one shuffle tree per row).  Every mbarrier wait is bounded; on expiry the CTA counts the event
-// and leaves.
+// fp32 scale products, one shuffle tree per row; Q4_K on four lanes per super-block where a CTA has three or more tiles,
+// on eight where the launch is latency bound).  A q|k|v product can carry a tail that rotates the q and k pairs of each
+// finished tile and appends k and v to the fp16 cache (DecodeRopeTail, ops.h).  Every mbarrier wait is bounded; on expiry
+// the CTA counts the event and leaves.
 
 #include "common.cuh"
 #include "ops.h"
