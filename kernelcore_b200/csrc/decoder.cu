@@ -1550,12 +1550,14 @@ private:
         }
 #undef KCB_ATTN
     }
-    // A matrix above fuse_limit_ bytes (32 MB; KCB_DECODE_FUSE_MB) streams for longer than its producer takes as a launch
-    // of its own, while a prologue repeated by every CTA grows with the vector: measured on Qwen3-8B shapes, the 41 MB
-    // down projection with its 12288-wide SwiGLU folded in and the 57 MB gate|up with its norm folded in gave 380 tokens/s,
-    // with both producers as launches 429 (no fusion at all: 402); on Llama-3.2-3B shapes only the lm_head is above the
-    // limit (723 against 720).
-    bool streams_long(const DMat& m) const { return kcb_kquant_bytes(m.rows, m.k, m.q6) > fuse_limit_; }
+    // Which producers stay launches of their own.  Measured on Qwen3-8B shapes (tokens/s): nothing folded in 402; q|k|v and
+    // wo only 429; the 57 MB gate|up with its norm as well 448-465; the 41 MB down projection with its 12288-wide SwiGLU as
+    // well 365-380.  On Llama-3.2-3B shapes only the lm_head is beyond the limits (723 against 720).
+    // The SwiGLU prologue costs per value (an exponential and a division in every CTA): folded in up to swiglu_limit_
+    // values (8192; KCB_DECODE_SWIGLU_MAX).  The norm prologue is a few thousand multiply-adds: folded in for every matrix
+    // the decode matvec kernel takes at all (norm_limit_, 64 MB; KCB_DECODE_FUSE_MB), beyond which the streaming kernel
+    // with its deeper ring is the better matvec anyway.
+    bool streams_long(const DMat& m) const { return m.k > swiglu_limit_ || kcb_kquant_bytes(m.rows, m.k, m.q6) > fuse_limit_; }
     // cur (+= add) -> RMSNorm * w -> Q8 -> y = [W...] a, for one matrix or a Q4_K / Q6_K pair on the same input.
     // Fused: one launch, the new residual stream lands in `other` and the two pointers swap.  Streaming: in place.
     // tail (q|k|v only): rotation and cache append inside the fused launch; *tail_done tells whether that happened.
@@ -1740,7 +1742,8 @@ private:
     cudaStream_t stream_ = nullptr;
     bool prompt_blocked_ = !(getenv("KCB_PROMPT_ATTN_BLOCKED") && atoi(getenv("KCB_PROMPT_ATTN_BLOCKED")) == 0);
     bool rope_tail_ = !(getenv("KCB_DECODE_ROPE_TAIL") && atoi(getenv("KCB_DECODE_ROPE_TAIL")) == 0);
-    size_t fuse_limit_ = (getenv("KCB_DECODE_FUSE_MB") ? static_cast<size_t>(atoi(getenv("KCB_DECODE_FUSE_MB"))) : 32) << 20;
+    size_t fuse_limit_ = (getenv("KCB_DECODE_FUSE_MB") ? static_cast<size_t>(atoi(getenv("KCB_DECODE_FUSE_MB"))) : 64) << 20;
+    int swiglu_limit_ = getenv("KCB_DECODE_SWIGLU_MAX") ? atoi(getenv("KCB_DECODE_SWIGLU_MAX")) : 8192;
     size_t rows_parity_ = 0;  // which half of the exchange area's row buffers the next K-split matmul of a prompt chunk writes
     int* trace_ = nullptr;
     size_t trace_words_ = 0, trace_off_ = 0;

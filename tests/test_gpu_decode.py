@@ -139,6 +139,9 @@ def test_graph_decoder_stage_by_stage_with_flip_count(shape_fn, fused, monkeypat
     difference, and stays inside 3e-2.  Both forms of the step (producers fused into the matvecs, and one kernel each)
     are held to the same numbers."""
     monkeypatch.setenv("KCB_DECODE_FUSED", str(fused))
+    # (by default a SwiGLU of more than 8192 values stays a launch of its own; here it is folded in, so that the
+    # four-warps-per-row matvec is checked with its prologue)
+    monkeypatch.setenv("KCB_DECODE_SWIGLU_MAX", "16384")
     shape = shape_fn(max_ctx=48)
     model = tm.build(shape, seed=5)
     staged, free = OracleModel(shape, model), OracleModel(shape, model)
