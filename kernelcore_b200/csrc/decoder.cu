@@ -1551,10 +1551,13 @@ private:
 #undef KCB_ATTN
     }
     // Which producers stay launches of their own.  Measured on Qwen3-8B shapes (tokens/s): nothing folded in 402; q|k|v and
-    // wo only 429; the 57 MB gate|up with its norm as well 448-465; the 41 MB down projection with its 12288-wide SwiGLU as
-    // well 365-380.  On Llama-3.2-3B shapes only the lm_head is beyond the limits (723 against 720).
-    // The SwiGLU prologue costs per value (an exponential and a division in every CTA): folded in up to swiglu_limit_
-    // values (8192; KCB_DECODE_SWIGLU_MAX).  The norm prologue is a few thousand multiply-adds: folded in for every matrix
+    // wo only 429; the 57 MB gate|up with its norm as well 448-455; the 41 MB down projection with its 12288-wide SwiGLU as
+    // well 365-380.  On Llama-3.2-3B shapes (SwiGLU a launch of its own): norms folded into q|k|v and gate|up 782, into
+    // q|k|v only 726, into neither 666; the lm_head's norm stays a launch (723 against 720 when that was the only change).
+    // The SwiGLU prologue costs per value (an exponential and a division in every CTA) and delays the matvec behind it,
+    // where the stand-alone kernel spreads the values over many CTAs and overlaps the matvec's weight requests: folded in
+    // up to swiglu_limit_ values only (4096; KCB_DECODE_SWIGLU_MAX) -- on Llama-3.2-3B shapes the 8192-wide one folded
+    // into the down projection gave 718 tokens/s, as a launch of its own 781.  The norm prologue is a few thousand multiply-adds: folded in for every matrix
     // the decode matvec kernel takes at all (norm_limit_, 64 MB; KCB_DECODE_FUSE_MB), beyond which the streaming kernel
     // with its deeper ring is the better matvec anyway.
     bool streams_long(const DMat& m) const { return m.k > swiglu_limit_ || kcb_kquant_bytes(m.rows, m.k, m.q6) > fuse_limit_; }
@@ -1743,7 +1746,7 @@ private:
     bool prompt_blocked_ = !(getenv("KCB_PROMPT_ATTN_BLOCKED") && atoi(getenv("KCB_PROMPT_ATTN_BLOCKED")) == 0);
     bool rope_tail_ = !(getenv("KCB_DECODE_ROPE_TAIL") && atoi(getenv("KCB_DECODE_ROPE_TAIL")) == 0);
     size_t fuse_limit_ = (getenv("KCB_DECODE_FUSE_MB") ? static_cast<size_t>(atoi(getenv("KCB_DECODE_FUSE_MB"))) : 64) << 20;
-    int swiglu_limit_ = getenv("KCB_DECODE_SWIGLU_MAX") ? atoi(getenv("KCB_DECODE_SWIGLU_MAX")) : 8192;
+    int swiglu_limit_ = getenv("KCB_DECODE_SWIGLU_MAX") ? atoi(getenv("KCB_DECODE_SWIGLU_MAX")) : 4096;
     size_t rows_parity_ = 0;  // which half of the exchange area's row buffers the next K-split matmul of a prompt chunk writes
     int* trace_ = nullptr;
     size_t trace_words_ = 0, trace_off_ = 0;

@@ -208,9 +208,10 @@ def test_full_size_logits_against_the_reference_decode_loop():
             ref_logits.append(out)
         oracle.ref.lib.kcref_model_close(h)
     with decoder.FastDecoder(shape, model) as d:
-        # the fused step is the one measured: embed, six launches per layer, the lm_head (above 32 MB: its norm a
-        # launch of its own, then the streaming matvec) and two for the pick
-        assert d.launches_per_token == 5 + 6 * shape.layers
+        # the fused step is the one measured: embed, seven launches per layer (q|k|v with norm and rotation, attention,
+        # merge, wo, gate|up with norm, SwiGLU, down), the lm_head (above 64 MB: its norm a launch of its own, then the
+        # streaming matvec) and two for the pick
+        assert d.launches_per_token == 5 + 7 * shape.layers
         words = d.enable_trace()
         assert words == staged.trace_words()
         d.set_prompt(toks)
