@@ -1631,7 +1631,7 @@ private:
             if (const int e = decode_matvec_q8(o.w4, o.y4, o.rows4, o.w6, o.y6, o.rows6, L.wo.k, xq_wo, xd_of(xq_wo, L.wo.k), pdl, stream_); e) return e;
             if (const int e = norm_then_matvecs(L.gu, gu, cur, other, t, L.ffn_norm, pdl); e) return e;
             if (streams_long(L.wd)) {  // SwiGLU + quantize as its own launch, then the streaming matvec
-                if (const int e = silu_mul_q8(gu, gu + inter, nullptr, nullptr, xq_wd, xd_of(xq_wd, L.wd.k), inter, 1, stream_); e) return e;
+                if (const int e = silu_mul_q8(gu, gu + inter, nullptr, nullptr, xq_wd, xd_of(xq_wd, L.wd.k), inter, 1, stream_, pdl); e) return e;
                 if (const int e = trace_copy(xq_wd, L.wd.k); e) return e;
                 if (const int e = mv(L.wd, xq_wd, t); e) return e;
             } else {

@@ -222,8 +222,12 @@ __global__ void silu_mul_kernel(const float* __restrict__ g, const float* __rest
     if (i < count) out[i] = swiglu(g[i], u[i]);
 }
 // One warp per block of 32; column c's slot is q + c * 11 * nb ints (or the flat xq/xd pair).
-__global__ void silu_mul_q8_kernel(const float* __restrict__ g, const float* __restrict__ u, float* y, int* q, int nb,
-                                   int cols, int* xq_flat, float* xd_flat) {
+// May be launched with a programmatic dependency on the kernel that writes g and u (the decode step does): results of
+// that kernel from griddepcontrol.wait on, and g / u through plain loads (no read-only path for data that changes while
+// this kernel is resident).
+__global__ void silu_mul_q8_kernel(const float* g, const float* u, float* y, int* q, int nb, int cols, int* xq_flat, float* xd_flat) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     if (wid >= static_cast<long long>(nb) * cols) return;
@@ -503,13 +507,22 @@ int silu_mul(const float* g, const float* u, float* out, size_t count, cudaStrea
     silu_mul_kernel<<<blocks_for(count, 256), 256, 0, s>>>(g, u, out, count);
     return launch_status();
 }
-int silu_mul_q8(const float* g, const float* u, float* y, int* q, int* xq, float* xd, int n, int cols, cudaStream_t s) {
+int silu_mul_q8(const float* g, const float* u, float* y, int* q, int* xq, float* xd, int n, int cols, cudaStream_t s, bool pdl) {
     if (n <= 0 || n % 32 || cols < 0 || !g || !u || (!q && !(xq && xd))) return KCB_INVALID_VALUE;
     if (any_misaligned4(g, u, y, q, xq, xd)) return KCB_INVALID_POINTER;
     if (cols == 0) return KCB_SUCCESS;
     const size_t warps = static_cast<size_t>(n / 32) * cols;
-    silu_mul_q8_kernel<<<blocks_for(warps, 8), 256, 0, s>>>(g, u, y, q, n / 32, cols, xq, xd);
-    return launch_status();
+    if (!pdl) {
+        silu_mul_q8_kernel<<<blocks_for(warps, 8), 256, 0, s>>>(g, u, y, q, n / 32, cols, xq, xd);
+        return launch_status();
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks_for(warps, 8)), cfg.blockDim = dim3(256), cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, silu_mul_q8_kernel, g, u, y, q, n / 32, cols, xq, xd) == cudaSuccess ? KCB_SUCCESS : KCB_LAUNCH_FAILURE;
 }
 int mul_rows(const float* x, const float* w, float* y, int n, size_t count, cudaStream_t s) {
     if (n <= 0 || !x || !w || !y) return KCB_INVALID_VALUE;

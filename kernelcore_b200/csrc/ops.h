@@ -81,7 +81,8 @@ int add_norm_q8(const float* a, const float* t, float* out, const float* w, floa
 int add_norm_q8_fast(float* x, const float* t, const float* w, int* xq, float* xd, int n, float eps, cudaStream_t s);
 int argmax_partial(const float* logits, int vocab, float* cand_v, int* cand_i, int ncand, cudaStream_t s);
 int silu_mul(const float* g, const float* u, float* out, size_t count, cudaStream_t s);
-int silu_mul_q8(const float* g, const float* u, float* y, int* q, int* xq, float* xd, int n, int cols, cudaStream_t s);
+// (pdl: launch with a programmatic dependency on the kernel before it in the stream)
+int silu_mul_q8(const float* g, const float* u, float* y, int* q, int* xq, float* xd, int n, int cols, cudaStream_t s, bool pdl = false);
 int mul_rows(const float* x, const float* w, float* y, int n, size_t count, cudaStream_t s);
 int vector_add(const float* a, const float* b, float* out, size_t count, cudaStream_t s);
 int rope(float* x, const float* ff, int pairs, int pos, int count, float log2_base, cudaStream_t s);
