@@ -16,6 +16,8 @@
 #include "common.cuh"
 #include "ops.h"
 
+#include <cooperative_groups.h>
+
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -32,6 +34,7 @@
 #endif
 namespace kcb {
 namespace {
+namespace cg = cooperative_groups;
 
 __device__ __forceinline__ int sbyte_of(unsigned w, int i) { return static_cast<int>(w << (24 - 8 * i)) >> 24; }
 
@@ -308,6 +311,174 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const float* qkv, con
     }
 }
 
+// One block of 32 attention outputs (a warp, one value per lane): the floats to attn and their quantize_q8x4 form -- words,
+// scale and sum -- to the Q8 scratch the wo matvec reads.
+__device__ __forceinline__ void attn_store_block_q8(float v, int b, int lane, float* attn, int* xq, float* xd) {
+    attn[b * 32 + lane] = v;
+    // quantize_q8x4 of this block
+    const float amax = warp_max(fabsf(v));
+    const float dq = __fdiv_rn(amax, 127.0f);
+    const float id = dq > 0.0f ? __fdiv_rn(1.0f, dq) : 0.0f;
+    const float t = __fmul_rn(v, id);
+    int qi = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
+    qi = max(-127, min(127, qi));
+    const int sum = warp_sum_i(qi);
+    unsigned word = (static_cast<unsigned>(qi) & 255u) << (8 * (lane & 3));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    if ((lane & 3) == 0) xq[b * 8 + (lane >> 2)] = static_cast<int>(word);
+    if (lane == 0) {
+        xd[b * 2] = dq;
+        xd[b * 2 + 1] = static_cast<float>(sum);
+    }
+}
+
+// Decode attention with the merge inside the launch: the kAttnCluster CTAs of a thread-block cluster split the positions
+// of one kv head (CTA `rank` takes [rank * chunk, (rank + 1) * chunk), eight warps, one position per lane group and step,
+// same online exp2 softmax as attn_partial_kernel), each leaves its partial {acc[G][HD], max, sum} in its own shared
+// memory, and after one cluster barrier the warps of the cluster merge the partials through distributed shared memory --
+// block b of 32 channels by warp b / kAttnCluster of CTA b % kAttnCluster, in split order with the arithmetic of
+// attn_combine_q8_kernel -- and write attn and its Q8 form.  Against the two launches it replaces: no trip of the partials
+// through L2, no second launch.  The position and the K / V rows of earlier steps do not depend on the kernel before
+// (only the newest row and q do), so they are requested before griddepcontrol.wait.
+constexpr int kAttnCluster = 8;
+template <int HD, int G>
+__global__ void __launch_bounds__(256) attn_decode_cluster_kernel(const float* qkv, const unsigned short* kc, const unsigned short* vc, const int* pos_p,
+                                                                  float* attn, int* xq, float* xd, int heads, int kv_heads, float scale, int max_ctx) {
+    constexpr int DPL = HD / 8, NW = 8, NV = DPL / 8, PW = HD + 2;
+    extern __shared__ float sm[];              // [NW * 4][G][PW] lane-group partials, then [G][PW]: this CTA's partial
+    float* cta_part = sm + NW * 4 * G * PW;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int sp = static_cast<int>(cluster.block_rank());
+    const int kvh = blockIdx.x / kAttnCluster, h0 = kvh * G;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, grp = lane >> 3, l8 = lane & 7;
+    // (*pos_p changes only in the step's last kernel, which is not launched with a programmatic dependency)
+    const int ctx = min(*pos_p, max_ctx - 1) + 1;
+    const int chunk = (ctx + kAttnCluster - 1) / kAttnCluster;
+    const int t0 = sp * chunk, t1 = min(ctx, t0 + chunk);
+    const int kvdim = kv_heads * HD;
+    uint4 kn[NV], vn[NV];
+    auto fetch = [&](int t, int limit) {
+        if (t < limit) {
+            const unsigned short* kr = kc + static_cast<size_t>(t) * kvdim + kvh * HD + l8 * DPL;
+            const unsigned short* vr = vc + static_cast<size_t>(t) * kvdim + kvh * HD + l8 * DPL;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                kn[i] = *reinterpret_cast<const uint4*>(kr + 8 * i);
+                vn[i] = *reinterpret_cast<const uint4*>(vr + 8 * i);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) kn[i] = vn[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    const int first = t0 + warp * 4 + grp;
+    fetch(first, min(t1, ctx - 1));  // rows of earlier steps: complete long before this step began
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (first == ctx - 1) fetch(first, t1);  // the row this step appended
+    float q[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) q[g][i] = qkv[static_cast<size_t>(h0 + g) * HD + l8 * DPL + i];
+    float m[G], l[G], acc[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[g][i] = 0.0f;
+    }
+    for (int tb = t0 + warp * 4; tb < t1; tb += NW * 4) {  // warp-uniform trip count
+        const int t = tb + grp;
+        const bool live = t < t1;
+        float kf[DPL], vf[DPL];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const unsigned ku[4] = {kn[i].x, kn[i].y, kn[i].z, kn[i].w}, vu[4] = {vn[i].x, vn[i].y, vn[i].z, vn[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                kf[8 * i + 2 * j] = half_bits_to_float(ku[j] & 0xFFFFu);
+                kf[8 * i + 2 * j + 1] = half_bits_to_float(ku[j] >> 16);
+                vf[8 * i + 2 * j] = half_bits_to_float(vu[j] & 0xFFFFu);
+                vf[8 * i + 2 * j + 1] = half_bits_to_float(vu[j] >> 16);
+            }
+        }
+        fetch(t + NW * 4, t1);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) s += q[g][i] * kf[i];
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            if (live) {
+                s *= scale;
+                const float mn = fmaxf(m[g], s);
+                const float corr = exp2f((m[g] - mn) * 1.44269504f);
+                const float p = exp2f((s - mn) * 1.44269504f);
+                l[g] = l[g] * corr + p;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) acc[g][i] = acc[g][i] * corr + p * vf[i];
+                m[g] = mn;
+            }
+        }
+    }
+    // lane groups -> shared memory -> one partial per CTA
+    float* mine = sm + static_cast<size_t>(warp * 4 + grp) * G * PW;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) mine[g * PW + l8 * DPL + i] = acc[g][i];
+        if (l8 == 0) {
+            mine[g * PW + HD] = m[g];
+            mine[g * PW + HD + 1] = l[g];
+        }
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < G * HD; o += blockDim.x) {
+        const int g = o / HD, d = o % HD;
+        float mm = -INFINITY;
+        for (int pi = 0; pi < NW * 4; ++pi) mm = fmaxf(mm, sm[pi * G * PW + g * PW + HD]);
+        float ll = 0.0f, aa = 0.0f;
+        for (int pi = 0; pi < NW * 4; ++pi) {
+            const float* pp = sm + pi * G * PW + g * PW;
+            const float wgt = pp[HD] == -INFINITY ? 0.0f : exp2f((pp[HD] - mm) * 1.44269504f);
+            ll += pp[HD + 1] * wgt;
+            aa += pp[d] * wgt;
+        }
+        cta_part[g * PW + d] = aa;
+        if (d == 0) {
+            cta_part[g * PW + HD] = mm;
+            cta_part[g * PW + HD + 1] = ll;
+        }
+    }
+    cluster.sync();  // every CTA's partial is in place (a hardware barrier over the co-scheduled cluster: nothing to poll)
+    const int bl = warp * kAttnCluster + sp;  // this warp's block of 32 channels among the G * HD / 32 of the kv head
+    if (bl < G * HD / 32) {
+        const int g = bl * 32 / HD, d = (bl * 32) % HD + lane;
+        float pv[kAttnCluster];
+#pragma unroll
+        for (int s = 0; s < kAttnCluster; ++s) pv[s] = cluster.map_shared_rank(cta_part, s)[g * PW + d];
+        const float* mine_ml = cluster.map_shared_rank(cta_part, lane % kAttnCluster) + g * PW + HD;
+        const float pm = lane < kAttnCluster ? mine_ml[0] : -INFINITY;
+        const float pl = lane < kAttnCluster ? mine_ml[1] : 0.0f;
+        const float mm = warp_max(pm);
+        const float wl = pm == -INFINITY ? 0.0f : exp2f((pm - mm) * 1.44269504f);
+        float ll = 0.0f, aa = 0.0f;
+#pragma unroll
+        for (int s = 0; s < kAttnCluster; ++s) {
+            const float wgt = __shfl_sync(0xffffffffu, wl, s), ls = __shfl_sync(0xffffffffu, pl, s);
+            ll = __fmaf_rn(ls, wgt, ll);
+            aa = __fmaf_rn(pv[s], wgt, aa);
+        }
+        attn_store_block_q8(__fdiv_rn(aa, ll), (h0 * HD) / 32 + bl, lane, attn, xq, xd);
+    }
+    cluster.sync();  // nobody leaves while its shared memory is still being read
+}
+
 // Causal attention of a prompt chunk over the fp16 cache, blocked over tokens: CTA (kv head, block of TB consecutive
 // tokens) brings the K and V rows of its kv head into shared memory 32 positions at a time (cp.async, double buffered)
 // and every one of its TB * G warps -- one per (token, query head of the group) -- scores them from there: a K / V row
@@ -486,24 +657,7 @@ __global__ void attn_combine_q8_kernel(const float* part, float* attn, int* xq, 
             aa = __fmaf_rn(ph[s * (hd + 2) + d], wgt, aa);
         }
     }
-    const float v = __fdiv_rn(aa, ll);
-    attn[b * 32 + lane] = v;
-    // quantize_q8x4 of this block
-    const float amax = warp_max(fabsf(v));
-    const float dq = __fdiv_rn(amax, 127.0f);
-    const float id = dq > 0.0f ? __fdiv_rn(1.0f, dq) : 0.0f;
-    const float t = __fmul_rn(v, id);
-    int qi = t >= 0.0f ? __float2int_rz(__fadd_rn(t, 0.5f)) : __float2int_rz(__fsub_rn(t, 0.5f));
-    qi = max(-127, min(127, qi));
-    const int sum = warp_sum_i(qi);
-    unsigned word = (static_cast<unsigned>(qi) & 255u) << (8 * (lane & 3));
-    word |= __shfl_xor_sync(0xffffffffu, word, 1);
-    word |= __shfl_xor_sync(0xffffffffu, word, 2);
-    if ((lane & 3) == 0) xq[b * 8 + (lane >> 2)] = static_cast<int>(word);
-    if (lane == 0) {
-        xd[b * 2] = dq;
-        xd[b * 2 + 1] = static_cast<float>(sum);
-    }
+    attn_store_block_q8(__fdiv_rn(aa, ll), b, lane, attn, xq, xd);
 }
 
 // Batched form of the merge: token blockIdx.y, normalised floats to out[token][heads * hd] (quantized per 256 afterwards).
@@ -1530,6 +1684,44 @@ private:
         cfg.attrs = attr, cfg.numAttrs = pdl ? 1 : 0;
         return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess ? KCB_SUCCESS : KCB_LAUNCH_FAILURE;
     }
+    // Decode attention and merge in one cluster launch: group sizes up to 4 (register budget of 256 threads) and contexts
+    // up to 4096 (a cluster of eight CTAs takes 256 positions per step; beyond that the 32-way split of the two-launch
+    // form wins back more than the launch it costs).
+    bool attn_in_cluster() const {
+        const int group = heads / kv_heads;
+        return attn_cluster_ && group <= 4 && group * kv_heads == heads && max_ctx <= 4096;
+    }
+    template <int HD, int G>
+    int attention_cluster_launch(const DLayer& L, bool pdl) {
+        constexpr size_t smem = static_cast<size_t>(33) * G * (HD + 2) * 4;
+        static PerDeviceFlag raised;
+        if (!raise_dynamic_smem(attn_decode_cluster_kernel<HD, G>, static_cast<int>(smem), raised)) return KCB_LAUNCH_FAILURE;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(kv_heads * kAttnCluster), cfg.blockDim = dim3(256), cfg.dynamicSmemBytes = smem, cfg.stream = stream_;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = kAttnCluster, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr, cfg.numAttrs = pdl ? 2 : 1;
+        const float scale = 1.0f / std::sqrt(static_cast<float>(HD));
+        const float* q = qkv;
+        const unsigned short *kc = L.kc, *vc = L.vc;
+        const int* pos_p = state;
+        return cudaLaunchKernelEx(&cfg, attn_decode_cluster_kernel<HD, G>, q, kc, vc, pos_p, attn, xq_wo, xd_of(xq_wo, L.wo.k), heads, kv_heads, scale,
+                                  max_ctx) == cudaSuccess
+                   ? KCB_SUCCESS
+                   : KCB_LAUNCH_FAILURE;
+    }
+    template <int HD>
+    int attention_cluster(const DLayer& L, bool pdl) {
+        switch (heads / kv_heads) {
+        case 1: return attention_cluster_launch<HD, 1>(L, pdl);
+        case 2: return attention_cluster_launch<HD, 2>(L, pdl);
+        case 3: return attention_cluster_launch<HD, 3>(L, pdl);
+        default: return attention_cluster_launch<HD, 4>(L, pdl);
+        }
+    }
     template <int HD>
     int attention_pdl(const DLayer& L, bool pdl) {
         const int group = heads / kv_heads;
@@ -1619,13 +1811,18 @@ private:
                     e)
                     return e;
             }
-            if (const int e = hd == 128 ? attention_pdl<128>(L, pdl) : attention_pdl<64>(L, pdl); e) return e;
-            // the merge of the partials stays a launch of its own: a block of 32 channels per warp over 24 CTAs is one
-            // round trip to L2, where every CTA of the wo launch redoing all 96 blocks took six
-            if (const int e = launch_pdl(attn_combine_q8_kernel, dim3((qd / 32 + 3) / 4), dim3(128), 0, pdl, const_cast<const float*>(part), attn, xq_wo,
-                                         xd_of(xq_wo, L.wo.k), heads, hd, nsplit);
-                e)
-                return e;
+            if (attn_in_cluster()) {  // partials merged through the cluster's shared memory
+                if (const int e = hd == 128 ? attention_cluster<128>(L, pdl) : attention_cluster<64>(L, pdl); e) return e;
+            } else {
+                if (const int e = hd == 128 ? attention_pdl<128>(L, pdl) : attention_pdl<64>(L, pdl); e) return e;
+                // the merge of the partials is a launch of its own here: a block of 32 channels per warp over 24 CTAs is one
+                // round trip to L2.  Every CTA of the wo launch redoing all 96 blocks as a prologue took six; the last CTA
+                // of each kv head merging behind a fence and a counter gave 737 tokens/s where this form gave 772.
+                if (const int e = launch_pdl(attn_combine_q8_kernel, dim3((qd / 32 + 3) / 4), dim3(128), 0, pdl, const_cast<const float*>(part), attn, xq_wo,
+                                             xd_of(xq_wo, L.wo.k), heads, hd, nsplit);
+                    e)
+                    return e;
+            }
             if (const int e = trace_copy(xq_wo, L.wo.k); e) return e;
             const Pair o = pair_of(L.wo, t);
             if (const int e = decode_matvec_q8(o.w4, o.y4, o.rows4, o.w6, o.y6, o.rows6, L.wo.k, xq_wo, xd_of(xq_wo, L.wo.k), pdl, stream_); e) return e;
@@ -1745,6 +1942,7 @@ private:
     cudaStream_t stream_ = nullptr;
     bool prompt_blocked_ = !(getenv("KCB_PROMPT_ATTN_BLOCKED") && atoi(getenv("KCB_PROMPT_ATTN_BLOCKED")) == 0);
     bool rope_tail_ = !(getenv("KCB_DECODE_ROPE_TAIL") && atoi(getenv("KCB_DECODE_ROPE_TAIL")) == 0);
+    bool attn_cluster_ = !(getenv("KCB_DECODE_ATTN_CLUSTER") && atoi(getenv("KCB_DECODE_ATTN_CLUSTER")) == 0);
     size_t fuse_limit_ = (getenv("KCB_DECODE_FUSE_MB") ? static_cast<size_t>(atoi(getenv("KCB_DECODE_FUSE_MB"))) : 64) << 20;
     int swiglu_limit_ = getenv("KCB_DECODE_SWIGLU_MAX") ? atoi(getenv("KCB_DECODE_SWIGLU_MAX")) : 4096;
     size_t rows_parity_ = 0;  // which half of the exchange area's row buffers the next K-split matmul of a prompt chunk writes

@@ -149,9 +149,9 @@ def test_graph_decoder_stage_by_stage_with_flip_count(shape_fn, fused, monkeypat
     total = clean = 0
     diverged = False
     with decoder.FastDecoder(shape, model) as d:
-        # embed + 7 launches per layer (6 where the rotation and the cache append ride on the q|k|v launch: adjacent-pair
-        # RoPE, no per-head norms) + lm_head + 2 for the pick when the producers are prologues of the matvecs
-        per_layer = 7 if (shape.neox or shape.qk_norm) else 6
+        # embed + 6 launches per layer (5 where the rotation and the cache append ride on the q|k|v launch: adjacent-pair
+        # RoPE, no per-head norms; the attention partials are merged inside the attention launch's clusters) + lm_head + 2 for the pick when the producers are prologues of the matvecs
+        per_layer = 6 if (shape.neox or shape.qk_norm) else 5
         assert (d.launches_per_token == 4 + per_layer * shape.layers) == bool(fused)
         words = d.enable_trace()
         assert words == staged.trace_words()
@@ -208,10 +208,10 @@ def test_full_size_logits_against_the_reference_decode_loop():
             ref_logits.append(out)
         oracle.ref.lib.kcref_model_close(h)
     with decoder.FastDecoder(shape, model) as d:
-        # the fused step is the one measured: embed, seven launches per layer (q|k|v with norm and rotation, attention,
-        # merge, wo, gate|up with norm, SwiGLU, down), the lm_head (above 64 MB: its norm a launch of its own, then the
+        # the fused step is the one measured: embed, six launches per layer (q|k|v with norm and rotation, attention
+        # with its merge, wo, gate|up with norm, SwiGLU, down), the lm_head (above 64 MB: its norm a launch of its own, then the
         # streaming matvec) and two for the pick
-        assert d.launches_per_token == 5 + 7 * shape.layers
+        assert d.launches_per_token == 5 + 6 * shape.layers
         words = d.enable_trace()
         assert words == staged.trace_words()
         d.set_prompt(toks)
