@@ -15,6 +15,9 @@
 //     activation slice still fits in registers.  (Two CTAs of 8 warps and 110 KB per SM, so that the next kernel's CTAs sit beside this
 //     one's and its weights arrive while this one computes, measured slower: 7.4 against 5.7 us on an 8192 x 3072
 //     Q4_K matrix, 638 against 687 tokens/s on the Llama-3.2-3B-shape decode step in the same run.)
+// (Having each CTA also ask the L2 for its share of the NEXT launch's matrix -- cp.async.bulk.prefetch.L2, right after its
+// own first tiles or behind its own last one -- measured slower both ways: 816 and 798 against 840 tokens/s on the
+// Llama-3.2-3B-shape step; the prefetches queue with the tiles the CTAs are waiting for.)
 // The per-row arithmetic is that of the bulk-copy matvec in kquant_matvec.cu (integer dot products, the reference's
 // fp32 scale products, one shuffle tree per row; Q4_K on four lanes per super-block where a CTA has three or more tiles,
 // on eight where the launch is latency bound).  A q|k|v product can carry a tail that rotates the q and k pairs of each
