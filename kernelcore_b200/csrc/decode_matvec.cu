@@ -679,9 +679,16 @@ int dmv_dispatch(const void* w4, float* y4, int rows4, const void* w6, float* y6
     DmvMat m4{static_cast<const uint8_t*>(w4), y4, rows4}, m6{static_cast<const uint8_t*>(w6), y6, rows6};
     m6.row_off = rows4;  // (read by the rotation tail only)
     if (pro.tail.hd != 0 && nsb > 16) return KCB_INVALID_VALUE;
-    if (nsb <= 16)  // 8-row tiles where they balance the SMs better (few tiles per CTA), else two rows per warp
-        return row_times(rows4, rows6, 16) < row_times(rows4, rows6, 32) ? dmv_launch_narrow<PRO, 16>(m4, m6, nsb, pro, pdl, s)
-                                                                          : dmv_launch_narrow<PRO, 32>(m4, m6, nsb, pro, pdl, s);
+    if (nsb <= 16) {
+        // 16-row tiles only where they balance the SMs clearly better (few tiles per CTA), else 32-row tiles, two rows per
+        // warp: a row of twelve super-blocks on a half-warp is three full steps, on a whole warp two with a quarter of the
+        // lanes idle in the second, and the 32-row tile has half the per-tile waits.  Measured per 27 KB of Q4_K, 0.65
+        // against 0.85 us; 16384 x 3072 (7 rounds of 16 rows or 4 of 32): 9.6 against 10.2 us, the Llama-3.2-3B-shape
+        // step 855 against 840 tokens/s.  KCB_DMV_TR16_BIAS sets the factor (1 = by rounds x rows alone).
+        static const float bias = getenv("KCB_DMV_TR16_BIAS") ? static_cast<float>(atof(getenv("KCB_DMV_TR16_BIAS"))) : 1.15f;
+        return row_times(rows4, rows6, 16) * bias < row_times(rows4, rows6, 32) ? dmv_launch_narrow<PRO, 16>(m4, m6, nsb, pro, pdl, s)
+                                                                                 : dmv_launch_narrow<PRO, 32>(m4, m6, nsb, pro, pdl, s);
+    }
     // k up to 8192: 8-row tiles, two warps per row (16 super-blocks each at most); up to 16384: four warps per row
     const bool has4 = rows4 > 0;
     if (rows4 > 0 && rows6 > 0) return KCB_UNSUPPORTED_OPERATION;
