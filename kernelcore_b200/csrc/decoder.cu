@@ -1623,8 +1623,8 @@ private:
         return launch_status();
     }
     // The step with the small vector kernels folded into the matvecs that read them (decode_matvec.cu): per layer
-    //   [add + norm + quantize | q|k (+ v)]  rope + cache append  attention partials  merge + quantize  wo
-    //   [add + norm + quantize | gate|up]  [SwiGLU + quantize | down]
+    //   [add + norm + quantize | q|k (+ v) | rope + cache append]  attention + merge + quantize (one cluster launch)  wo
+    //   [add + norm + quantize | gate|up]  SwiGLU + quantize  down      (SwiGLU a prologue of down up to 4096 values)
     // chained by programmatic dependent launches, so each kernel's weights are requested while its predecessor still runs.
     // Single GPU; matrices whose shapes the fused kernels do not take keep the step on the unfused path (record()).
     // where the next traced vector of k int8 values goes (nullptr when tracing is off)
@@ -1749,7 +1749,8 @@ private:
     // The SwiGLU prologue costs per value (an exponential and a division in every CTA) and delays the matvec behind it,
     // where the stand-alone kernel spreads the values over many CTAs and overlaps the matvec's weight requests: folded in
     // up to swiglu_limit_ values only (4096; KCB_DECODE_SWIGLU_MAX) -- on Llama-3.2-3B shapes the 8192-wide one folded
-    // into the down projection gave 718 tokens/s, as a launch of its own 781.  The norm prologue is a few thousand multiply-adds: folded in for every matrix
+    // into the down projection gave 718 tokens/s, as a launch of its own 781 (801 once that launch carried a programmatic
+    // dependency as well).  The norm prologue is a few thousand multiply-adds: folded in for every matrix
     // the decode matvec kernel takes at all (norm_limit_, 64 MB; KCB_DECODE_FUSE_MB), beyond which the streaming kernel
     // with its deeper ring is the better matvec anyway.
     bool streams_long(const DMat& m) const { return m.k > swiglu_limit_ || kcb_kquant_bytes(m.rows, m.k, m.q6) > fuse_limit_; }
