@@ -1691,8 +1691,9 @@ private:
         const int group = heads / kv_heads;
         return attn_cluster_ && group <= 4 && group * kv_heads == heads && max_ctx <= 4096;
     }
+    // (xq_out / xd_out: where the quantized output goes; default the wo scratch from its first block)
     template <int HD, int G>
-    int attention_cluster_launch(const DLayer& L, bool pdl) {
+    int attention_cluster_launch(const DLayer& L, bool pdl, int* xq_out, float* xd_out) {
         constexpr size_t smem = static_cast<size_t>(33) * G * (HD + 2) * 4;
         static PerDeviceFlag raised;
         if (!raise_dynamic_smem(attn_decode_cluster_kernel<HD, G>, static_cast<int>(smem), raised)) return KCB_LAUNCH_FAILURE;
@@ -1708,18 +1709,19 @@ private:
         const float* q = qkv;
         const unsigned short *kc = L.kc, *vc = L.vc;
         const int* pos_p = state;
-        return cudaLaunchKernelEx(&cfg, attn_decode_cluster_kernel<HD, G>, q, kc, vc, pos_p, attn, xq_wo, xd_of(xq_wo, L.wo.k), heads, kv_heads, scale,
-                                  max_ctx) == cudaSuccess
+        if (!xq_out) xq_out = xq_wo, xd_out = xd_of(xq_wo, L.wo.k);
+        return cudaLaunchKernelEx(&cfg, attn_decode_cluster_kernel<HD, G>, q, kc, vc, pos_p, attn, xq_out, xd_out, heads, kv_heads, scale, max_ctx) ==
+                       cudaSuccess
                    ? KCB_SUCCESS
                    : KCB_LAUNCH_FAILURE;
     }
     template <int HD>
-    int attention_cluster(const DLayer& L, bool pdl) {
+    int attention_cluster(const DLayer& L, bool pdl, int* xq_out = nullptr, float* xd_out = nullptr) {
         switch (heads / kv_heads) {
-        case 1: return attention_cluster_launch<HD, 1>(L, pdl);
-        case 2: return attention_cluster_launch<HD, 2>(L, pdl);
-        case 3: return attention_cluster_launch<HD, 3>(L, pdl);
-        default: return attention_cluster_launch<HD, 4>(L, pdl);
+        case 1: return attention_cluster_launch<HD, 1>(L, pdl, xq_out, xd_out);
+        case 2: return attention_cluster_launch<HD, 2>(L, pdl, xq_out, xd_out);
+        case 3: return attention_cluster_launch<HD, 3>(L, pdl, xq_out, xd_out);
+        default: return attention_cluster_launch<HD, 4>(L, pdl, xq_out, xd_out);
         }
     }
     template <int HD>
@@ -1875,10 +1877,15 @@ private:
             rope_kv_f16_kernel<<<(heads + 2 * kv_heads + 3) / 4, 128, 0, stream_>>>(qkv, qkv + qd + kv_heads * hd, 0, 0, pos_p, 0, L.kc, L.vc, rope_ff,
                                                                                      L.q_norm, L.k_norm, heads, kv_heads, hd, log2_base, neox, eps, max_ctx);
             if (const int e = launch_status(); e) return e;
-            if (const int e = hd == 128 ? attention<128>(L) : attention<64>(L); e) return e;
-            attn_combine_q8_kernel<<<(qd / 32 + 3) / 4, 128, 0, stream_>>>(part, attn, xq_wo + wo_win.first_block * 8,
-                                                                            xd_of(xq_wo, L.wo.k) + wo_win.first_block * 2, heads, hd, nsplit);
-            if (const int e = launch_status(); e) return e;
+            int* xq_attn = xq_wo + wo_win.first_block * 8;  // (tensor parallel: this rank's heads are a window of wo's input)
+            float* xd_attn = xd_of(xq_wo, L.wo.k) + wo_win.first_block * 2;
+            if (attn_in_cluster()) {
+                if (const int e = hd == 128 ? attention_cluster<128>(L, false, xq_attn, xd_attn) : attention_cluster<64>(L, false, xq_attn, xd_attn); e) return e;
+            } else {
+                if (const int e = hd == 128 ? attention<128>(L) : attention<64>(L); e) return e;
+                attn_combine_q8_kernel<<<(qd / 32 + 3) / 4, 128, 0, stream_>>>(part, attn, xq_attn, xd_attn, heads, hd, nsplit);
+                if (const int e = launch_status(); e) return e;
+            }
             if (const int e = trace_copy(xq_wo, L.wo.k); e) return e;
             float* po = partial_out();
             if (const int e = mv(L.wo, xq_wo, po); e) return e;
