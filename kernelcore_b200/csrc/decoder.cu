@@ -346,7 +346,7 @@ template <int HD, int G>
 __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(const float* qkv, const unsigned short* kc, const unsigned short* vc, const int* pos_p,
                                                                   float* attn, int* xq, float* xd, int heads, int kv_heads, float scale, int max_ctx) {
     constexpr int DPL = HD / 8, NW = 8, NV = DPL / 8, PW = HD + 2;
-    extern __shared__ float sm[];              // [NW * 4][G][PW] lane-group partials, then [G][PW]: this CTA's partial
+    extern __shared__ float sm[];              // [NW * 4][G][PW] lane-group partials, [G][PW] this CTA's partial, [G][32] weights
     float* cta_part = sm + NW * 4 * G * PW;
     cg::cluster_group cluster = cg::this_cluster();
     const int sp = static_cast<int>(cluster.block_rank());
@@ -438,22 +438,31 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(const float* q
         }
     }
     __syncthreads();
+    // warp g: the CTA-wide max of head g, every lane group's weight (lane = lane group) and the weighted sum of the sums,
+    // once per head instead of once per output channel; then a channel is 32 multiply-adds in lane-group order
+    static_assert(NW * 4 == 32 && G <= NW, "one lane per lane group, one warp per head of the group");
+    float* wsm = cta_part + G * PW;  // [G][32]
+    if (warp < G) {
+        const float* pp = sm + lane * G * PW + warp * PW;
+        const float pm = pp[HD], pl = pp[HD + 1];
+        const float mm = warp_max(pm);
+        const float wgt = pm == -INFINITY ? 0.0f : exp2f((pm - mm) * 1.44269504f);
+        wsm[warp * 32 + lane] = wgt;
+        float ll = 0.0f;
+#pragma unroll
+        for (int pi = 0; pi < 32; ++pi) ll = __fmaf_rn(__shfl_sync(0xffffffffu, pl, pi), __shfl_sync(0xffffffffu, wgt, pi), ll);
+        if (lane == 0) {
+            cta_part[warp * PW + HD] = mm;
+            cta_part[warp * PW + HD + 1] = ll;
+        }
+    }
+    __syncthreads();
     for (int o = threadIdx.x; o < G * HD; o += blockDim.x) {
         const int g = o / HD, d = o % HD;
-        float mm = -INFINITY;
-        for (int pi = 0; pi < NW * 4; ++pi) mm = fmaxf(mm, sm[pi * G * PW + g * PW + HD]);
-        float ll = 0.0f, aa = 0.0f;
-        for (int pi = 0; pi < NW * 4; ++pi) {
-            const float* pp = sm + pi * G * PW + g * PW;
-            const float wgt = pp[HD] == -INFINITY ? 0.0f : exp2f((pp[HD] - mm) * 1.44269504f);
-            ll += pp[HD + 1] * wgt;
-            aa += pp[d] * wgt;
-        }
+        float aa = 0.0f;
+#pragma unroll 8
+        for (int pi = 0; pi < 32; ++pi) aa = __fmaf_rn(sm[pi * G * PW + g * PW + d], wsm[g * 32 + pi], aa);
         cta_part[g * PW + d] = aa;
-        if (d == 0) {
-            cta_part[g * PW + HD] = mm;
-            cta_part[g * PW + HD + 1] = ll;
-        }
     }
     cluster.sync();  // every CTA's partial is in place (a hardware barrier over the co-scheduled cluster: nothing to poll)
     const int bl = warp * kAttnCluster + sp;  // this warp's block of 32 channels among the G * HD / 32 of the kv head
@@ -1694,7 +1703,7 @@ private:
     // (xq_out / xd_out: where the quantized output goes; default the wo scratch from its first block)
     template <int HD, int G>
     int attention_cluster_launch(const DLayer& L, bool pdl, int* xq_out, float* xd_out) {
-        constexpr size_t smem = static_cast<size_t>(33) * G * (HD + 2) * 4;
+        constexpr size_t smem = (static_cast<size_t>(33) * G * (HD + 2) + G * 32) * 4;
         static PerDeviceFlag raised;
         if (!raise_dynamic_smem(attn_decode_cluster_kernel<HD, G>, static_cast<int>(smem), raised)) return KCB_LAUNCH_FAILURE;
         cudaLaunchConfig_t cfg{};
