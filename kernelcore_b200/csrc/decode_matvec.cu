@@ -21,8 +21,10 @@
 // The per-row arithmetic is that of the bulk-copy matvec in kquant_matvec.cu (integer dot products, the reference's
 // fp32 scale products, one shuffle tree per row; Q4_K on four lanes per super-block where a CTA has three or more tiles,
 // on eight where the launch is latency bound).  A q|k|v product can carry a tail that rotates the q and k pairs of each
-// finished tile and appends k and v to the fp16 cache (DecodeRopeTail, ops.h).  Every mbarrier wait is bounded; on expiry
-// the CTA counts the event and leaves.
+// finished tile and appends k and v to the fp16 cache (DecodeRopeTail, ops.h); a gate|up product can carry one that turns
+// each pair of gate / up tiles into a quantized block of SwiGLU values (DecodeSwigluTail): unlike the SwiGLU PROLOGUE of
+// the down projection, which every CTA repeats for the whole vector, the tail computes each value once.  Every mbarrier
+// wait is bounded; on expiry the CTA counts the event and leaves.
 
 #include "common.cuh"
 #include "ops.h"
@@ -164,13 +166,27 @@ __device__ __forceinline__ void pro_combine(const float* part, int* xq, float* x
     }
 }
 
+// Which tiles a CTA takes.  Plain: tiles cta, cta + nctas, ... of the matrix.  With a SwiGLU tail (sw_inter != 0): PAIRS
+// cta, cta + nctas, ... -- even steps the pair's tile of gate rows, odd steps the tile of the same up rows.
+__device__ __forceinline__ int dmv_my_tiles(int rows, int tr, int cta, int nctas, int sw_inter) {
+    if (sw_inter) {
+        const int np = sw_inter / tr;
+        return cta < np ? 2 * ((np - 1 - cta) / nctas + 1) : 0;
+    }
+    const int nt = (rows + tr - 1) / tr;
+    return cta < nt ? (nt - 1 - cta) / nctas + 1 : 0;
+}
+__device__ __forceinline__ int dmv_tile_row0(int i, int tr, int cta, int nctas, int sw_inter) {
+    return sw_inter ? (i & 1) * sw_inter + (cta + (i >> 1) * nctas) * tr : (cta + i * nctas) * tr;
+}
+
 // ---- the matvec body --------------------------------------------------------------------------------------------------
 // CTA `cta` of `nctas` takes tiles cta, cta + nctas, ... of TR rows.  KSPLIT warps share a row: warp w works on tile
 // row (w % (kWarps / KSPLIT)) [+ multiples of that], super-blocks [ks * nsb / KSPLIT, (ks + 1) * nsb / KSPLIT) with
 // ks = w / (kWarps / KSPLIT).  ITERS = ceil(nsb / KSPLIT / 4).
 template <bool kQ6, int ITERS, int TR, int KSPLIT, bool kLanes4>
 __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq, const float* sxd, uint64_t* full, uint8_t* buf, int stages, int cta,
-                                         int nctas, float (*ytile)[TR * KSPLIT], const DecodeRopeTail& tail) {
+                                         int nctas, float (*ytile)[TR * KSPLIT], const DecodeRopeTail& tail, const DecodeSwigluTail& sw) {
     constexpr int kBlk = kQ6 ? kQ6KBlock : kQ4KBlock;
     constexpr int NR = kWarps / KSPLIT;  // rows worked on at once (Q4_K: twice that, see below)
     constexpr int RPW = TR / NR;         // rows per warp and tile
@@ -191,14 +207,15 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
     const int g = lane >> 3, c8 = lane & 7;
     const int wr = warp % NR, ks = warp / NR;
     const int nsb_w = nsb / KSPLIT, sb_base = ks * nsb_w;
-    const int ntiles = (rows + TR - 1) / TR;
-    const int my_tiles = cta < ntiles ? (ntiles - 1 - cta) / nctas + 1 : 0;
+    const int sw_inter = (KSPLIT == 1 && TR == 32) ? sw.inter : 0;  // SwiGLU tail: whole Q8 blocks need 32-row tiles
+    const int my_tiles = dmv_my_tiles(rows, TR, cta, nctas, sw_inter);
     const size_t nblk = static_cast<size_t>(rows) * nsb;
     const bool with_tail = KSPLIT == 1 && tail.hd != 0;  // results go through ytile and the rotation / cache tail
+    const bool to_tile = with_tail || sw_inter != 0;     // results go to ytile only (a tail consumes them)
 
     auto issue = [&](int i) {  // thread 0 only; the kernel has already requested tiles 0 .. stages - 1
         const int s = i % stages;
-        const int r0 = (cta + i * nctas) * TR;
+        const int r0 = dmv_tile_row0(i, TR, cta, nctas, sw_inter);
         const int nr = min(TR, rows - r0);
         uint8_t* dst = buf + static_cast<size_t>(s) * stage_bytes;
         const size_t b0 = static_cast<size_t>(r0) * nsb;
@@ -369,7 +386,7 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
             for (int t = 0; t < 1000; ++t) __nanosleep(1000);  // bounded grace for copies still in flight
             return;  // data never arrived: leave without touching y
         }
-        const int row0 = (cta + i * nctas) * TR;
+        const int row0 = dmv_tile_row0(i, TR, cta, nctas, sw_inter);
         const uint8_t* st = buf + static_cast<size_t>(s) * stage_bytes;
         if constexpr (kEight) {
             float acc[RPW];
@@ -388,10 +405,10 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
             for (int r = 0; r < RPW; ++r) {
                 const float v = warp_sum(acc[r]);
                 const int rl = wr + r * NR;
-                if (KSPLIT == 1 && !with_tail) {
+                if (KSPLIT == 1 && !to_tile) {
                     if (lane == 0 && row0 + rl < rows) m.y[row0 + rl] = v;
                 } else if (lane == 0) {
-                    ytile[i & 1][ks * TR + rl] = v;  // double-buffered: tile i + 2 writes it only after the barrier of tile i + 1
+                    ytile[i & 3][ks * TR + rl] = v;  // four buffers: tile i + 4 writes this one only after the barriers of tiles i + 1 .. i + 3
                 }
             }
         } else if constexpr (!kPair) {  // both half-warps on row wr + r NR, eight super-blocks per step
@@ -411,10 +428,10 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
             for (int r = 0; r < RPW; ++r) {
                 const float v = warp_sum(acc[r]);
                 const int rl = wr + r * NR;
-                if (KSPLIT == 1 && !with_tail) {
+                if (KSPLIT == 1 && !to_tile) {
                     if (lane == 0 && row0 + rl < rows) m.y[row0 + rl] = v;
                 } else if (lane == 0) {
-                    ytile[i & 1][ks * TR + rl] = v;
+                    ytile[i & 3][ks * TR + rl] = v;
                 }
             }
         } else {  // half-warp hw on rows wr + (2 p + hw) NR
@@ -437,10 +454,10 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
                 for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);  // within the half-warp
                 const int rl = wr + (2 * p + hw) * NR;
                 if ((lane & 15) != 0) continue;
-                if (KSPLIT == 1 && !with_tail) {
+                if (KSPLIT == 1 && !to_tile) {
                     if (row0 + rl < rows) m.y[row0 + rl] = v;
                 } else {
-                    ytile[i & 1][ks * TR + rl] = v;
+                    ytile[i & 3][ks * TR + rl] = v;
                 }
             }
         }
@@ -450,7 +467,7 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
             // the tile's rows sit in ytile: rotate the q and k pairs, append k and v to the cache (see DecodeRopeTail)
             const int r = row0 + 2 * static_cast<int>(threadIdx.x);
             if (r < rows) {
-                const float x0 = ytile[i & 1][2 * threadIdx.x], x1 = ytile[i & 1][2 * threadIdx.x + 1];
+                const float x0 = ytile[i & 3][2 * threadIdx.x], x1 = ytile[i & 3][2 * threadIdx.x + 1];
                 const int L = m.row_off + r, qd = tail.heads * tail.hd, kvd = tail.kv_heads * tail.hd;
                 const int pos = min(*tail.pos_p, tail.max_ctx - 1);
                 if (L >= qd + kvd) {  // v: cast and append
@@ -471,10 +488,16 @@ __device__ __forceinline__ void dmv_body(const DmvMat m, int nsb, const int* sxq
                 }
             }
         }
+        if (sw_inter != 0 && (i & 1) && warp == 0) {
+            // the pair is complete: gate rows in the buffer of tile i - 1, up rows in this tile's (see DecodeSwigluTail)
+            const float gv = ytile[(i - 1) & 3][lane], uv = ytile[i & 3][lane];
+            const float e = exp2f(__fmul_rn(-gv, 1.44269504f));
+            quantize_block_warp(__fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, e)), uv), sw.xq, sw.xd, cta + (i >> 1) * nctas, lane);
+        }
         if (KSPLIT > 1 && threadIdx.x < TR && row0 + static_cast<int>(threadIdx.x) < rows) {
-            float v = ytile[i & 1][threadIdx.x];
+            float v = ytile[i & 3][threadIdx.x];
 #pragma unroll
-            for (int q = 1; q < KSPLIT; ++q) v = __fadd_rn(v, ytile[i & 1][q * TR + threadIdx.x]);  // shares added in K order
+            for (int q = 1; q < KSPLIT; ++q) v = __fadd_rn(v, ytile[i & 3][q * TR + threadIdx.x]);  // shares added in K order
             m.y[row0 + threadIdx.x] = v;
         }
     }
@@ -500,6 +523,8 @@ struct DmvPro {
     int heads = 0, hd = 0, nsplit = 0;
     // optional tail of a q|k|v product (hd == 0: none)
     DecodeRopeTail tail;
+    // optional tail of a gate|up product (inter == 0: none)
+    DecodeSwigluTail sw;
 };
 
 // One launch: matrix m4 (Q4_K) on CTAs [0, c4) and, when c6 > 0, matrix m6 (Q6_K planes) on CTAs [c4, c4 + c6), both on
@@ -507,7 +532,7 @@ struct DmvPro {
 template <int ITERS, int TR, int KSPLIT, int PRO, bool kHas4, bool kHas6, bool kLanes4 = false>
 __global__ void __launch_bounds__(kThreads, 1) dmv_kernel(const DmvMat m4, const DmvMat m6, int c4, int nsb, const DmvPro pro, int stages4, int stages6) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float ytile[2][TR * KSPLIT];
+    __shared__ float ytile[4][TR * KSPLIT];
     __shared__ float gsum[64];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     int* sxq = reinterpret_cast<int*>(smem + kBarBytes);
@@ -524,12 +549,12 @@ __global__ void __launch_bounds__(kThreads, 1) dmv_kernel(const DmvMat m4, const
         mbar_init_fence();
         const DmvMat& m = is4 ? m4 : m6;
         const int blkb = is4 ? kQ4KBlock : kQ6KBlock;
-        const int ntiles = (m.rows + TR - 1) / TR;
-        const int my_tiles = cta < ntiles ? (ntiles - 1 - cta) / nctas + 1 : 0;
+        const int sw_inter = (KSPLIT == 1 && TR == 32) ? pro.sw.inter : 0;
+        const int my_tiles = dmv_my_tiles(m.rows, TR, cta, nctas, sw_inter);
         const uint32_t stage_bytes = static_cast<uint32_t>(TR) * nsb * blkb;
         const size_t nblk = static_cast<size_t>(m.rows) * nsb;
         for (int i = 0; i < stages && i < my_tiles; ++i) {
-            const int r0 = (cta + i * nctas) * TR;
+            const int r0 = dmv_tile_row0(i, TR, cta, nctas, sw_inter);
             const int nr = min(TR, m.rows - r0);
             uint8_t* dst = buf + static_cast<size_t>(i) * stage_bytes;
             const size_t b0 = static_cast<size_t>(r0) * nsb;
@@ -565,9 +590,9 @@ __global__ void __launch_bounds__(kThreads, 1) dmv_kernel(const DmvMat m4, const
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (is4) {
-        if constexpr (kHas4) dmv_body<false, ITERS, TR, KSPLIT, kLanes4>(m4, nsb, sxq, sxd, full, buf, stages, cta, nctas, ytile, pro.tail);
+        if constexpr (kHas4) dmv_body<false, ITERS, TR, KSPLIT, kLanes4>(m4, nsb, sxq, sxd, full, buf, stages, cta, nctas, ytile, pro.tail, pro.sw);
     } else {
-        if constexpr (kHas6) dmv_body<true, ITERS, TR, KSPLIT, false>(m6, nsb, sxq, sxd, full, buf, stages, cta, nctas, ytile, pro.tail);
+        if constexpr (kHas6) dmv_body<true, ITERS, TR, KSPLIT, false>(m6, nsb, sxq, sxd, full, buf, stages, cta, nctas, ytile, pro.tail, pro.sw);
     }
 }
 
@@ -612,13 +637,18 @@ int dmv_launch_narrow(const DmvMat& m4, const DmvMat& m6, int nsb, const DmvPro&
     const int t4 = (m4.rows + TR - 1) / TR, t6 = (m6.rows + TR - 1) / TR;
     int c4, c6;
     share_ctas(t4, t6, m4.rows, m6.rows, c4, c6);
-    const int st4 = has4 ? stages_for((t4 + c4 - 1) / c4, static_cast<size_t>(TR) * nsb * kQ4KBlock, fixed) : 1;
-    const int st6 = has6 ? stages_for((t6 + c6 - 1) / c6, static_cast<size_t>(TR) * nsb * kQ6KBlock, fixed) : 1;
+    // SwiGLU tail (one matrix, 32-row tiles): the unit of work is a pair of tiles
+    const int sw_pairs = (TR == 32 && pro.sw.inter) ? pro.sw.inter / TR : 0;
+    if (sw_pairs) (has4 ? c4 : c6) = std::min(sw_pairs, kSmCount);
+    const int per4 = !has4 ? 0 : sw_pairs ? 2 * ((sw_pairs + c4 - 1) / c4) : (t4 + c4 - 1) / c4;  // tiles of the busiest CTA
+    const int per6 = !has6 ? 0 : sw_pairs ? 2 * ((sw_pairs + c6 - 1) / c6) : (t6 + c6 - 1) / c6;
+    const int st4 = has4 ? stages_for(per4, static_cast<size_t>(TR) * nsb * kQ4KBlock, fixed) : 1;
+    const int st6 = has6 ? stages_for(per6, static_cast<size_t>(TR) * nsb * kQ6KBlock, fixed) : 1;
     if (st4 < 1 || st6 < 1) return KCB_UNSUPPORTED_OPERATION;
     const size_t smem = fixed + std::max(has4 ? static_cast<size_t>(st4) * TR * nsb * kQ4KBlock : 0, has6 ? static_cast<size_t>(st6) * TR * nsb * kQ6KBlock : 0);
     // Q4_K with three or more tiles per CTA is bound by its instruction stream: four lanes per super-block; with fewer the
     // launch is latency bound and eight lanes (more independent work per lane) are faster (8192 x 3072: 5.6 against 5.9 us)
-    const bool lanes4 = has4 && (t4 + c4 - 1) / c4 >= 3;
+    const bool lanes4 = has4 && per4 >= 3;
 #define KCB_DMV(ITERS_, H4, H6)                                                                                                            \
     do {                                                                                                                                   \
         static PerDeviceFlag raised, raised4;                                                                                              \
@@ -679,6 +709,7 @@ int dmv_dispatch(const void* w4, float* y4, int rows4, const void* w6, float* y6
     DmvMat m4{static_cast<const uint8_t*>(w4), y4, rows4}, m6{static_cast<const uint8_t*>(w6), y6, rows6};
     m6.row_off = rows4;  // (read by the rotation tail only)
     if (pro.tail.hd != 0 && nsb > 16) return KCB_INVALID_VALUE;
+    if (pro.sw.inter) return nsb <= 16 ? dmv_launch_narrow<PRO, 32>(m4, m6, nsb, pro, pdl, s) : KCB_INVALID_VALUE;
     if (nsb <= 16) {
         // 16-row tiles only where they balance the SMs clearly better (few tiles per CTA), else 32-row tiles, two rows per
         // warp: a row of twelve super-blocks on a half-warp is three full steps, on a whole warp two with a quarter of the
@@ -735,7 +766,7 @@ int decode_matvec_q8(const void* w4, float* y4, int rows4, const void* w6, float
     return dmv_dispatch<0>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
 }
 int decode_matvec_norm(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* x_in, const float* t, float* x_out,
-                       const float* wn, float eps, bool pdl, cudaStream_t s, int* trace, const DecodeRopeTail* tail) {
+                       const float* wn, float eps, bool pdl, cudaStream_t s, int* trace, const DecodeRopeTail* tail, const DecodeSwigluTail* swiglu) {
     if (!decode_matvec_shape_ok(rows4, rows6, k) || k % 128 || k > 8192 || !x_in || !x_out || !wn) return KCB_INVALID_VALUE;
     if (misaligned(x_in, 16) || misaligned(t, 16) || misaligned(x_out, 16) || misaligned(wn, 16)) return KCB_INVALID_POINTER;
     DmvPro p;
@@ -745,6 +776,12 @@ int decode_matvec_norm(const void* w4, float* y4, int rows4, const void* w6, flo
         if (k > 4096 || tail->hd <= 0 || tail->hd % 2 || rows4 + rows6 != all || rows4 % tail->hd || !tail->pos_p || !tail->kc || !tail->vc)
             return KCB_INVALID_VALUE;
         p.tail = *tail;
+    }
+    if (swiglu && swiglu->inter) {  // one matrix of gate rows then up rows, whole 32-row tiles each
+        if (tail || k > 4096 || (rows4 && rows6) || swiglu->inter % 32 || rows4 + rows6 != 2 * swiglu->inter || !swiglu->xq || !swiglu->xd)
+            return KCB_INVALID_VALUE;
+        if (misaligned(swiglu->xq, 16) || misaligned(swiglu->xd, 8)) return KCB_INVALID_POINTER;
+        p.sw = *swiglu;
     }
     return dmv_dispatch<1>(w4, y4, rows4, w6, y6, rows6, k, p, pdl, s);
 }

@@ -1769,7 +1769,7 @@ private:
     // Fused: one launch, the new residual stream lands in `other` and the two pointers swap.  Streaming: in place.
     // tail (q|k|v only): rotation and cache append inside the fused launch; *tail_done tells whether that happened.
     int norm_then_matvecs(const std::vector<DMat>& mats, float* y, float*& cur, float*& other, const float* add, const float* w, bool pdl,
-                          const DecodeRopeTail* tail = nullptr, bool* tail_done = nullptr) {
+                          const DecodeRopeTail* tail = nullptr, bool* tail_done = nullptr, const DecodeSwigluTail* swiglu = nullptr) {
         if (tail_done) *tail_done = false;
         size_t bytes = 0;
         for (const DMat& m : mats) bytes += kcb_kquant_bytes(m.rows, m.k, m.q6);
@@ -1786,11 +1786,12 @@ private:
         }
         const Pair p = pair_of(mats, y);
         const bool use_tail = tail && p.rows4 % tail->hd == 0;  // (whole heads in the Q4_K matrix)
+        const bool use_swiglu = swiglu && mats.size() == 1 && hidden <= 4096 && swiglu->inter % 32 == 0;
         if (const int e = decode_matvec_norm(p.w4, p.y4, p.rows4, p.w6, p.y6, p.rows6, hidden, cur, add, other, w, eps, pdl, stream_, trace_slot(hidden),
-                                             use_tail ? tail : nullptr);
+                                             use_tail ? tail : nullptr, use_swiglu ? swiglu : nullptr);
             e)
             return e;
-        if (tail_done) *tail_done = use_tail;
+        if (tail_done) *tail_done = use_tail || use_swiglu;
         std::swap(cur, other);
         if (xs) CU(cudaMemcpyAsync(xs, cur, static_cast<size_t>(hidden) * 4, cudaMemcpyDeviceToDevice, stream_));
         return KCB_SUCCESS;
@@ -1838,8 +1839,17 @@ private:
             if (const int e = trace_copy(xq_wo, L.wo.k); e) return e;
             const Pair o = pair_of(L.wo, t);
             if (const int e = decode_matvec_q8(o.w4, o.y4, o.rows4, o.w6, o.y6, o.rows6, L.wo.k, xq_wo, xd_of(xq_wo, L.wo.k), pdl, stream_); e) return e;
-            if (const int e = norm_then_matvecs(L.gu, gu, cur, other, t, L.ffn_norm, pdl); e) return e;
-            if (streams_long(L.wd)) {  // SwiGLU + quantize as its own launch, then the streaming matvec
+            // SwiGLU: a tail of the gate|up launch where that takes one (every value computed once, no launch), else a
+            // prologue of the down projection (small vectors) or a launch of its own
+            DecodeSwigluTail sw;
+            sw.inter = inter, sw.xq = xq_wd, sw.xd = xd_of(xq_wd, L.wd.k);
+            const bool want_sw = swiglu_tail_ && streams_long(L.wd);
+            bool swiglu_done = false;
+            if (const int e = norm_then_matvecs(L.gu, gu, cur, other, t, L.ffn_norm, pdl, nullptr, &swiglu_done, want_sw ? &sw : nullptr); e) return e;
+            if (swiglu_done) {
+                if (const int e = trace_copy(xq_wd, L.wd.k); e) return e;
+                if (const int e = mv(L.wd, xq_wd, t); e) return e;
+            } else if (streams_long(L.wd)) {  // SwiGLU + quantize as its own launch, then the streaming matvec
                 if (const int e = silu_mul_q8(gu, gu + inter, nullptr, nullptr, xq_wd, xd_of(xq_wd, L.wd.k), inter, 1, stream_, pdl); e) return e;
                 if (const int e = trace_copy(xq_wd, L.wd.k); e) return e;
                 if (const int e = mv(L.wd, xq_wd, t); e) return e;
@@ -1960,6 +1970,7 @@ private:
     bool prompt_blocked_ = !(getenv("KCB_PROMPT_ATTN_BLOCKED") && atoi(getenv("KCB_PROMPT_ATTN_BLOCKED")) == 0);
     bool rope_tail_ = !(getenv("KCB_DECODE_ROPE_TAIL") && atoi(getenv("KCB_DECODE_ROPE_TAIL")) == 0);
     bool attn_cluster_ = !(getenv("KCB_DECODE_ATTN_CLUSTER") && atoi(getenv("KCB_DECODE_ATTN_CLUSTER")) == 0);
+    bool swiglu_tail_ = !(getenv("KCB_DECODE_SWIGLU_TAIL") && atoi(getenv("KCB_DECODE_SWIGLU_TAIL")) == 0);
     size_t fuse_limit_ = (getenv("KCB_DECODE_FUSE_MB") ? static_cast<size_t>(atoi(getenv("KCB_DECODE_FUSE_MB"))) : 64) << 20;
     int swiglu_limit_ = getenv("KCB_DECODE_SWIGLU_MAX") ? atoi(getenv("KCB_DECODE_SWIGLU_MAX")) : 4096;
     size_t rows_parity_ = 0;  // which half of the exchange area's row buffers the next K-split matmul of a prompt chunk writes

@@ -62,11 +62,22 @@ struct DecodeRopeTail {
     int heads = 0, kv_heads = 0, hd = 0, max_ctx = 0;
     float log2_base = 0.0f;
 };
+// Optional tail of decode_matvec_norm for a gate|up product (one matrix of 2 * inter rows: gate rows, then up rows;
+// k <= 4096, inter a multiple of 32): a CTA takes the 32-row tile of gate rows and the tile of the same up rows one after
+// the other, and one warp turns the pair into 32 values of SwiGLU(gate) * up and their quantize_q8x4 block (the arithmetic
+// of silu_mul_q8), written to xq / xd -- the down projection's input -- so that the step needs no SwiGLU launch.  The
+// gate and up products themselves are not stored.
+struct DecodeSwigluTail {
+    int inter = 0;  // 0: none
+    int* xq = nullptr;
+    float* xd = nullptr;
+};
 bool decode_matvec_shape_ok(int rows4, int rows6, int k);
 int decode_matvec_q8(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const int* xq, const float* xd, bool pdl,
                      cudaStream_t s);
 int decode_matvec_norm(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* x_in, const float* t, float* x_out,
-                       const float* wn, float eps, bool pdl, cudaStream_t s, int* trace = nullptr, const DecodeRopeTail* tail = nullptr);
+                       const float* wn, float eps, bool pdl, cudaStream_t s, int* trace = nullptr, const DecodeRopeTail* tail = nullptr,
+                       const DecodeSwigluTail* swiglu = nullptr);
 int decode_matvec_swiglu(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* g, const float* u, bool pdl,
                          cudaStream_t s, int* trace = nullptr);
 int decode_matvec_combine(const void* w4, float* y4, int rows4, const void* w6, float* y6, int rows6, int k, const float* part, int heads, int hd,

@@ -119,7 +119,7 @@ def _wide_ffn(max_ctx):
     return tm.Shape("wide-ffn", 256, 9216, 2, 4, 2, 64, 256, max_ctx)
 
 
-@pytest.mark.parametrize("fused", [1, 0])
+@pytest.mark.parametrize("fused", [1, 0, "swiglu-tail"])
 @pytest.mark.parametrize("shape_fn", [tm.tiny, tm.tiny_qwen, _wide_ffn])
 def test_graph_decoder_stage_by_stage_with_flip_count(shape_fn, fused, monkeypatch):
     """Why the test above needs 3e-2, measured instead of argued.  The decoder traces the int8 words of every activation
@@ -138,10 +138,11 @@ def test_graph_decoder_stage_by_stage_with_flip_count(shape_fn, fused, monkeypat
     random-weight models amplify it: one step in one vector changes tens of values in the next), not an arithmetic
     difference, and stays inside 3e-2.  Both forms of the step (producers fused into the matvecs, and one kernel each)
     are held to the same numbers."""
-    monkeypatch.setenv("KCB_DECODE_FUSED", str(fused))
-    # (by default a SwiGLU of more than 8192 values stays a launch of its own; here it is folded in, so that the
-    # four-warps-per-row matvec is checked with its prologue)
-    monkeypatch.setenv("KCB_DECODE_SWIGLU_MAX", "16384")
+    monkeypatch.setenv("KCB_DECODE_FUSED", "0" if fused == 0 else "1")
+    # The SwiGLU as a prologue of the down projection whatever its width (by default only up to 4096 values), so that the
+    # four-warps-per-row matvec is checked with its prologue; "swiglu-tail": never a prologue, which makes it the tail
+    # of the gate|up launch's tile pairs as on the full-size models (same number of launches either way).
+    monkeypatch.setenv("KCB_DECODE_SWIGLU_MAX", "0" if fused == "swiglu-tail" else "16384")
     shape = shape_fn(max_ctx=48)
     model = tm.build(shape, seed=5)
     staged, free = OracleModel(shape, model), OracleModel(shape, model)
@@ -208,10 +209,10 @@ def test_full_size_logits_against_the_reference_decode_loop():
             ref_logits.append(out)
         oracle.ref.lib.kcref_model_close(h)
     with decoder.FastDecoder(shape, model) as d:
-        # the fused step is the one measured: embed, six launches per layer (q|k|v with norm and rotation, attention
-        # with its merge, wo, gate|up with norm, SwiGLU, down), the lm_head (above 64 MB: its norm a launch of its own, then the
+        # the fused step is the one measured: embed, five launches per layer (q|k|v with norm and rotation, attention
+        # with its merge, wo, gate|up with norm and SwiGLU, down), the lm_head (above 64 MB: its norm a launch of its own, then the
         # streaming matvec) and two for the pick
-        assert d.launches_per_token == 5 + 6 * shape.layers
+        assert d.launches_per_token == 5 + 5 * shape.layers
         words = d.enable_trace()
         assert words == staged.trace_words()
         d.set_prompt(toks)
